@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (N = 1): the decode GEMV sweep of the benchmark configuration "batched decode GEMV over every
+linear of a Qwen2.5-7B-shaped layer" at M = 1 -- one STEP is one pass over the seven int4 group-128 linears
+of a layer (q, k, v, o, gate, up, down): seven launches of the library's GEMV through its C ABI.  Weights
+rotate through eight distinct layer copies (961 MB) so every step streams from HBM, not from the 126 MB L2.
+Metric: algorithmic bytes moved per second (packed weights + scales + X + bf16 Y, the reference's byte model,
+bench/bench_w4a16.cu:239).
+
+With N > 1 ranks (one per GPU) every matrix is sharded by output rows over the ranks (tensor parallel) and
+the outputs are all-gathered with NCCL at the four layer boundaries (after q/k/v, o, gate/up, down); the value
+is the whole-layer bytes over the slowest rank's time, so scaling is "strong".
+
+One JSON line is printed by rank 0.  `value` is measured with inputs resident in HBM; `e2e` is the same
+pass through the public Python/C-ABI call path with the step's activations copied from pinned host memory and
+all outputs copied back inside the timed region; `roofline` times the dominant kernel (the 18944 x 3584 GEMV)
+alone; `cpu_baseline` times the CPU oracle (a port of the reference's host dequant-then-matmul check,
+bench/bench_w4a16.cu:156-173) on a bounded sample.  `--impl reference` times that CPU path alone with all host
+threads.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from nanoserve_b200 import synth  # noqa: E402
+
+METRIC = "W4A16 GEMV HBM GB/s at M=1 (Qwen2.5-7B-shaped layer, int4 g128)"
+UNIT = "GB/s"
+G = 128
+M_DECODE = 1
+LAYER = synth.QWEN25_7B_LAYER
+ORDER = ["q", "k", "v", "o", "gate", "up", "down"]
+N_COPIES = 8
+L2_BYTES = 126 * 2**20
+
+
+def layer_bytes(M):
+    return sum(synth.gemv_bytes(M, n, k, G) for n, k in (LAYER[x] for x in ORDER))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ---------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------- CPU legs (oracle)
+def cpu_layer_pass(threads, n_passes, seed=100):
+    """Times `n_passes` passes over the layer's seven linears at M = 1 on the host with the CPU oracle.
+    Returns (seconds per pass, threads used)."""
+    import oracle  # test infrastructure: used here only as the timed CPU baseline
+    mats = {}
+    for name in ORDER:
+        n, k = LAYER[name]
+        mats[name] = synth.synth_weight(n, k, G, seed)
+    xs = {k: synth.synth_x(M_DECODE, k, seed) for k in {LAYER[x][1] for x in ORDER}}
+    t0 = time.perf_counter()
+    for _ in range(n_passes):
+        for name in ORDER:
+            Wq, S = mats[name]
+            oracle.w4_linear_f32(xs[LAYER[name][1]], Wq, S, G, threads=threads)
+    dt = (time.perf_counter() - t0) / n_passes
+    return dt, (threads if threads > 1 else 1)
+
+
+def run_reference_arm(args):
+    """The reference's CPU implementation of the path (its host dequant-then-FP32/double check), all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    threads = oracle.max_threads()
+    for _ in range(max(0, min(args.warmup, 2))):
+        cpu_layer_pass(threads, 1)
+    steps = max(1, args.steps)
+    per_step_budget = 120.0 / steps  # keep the whole run within a few minutes
+    one, _ = cpu_layer_pass(threads, 1)
+    passes_per_step = 1
+    if one > per_step_budget:
+        passes_per_step = 1  # a step is never less than one pass; the cap below bounds the total instead
+    steps_run = steps if one * steps <= 240.0 else max(1, int(240.0 / one))
+    dt, used = cpu_layer_pass(threads, steps_run * passes_per_step)
+    value = layer_bytes(M_DECODE) / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights x bf16 activations, fp64 accumulate (host)",
+        "data": "synthetic",
+        "config": {"workload": "decode GEMV pass over the 7 linears of a Qwen2.5-7B-shaped layer, M=1, int4 g128",
+                   "steps_timed": steps_run},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": used, "kind": "port",
+                         "sample": f"{steps_run} full layer passes (7 linears, 233M weights each pass)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=M_DECODE, help="tokens per step (1..16); the headline is 1")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--flags", type=int, default=0, help="library flags for every launch (see include/nanoserve_b200.h)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from nanoserve_b200 import build as b2build
+    from nanoserve_b200.ops import Kernels
+    from nanoserve_b200.tp import ShardedLayer
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if not os.path.exists(b2build.LIB_PATH):
+        if rank == 0:
+            b2build.build()
+        if world > 1:
+            dist.barrier()
+    k = Kernels(b2build.LIB_PATH)
+    k.init()
+    M = args.m
+    warm = max(3, args.warmup)
+
+    # ---- resident weights: N_COPIES layer copies, sharded by output rows over the ranks
+    layers = [ShardedLayer.synthetic(k, LAYER, ORDER, G, seed=1000 + c, rank=rank, world=world, device=dev,
+                                     flags=args.flags)
+              for c in range(N_COPIES)]
+    x_h = torch.from_numpy(synth.synth_x(M, 3584, 1).view(np.int16)).view(torch.bfloat16).pin_memory()
+    a_h = torch.from_numpy(synth.synth_x(M, 18944, 2).view(np.int16)).view(torch.bfloat16).pin_memory()
+    x_d, a_d = x_h.to(dev), a_h.to(dev)
+    resident = sum(l.resident_bytes() for l in layers)
+
+    # ---- device-resident timing: one CUDA graph per layer copy (7 launches + the gathers), replayed in rotation
+    stream = torch.cuda.Stream(device=dev)
+    graphs = []
+    with torch.cuda.stream(stream):
+        for l in layers:
+            l.decode_pass(x_d, a_d)  # warm every kernel variant before capture
+        torch.cuda.synchronize()
+        for l in layers:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                l.decode_pass(x_d, a_d)
+            graphs.append(g)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_replays(n):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with torch.cuda.stream(stream):
+            ev0.record(stream)
+            for i in range(n):
+                graphs[i % N_COPIES].replay()
+            ev1.record(stream)
+        barrier()
+        return ev0.elapsed_time(ev1) * 1e-3
+
+    timed_replays(warm)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t_dev = timed_replays(args.steps)
+    # keep the GPU under the same load a little longer so the 100 ms clock sampler sees it
+    t_extra0 = time.perf_counter()
+    while rank == 0 and time.perf_counter() - t_extra0 < 0.6:
+        timed_replays(200)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end: public API, host buffers, copies inside the timed region
+    outs_h = None
+
+    def e2e_step(l):
+        nonlocal outs_h
+        xd = x_h.to(dev, non_blocking=True)
+        ad = a_h.to(dev, non_blocking=True)
+        outs = l.decode_pass(xd, ad)
+        if outs_h is None:
+            outs_h = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        for oh, o in zip(outs_h, outs):
+            oh.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    with torch.cuda.stream(stream):
+        for i in range(warm):
+            e2e_step(layers[i % N_COPIES])
+        barrier()
+        t0 = time.perf_counter()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for i in range(args.steps):
+            e2e_step(layers[i % N_COPIES])
+        ev1.record(stream)
+        barrier()
+        t_e2e = max(ev0.elapsed_time(ev1) * 1e-3, 0.0)
+        t_e2e_wall = time.perf_counter() - t0
+    h2d = x_h.numel() * 2 + a_h.numel() * 2
+    d2h = sum(o.numel() * 2 for o in outs_h)
+
+    # ---- the dominant kernel alone: the 18944 x 3584 GEMV over 16 distinct matrices (gate and up of 8 copies)
+    roof = None
+    if world == 1:
+        big = [(l.full["gate"]) for l in layers] + [(l.full["up"]) for l in layers]
+        y_big = torch.empty(M, 18944, dtype=torch.bfloat16, device=dev)
+        with torch.cuda.stream(stream):
+            gk = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gk, stream=stream):
+                for (Wq, S) in big:
+                    k.w4_linear(x_d, Wq, S, G, flags=args.flags, out=y_big)
+            for _ in range(3):
+                gk.replay()
+            torch.cuda.synchronize()
+            reps = max(5, min(50, args.steps))
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(stream)
+            for _ in range(reps):
+                gk.replay()
+            ev1.record(stream)
+            torch.cuda.synchronize()
+            t_k = ev0.elapsed_time(ev1) * 1e-3 / (reps * len(big))
+        peaks, which = measured_peaks()
+        kb = synth.gemv_bytes(M, 18944, 3584, G)
+        ach = kb / t_k / 1e9
+        roof = {"bound": "hbm", "kernel": "w4_gemv_kernel (N=18944, K=3584, M=%d)" % M, "achieved": ach,
+                "peak": peaks["hbm_gbs"], "peak_source": which + " copy bandwidth (MEASURED_PEAKS.json)"
+                if which == "measured" else "fallback 6650 GB/s",
+                "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "us_per_launch": t_k * 1e6,
+                "bytes_per_launch": kb, "traffic": None}
+        traffic_file = os.path.join(ROOT, "profiles", "gemv_traffic.json")
+        if os.path.exists(traffic_file):
+            with open(traffic_file) as f:
+                roof["traffic"] = json.load(f).get("dram_bytes_per_launch_m%d" % M)
+
+    # ---- max over ranks
+    times = torch.tensor([t_dev, t_e2e, t_e2e_wall], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    t_dev, t_e2e, t_e2e_wall = times.tolist()
+    status = k.device_status()
+    if status != 0:
+        raise SystemExit(f"device status {status}: a kernel reported a time-out; numbers are invalid")
+
+    if rank == 0:
+        nbytes = layer_bytes(M)
+        launches_per_step = len(ORDER)
+        line = {
+            "metric": METRIC if M == 1 else METRIC.replace("M=1", f"M={M}"), "value": nbytes * args.steps / t_dev / 1e9,
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
+            "ms_per_step": t_dev / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int4 weights x bf16 activations, fp32 accumulate", "data": "synthetic",
+            "config": {
+                "workload": f"decode GEMV pass over the 7 linears of a Qwen2.5-7B-shaped layer, M={M}, int4 g128",
+                "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                "l2": f"weights rotate through {N_COPIES} layer copies ({resident * world / 1e6:.0f} MB) > 126 MB L2",
+                "bytes_per_step": nbytes, "launch": "one CUDA graph per layer copy, replayed in rotation",
+                "seeds": "X 1/2, layer copy c: 1000+c", "flags": args.flags,
+            },
+            "e2e": {"value": nbytes * args.steps / t_e2e_wall / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e_wall / args.steps * 1e3,
+                    "path": "Kernels.w4_linear per linear (ctypes -> C ABI), pinned host X in, all outputs out"},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if roof is not None:
+            line["roofline"] = roof
+        if world == 1 and not args.no_cpu_baseline:
+            one, _ = cpu_layer_pass(1, 1)
+            n = max(1, min(8, int(15.0 / max(one, 1e-3))))
+            dt, used = cpu_layer_pass(1, n)
+            line["cpu_baseline"] = {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": used, "kind": "port",
+                                    "sample": f"{n} full layer passes at M=1 on one host thread (as the reference "
+                                              f"runs its check), {dt:.2f} s per pass"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

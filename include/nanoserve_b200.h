@@ -1,0 +1,103 @@
+/*
+ * C ABI of libnanoserve.so for NVIDIA B200 (sm_100a): the W4A16 quantized-linear path.
+ *
+ * The first group of entry points has the exact names, argument lists and return conventions of the
+ * reference library's C ABI (csrc/nanoserve_ops.cu of the reference project), so the reference's own
+ * ctypes binding (python/nanoserve/ops.py:19-30) loads this library unchanged.  All pointers are device
+ * pointers owned and allocated by the caller; `stream` is a raw cudaStream_t; every call is asynchronous
+ * and returns right after the launch.  Return value: 0 on success, a positive CUDA error code, or one of
+ * the negative codes below.
+ *
+ * Weight format (reference kernels/quant/w4a16.cuh:5-9):
+ *   Wq [N, K/8] uint32  word j of row n packs k = 8j..8j+7, value k = 8j+i in bits 4i..4i+3
+ *   S  [N, K/G] bf16    w[n,k] = (q - 8) * S[n, k/G], q in [0, 15]; the zero-point is the constant 8
+ */
+#ifndef NANOSERVE_B200_H_
+#define NANOSERVE_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2_OK 0
+#define B2_ERR_BAD_SHAPE (-1)       /* K % G, G % 32 or K % 32 violated (reference: -1) */
+#define B2_ERR_UNSUPPORTED_M (-2)   /* M < 1 (reference: -2 for M it cannot serve) */
+#define B2_ERR_NOT_IMPLEMENTED (-3) /* operator outside the W4A16 path */
+#define B2_ERR_BAD_POINTER (-4)     /* null or misaligned pointer (X, Wq: 16 bytes) */
+#define B2_ERR_WORKSPACE (-5)       /* per-device scratch could not be set up */
+#define B2_ERR_TOO_LARGE (-6)       /* size beyond a documented maximum */
+#define B2_ERR_DEVICE (-7)          /* a kernel recorded a device-side time-out */
+
+/* ---- drop-in entry points (same symbols as the reference library) ------------------------------ */
+
+/*
+ * Y[M,N] (bf16) = X[M,K] (bf16) . dequant(Wq, S)^T, fp32 accumulation, one rounding to bf16 at the store.
+ * Replaces ns_w4_linear, csrc/nanoserve_ops.cu:75-90.  The reference serves M in {1,2,4,8} (GEMV) and
+ * M % 128 == 0 with N % 128 == 0 (GEMM) and returns -2 otherwise; this library serves every M >= 1 and
+ * every N >= 1: M <= 16 runs the decode GEMV, larger M the tensor-core GEMM.  Needs K % 32 == 0,
+ * G % 32 == 0, K % G == 0 (the reference calls exit() on these inside w4a16.cuh:100-103; this library
+ * returns -1 instead).
+ */
+int ns_w4_linear(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                 void* stream);
+
+/*
+ * W[N,K] (bf16) -> Wq[N,K/8] (uint32) + S[N,K/G] (bf16): round-to-nearest symmetric group quantizer,
+ * bit-identical to the reference's.  Replaces ns_w4_quantize, csrc/nanoserve_ops.cu:66-71.
+ * Returns -1 if K % G or G % 32.
+ */
+int ns_w4_quantize(const void* W, void* Wq, void* S, int N, int K, int G, void* stream);
+
+/*
+ * The reference's Python binding resolves these four symbols when it loads the library
+ * (python/nanoserve/ops.py:19-30), so they are exported.  They lie outside the W4A16 path.
+ * ns_rmsnorm / ns_rope / ns_swiglu replace csrc/nanoserve_ops.cu:21-45 with the same semantics;
+ * ns_flash_fwd (csrc/nanoserve_ops.cu:47-63) returns B2_ERR_NOT_IMPLEMENTED.
+ */
+int ns_rmsnorm(void* x, const void* r, const void* w, void* y, int T, int H, float eps, void* stream);
+int ns_rope(void* q, void* k, const void* inv_freq, int T, int Hq, int Hk, int D, int pos0,
+            long long q_stride, long long k_stride, void* stream);
+int ns_swiglu(const void* gate, const void* up, void* out, int T, int I, void* stream);
+int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, int Hq, int Hk, int D,
+                 long long q_t, long long kv_t, long long o_t, int causal, int variant, void* stream);
+
+/* ---- additions (no counterpart in the reference library) --------------------------------------- */
+
+/* Flags for b2_w4_linear. */
+#define B2_FLAG_FOLD_ZERO_POINT 1 /* GEMV: apply the -8 as one fp32 correction per 128-wide chunk */
+#define B2_FLAG_NO_SPLIT_K 2      /* GEMV: never split K across CTAs (uses no scratch memory) */
+#define B2_FLAG_NARROW_CTA 4      /* GEMV: 8 consumer warps per CTA instead of 16 */
+
+/*
+ * Sets up the calling thread's current device: queries the SM count and allocates the per-device scratch
+ * (split-K partial sums, arrival counters, a status word; 64 MiB + 256 KiB).  ns_w4_linear does this on
+ * its first call on a device; call b2_init first when that first call would fall inside a CUDA-graph
+ * capture.  Launches on different streams of one device share the scratch: split-K launches that overlap
+ * in time race (shapes that fill the GPU without split-K never touch it).
+ */
+int b2_init(void);
+
+/* ns_w4_linear with flags (0 = the defaults ns_w4_linear uses). */
+int b2_w4_linear(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                 int flags, void* stream);
+
+/*
+ * Synchronises the current device and returns its status word: 0, or B2_ERR_DEVICE if a kernel gave up
+ * on a bounded wait since the last b2_clear_status.  A non-zero status makes later launches return at
+ * once on the device, so the error cannot be missed.
+ */
+int b2_device_status(void);
+int b2_clear_status(void);
+
+/* Scratch bytes the GEMV would use for this shape on the current device (0 = no split-K). */
+size_t b2_w4_gemv_scratch_bytes(int M, int N, int K, int G, int flags);
+
+/* Library identification: "nanoserve-b200 <version> sm_100a". */
+const char* b2_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NANOSERVE_B200_H_ */

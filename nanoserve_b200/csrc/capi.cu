@@ -1,0 +1,143 @@
+// extern "C" entry points of libnanoserve.so (declared in include/nanoserve_b200.h).
+//
+// Plain pointers and sizes only; no PyTorch types.  Per-device state (SM count, scratch memory, status
+// word) is created lazily under a mutex, once per device, with that device current.
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/nanoserve_b200.h"
+#include "fused_ops.h"
+#include "w4_internal.h"
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+constexpr size_t kPartialBytes = 64ull << 20;  // split-K partial sums
+constexpr int kCounters = 1 << 16;             // one per 32-row group: N up to 2 M rows
+
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  b2::Workspace ws;
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;
+
+// Returns the state of the current device, creating it on first use.  rc receives 0 or an error code.
+DeviceState* device_state(int* rc) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { *rc = (int)e; return nullptr; }
+  if (dev < 0 || dev >= kMaxDevices) { *rc = b2::kErrTooLarge; return nullptr; }
+  DeviceState& st = g_dev[dev];
+  if (st.ready) { *rc = 0; return &st; }
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (st.ready) { *rc = 0; return &st; }
+  e = cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) { *rc = (int)e; return nullptr; }
+  void *partial = nullptr, *small = nullptr;
+  e = cudaMalloc(&partial, kPartialBytes);
+  if (e != cudaSuccess) { *rc = b2::kErrWorkspace; return nullptr; }
+  e = cudaMalloc(&small, (kCounters + 64) * sizeof(int));
+  if (e != cudaSuccess) { cudaFree(partial); *rc = b2::kErrWorkspace; return nullptr; }
+  e = cudaMemset(small, 0, (kCounters + 64) * sizeof(int));
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();  // the memset is not ordered with non-blocking streams
+  if (e != cudaSuccess) { cudaFree(partial); cudaFree(small); *rc = (int)e; return nullptr; }
+  st.ws.partial = static_cast<float*>(partial);
+  st.ws.partial_bytes = kPartialBytes;
+  st.ws.status = static_cast<int*>(small);          // word 0
+  st.ws.counters = static_cast<int*>(small) + 64;   // 256-byte offset
+  st.ws.n_counters = kCounters;
+  st.ready = true;
+  *rc = 0;
+  return &st;
+}
+
+int linear_dispatch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                    int flags, void* stream) {
+  if (M < 1) return b2::kErrUnsupportedM;
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return rc;
+  const auto s = static_cast<cudaStream_t>(stream);
+  if (M <= 16) return b2::gemv_launch(X, Wq, S, Y, M, N, K, G, st->ws, flags, st->sm_count, s);
+  return b2::gemm_launch(X, Wq, S, Y, M, N, K, G, st->ws, flags, st->sm_count, s);
+}
+
+}  // namespace
+
+extern "C" {
+
+int ns_w4_linear(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                 void* stream) {
+  return linear_dispatch(X, Wq, S, Y, M, N, K, G, 0, stream);
+}
+
+int b2_w4_linear(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                 int flags, void* stream) {
+  return linear_dispatch(X, Wq, S, Y, M, N, K, G, flags, stream);
+}
+
+int ns_w4_quantize(const void* W, void* Wq, void* S, int N, int K, int G, void* stream) {
+  return b2::quantize_launch(W, Wq, S, N, K, G, static_cast<cudaStream_t>(stream));
+}
+
+int ns_rmsnorm(void* x, const void* r, const void* w, void* y, int T, int H, float eps, void* stream) {
+  return b2::rmsnorm_launch(x, r, w, y, T, H, eps, static_cast<cudaStream_t>(stream));
+}
+
+int ns_rope(void* q, void* k, const void* inv_freq, int T, int Hq, int Hk, int D, int pos0,
+            long long q_stride, long long k_stride, void* stream) {
+  return b2::rope_launch(q, k, inv_freq, T, Hq, Hk, D, pos0, q_stride, k_stride,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int ns_swiglu(const void* gate, const void* up, void* out, int T, int I, void* stream) {
+  return b2::swiglu_launch(gate, up, out, T, I, static_cast<cudaStream_t>(stream));
+}
+
+int ns_flash_fwd(const void*, const void*, const void*, void*, int, int, int, int, long long, long long,
+                 long long, int, int, void*) {
+  return b2::kErrNotImplemented;
+}
+
+int b2_init(void) {
+  int rc = 0;
+  device_state(&rc);
+  return rc;
+}
+
+int b2_device_status(void) {
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  int word = 0;
+  e = cudaMemcpy(&word, st->ws.status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return (int)e;
+  return word == 0 ? 0 : b2::kErrDevice;
+}
+
+int b2_clear_status(void) {
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  // a time-out may have left arrival counters half counted: clear them with the status word
+  e = cudaMemset(st->ws.status, 0, (kCounters + 64) * sizeof(int));
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  return (int)e;
+}
+
+size_t b2_w4_gemv_scratch_bytes(int M, int N, int K, int G, int flags) {
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return 0;
+  return b2::gemv_scratch_bytes(M, N, K, G, flags, st->sm_count, st->ws.partial_bytes);
+}
+
+const char* b2_version(void) { return "nanoserve-b200 0.1 sm_100a"; }
+
+}  // extern "C"

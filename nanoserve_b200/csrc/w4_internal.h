@@ -1,0 +1,57 @@
+// Host-side declarations shared by the C-ABI layer and the kernel translation units.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace b2 {
+
+// Return codes of the C ABI.  0 and positive values follow the reference library
+// (csrc/nanoserve_ops.cu:3: 0 on success, else a CUDA error code); -1 / -2 keep its meaning
+// (-1 bad shape for the quantizer :67, -2 unsupported M for the linear :86-88); the rest are new.
+enum : int {
+  kOk = 0,
+  kErrBadShape = -1,     // K % G, G % 32 or K % 32 violated
+  kErrUnsupportedM = -2, // M < 1
+  kErrNotImplemented = -3,
+  kErrBadPointer = -4,   // null or misaligned pointer
+  kErrWorkspace = -5,    // workspace missing or too small
+  kErrTooLarge = -6,     // size beyond a documented maximum
+  kErrDevice = -7,       // a kernel reported a device-side time-out in the status word
+};
+
+// Device status word values written by kernels (0 = fine).
+enum : int {
+  kStatusOk = 0,
+  kStatusGemvTimeout = 1,
+  kStatusGemmTimeout = 2,
+};
+
+// Scratch memory a launch may use.  `partial` holds split-K partial sums, `counters` one arrival
+// counter per 32-row group (zero between launches: the last arriver resets it), `status` one int.
+struct Workspace {
+  float* partial = nullptr;
+  size_t partial_bytes = 0;
+  int* counters = nullptr;
+  int n_counters = 0;
+  int* status = nullptr;
+};
+
+// Flags for the linear launches.
+enum : int {
+  kFlagFoldZeroPoint = 1,  // GEMV: fold the zero-point into one correction per group instead of a
+                           // bf16x2 subtract per weight pair (fewer ALU ops, fp32-level cancellation)
+  kFlagForceNoSplitK = 2,  // GEMV: never use split-K (no scratch needed)
+  kFlagNarrowCta = 4,      // GEMV: use the 8-consumer-warp CTA even when the 16-warp one applies
+};
+
+int gemv_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                const Workspace& ws, int flags, int sm_count, cudaStream_t stream);
+int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                const Workspace& ws, int flags, int sm_count, cudaStream_t stream);
+int quantize_launch(const void* W, void* Wq, void* S, int N, int K, int G, cudaStream_t stream);
+
+// Scratch bytes gemv_launch would use for this shape (0 when it runs without split-K).
+size_t gemv_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);
+
+}  // namespace b2

@@ -1,0 +1,158 @@
+"""ctypes binding to build/libnanoserve.so: the host-side mirror of the reference's operator interface.
+
+``Kernels`` has the same constructor, method names, argument meaning and error behaviour as the
+reference's ``python/nanoserve/ops.py`` (class ``Kernels``, lines 15-97): torch tensors in and out on the
+current CUDA stream, ``RuntimeError("<symbol> failed with code <rc>")`` on a non-zero return code.  The one
+deliberate difference is that ``w4_linear`` no longer pads M (reference ops.py:89-91): the B200 library
+serves every M >= 1 natively.
+
+There is no CPU path: if the shared library is missing or a tensor is not on a CUDA device the call
+raises.
+"""
+import ctypes
+import os
+
+import torch
+
+_LIB_DEFAULT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "build", "libnanoserve.so")
+
+FLAG_FOLD_ZERO_POINT = 1
+FLAG_NO_SPLIT_K = 2
+FLAG_NARROW_CTA = 4
+
+# Every symbol include/nanoserve_b200.h declares, with its ctypes signature.
+_vp, _i32, _f32, _i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+SIGNATURES = {
+    # the six symbols of the reference library (python/nanoserve/ops.py:19-26)
+    "ns_rmsnorm": ([_vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp], _i32),
+    "ns_rope": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _vp], _i32),
+    "ns_swiglu": ([_vp, _vp, _vp, _i32, _i32, _vp], _i32),
+    "ns_flash_fwd": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _vp], _i32),
+    "ns_w4_quantize": ([_vp, _vp, _vp, _i32, _i32, _i32, _vp], _i32),
+    "ns_w4_linear": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
+    # additions
+    "b2_init": ([], _i32),
+    "b2_w4_linear": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp], _i32),
+    "b2_device_status": ([], _i32),
+    "b2_clear_status": ([], _i32),
+    "b2_w4_gemv_scratch_bytes": ([_i32, _i32, _i32, _i32, _i32], ctypes.c_size_t),
+    "b2_version": ([], ctypes.c_char_p),
+}
+
+
+def load_library(path: str = _LIB_DEFAULT) -> ctypes.CDLL:
+    """Loads the C-ABI library and sets the signature of every exported entry point."""
+    path = os.path.abspath(path)
+    if not os.path.exists(path):
+        raise FileNotFoundError(
+            f"{path} not found: build it with `python -m nanoserve_b200.build` (needs nvcc); "
+            "there is no CPU fallback")
+    lib = ctypes.CDLL(path)
+    for name, (args, res) in SIGNATURES.items():
+        if not hasattr(lib, name):
+            continue  # optional additions may be absent in an older build; required ones fail on use
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = res
+    return lib
+
+
+class Kernels:
+    def __init__(self, path: str = _LIB_DEFAULT):
+        self.lib = load_library(path)
+        for name in ("ns_rmsnorm", "ns_rope", "ns_swiglu", "ns_flash_fwd", "ns_w4_quantize", "ns_w4_linear"):
+            getattr(self.lib, name)  # AttributeError if the library is not a drop-in
+
+    @staticmethod
+    def _stream():
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    @staticmethod
+    def _check(rc: int, name: str):
+        if rc != 0:
+            raise RuntimeError(f"{name} failed with code {rc}")
+
+    @staticmethod
+    def _cuda(*tensors):
+        for t in tensors:
+            if t is not None and not t.is_cuda:
+                raise RuntimeError("nanoserve_b200 operators take CUDA tensors only (no CPU path)")
+
+    # x: [T, H] residual stream, updated in place when r is given. Returns rmsnorm(x) * w.
+    def rmsnorm(self, x, r, w, eps):
+        self._cuda(x, r, w)
+        assert x.is_contiguous() and x.dtype == torch.bfloat16
+        y = torch.empty_like(x)
+        rc = self.lib.ns_rmsnorm(x.data_ptr(), None if r is None else r.data_ptr(), w.data_ptr(),
+                                 y.data_ptr(), x.shape[0], x.shape[1], eps, self._stream())
+        self._check(rc, "ns_rmsnorm")
+        return y
+
+    # In place on q [T, Hq*D] and k [T, Hk*D] (row stride may exceed Hq*D / Hk*D).
+    def rope(self, q, k, inv_freq, n_heads, n_kv_heads, head_dim, pos0):
+        self._cuda(q, k, inv_freq)
+        rc = self.lib.ns_rope(q.data_ptr(), k.data_ptr(), inv_freq.data_ptr(), q.shape[0], n_heads,
+                              n_kv_heads, head_dim, pos0, q.stride(0), k.stride(0), self._stream())
+        self._check(rc, "ns_rope")
+
+    def swiglu(self, gate, up):
+        self._cuda(gate, up)
+        assert gate.is_contiguous() and up.is_contiguous()
+        out = torch.empty_like(gate)
+        rc = self.lib.ns_swiglu(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.shape[0],
+                                gate.shape[1], self._stream())
+        self._check(rc, "ns_swiglu")
+        return out
+
+    def flash_attention(self, q, k, v, n_heads, n_kv_heads, head_dim, causal=True):
+        # Attention is outside the quantized-linear path; the library exports the symbol and reports
+        # "not implemented" (-3), which surfaces here as the reference's RuntimeError.
+        N = q.shape[0]
+        o = torch.empty((N, n_heads * head_dim), dtype=q.dtype, device=q.device)
+        rc = self.lib.ns_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), N, n_heads,
+                                   n_kv_heads, head_dim, q.stride(0), k.stride(0), o.stride(0),
+                                   int(causal), 1, self._stream())
+        self._check(rc, "ns_flash_fwd")
+        return o
+
+    def w4_quantize(self, W, group=128):
+        self._cuda(W)
+        N, K = W.shape
+        Wq = torch.empty((N, K // 8), dtype=torch.int32, device=W.device)
+        S = torch.empty((N, K // group), dtype=torch.bfloat16, device=W.device)
+        rc = self.lib.ns_w4_quantize(W.contiguous().data_ptr(), Wq.data_ptr(), S.data_ptr(), N, K,
+                                     group, self._stream())
+        self._check(rc, "ns_w4_quantize")
+        return Wq, S
+
+    # x [M, K] -> [M, N] for any M >= 1 (decode GEMV for M <= 16, tensor-core GEMM above).
+    def w4_linear(self, x, Wq, S, group=128, flags=0, out=None):
+        self._cuda(x, Wq, S, out)
+        M, K = x.shape
+        N = Wq.shape[0]
+        x = x.contiguous()
+        y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        if flags:
+            rc = self.lib.b2_w4_linear(x.data_ptr(), Wq.data_ptr(), S.data_ptr(), y.data_ptr(), M, N, K,
+                                       group, flags, self._stream())
+        else:
+            rc = self.lib.ns_w4_linear(x.data_ptr(), Wq.data_ptr(), S.data_ptr(), y.data_ptr(), M, N, K,
+                                       group, self._stream())
+        self._check(rc, "ns_w4_linear")
+        return y
+
+    # ---- additions
+    def init(self):
+        self._check(self.lib.b2_init(), "b2_init")
+
+    def device_status(self) -> int:
+        return int(self.lib.b2_device_status())
+
+    def clear_status(self):
+        self._check(self.lib.b2_clear_status(), "b2_clear_status")
+
+    def gemv_scratch_bytes(self, M, N, K, group=128, flags=0) -> int:
+        return int(self.lib.b2_w4_gemv_scratch_bytes(M, N, K, group, flags))
+
+    def version(self) -> str:
+        return self.lib.b2_version().decode()

@@ -1,0 +1,193 @@
+"""GPU parity tests of the decode GEMV (M <= 16) through the C ABI, against the CPU oracle.
+
+Integer work (the int4 unpack) must be bit-exact.  Floating-point outputs are bf16: the bound is one
+correct rounding (2^-8 relative) plus fp32-accumulation slack relative to the largest output:
+3e-6 for the default path, 3e-5 when the zero-point is folded (fp32 cancellation of the +128 bias),
+2e-3 for G < 128 where each weight is rounded to bf16 as the reference's tensor-core path does.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from nanoserve_b200 import ops
+from tests.util import bits_to_torch, check_bf16_output, torch_to_bits, u32_to_torch
+
+pytestmark = pytest.mark.gpu
+
+SLACK_EXACT, SLACK_FOLD, SLACK_SMALL_G = 3e-6, 3e-5, 2e-3
+
+
+def run(k, X, Wq, S, G, flags=0):
+    y = k.w4_linear(bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S), G, flags=flags)
+    torch.cuda.synchronize()
+    return torch_to_bits(y)
+
+
+def slack_for(G, flags):
+    if G % 128:
+        return SLACK_SMALL_G
+    return SLACK_FOLD if flags & ops.FLAG_FOLD_ZERO_POINT else SLACK_EXACT
+
+
+@pytest.mark.parametrize("flags", [0, ops.FLAG_FOLD_ZERO_POINT, ops.FLAG_NARROW_CTA])
+@pytest.mark.parametrize("G", [128, 32])
+def test_unpack_is_bit_exact(kernels, flags, G):
+    """S == 1 and one-hot X rows make Y[m, n] = q[n, k_m] - 8: every nibble value in every in-word
+    position, in the first and last word of a group and of a row, must come back as that integer."""
+    N, K = 48, 256
+    rng = np.random.default_rng(7)
+    Wq = rng.integers(0, 2**32, size=(N, K // 8), dtype=np.uint32)
+    for v in range(16):  # rows 0..15: constant nibble v everywhere
+        Wq[v, :] = np.uint32(v * 0x11111111)
+    Wq[16, :] = 0x76543210  # ascending nibbles in every word
+    Wq[17, :] = 0xFEDCBA98
+    S = np.full((N, K // G), 0x3F80, dtype=np.uint16)
+    Q = oracle.w4_unpack(Wq)  # [N, K] int8
+    for k0 in range(0, K, 16):
+        X = np.zeros((16, K), dtype=np.float32)
+        X[np.arange(16), k0 + np.arange(16)] = 1.0
+        y = oracle.bf16_bits_to_f32(run(kernels, oracle.f32_to_bf16_bits(X), Wq, S, G, flags))
+        want = Q[:, k0:k0 + 16].T.astype(np.float32)
+        assert np.array_equal(y, want), (k0, flags, G)
+    # M = 1 goes through the other kernel variant
+    for k0 in (0, 7, 127, 128, 255):
+        X = np.zeros((1, K), dtype=np.float32)
+        X[0, k0] = 1.0
+        y = oracle.bf16_bits_to_f32(run(kernels, oracle.f32_to_bf16_bits(X), Wq, S, G, flags))
+        assert np.array_equal(y[0], Q[:, k0].astype(np.float32))
+    assert kernels.device_status() == 0
+
+
+SMALL_SHAPES = [(64, 128, 128), (96, 256, 128), (100, 384, 128), (33, 1024, 128), (1, 128, 128),
+                (31, 256, 256), (257, 512, 128), (64, 32, 32), (40, 160, 32), (72, 192, 64), (50, 96, 96)]
+
+
+@pytest.mark.parametrize("N,K,G", SMALL_SHAPES)
+@pytest.mark.parametrize("flags", [0, ops.FLAG_FOLD_ZERO_POINT])
+def test_small_shapes_all_m(kernels, N, K, G, flags):
+    for M in range(1, 17):
+        X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=11)
+        ref = oracle.w4_linear_f32(X, Wq, S, G)
+        y = run(kernels, X, Wq, S, G, flags)
+        check_bf16_output(y, ref, slack_for(G, flags))
+    assert kernels.device_status() == 0
+
+
+# the linears of a Qwen2.5-7B-shaped layer, their 8-way tensor-parallel shards, and a 70B-class shape
+LAYER_SHAPES = [(3584, 3584), (512, 3584), (18944, 3584), (3584, 18944), (448, 3584), (64, 3584),
+                (2368, 3584), (448, 18944), (1024, 8192)]
+
+
+@pytest.mark.parametrize("N,K", LAYER_SHAPES)
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16])
+def test_layer_shapes(kernels, N, K, M):
+    G = 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=3)
+    ref = oracle.w4_linear_f32(X, Wq, S, G, threads=oracle.max_threads())
+    for flags in (0, ops.FLAG_FOLD_ZERO_POINT):
+        y = run(kernels, X, Wq, S, G, flags)
+        _, rel = check_bf16_output(y, ref, slack_for(G, flags))
+        assert rel < 1e-2  # the reference's own gate (bench/bench_w4a16.cu:120,174-180)
+    assert kernels.device_status() == 0
+
+
+@pytest.mark.parametrize("N,K", [(3584, 18944), (512, 3584), (18944, 3584)])
+def test_split_k_matches_single_pass_and_is_deterministic(kernels, N, K):
+    G, M = 128, 4
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=21)
+    ref = oracle.w4_linear_f32(X, Wq, S, G, threads=oracle.max_threads())
+    a = run(kernels, X, Wq, S, G, 0)
+    b = run(kernels, X, Wq, S, G, 0)
+    c = run(kernels, X, Wq, S, G, ops.FLAG_NO_SPLIT_K)
+    assert np.array_equal(a, b), "two identical launches differ: the K reduction is not deterministic"
+    check_bf16_output(a, ref, SLACK_EXACT)
+    check_bf16_output(c, ref, SLACK_EXACT)
+    assert kernels.device_status() == 0
+
+
+def test_scaling_x_by_two_is_exact(kernels):
+    """Linearity at full size: doubling X doubles every partial sum exactly, so outputs double bit for bit."""
+    M, N, K, G = 2, 18944, 3584, 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=4)
+    X2 = oracle.f32_to_bf16_bits(2.0 * oracle.bf16_bits_to_f32(X))
+    y1 = oracle.bf16_bits_to_f32(run(kernels, X, Wq, S, G))
+    y2 = oracle.bf16_bits_to_f32(run(kernels, X2, Wq, S, G))
+    assert np.array_equal(y2, 2.0 * y1)
+
+
+def test_row_permutation_equivariance(kernels):
+    """Permuting the rows of (Wq, S) permutes the output columns and changes nothing else."""
+    M, N, K, G = 3, 3584, 3584, 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=6)
+    perm = np.random.default_rng(0).permutation(N)
+    y = run(kernels, X, Wq, S, G)
+    yp = run(kernels, X, Wq[perm], S[perm], G)
+    assert np.array_equal(yp, y[:, perm])
+
+
+def test_output_is_fully_overwritten_and_nothing_else(kernels):
+    M, N, K, G = 5, 100, 384, 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=8)
+    buf = torch.full((M * N + 64,), 7.0, dtype=torch.bfloat16, device="cuda")
+    out = buf[32:32 + M * N].view(M, N)
+    kernels.w4_linear(bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S), G, out=out)
+    torch.cuda.synchronize()
+    assert torch.all(buf[:32] == 7.0) and torch.all(buf[32 + M * N:] == 7.0)
+    check_bf16_output(torch_to_bits(out), oracle.w4_linear_f32(X, Wq, S, G), SLACK_EXACT)
+
+
+def test_error_codes(kernels):
+    lib = kernels.lib
+    x = torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda")
+    wq = torch.zeros(8, 32, dtype=torch.int32, device="cuda")
+    s = torch.ones(8, 2, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(1, 8, dtype=torch.bfloat16, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    P = lambda t: t.data_ptr()
+    assert lib.ns_w4_linear(P(x), P(wq), P(s), P(y), 1, 8, 256, 128, st) == 0
+    assert lib.ns_w4_linear(P(x), P(wq), P(s), P(y), 0, 8, 256, 128, st) == -2   # reference: -2, nanoserve_ops.cu:86-88
+    assert lib.ns_w4_linear(P(x), P(wq), P(s), P(y), 1, 8, 256, 96, st) == -1    # K % G
+    assert lib.ns_w4_linear(P(x), P(wq), P(s), P(y), 1, 8, 256, 16, st) == -1    # G % 32
+    assert lib.ns_w4_linear(P(x), P(wq), P(s), P(y), 1, 8, 40, 8, st) == -1      # K % 32
+    assert lib.ns_w4_linear(None, P(wq), P(s), P(y), 1, 8, 256, 128, st) == -4
+    assert lib.ns_w4_linear(P(x) + 2, P(wq), P(s), P(y), 1, 8, 256, 128, st) == -4
+    with pytest.raises(RuntimeError, match="ns_w4_linear failed with code -1"):
+        kernels.w4_linear(x, wq, s, 96)
+    torch.cuda.synchronize()
+    assert kernels.device_status() == 0
+
+
+def _ref_lib():
+    path = oracle.REF_LIB_PATH
+    if not os.path.exists(path):
+        pytest.skip("reference library not built (oracle/_ref/libnanoserve_ref.so)")
+    lib = ctypes.CDLL(path)
+    vp, i32 = ctypes.c_void_p, ctypes.c_int
+    lib.ns_w4_linear.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.ns_w4_linear.restype = i32
+    return lib
+
+
+@pytest.mark.parametrize("N,K", [(18944, 3584), (3584, 18944), (512, 3584)])
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+def test_against_reference_kernels(kernels, N, K, M):
+    """Same inputs through the reference's own GEMV (kernels/quant/w4a16.cuh:42-115, built unchanged for
+    sm_100a): both round an fp32 sum once to bf16, so they agree to one bf16 ulp, and almost always exactly."""
+    ref = _ref_lib()
+    G = 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=13)
+    x, wq, s = bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S)
+    y_ref = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    rc = ref.ns_w4_linear(x.data_ptr(), wq.data_ptr(), s.data_ptr(), y_ref.data_ptr(), M, N, K, G,
+                          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    y = kernels.w4_linear(x, wq, s, G)
+    torch.cuda.synchronize()
+    a, b = y.float(), y_ref.float()
+    ulp = torch.maximum(a.abs(), b.abs()) * 2.0**-7
+    assert torch.all((a - b).abs() <= ulp + 1e-30)
+    assert (a != b).float().mean().item() < 0.02
