@@ -42,14 +42,17 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// One try: the hardware suspends the thread until the phase completes or a time limit of about
+// `kSuspendHintNs` passes, so a waiting warp issues almost no instructions.
+constexpr uint32_t kSuspendHintNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
@@ -60,18 +63,21 @@ constexpr long long kWaitLimitCycles = 1000000000LL;
 // Waits for the phase with the given parity to complete.  `*abort_flag` (shared memory) is set by the
 // first wait in the CTA that runs out; once it is set every later wait gives up at once, so a broken
 // pipeline costs one time-out per CTA rather than one per wait.  Returns false on time-out.
+// The polling loop is kept to a few instructions per try (a spinning warp shares its scheduler with
+// the warps doing the math) and looks at the clock only every 64 tries.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  if (*abort_flag) return false;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitLimitCycles) {
       *abort_flag = 1;
       return false;
     }
   }
-  return true;
 }
 
 // ------------------------------------------------------------------ bulk-async copies (TMA)
@@ -110,6 +116,16 @@ __device__ __forceinline__ void mma_16816_bf16(float (&d)[4], uint32_t a0, uint3
       "{%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// D[16x8] = A[16x16] * B[16x8] (accumulator starts at zero).
+__device__ __forceinline__ void mma_16816_bf16_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                    uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 // ------------------------------------------------------------------ tcgen05: TMEM + UMMA

@@ -1,7 +1,300 @@
+// W4A16 prefill GEMM for sm_100a:  Y[M,N] (bf16) = X[M,K] (bf16) . dequant(Wq, S)^T  for M > 16.
+//
+// Replaces the reference's w4a16_gemm_kernel / w4a16_gemm_cfg (kernels/quant/w4a16.cuh:124-270): cp.async
+// staging, a dequant pass into shared memory and mma.sync.m16n8k16 with 128x128x32 tiles, M and N
+// multiples of 128 only.  Same numerics: each weight is dequantised to RN_bf16((q - 8) * s)
+// (w4a16.cuh:196-197), the contraction accumulates in fp32, one rounding to bf16 at the store.
+//
+// Design (tensor-bound; one CTA per SM, one output tile per CTA):
+//   tile     MI x 128 tokens by 256 output features, K walked in blocks of 64
+//   warp 0   TMA producer: per K block, the X tile(s) (128 rows x 128 B, 128-byte swizzle) and the packed
+//            weight tile (256 rows x 32 B) land in a ring stage; completion counted on an mbarrier
+//   warp 1   MMA issuer: one elected lane issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=256, K=16)
+//            from shared-memory descriptors into fp32 accumulators in TMEM (MI x 256 columns); the weight
+//            operand is shared by the MI token tiles, so every weight is dequantised once per 128*MI tokens
+//   warps 2-9 dequant: thread r owns weight row r of the tile: two 16-byte shared loads of packed nibbles,
+//            LOP3 unpack to bf16 pairs, exact -8 (bf16x2 subtract), one bf16x2 multiply by the group scale,
+//            and eight 16-byte stores into a K-major, 128-byte-swizzled bf16 tile (two buffers) that the
+//            MMA reads through the async proxy (fence.proxy.async before the arrive)
+//   epilogue the same eight warps read the accumulators with tcgen05.ld (32 lanes x 32 columns), convert to
+//            bf16 and store rows of Y
+// Ragged M, N and a K tail of 32 need no special path: TMA zero-fills out-of-range rows and columns, the
+// scale of an out-of-range row or group is taken as 0, and the epilogue masks its stores.
+// Every mbarrier wait is bounded; on a time-out the CTA records a status, still frees its TMEM and returns.
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <mutex>
+
+#include "ptx.cuh"
+#include "tensor_map.h"
+#include "w4_common.cuh"
 #include "w4_internal.h"
+
 namespace b2 {
-int gemm_launch(const void*, const void*, const void*, void*, int, int, int, int, const Workspace&, int, int,
-                cudaStream_t) {
-  return kErrNotImplemented;
+namespace {
+
+constexpr int kBN = 256;            // output features per tile (UMMA N)
+constexpr int kBK = 64;             // K per block: one 128-byte swizzled row of bf16
+constexpr int kATileBytes = 128 * 128;        // 128 tokens x 64 bf16
+constexpr int kWpTileBytes = kBN * 32;        // 256 rows x 8 packed words
+constexpr int kBdTileBytes = kBN * 128;       // 256 rows x 64 bf16
+constexpr int kDequantThreads = 256;
+constexpr int kGemmThreads = 32 * 2 + kDequantThreads;
+constexpr int kGemmSmemLimit = 232448;
+
+struct GemmParams {
+  const __nv_bfloat16* S;
+  __nv_bfloat16* Y;
+  int M, N, K, G, KG;
+  int nkb;  // K blocks of 64
+  int* status;
+};
+
+template <int MI>
+struct GemmGeo {
+  static constexpr int kStageBytes = MI * kATileBytes + kWpTileBytes;
+  static constexpr int kStages = MI == 2 ? 3 : 5;
+  static constexpr int kRingBytes = kStages * kStageBytes;
+  static constexpr int kBdOffset = kRingBytes;
+  static constexpr int kBarOffset = kBdOffset + 2 * kBdTileBytes;
+  static constexpr int kSmemBytes = kBarOffset + 256 + 1024;  // barriers + slack for 1024-byte alignment
+  static constexpr int kTmemCols = MI * kBN;                  // 256 or 512: powers of two
+};
+
+template <int MI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    w4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                   const GemmParams p) {
+  using geo = GemmGeo<MI>;
+  extern __shared__ unsigned char smem_raw[];
+  // 128-byte-swizzled tiles need a 1024-byte aligned base
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar_base = base + geo::kBarOffset;
+  const uint32_t bar_full = bar_base;                        // [kStages]
+  const uint32_t bar_empty = bar_base + 8 * 8;               // [kStages]
+  const uint32_t bar_bd_full = bar_base + 16 * 8;            // [2]
+  const uint32_t bar_bd_empty = bar_base + 18 * 8;           // [2]
+  const uint32_t bar_acc = bar_base + 20 * 8;                // [1]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + geo::kBarOffset + 22 * 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + geo::kBarOffset + 23 * 8);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * kBN;
+  const int m0 = blockIdx.y * (128 * MI);
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < geo::kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, kDequantThreads + 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_bd_full + 8 * b, kDequantThreads);
+      mbar_init(bar_bd_empty + 8 * b, 1);
+    }
+    mbar_init(bar_acc, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_x);
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), geo::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool poisoned = *reinterpret_cast<volatile int*>(p.status) != 0;
+
+  if (!poisoned) {
+    if (warp == 0) {
+      // ------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        for (int kb = 0; kb < p.nkb; ++kb) {
+          const int s = kb % geo::kStages;
+          const uint32_t ph = (kb / geo::kStages) & 1;
+          mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag);
+          const uint32_t stage = base + s * geo::kStageBytes;
+          mbar_arrive_expect_tx(bar_full + 8 * s, geo::kStageBytes);
+#pragma unroll
+          for (int mi = 0; mi < MI; ++mi)
+            tma_load_2d(stage + mi * kATileBytes, &tmap_x, kb * kBK, m0 + mi * 128, bar_full + 8 * s);
+          tma_load_2d(stage + MI * kATileBytes, &tmap_w, kb * (kBK / 8), n0, bar_full + 8 * s);
+        }
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      // ------------------------------------------------------------ MMA issuer
+      if (lane == 0) {
+        constexpr uint32_t idesc = umma_idesc_bf16(128, kBN);
+        for (int kb = 0; kb < p.nkb; ++kb) {
+          const int s = kb % geo::kStages, b = kb & 1;
+          mbar_wait(bar_full + 8 * s, (kb / geo::kStages) & 1, abort_flag);
+          mbar_wait(bar_bd_full + 8 * b, (kb >> 1) & 1, abort_flag);
+          tc_fence_after_sync();
+          const uint32_t a_addr = base + s * geo::kStageBytes;
+          const uint32_t b_addr = base + geo::kBdOffset + b * kBdTileBytes;
+#pragma unroll
+          for (int kk = 0; kk < kBK / 16; ++kk) {
+            const uint64_t db = umma_desc_k128(b_addr + kk * 32);
+#pragma unroll
+            for (int mi = 0; mi < MI; ++mi) {
+              const uint64_t da = umma_desc_k128(a_addr + mi * kATileBytes + kk * 32);
+              umma_f16_ss(tmem_base + mi * kBN, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            }
+          }
+          umma_commit(bar_empty + 8 * s);      // the X tile and the packed tile of this stage are consumed
+          umma_commit(bar_bd_empty + 8 * b);   // the dequantised tile may be overwritten
+        }
+        umma_commit(bar_acc);
+      }
+      __syncwarp();
+    } else {
+      // ------------------------------------------------------------ dequant warps, then epilogue
+      const int r = tid - 64;  // weight row of the tile owned by this thread
+      const int n = n0 + r;
+      const uint32_t bd_row = base + geo::kBdOffset + r * 128;
+      const uint32_t sw = (uint32_t)(r & 7);
+      for (int kb = 0; kb < p.nkb; ++kb) {
+        const int s = kb % geo::kStages, b = kb & 1;
+        const int k0 = kb * kBK;
+        __nv_bfloat16 sv0 = __float2bfloat16(0.f), sv1 = sv0;
+        if (n < p.N) {
+          sv0 = p.S[(size_t)n * p.KG + k0 / p.G];
+          if (k0 + 32 < p.K) sv1 = p.S[(size_t)n * p.KG + (k0 + 32) / p.G];
+        }
+        const uint32_t s2[2] = {bf16_dup(sv0), bf16_dup(sv1)};
+
+        // one lane per warp polls: many threads spinning on a shared-memory barrier slow the copies down
+        if (lane == 0) mbar_wait(bar_full + 8 * s, (kb / geo::kStages) & 1, abort_flag);
+        __syncwarp();
+        const uint32_t wp = base + s * geo::kStageBytes + MI * kATileBytes + r * 32;
+        const uint4 w0 = lds128(wp), w1 = lds128(wp + 16);
+        mbar_arrive(bar_empty + 8 * s);  // packed words are in registers
+        const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+
+        if (lane == 0) mbar_wait(bar_bd_empty + 8 * b, ((kb >> 1) & 1) ^ 1, abort_flag);
+        __syncwarp();
+        const uint32_t dst = bd_row + b * kBdTileBytes;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t v[4];
+          unpack_w4_biased(words[c], v);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) v[q] = mul_bf16x2(sub136_bf16x2(v[q]), s2[c >> 2]);
+          // v[q] = {w[q], w[q+4]}  ->  natural order pairs {w0,w1} {w2,w3} {w4,w5} {w6,w7}
+          uint4 o;
+          o.x = __byte_perm(v[0], v[1], 0x5410);
+          o.y = __byte_perm(v[2], v[3], 0x5410);
+          o.z = __byte_perm(v[0], v[1], 0x7632);
+          o.w = __byte_perm(v[2], v[3], 0x7632);
+          sts128(dst + ((uint32_t(c) ^ sw) << 4), o);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(bar_bd_full + 8 * b);
+      }
+
+      // ---- epilogue: TMEM -> registers -> bf16 -> global
+      if (lane == 0) mbar_wait(bar_acc, 0, abort_flag);
+      __syncwarp();
+      tc_fence_after_sync();
+      const int ew = warp - 2;           // 0..7
+      const int quad = warp & 3;         // TMEM lane quadrant this warp may read
+      const int grp = ew >> 2;           // 0 or 1
+      const int mi = MI == 2 ? grp : 0;
+      const int col_begin = MI == 2 ? 0 : grp * (kBN / 2);
+      const int col_end = MI == 2 ? kBN : col_begin + kBN / 2;
+      const int m = m0 + mi * 128 + quad * 32 + lane;
+      const bool vec_ok = (p.N % 8) == 0;
+      for (int c0 = col_begin; c0 < col_end; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(mi * kBN + c0), v);
+        tmem_ld_wait();
+        if (m < p.M) {
+          __nv_bfloat16* yrow = p.Y + (size_t)m * p.N + n0 + c0;
+          if (vec_ok && n0 + c0 + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * e]),
+                                                               __uint_as_float(v[8 * q + 2 * e + 1]));
+                ow[e] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(yrow + 8 * q) = o;
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (n0 + c0 + e < p.N) yrow[e] = __float2bfloat16(__uint_as_float(v[e]));
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusGemmTimeout);
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);  // let copies in flight land before the smem is released
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, geo::kTmemCols);
+  }
 }
+
+// ------------------------------------------------------------------ host side
+template <int MI>
+int launch_gemm(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& p, cudaStream_t stream) {
+  auto kernel = w4_gemm_kernel<MI>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmGeo<MI>::kSmemBytes);
+  if (e != cudaSuccess) return (int)e;
+  const dim3 grid((p.N + kBN - 1) / kBN, (p.M + 128 * MI - 1) / (128 * MI));
+  kernel<<<grid, kGemmThreads, GemmGeo<MI>::kSmemBytes, stream>>>(tx, tw, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                const Workspace& ws, int flags, int sm_count, cudaStream_t stream) {
+  (void)flags;
+  (void)sm_count;
+  static_assert(GemmGeo<2>::kSmemBytes <= kGemmSmemLimit && GemmGeo<1>::kSmemBytes <= kGemmSmemLimit, "smem");
+  if (M < 1) return kErrUnsupportedM;
+  if (N < 1 || K < 32 || G < 32 || K % 32 || G % 32 || K % G) return kErrBadShape;
+  if (!X || !Wq || !S || !Y) return kErrBadPointer;
+  if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(Wq) & 15) ||
+      (reinterpret_cast<uintptr_t>(S) & 1) || (reinterpret_cast<uintptr_t>(Y) & 15))
+    return kErrBadPointer;
+  if (!ws.status) return kErrWorkspace;
+
+  CUtensorMap tx, tw;
+  if (!make_tensor_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, (uint64_t)M, (uint64_t)K, 128, kBK,
+                 CU_TENSOR_MAP_SWIZZLE_128B))
+    return kErrDevice;
+  if (!make_tensor_map_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, Wq, (uint64_t)N, (uint64_t)K / 8, kBN, kBK / 8,
+                 CU_TENSOR_MAP_SWIZZLE_NONE))
+    return kErrDevice;
+
+  GemmParams p{};
+  p.S = static_cast<const __nv_bfloat16*>(S);
+  p.Y = static_cast<__nv_bfloat16*>(Y);
+  p.M = M; p.N = N; p.K = K; p.G = G;
+  p.KG = K / G;
+  p.nkb = (K + kBK - 1) / kBK;
+  p.status = ws.status;
+  return M <= 128 ? launch_gemm<1>(tx, tw, p, stream) : launch_gemm<2>(tx, tw, p, stream);
+}
+
 }  // namespace b2

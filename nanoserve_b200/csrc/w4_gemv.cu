@@ -4,12 +4,15 @@
 // serves M in {1,2,4,8} only on CUDA cores.  Same operands, same weight format, fp32 accumulation.
 //
 // Design (HBM-bound: every weight byte is read exactly once, X is tiny and lives in shared memory):
-//   * One persistent CTA per SM.  A producer warp streams the packed weights of a 32-row group into a
-//     shared-memory ring with untiled bulk-async copies (one row segment per lane, up to 1 KB each,
-//     completion counted on an mbarrier); several stages are in flight from the first instruction.
+//   * One persistent CTA per SM.  A producer lane streams the packed weights of a 32-row group into a
+//     shared-memory ring with tiled TMA loads through a tensor map over Wq: boxes of 32 rows x 128 bytes
+//     (two K chunks) with the 128-byte swizzle, up to NCW/2 boxes per stage, completion counted on an
+//     mbarrier; several stages are in flight from the first instruction.  (Per-row untiled bulk copies
+//     were measured first: the TMA unit retires about one copy per 70 cycles whatever its size, so 1 KB
+//     row segments cap at ~4 TB/s; tiled boxes reach the copy-kernel bandwidth.)
 //   * NCW consumer warps each take one 128-wide K chunk of the stage for both 16-row blocks.  A lane
-//     reads 16 bytes (32 nibbles) per row with one conflict-free 128-bit shared load (row pitch is
-//     64 mod 128 bytes).
+//     reads 16 bytes (32 nibbles) per row with one 128-bit shared load; the swizzle plus a fixed
+//     permutation of which tile row feeds which mma row makes those loads bank-conflict free.
 //   * Unpack: three shifts + four LOP3 per word give bf16 pairs {128+q[p], 128+q[p+4]}; these feed the
 //     A operand of mma.sync.m16n8k16 directly.  The contraction index of an mma is a dummy, so the
 //     pairing is matched by permuting X once, when it is staged into shared memory -- the weights are
@@ -26,6 +29,7 @@
 #include <cstdio>
 
 #include "ptx.cuh"
+#include "tensor_map.h"
 #include "w4_common.cuh"
 #include "w4_internal.h"
 
@@ -39,7 +43,7 @@ constexpr int kChunkBytes = 64;        // packed bytes of one row in one chunk
 constexpr int kRedPitch = 36;          // floats per (warp, token) row of the reduction buffer: 32 + 4 pad
 constexpr int kMaxStages = 8;
 constexpr int kSmemLimit = 232448;     // 227 KB opt-in maximum per CTA on sm_100
-constexpr int kHeaderBytes = 256;
+constexpr int kHeaderBytes = 512;      // flags + barriers (first 256 B), a 256-byte block of zeros
 
 struct GemvParams {
   const __nv_bfloat16* X;
@@ -48,7 +52,6 @@ struct GemvParams {
   __nv_bfloat16* Y;
   int M, N, K, G;
   int KG;           // K / G
-  int row_bytes;    // K / 2
   int nchunks;      // ceil(K / 128)
   int nrg;          // ceil(N / 32)
   int nslices;      // CTAs sharing one row group along K
@@ -59,12 +62,13 @@ struct GemvParams {
   float* partial;   // [nslices][M][N]
   int* counters;    // [nrg]
   int* status;
+  int dbg;  // diagnostics: bit 0 = take every scale as 1 (no scale loads), bit 1 = skip the math
 };
 
 template <int NCW>
 struct Geo {
-  static constexpr int kStageRowPitch = NCW * kChunkBytes + 64;  // == 64 (mod 128): conflict-free quads
-  static constexpr int kStageBytes = kRowsPerGroup * kStageRowPitch;
+  static constexpr int kBoxBytes = kRowsPerGroup * 128;           // 32 rows x 128 B (two chunks), swizzled
+  static constexpr int kStageBytes = (NCW / 2) * kBoxBytes;
   static constexpr int kThreads = (NCW + 1) * 32;
   static constexpr int kConsumerThreads = NCW * 32;
 };
@@ -120,13 +124,15 @@ __device__ __forceinline__ void stage_x(const GemvParams& p, uint32_t xs_base, f
 // MT: token tiles of 8 (1 or 2).  NCW: consumer warps (= chunks per stage).  G128: G % 128 == 0.
 // FOLD: zero-point folded into a per-chunk correction (only with G128).
 template <int MT, int NCW, bool G128, bool FOLD>
-__global__ void __launch_bounds__((NCW + 1) * 32, 1) w4_gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__((NCW + 1) * 32, 1)
+    w4_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemvParams p) {
   using geo = Geo<NCW>;
   extern __shared__ __align__(1024) unsigned char smem[];
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
   int* last_flag = reinterpret_cast<int*>(smem + 8);
   const uint32_t bar_full = smem_u32(smem + 64);
   const uint32_t bar_empty = bar_full + 8 * kMaxStages;
+  const uint32_t zero_base = smem_u32(smem + 256);
   float* red = reinterpret_cast<float*>(smem + kHeaderBytes);
   float* xsum = reinterpret_cast<float*>(smem + kHeaderBytes + red_bytes(NCW, MT));
   // xsum holds M * cps floats (<= 16 * 148 * 4 B is too much in general; the host caps cps so that
@@ -134,8 +140,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) w4_gemv_kernel(const GemvPa
   const int xsum_bytes = (p.M * p.cps * 4 + 127) & ~127;
   const uint32_t xs_base = smem_u32(smem + kHeaderBytes + red_bytes(NCW, MT) + xsum_bytes);
   const int xs_bytes = (p.M * p.xs_m_stride + 127) & ~127;
-  const uint32_t ring_base =
-      (xs_base + xs_bytes + 127) & ~127u;
+  const uint32_t ring_base = (xs_base + xs_bytes + 1023) & ~1023u;  // swizzled boxes: 1024-byte aligned
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -149,47 +154,73 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) w4_gemv_kernel(const GemvPa
     fence_mbar_init();
   }
   __syncthreads();
-  const bool poisoned = *reinterpret_cast<volatile int*>(p.status) != 0;  // an earlier launch timed out
-
-  if (!poisoned) {
+  {
     if (warp == NCW) {
       // ------------------------------------------------------------ producer warp
-      const unsigned char* wbytes = reinterpret_cast<const unsigned char*>(p.Wq);
-      int it = 0;
-      for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
-        const int sl = tile / p.nrg, rg = tile - sl * p.nrg;
-        const int cb = sl * p.cps, ce = min(p.nchunks, cb + p.cps);
-        const int row0 = rg * kRowsPerGroup;
-        const int rows_valid = min(kRowsPerGroup, p.N - row0);
-        for (int c0 = cb; c0 < ce; c0 += NCW, ++it) {
-          const int s = it % p.nstages;
-          const uint32_t ph = (it / p.nstages) & 1;
-          const int off = c0 * kChunkBytes;
-          const int bytes_row = min(min(NCW, ce - c0) * kChunkBytes, p.row_bytes - off);
-          mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag);
-          if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)(rows_valid * bytes_row));
-          __syncwarp();
-          if (lane < rows_valid)
-            bulk_g2s(ring_base + s * geo::kStageBytes + lane * geo::kStageRowPitch,
-                     wbytes + (size_t)(row0 + lane) * p.row_bytes + off, (uint32_t)bytes_row,
-                     bar_full + 8 * s);
+      if (lane == 0) {
+        tma_prefetch_desc(&tmap_w);
+        int s = 0;
+        uint32_t ph = 0;
+        for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+          const int sl = tile / p.nrg, rg = tile - sl * p.nrg;
+          const int cb = sl * p.cps, ce = min(p.nchunks, cb + p.cps);
+          const int row0 = rg * kRowsPerGroup;
+          for (int c0 = cb; c0 < ce; c0 += NCW) {
+            const int nbox = (min(NCW, ce - c0) + 1) >> 1;
+            mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag);
+            // out-of-range rows and K columns are zero-filled and still counted in the transaction bytes
+            mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)(nbox * geo::kBoxBytes));
+            for (int b = 0; b < nbox; ++b)
+              tma_load_2d(ring_base + s * geo::kStageBytes + b * geo::kBoxBytes, &tmap_w, (c0 + 2 * b) * 16, row0,
+                          bar_full + 8 * s);
+            if (++s == p.nstages) {
+              s = 0;
+              ph ^= 1;
+            }
+          }
         }
       }
+      __syncwarp();
     } else {
       // ------------------------------------------------------------ consumer warps
       const int g = lane >> 2, t = lane & 3;
+      // tile row fed to mma row g: neighbouring g get rows 4 apart, so that the eight lanes of one shared-
+      // memory access phase land in opposite halves of the swizzled 128-byte rows (no bank conflicts)
+      const int gr = (g >> 1) | ((g & 1) << 2);
       const int ctid = tid;  // consumer warps are warps 0..NCW-1
-      int it = 0, staged_slice = -1, tcount = 0;
+      // chunk `warp` of a stage sits in box warp/2, 64-byte half warp%2; 16-byte unit index XOR (row % 8 = gr)
+      const uint32_t w_lane_off = (warp >> 1) * geo::kBoxBytes + gr * 128 +
+                                  ((uint32_t(((warp & 1) << 2) | t) ^ uint32_t(gr)) << 4);
+      const int gdiv = G128 ? p.G / kChunkK : 1;  // chunks per quantization group
+      // the stage ring is walked with counters: no division in the loop
+      int s = 0;
+      uint32_t ph = 0;
+      int staged_slice = -1, tcount = 0;
       for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
         const int sl = tile / p.nrg, rg = tile - sl * p.nrg;
         const int cb = sl * p.cps, ce = min(p.nchunks, cb + p.cps);
+        const int nch = ce - cb;
         const int row0 = rg * kRowsPerGroup;
         if (sl != staged_slice) {
           if (staged_slice >= 0) consumer_sync(geo::kConsumerThreads);  // all done with the old slice
           stage_x<NCW>(p, xs_base, xsum, cb, ce, ctid);
+          if (ctid < 16) sts128(zero_base + ctid * 16, make_uint4(0u, 0u, 0u, 0u));
           consumer_sync(geo::kConsumerThreads);
           staged_slice = sl;
         }
+        // B-fragment source of this lane: its token's staged X, or a block of zeros for padding tokens
+        uint32_t xaddr[MT], xstep[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const int m = mt * 8 + g;
+          const bool real = m < p.M;
+          xaddr[mt] = real ? xs_base + m * p.xs_m_stride + warp * 256 + t * 16 : zero_base + t * 16;
+          xstep[mt] = real ? NCW * 256 : 0;
+        }
+        // G128: lane i fetches the scale of row row0 + i; the quad layout is rebuilt with shuffles
+        const int n_lane = row0 + lane;
+        const __nv_bfloat16* s_lane = p.S + (size_t)(n_lane < p.N ? n_lane : 0) * p.KG;
+        const bool s_valid = n_lane < p.N && !(p.dbg & 1);
 
         float fin[2][MT][4];
 #pragma unroll
@@ -199,68 +230,63 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) w4_gemv_kernel(const GemvPa
 #pragma unroll
             for (int i = 0; i < 4; ++i) fin[rb][mt][i] = 0.f;
 
-        for (int c0 = cb; c0 < ce; c0 += NCW, ++it) {
-          const int s = it % p.nstages;
-          const uint32_t ph = (it / p.nstages) & 1;
-          const int c = c0 + warp;
+        for (int c = cb + warp, c0 = cb; c0 < ce; c0 += NCW, c += NCW) {
           const bool active = c < ce;
 
           // scales first: their latency overlaps the wait for the stage
-          float sc[2][2];
-          uint32_t sc2[2][2];
+          float sc[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
+          uint32_t sc2[2][2] = {{0x3F803F80u, 0x3F803F80u}, {0x3F803F80u, 0x3F803F80u}};
+          uint32_t srow = p.dbg & 1 ? 0x3F80u : 0u;
           if (active) {
-            const int k_lane = c * kChunkK + 32 * t;
-            const int grp = G128 ? (c * kChunkK) / p.G : (k_lane < p.K ? k_lane / p.G : -1);
+            if constexpr (G128) {
+              if (s_valid) srow = __bfloat16_as_ushort(__ldg(s_lane + (gdiv == 1 ? c : c / gdiv)));
+            } else if (!(p.dbg & 1)) {
+              const int k_lane = c * kChunkK + 32 * t;
+              const int grp = k_lane < p.K ? k_lane / p.G : -1;
 #pragma unroll
-            for (int rb = 0; rb < 2; ++rb)
+              for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
-              for (int hh = 0; hh < 2; ++hh) {
-                const int n = row0 + rb * 16 + g + 8 * hh;
-                __nv_bfloat16 sv = __float2bfloat16(0.f);
-                if (n < p.N && grp >= 0) sv = p.S[(size_t)n * p.KG + grp];
-                sc[rb][hh] = __bfloat162float(sv);
-                sc2[rb][hh] = bf16_dup(sv);
-              }
+                for (int hh = 0; hh < 2; ++hh) {
+                  const int n = row0 + rb * 16 + gr + 8 * hh;
+                  __nv_bfloat16 sv = __float2bfloat16(0.f);
+                  if (n < p.N && grp >= 0) sv = __ldg(p.S + (size_t)n * p.KG + grp);
+                  sc2[rb][hh] = bf16_dup(sv);
+                }
+            }
           }
 
-          mbar_wait(bar_full + 8 * s, ph, abort_flag);
+          if (lane == 0) mbar_wait(bar_full + 8 * s, ph, abort_flag);
+          __syncwarp();
 
-          if (active) {
-            // B fragments: this lane's token is mt*8 + g
+          if (active && !(p.dbg & 2)) {
+            if constexpr (G128) {
+#pragma unroll
+              for (int rb = 0; rb < 2; ++rb)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+                  sc[rb][hh] = __uint_as_float(__shfl_sync(0xffffffffu, srow, rb * 16 + gr + 8 * hh) << 16);
+            }
             uint32_t xf[MT][16];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-              const int m = mt * 8 + g;
-              if (m < p.M) {
-                const uint32_t xa = xs_base + m * p.xs_m_stride + (c - cb) * 256 + t * 16;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const uint4 v = lds128(xa + j * 64);
-                  xf[mt][4 * j + 0] = v.x;
-                  xf[mt][4 * j + 1] = v.y;
-                  xf[mt][4 * j + 2] = v.z;
-                  xf[mt][4 * j + 3] = v.w;
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) xf[mt][i] = 0u;
+              for (int j = 0; j < 4; ++j) {
+                const uint4 v = lds128(xaddr[mt] + j * 64);
+                xf[mt][4 * j + 0] = v.x;
+                xf[mt][4 * j + 1] = v.y;
+                xf[mt][4 * j + 2] = v.z;
+                xf[mt][4 * j + 3] = v.w;
               }
             }
-            const uint32_t wa = ring_base + s * geo::kStageBytes + warp * kChunkBytes + t * 16;
+            const uint32_t wa = ring_base + s * geo::kStageBytes + w_lane_off;
 #pragma unroll
             for (int rb = 0; rb < 2; ++rb) {
-              const uint4 wl4 = lds128(wa + (rb * 16 + g) * geo::kStageRowPitch);
-              const uint4 wh4 = lds128(wa + (rb * 16 + g + 8) * geo::kStageRowPitch);
+              const uint4 wl4 = lds128(wa + rb * 2048);
+              const uint4 wh4 = lds128(wa + rb * 2048 + 1024);
               const uint32_t wl[4] = {wl4.x, wl4.y, wl4.z, wl4.w};
               const uint32_t wh[4] = {wh4.x, wh4.y, wh4.z, wh4.w};
               if constexpr (G128) {
                 float acc[MT][2][4];
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                  for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[mt][h][i] = 0.f;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   uint32_t rl[4], rh[4];
@@ -276,9 +302,14 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) w4_gemv_kernel(const GemvPa
 #pragma unroll
                   for (int h = 0; h < 2; ++h)
 #pragma unroll
-                    for (int mt = 0; mt < MT; ++mt)
-                      mma_16816_bf16(acc[mt][h], rl[2 * h], rh[2 * h], rl[2 * h + 1], rh[2 * h + 1],
-                                     xf[mt][4 * j + 2 * h], xf[mt][4 * j + 2 * h + 1]);
+                    for (int mt = 0; mt < MT; ++mt) {
+                      if (j == 0)
+                        mma_16816_bf16_zero(acc[mt][h], rl[2 * h], rh[2 * h], rl[2 * h + 1], rh[2 * h + 1],
+                                            xf[mt][4 * j + 2 * h], xf[mt][4 * j + 2 * h + 1]);
+                      else
+                        mma_16816_bf16(acc[mt][h], rl[2 * h], rh[2 * h], rl[2 * h + 1], rh[2 * h + 1],
+                                       xf[mt][4 * j + 2 * h], xf[mt][4 * j + 2 * h + 1]);
+                    }
                 }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
@@ -287,8 +318,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) w4_gemv_kernel(const GemvPa
                   if constexpr (FOLD) {
                     // columns 2t, 2t+1 of this tile are tokens mt*8 + 2t (+1)
                     const int m0 = mt * 8 + 2 * t;
-                    const float xs0 = m0 < p.M ? xsum[m0 * (ce - cb) + (c - cb)] : 0.f;
-                    const float xs1 = m0 + 1 < p.M ? xsum[(m0 + 1) * (ce - cb) + (c - cb)] : 0.f;
+                    const float xs0 = m0 < p.M ? xsum[m0 * nch + (c - cb)] : 0.f;
+                    const float xs1 = m0 + 1 < p.M ? xsum[(m0 + 1) * nch + (c - cb)] : 0.f;
                     v0 = fmaf(-136.f, xs0, v0);
                     v1 = fmaf(-136.f, xs1, v1);
                     v2 = fmaf(-136.f, xs0, v2);
@@ -322,15 +353,22 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) w4_gemv_kernel(const GemvPa
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) xaddr[mt] += xstep[mt];
+          if (++s == p.nstages) {
+            s = 0;
+            ph ^= 1;
+          }
         }
 
+        if (p.dbg & 4) continue;  // diagnostics: no reduction, no output
         // ---- K reduction across the consumer warps of this CTA
         float* rbuf = red + (tcount & 1) * (NCW * MT * 8 * kRedPitch);
 #pragma unroll
         for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            float* r0 = rbuf + (warp * MT * 8 + mt * 8 + 2 * t) * kRedPitch + rb * 16 + g;
+            float* r0 = rbuf + (warp * MT * 8 + mt * 8 + 2 * t) * kRedPitch + rb * 16 + gr;
             r0[0] = fin[rb][mt][0];
             r0[kRedPitch] = fin[rb][mt][1];
             r0[8] = fin[rb][mt][2];
@@ -400,7 +438,7 @@ size_t smem_without_ring(int M, int mt, int ncw, int cps) {
   const int xs_m_stride = cps * 256 + 64;
   const size_t xsum_bytes = ((size_t)M * cps * 4 + 127) & ~(size_t)127;
   const size_t xs_bytes = ((size_t)M * xs_m_stride + 127) & ~(size_t)127;
-  return kHeaderBytes + red_bytes(ncw, mt) + xsum_bytes + xs_bytes + 128;
+  return kHeaderBytes + red_bytes(ncw, mt) + xsum_bytes + xs_bytes + 1024;
 }
 
 bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap,
@@ -412,7 +450,7 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
   pl.fold = pl.g128 && (flags & kFlagFoldZeroPoint);
   const int nchunks = (K + kChunkK - 1) / kChunkK;
   const int nrg = (N + kRowsPerGroup - 1) / kRowsPerGroup;
-  const int stage_bytes = kRowsPerGroup * (pl.ncw * kChunkBytes + 64);
+  const int stage_bytes = (pl.ncw / 2) * kRowsPerGroup * 128;
   pl.grid = std::max(1, sm_count);
 
   // Cost model in units of "one chunk of one row group" (2 KB of weights): a tile costs its chunk
@@ -442,7 +480,11 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
       best_cps = cps;
     }
   }
-  if (best_ns == 0) return false;
+  if (best_ns == 0) {
+    // the staged X of the wide CTA does not fit: the narrow one leaves more shared memory for it
+    if (pl.ncw == 16) return make_plan(M, N, K, G, flags | kFlagNarrowCta, sm_count, partial_cap, counters_cap, out);
+    return false;
+  }
   pl.nslices = best_ns;
   pl.cps = best_cps;
   pl.xs_m_stride = pl.cps * 256 + 64;
@@ -458,13 +500,13 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
 }
 
 template <int MT, int NCW, bool G128, bool FOLD>
-int launch_variant(const GemvParams& p, const GemvPlan& pl, cudaStream_t stream) {
+int launch_variant(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan& pl, cudaStream_t stream) {
   auto kernel = w4_gemv_kernel<MT, NCW, G128, FOLD>;
   // Raising the dynamic shared-memory limit is idempotent and cheap; doing it on every launch keeps
   // the call correct on every device of a multi-GPU process without per-device bookkeeping.
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
   if (e != cudaSuccess) return (int)e;
-  kernel<<<pl.grid, Geo<NCW>::kThreads, pl.smem, stream>>>(p);
+  kernel<<<pl.grid, Geo<NCW>::kThreads, pl.smem, stream>>>(tmap, p);
   return (int)cudaGetLastError();
 }
 
@@ -491,6 +533,12 @@ int gemv_launch(const void* X, const void* Wq, const void* S, void* Y, int M, in
                  ws.partial_bytes, ws.n_counters, &pl))
     return kErrTooLarge;
 
+  // Wq as a 2-D tensor of 32-bit words [N rows, K/8 columns]; boxes of 32 words (two chunks) x 32 rows
+  CUtensorMap tmap;
+  if (!make_tensor_map_2d(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, Wq, (uint64_t)N, (uint64_t)K / 8, kRowsPerGroup,
+                          32, CU_TENSOR_MAP_SWIZZLE_128B))
+    return kErrDevice;
+
   GemvParams p{};
   p.X = static_cast<const __nv_bfloat16*>(X);
   p.Wq = static_cast<const uint32_t*>(Wq);
@@ -498,7 +546,6 @@ int gemv_launch(const void* X, const void* Wq, const void* S, void* Y, int M, in
   p.Y = static_cast<__nv_bfloat16*>(Y);
   p.M = M; p.N = N; p.K = K; p.G = G;
   p.KG = K / G;
-  p.row_bytes = K / 2;
   p.nchunks = (K + kChunkK - 1) / kChunkK;
   p.nrg = (N + kRowsPerGroup - 1) / kRowsPerGroup;
   p.nslices = pl.nslices;
@@ -509,20 +556,21 @@ int gemv_launch(const void* X, const void* Wq, const void* S, void* Y, int M, in
   p.partial = ws.partial;
   p.counters = ws.counters;
   p.status = ws.status;
+  p.dbg = (flags >> 8) & 15;
 
   if (pl.mt == 1) {
     if (pl.ncw == 16) {
-      if (!pl.g128) return launch_variant<1, 16, false, false>(p, pl, stream);
-      return pl.fold ? launch_variant<1, 16, true, true>(p, pl, stream)
-                     : launch_variant<1, 16, true, false>(p, pl, stream);
+      if (!pl.g128) return launch_variant<1, 16, false, false>(tmap, p, pl, stream);
+      return pl.fold ? launch_variant<1, 16, true, true>(tmap, p, pl, stream)
+                     : launch_variant<1, 16, true, false>(tmap, p, pl, stream);
     }
-    if (!pl.g128) return launch_variant<1, 8, false, false>(p, pl, stream);
-    return pl.fold ? launch_variant<1, 8, true, true>(p, pl, stream)
-                   : launch_variant<1, 8, true, false>(p, pl, stream);
+    if (!pl.g128) return launch_variant<1, 8, false, false>(tmap, p, pl, stream);
+    return pl.fold ? launch_variant<1, 8, true, true>(tmap, p, pl, stream)
+                   : launch_variant<1, 8, true, false>(tmap, p, pl, stream);
   }
-  if (!pl.g128) return launch_variant<2, 8, false, false>(p, pl, stream);
-  return pl.fold ? launch_variant<2, 8, true, true>(p, pl, stream)
-                 : launch_variant<2, 8, true, false>(p, pl, stream);
+  if (!pl.g128) return launch_variant<2, 8, false, false>(tmap, p, pl, stream);
+  return pl.fold ? launch_variant<2, 8, true, true>(tmap, p, pl, stream)
+                 : launch_variant<2, 8, true, false>(tmap, p, pl, stream);
 }
 
 }  // namespace b2

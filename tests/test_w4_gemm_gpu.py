@@ -1,0 +1,114 @@
+"""GPU parity tests of the prefill GEMM (M > 16) through the C ABI, against the CPU oracle.
+
+The tensor-core path rounds every dequantised weight to bf16 before the multiply, exactly as the reference
+does (kernels/quant/w4a16.cuh:196-197), so against the oracle's exact-weight double sum the bound is the
+reference's own gate: 1e-2 of the largest output (bench/bench_w4a16.cu:120,181-191; it records 2.2e-3).
+Against an oracle that applies the same weight rounding the bound is one bf16 rounding plus fp32 noise.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests.util import bits_to_torch, check_bf16_output, torch_to_bits, u32_to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def run(k, X, Wq, S, G):
+    y = k.w4_linear(bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S), G)
+    torch.cuda.synchronize()
+    return torch_to_bits(y)
+
+
+def rounded_weight_reference(X, Wq, S, G):
+    """fp64 matmul with each weight rounded to bf16 first: the value the tensor-core path should produce."""
+    Wd = oracle.bf16_bits_to_f32(oracle.w4_dequant_bf16(Wq, S, G)).astype(np.float64)
+    return (oracle.bf16_bits_to_f32(X).astype(np.float64) @ Wd.T).astype(np.float32)
+
+
+@pytest.mark.parametrize("G", [128, 32])
+def test_unpack_is_bit_exact(kernels, G):
+    """S == 1, one-hot X rows: Y[m, n] = q[n, k_m] - 8 exactly, for every k of a 256-wide row."""
+    N, K = 48, 256
+    rng = np.random.default_rng(7)
+    Wq = rng.integers(0, 2**32, size=(N, K // 8), dtype=np.uint32)
+    for v in range(16):
+        Wq[v, :] = np.uint32(v * 0x11111111)
+    Wq[16, :] = 0x76543210
+    Wq[17, :] = 0xFEDCBA98
+    S = np.full((N, K // G), 0x3F80, dtype=np.uint16)
+    Q = oracle.w4_unpack(Wq)
+    X = np.eye(K, dtype=np.float32)  # M = 256: row m is the one-hot of k = m
+    y = oracle.bf16_bits_to_f32(run(kernels, oracle.f32_to_bf16_bits(X), Wq, S, G))
+    assert np.array_equal(y, Q.T.astype(np.float32))
+    assert kernels.device_status() == 0
+
+
+def test_dequantised_tile_is_single_rounding(kernels):
+    """One-hot X with real scales: Y[m, n] must be exactly RN_bf16((q - 8) * s), the reference's tile value."""
+    N, K, G = 64, 256, 128
+    _, Wq, S = oracle.synth_inputs(1, N, K, G, seed=5)
+    X = np.eye(K, dtype=np.float32)
+    y = run(kernels, oracle.f32_to_bf16_bits(X), Wq, S, G)
+    assert np.array_equal(y, oracle.w4_dequant_bf16(Wq, S, G).T)
+
+
+SHAPES = [(17, 64, 128, 128), (32, 256, 256, 128), (100, 300, 384, 128), (128, 256, 512, 128),
+          (129, 512, 1024, 128), (256, 256, 512, 128), (300, 520, 640, 64), (64, 40, 96, 32), (257, 1, 160, 32),
+          (512, 448, 3584, 128), (384, 2368, 512, 128)]
+
+
+@pytest.mark.parametrize("M,N,K,G", SHAPES)
+def test_against_oracle(kernels, M, N, K, G):
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=31)
+    y = run(kernels, X, Wq, S, G)
+    ref = oracle.w4_linear_f32(X, Wq, S, G, threads=oracle.max_threads())
+    _, rel = check_bf16_output(y, ref, 1e-2)
+    assert rel < 1e-2
+    check_bf16_output(y, rounded_weight_reference(X, Wq, S, G), 2e-5)
+    assert kernels.device_status() == 0
+
+
+def test_reference_bench_case(kernels):
+    """The reference's own GEMM check: N=256, K=512, M=128 on its seeded inputs (bench_w4a16.cu:142-191)."""
+    N, K, M, G = 256, 512, 128, 128
+    W = oracle.fill_bf16(N * K, 11, 0.05).reshape(N, K)
+    X = oracle.fill_bf16(M * K, 12, 1.0).reshape(M, K)
+    Wq, S = oracle.w4_quantize(W, G)
+    y = oracle.bf16_bits_to_f32(run(kernels, X, Wq, S, G))
+    ref = oracle.w4_linear_f32(X, Wq, S, G)
+    assert oracle.max_rel_err(y, ref) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 18944, 3584), (2048, 3584, 18944)])
+def test_prefill_shapes_sampled(kernels, M, N, K):
+    """Full benchmark shapes; the oracle checks a sample of output rows (the full product is ~1e11 MACs)."""
+    G = 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=2)
+    y = run(kernels, X, Wq, S, G)
+    rows = np.unique(np.concatenate([[0, 127, 128, M - 1], np.random.default_rng(0).integers(0, M, 8)]))
+    ref = oracle.w4_linear_f32(X[rows], Wq, S, G, threads=oracle.max_threads())
+    check_bf16_output(y[rows], ref, 1e-2)
+    check_bf16_output(y[rows], rounded_weight_reference(X[rows], Wq, S, G), 3e-5)
+    assert kernels.device_status() == 0
+
+
+def test_x_doubling_is_exact(kernels):
+    M, N, K, G = 256, 512, 1024, 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=4)
+    X2 = oracle.f32_to_bf16_bits(2.0 * oracle.bf16_bits_to_f32(X))
+    y1 = oracle.bf16_bits_to_f32(run(kernels, X, Wq, S, G))
+    y2 = oracle.bf16_bits_to_f32(run(kernels, X2, Wq, S, G))
+    assert np.array_equal(y2, 2.0 * y1)
+
+
+def test_output_bounds(kernels):
+    M, N, K, G = 130, 100, 256, 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=8)
+    buf = torch.full((M * N + 128,), 7.0, dtype=torch.bfloat16, device="cuda")
+    out = buf[64:64 + M * N].view(M, N)
+    kernels.w4_linear(bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S), G, out=out)
+    torch.cuda.synchronize()
+    assert torch.all(buf[:64] == 7.0) and torch.all(buf[64 + M * N:] == 7.0)
+    check_bf16_output(torch_to_bits(out), oracle.w4_linear_f32(X, Wq, S, G), 1e-2)

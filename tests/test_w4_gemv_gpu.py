@@ -188,6 +188,8 @@ def test_against_reference_kernels(kernels, N, K, M):
     y = kernels.w4_linear(x, wq, s, G)
     torch.cuda.synchronize()
     a, b = y.float(), y_ref.float()
-    ulp = torch.maximum(a.abs(), b.abs()) * 2.0**-7
-    assert torch.all((a - b).abs() <= ulp + 1e-30)
+    # one bf16 ulp of the value, plus fp32 summation-order noise relative to the largest output
+    # (outputs near zero come from cancellation and carry the absolute error of the large terms)
+    tol = torch.maximum(a.abs(), b.abs()) * 2.0**-7 + 1e-5 * b.abs().max()
+    assert torch.all((a - b).abs() <= tol)
     assert (a != b).float().mean().item() < 0.02
