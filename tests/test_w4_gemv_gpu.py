@@ -2,7 +2,7 @@
 
 Integer work (the int4 unpack) must be bit-exact.  Floating-point outputs are bf16: the bound is one
 correct rounding (2^-8 relative) plus fp32-accumulation slack relative to the largest output:
-3e-6 for the default path, 3e-5 when the zero-point is folded (fp32 cancellation of the +128 bias),
+3e-6 for the default path, 2e-4 when the zero-point is folded (fp32 cancellation of the +1024 bias of the fp16 unpack),
 2e-3 for G < 128 where each weight is rounded to bf16 as the reference's tensor-core path does.
 """
 import ctypes
@@ -18,7 +18,7 @@ from tests.util import bits_to_torch, check_bf16_output, torch_to_bits, u32_to_t
 
 pytestmark = pytest.mark.gpu
 
-SLACK_EXACT, SLACK_FOLD, SLACK_SMALL_G = 3e-6, 3e-5, 2e-3
+SLACK_EXACT, SLACK_FOLD, SLACK_SMALL_G = 3e-6, 2e-4, 2e-3
 
 
 def run(k, X, Wq, S, G, flags=0):
