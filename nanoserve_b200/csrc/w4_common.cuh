@@ -25,6 +25,13 @@ __device__ __forceinline__ void unpack_w4_biased(uint32_t w, uint32_t (&r)[4]) {
   r[3] = ((w >> 12) & kNibblePairMask) | kMagic128x2;
 }
 
+// (a & b) | c as one LOP3; pass the constants in registers (two immediates would cost two instructions).
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
 // bf16x2 subtract of 136: (128 + q) - 136 = q - 8, exact.
 __device__ __forceinline__ uint32_t sub136_bf16x2(uint32_t v) {
   __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&v);

@@ -12,11 +12,12 @@
 //   warp 1   MMA issuer: one elected lane issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=256, K=16)
 //            from shared-memory descriptors into fp32 accumulators in TMEM (MI x 256 columns); the weight
 //            operand is shared by the MI token tiles, so every weight is dequantised once per 128*MI tokens
-//   warps 2-9 dequant: thread r owns weight row r of the tile: two 16-byte shared loads of packed nibbles,
-//            LOP3 unpack to bf16 pairs, exact -8 (bf16x2 subtract), one bf16x2 multiply by the group scale,
-//            and eight 16-byte stores into a K-major, 128-byte-swizzled bf16 tile (two buffers) that the
-//            MMA reads through the async proxy (fence.proxy.async before the arrive)
-//   epilogue the same eight warps read the accumulators with tcgen05.ld (32 lanes x 32 columns), convert to
+//   warps 2-17 dequant: two threads per weight row of the tile, each owning a 32-wide half of the K block:
+//            one 16-byte shared load of packed nibbles, LOP3 unpack to bf16 pairs, exact -8 (bf16x2
+//            subtract), one bf16x2 multiply by the group scale, and four 16-byte stores into a K-major,
+//            128-byte-swizzled bf16 tile (three buffers in rotation) that the MMA reads through the async
+//            proxy (fence.proxy.async before the arrive)
+//   epilogue the same sixteen warps read the accumulators with tcgen05.ld (32 lanes x 32 columns), convert to
 //            bf16 and store rows of Y
 // Ragged M, N and a K tail of 32 need no special path: TMA zero-fills out-of-range rows and columns, the
 // scale of an out-of-range row or group is taken as 0, and the epilogue masks its stores.
@@ -40,7 +41,8 @@ constexpr int kBK = 64;             // K per block: one 128-byte swizzled row of
 constexpr int kATileBytes = 128 * 128;        // 128 tokens x 64 bf16
 constexpr int kWpTileBytes = kBN * 32;        // 256 rows x 8 packed words
 constexpr int kBdTileBytes = kBN * 128;       // 256 rows x 64 bf16
-constexpr int kDequantThreads = 256;
+constexpr int kBdBuffers = 3;                 // dequantised tiles in rotation
+constexpr int kDequantThreads = 512;        // two threads per weight row of the tile
 constexpr int kGemmThreads = 32 * 2 + kDequantThreads;
 constexpr int kGemmSmemLimit = 232448;
 
@@ -58,7 +60,7 @@ struct GemmGeo {
   static constexpr int kStages = MI == 2 ? 3 : 5;
   static constexpr int kRingBytes = kStages * kStageBytes;
   static constexpr int kBdOffset = kRingBytes;
-  static constexpr int kBarOffset = kBdOffset + 2 * kBdTileBytes;
+  static constexpr int kBarOffset = kBdOffset + kBdBuffers * kBdTileBytes;
   static constexpr int kSmemBytes = kBarOffset + 256 + 1024;  // barriers + slack for 1024-byte alignment
   static constexpr int kTmemCols = MI * kBN;                  // 256 or 512: powers of two
 };
@@ -75,11 +77,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const uint32_t bar_base = base + geo::kBarOffset;
   const uint32_t bar_full = bar_base;                        // [kStages]
   const uint32_t bar_empty = bar_base + 8 * 8;               // [kStages]
-  const uint32_t bar_bd_full = bar_base + 16 * 8;            // [2]
-  const uint32_t bar_bd_empty = bar_base + 18 * 8;           // [2]
-  const uint32_t bar_acc = bar_base + 20 * 8;                // [1]
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + geo::kBarOffset + 22 * 8);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + geo::kBarOffset + 23 * 8);
+  const uint32_t bar_bd_full = bar_base + 16 * 8;            // [kBdBuffers]
+  const uint32_t bar_bd_empty = bar_base + 20 * 8;           // [kBdBuffers]
+  const uint32_t bar_acc = bar_base + 24 * 8;                // [1]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + geo::kBarOffset + 26 * 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + geo::kBarOffset + 27 * 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kBN;
@@ -91,7 +93,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, kDequantThreads + 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kBdBuffers; ++b) {
       mbar_init(bar_bd_full + 8 * b, kDequantThreads);
       mbar_init(bar_bd_empty + 8 * b, 1);
     }
@@ -114,9 +116,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (warp == 0) {
       // ------------------------------------------------------------ TMA producer
       if (lane == 0) {
+        int s = 0;
+        uint32_t ph = 0;
         for (int kb = 0; kb < p.nkb; ++kb) {
-          const int s = kb % geo::kStages;
-          const uint32_t ph = (kb / geo::kStages) & 1;
           mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag);
           const uint32_t stage = base + s * geo::kStageBytes;
           mbar_arrive_expect_tx(bar_full + 8 * s, geo::kStageBytes);
@@ -124,6 +126,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int mi = 0; mi < MI; ++mi)
             tma_load_2d(stage + mi * kATileBytes, &tmap_x, kb * kBK, m0 + mi * 128, bar_full + 8 * s);
           tma_load_2d(stage + MI * kATileBytes, &tmap_w, kb * (kBK / 8), n0, bar_full + 8 * s);
+          if (++s == geo::kStages) { s = 0; ph ^= 1; }
         }
       }
       __syncwarp();
@@ -131,10 +134,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // ------------------------------------------------------------ MMA issuer
       if (lane == 0) {
         constexpr uint32_t idesc = umma_idesc_bf16(128, kBN);
+        int s = 0, b = 0;
+        uint32_t ph = 0, bph = 0;
         for (int kb = 0; kb < p.nkb; ++kb) {
-          const int s = kb % geo::kStages, b = kb & 1;
-          mbar_wait(bar_full + 8 * s, (kb / geo::kStages) & 1, abort_flag);
-          mbar_wait(bar_bd_full + 8 * b, (kb >> 1) & 1, abort_flag);
+          mbar_wait(bar_full + 8 * s, ph, abort_flag);
+          mbar_wait(bar_bd_full + 8 * b, bph, abort_flag);
           tc_fence_after_sync();
           const uint32_t a_addr = base + s * geo::kStageBytes;
           const uint32_t b_addr = base + geo::kBdOffset + b * kBdTileBytes;
@@ -149,65 +153,75 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           umma_commit(bar_empty + 8 * s);      // the X tile and the packed tile of this stage are consumed
           umma_commit(bar_bd_empty + 8 * b);   // the dequantised tile may be overwritten
+          if (++s == geo::kStages) { s = 0; ph ^= 1; }
+          if (++b == kBdBuffers) { b = 0; bph ^= 1; }
         }
         umma_commit(bar_acc);
       }
       __syncwarp();
     } else {
       // ------------------------------------------------------------ dequant warps, then epilogue
-      const int r = tid - 64;  // weight row of the tile owned by this thread
+      const int dt = tid - 64;          // 0..511
+      const int r = dt >> 1;            // weight row of the tile
+      const int hf = dt & 1;            // which 32-wide half of the 64-wide K block (one scale each)
       const int n = n0 + r;
       const uint32_t bd_row = base + geo::kBdOffset + r * 128;
       const uint32_t sw = (uint32_t)(r & 7);
+      // unpack constants pinned in registers: each (x & mask) | magic is then a single LOP3
+      uint32_t k_mask = kNibblePairMask, k_magic = kMagic128x2;
+      asm volatile("" : "+r"(k_mask), "+r"(k_magic));
+      const __nv_bfloat16* s_row = p.S + (size_t)(n < p.N ? n : 0) * p.KG;
+      int s = 0, b = 0;
+      uint32_t ph = 0, bph = 0;
       for (int kb = 0; kb < p.nkb; ++kb) {
-        const int s = kb % geo::kStages, b = kb & 1;
-        const int k0 = kb * kBK;
-        __nv_bfloat16 sv0 = __float2bfloat16(0.f), sv1 = sv0;
-        if (n < p.N) {
-          sv0 = p.S[(size_t)n * p.KG + k0 / p.G];
-          if (k0 + 32 < p.K) sv1 = p.S[(size_t)n * p.KG + (k0 + 32) / p.G];
-        }
-        const uint32_t s2[2] = {bf16_dup(sv0), bf16_dup(sv1)};
+        const int k0 = kb * kBK + hf * 32;
+        __nv_bfloat16 sv = __float2bfloat16(0.f);
+        if (n < p.N && k0 < p.K) sv = __ldg(s_row + k0 / p.G);
+        const uint32_t s2 = bf16_dup(sv);
 
         // one lane per warp polls: many threads spinning on a shared-memory barrier slow the copies down
-        if (lane == 0) mbar_wait(bar_full + 8 * s, (kb / geo::kStages) & 1, abort_flag);
+        if (lane == 0) mbar_wait(bar_full + 8 * s, ph, abort_flag);
         __syncwarp();
-        const uint32_t wp = base + s * geo::kStageBytes + MI * kATileBytes + r * 32;
-        const uint4 w0 = lds128(wp), w1 = lds128(wp + 16);
+        const uint4 w4 = lds128(base + s * geo::kStageBytes + MI * kATileBytes + r * 32 + hf * 16);
         mbar_arrive(bar_empty + 8 * s);  // packed words are in registers
-        const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
 
-        if (lane == 0) mbar_wait(bar_bd_empty + 8 * b, ((kb >> 1) & 1) ^ 1, abort_flag);
+        if (lane == 0) mbar_wait(bar_bd_empty + 8 * b, bph ^ 1, abort_flag);
         __syncwarp();
         const uint32_t dst = bd_row + b * kBdTileBytes;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t v[4];
-          unpack_w4_biased(words[c], v);
+          v[0] = lop3_and_or(words[c], k_mask, k_magic);
+          v[1] = lop3_and_or(words[c] >> 4, k_mask, k_magic);
+          v[2] = lop3_and_or(words[c] >> 8, k_mask, k_magic);
+          v[3] = lop3_and_or(words[c] >> 12, k_mask, k_magic);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) v[q] = mul_bf16x2(sub136_bf16x2(v[q]), s2[c >> 2]);
+          for (int q = 0; q < 4; ++q) v[q] = mul_bf16x2(sub136_bf16x2(v[q]), s2);
           // v[q] = {w[q], w[q+4]}  ->  natural order pairs {w0,w1} {w2,w3} {w4,w5} {w6,w7}
           uint4 o;
           o.x = __byte_perm(v[0], v[1], 0x5410);
           o.y = __byte_perm(v[2], v[3], 0x5410);
           o.z = __byte_perm(v[0], v[1], 0x7632);
           o.w = __byte_perm(v[2], v[3], 0x7632);
-          sts128(dst + ((uint32_t(c) ^ sw) << 4), o);
+          sts128(dst + ((uint32_t(hf * 4 + c) ^ sw) << 4), o);
         }
         fence_proxy_async_smem();
         mbar_arrive(bar_bd_full + 8 * b);
+        if (++s == geo::kStages) { s = 0; ph ^= 1; }
+        if (++b == kBdBuffers) { b = 0; bph ^= 1; }
       }
 
       // ---- epilogue: TMEM -> registers -> bf16 -> global
       if (lane == 0) mbar_wait(bar_acc, 0, abort_flag);
       __syncwarp();
       tc_fence_after_sync();
-      const int ew = warp - 2;           // 0..7
+      const int ew = warp - 2;           // 0..15
       const int quad = warp & 3;         // TMEM lane quadrant this warp may read
-      const int grp = ew >> 2;           // 0 or 1
-      const int mi = MI == 2 ? grp : 0;
-      const int col_begin = MI == 2 ? 0 : grp * (kBN / 2);
-      const int col_end = MI == 2 ? kBN : col_begin + kBN / 2;
+      const int grp = ew >> 2;           // 0..3: four warps share a quadrant and split the columns
+      const int mi = MI == 2 ? grp >> 1 : 0;
+      const int col_begin = MI == 2 ? (grp & 1) * (kBN / 2) : grp * (kBN / 4);
+      const int col_end = col_begin + (MI == 2 ? kBN / 2 : kBN / 4);
       const int m = m0 + mi * 128 + quad * 32 + lane;
       const bool vec_ok = (p.N % 8) == 0;
       for (int c0 = col_begin; c0 < col_end; c0 += 32) {
