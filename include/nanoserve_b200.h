@@ -94,6 +94,19 @@ int b2_clear_status(void);
 /* Scratch bytes the GEMV would use for this shape on the current device (0 = no split-K). */
 size_t b2_w4_gemv_scratch_bytes(int M, int N, int K, int G, int flags);
 
+/*
+ * No counterpart in the reference library.  The decode GEMV (1 <= M <= 16, same operands and result as
+ * ns_w4_linear) for callers that cannot allocate device memory at the point of the call -- a process whose
+ * memory budget is handed to a pool at start-up, a plugin inside another runtime's capture or callback.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine: the split-K scratch is a fixed
+ * array inside the library's device image (8 MiB + 16.25 KiB per GPU that loads the library, held until
+ * exit).  Limits: M * N <= 1048576 and N <= 131072, otherwise B2_ERR_TOO_LARGE.  All calls on a device
+ * share the array: calls whose kernels overlap in time race, so keep them on one stream.  The first call
+ * on a device looks up the array's address; make that call before any stream capture.
+ */
+int b2_w4_gemv_noalloc(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                       void* stream);
+
 /* Library identification: "nanoserve-b200 <version> sm_100a". */
 const char* b2_version(void);
 
