@@ -192,7 +192,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a short collective time-out: a rank that falls out of step fails the run in a minute instead of hanging it
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     if not os.path.exists(b2build.LIB_PATH):
         if rank == 0:
             b2build.build()
@@ -246,9 +248,12 @@ def main():
     if rank == 0:
         sampler.start()
     t_dev = timed_replays(args.steps)
-    # keep the GPU under the same load a little longer so the 100 ms clock sampler sees it
-    t_extra0 = time.perf_counter()
-    while rank == 0 and time.perf_counter() - t_extra0 < 0.6:
+    # keep the GPUs under the same load a little longer so the 100 ms clock sampler sees it; every rank runs
+    # the same number of extra replays (the count comes from rank 0), because the replays contain collectives
+    n_extra = [max(1, int(0.6 / max(t_dev / args.steps, 1e-6) / 200))]
+    if world > 1:
+        dist.broadcast_object_list(n_extra, src=0)
+    for _ in range(min(n_extra[0], 200)):
         timed_replays(200)
     clocks = sampler.stop() if rank == 0 else None
 
@@ -357,8 +362,14 @@ def main():
                                               f"runs its check), {dt:.2f} s per pass"}
         print(json.dumps(line), flush=True)
     if world > 1:
+        # Captured graphs hold NCCL work; tearing the communicator down under them can block.  Everything is
+        # measured and printed: synchronise, meet once more, and leave without running the destructors.
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
