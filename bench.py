@@ -170,6 +170,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=M_DECODE, help="tokens per step (1..16); the headline is 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the Qwen2.5-7B-shaped greedy-decode tokens/s leg")
     ap.add_argument("--flags", type=int, default=0, help="library flags for every launch (see include/nanoserve_b200.h)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -321,6 +322,26 @@ def main():
             with open(traffic_file) as f:
                 roof["traffic"] = json.load(f).get("dram_bytes_per_launch_m%d" % M)
 
+    # ---- second half of the headline metric: W4 greedy decode tokens/s of a Qwen2.5-7B-shaped model (512-token prompt,
+    # 256 new tokens, batch 1, tensor parallel over the ranks); free the GEMV benchmark's weights first
+    decode = None
+    if not args.no_decode:
+        del graphs, layers
+        torch.cuda.empty_cache()
+        try:
+            from nanoserve_b200.qwen import decode_rate
+            d = decode_rate(k, dev, rank=rank, world=world)
+            t = torch.tensor([d["ms_per_token"]], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            d["ms_per_token"] = float(t.item())
+            d["tok_s"] = 1e3 / d["ms_per_token"]
+            peaks, which = measured_peaks()
+            d["hbm_frac_of_" + which] = d["weight_bytes_per_token_per_rank"] / (d["ms_per_token"] * 1e-3) / 1e9 / peaks["hbm_gbs"]
+            decode = d
+        except Exception as e:  # the GEMV line must not be lost to a failure of the wider leg
+            decode = {"error": f"{type(e).__name__}: {e}"}
+
     # ---- max over ranks
     times = torch.tensor([t_dev, t_e2e, t_e2e_wall], dtype=torch.float64, device=dev)
     if world > 1:
@@ -353,6 +374,8 @@ def main():
         }
         if roof is not None:
             line["roofline"] = roof
+        if decode is not None:
+            line["decode"] = decode
         if world == 1 and not args.no_cpu_baseline:
             one, _ = cpu_layer_pass(1, 1)
             n = max(1, min(8, int(15.0 / max(one, 1e-3))))

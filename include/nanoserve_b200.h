@@ -107,6 +107,23 @@ size_t b2_w4_gemv_scratch_bytes(int M, int N, int K, int G, int flags);
 int b2_w4_gemv_noalloc(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
                        void* stream);
 
+/*
+ * Batch-1 decode helpers that read the current position from device memory, so one captured CUDA graph serves
+ * every decode step.  No counterpart in the reference library: the reference does these steps with PyTorch ops and
+ * a host-side position (python/nanoserve/qwen.py:119-133,147-151,174-177).
+ *   b2_rope_kv_store: qkv [(Hq+2Hk)*D] bf16 of the new token, in place: += bias (may be NULL), rotate-half RoPE on
+ *     the q and k heads at position *pos, k and v written to cache_k / cache_v [Hk, max_len, D] at that position.
+ *   b2_decode_attention: out [Hq*D] = softmax(q K^T / sqrt(D)) V over cache positions 0..*pos (D = 64 or 128).
+ *   b2_greedy_next: token = argmax(logits[0..V)) (lowest index on ties); out_tokens[*step] = token; *step += 1;
+ *     *pos += 1; x_next[0..H) = embed[token].  pos, step: int32 on the device; out_tokens: int64 on the device.
+ */
+int b2_rope_kv_store(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k, void* cache_v,
+                     int Hq, int Hk, int D, int max_len, void* stream);
+int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v, const void* pos, void* out, int Hq,
+                        int Hk, int D, int max_len, void* stream);
+int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* pos, void* out_tokens, void* step,
+                   void* x_next, void* stream);
+
 /* Library identification: "nanoserve-b200 <version> sm_100a". */
 const char* b2_version(void);
 

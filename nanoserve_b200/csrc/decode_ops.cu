@@ -1,0 +1,210 @@
+// Small kernels that sit between the quantized linears of a batch-1 decode step and read the current
+// position from device memory, so that one captured CUDA graph serves every step:
+//   b2_rope_kv_store     bias add + rotary embedding on q and k of the new token, k/v appended to the cache
+//   b2_decode_attention  one query token against the cached keys/values (grouped-query attention)
+//   b2_greedy_next       argmax over the logits, position += 1, embedding row of the chosen token
+// The reference does these steps with PyTorch ops and a Python-side position (python/nanoserve/qwen.py:119-133,
+// 147-151, 174-177: bias add, rope, _store_kv, SDPA over the cache, argmax); a host-side position would force one
+// graph per step.  Arithmetic follows the reference's conventions: bf16 storage, fp32 math, rotate-half RoPE with
+// angle = pos * inv_freq[i] (kernels/fused/rope.cuh:14-43), softmax scale 1/sqrt(D).
+#include <cfloat>
+#include <cstdint>
+#include <cuda_bf16.h>
+
+#include "../../include/nanoserve_b200.h"
+#include "w4_internal.h"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+// grid: Hq + 2*Hk blocks (one per head of the fused qkv row), block: D/2 threads.
+__global__ void rope_kv_store_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ bias,
+                                     const float* __restrict__ inv_freq, const int* __restrict__ pos_ptr,
+                                     bf16* __restrict__ cache_k, bf16* __restrict__ cache_v, int Hq, int Hk, int D,
+                                     int max_len) {
+  const int h = blockIdx.x, i = threadIdx.x, half = D / 2;
+  const int pos = *pos_ptr;
+  bf16* x = qkv + (size_t)h * D;
+  float a = __bfloat162float(x[i]), b = __bfloat162float(x[i + half]);
+  if (bias != nullptr) {  // the projection output is stored in bf16, then the bias is added in bf16 (q += bq)
+    a = __bfloat162float(__float2bfloat16(a + __bfloat162float(bias[(size_t)h * D + i])));
+    b = __bfloat162float(__float2bfloat16(b + __bfloat162float(bias[(size_t)h * D + i + half])));
+  }
+  if (h < Hq + Hk) {  // q and k heads rotate, v heads do not
+    float sn, cs;
+    sincosf((float)pos * inv_freq[i], &sn, &cs);
+    const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+    a = ra;
+    b = rb;
+  }
+  const bf16 oa = __float2bfloat16(a), ob = __float2bfloat16(b);
+  x[i] = oa;
+  x[i + half] = ob;
+  if (h >= Hq && pos < max_len) {
+    const int kh = h - Hq;
+    bf16* dst = (kh < Hk ? cache_k + ((size_t)kh * max_len + pos) * D
+                         : cache_v + ((size_t)(kh - Hk) * max_len + pos) * D);
+    dst[i] = oa;
+    dst[i + half] = ob;
+  }
+}
+
+// grid: Hq blocks, block: 256 threads (8 warps).  Each warp walks keys j = warp, warp+8, ... with an online
+// softmax; lanes split the head dimension (D = 128: 4 elements per lane).  Partial (max, sum, acc) of the
+// warps are merged through shared memory.
+template <int D>
+__global__ void __launch_bounds__(256) decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache_k,
+                                                               const bf16* __restrict__ cache_v,
+                                                               const int* __restrict__ pos_ptr, bf16* __restrict__ out,
+                                                               int Hq, int Hk, int max_len, float scale) {
+  constexpr int E = D / 32;  // elements per lane
+  __shared__ float s_m[8], s_l[8], s_acc[8][D];
+  const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = min(*pos_ptr + 1, max_len);
+  const int kh = h / (Hq / Hk);
+  const bf16* kbase = cache_k + (size_t)kh * max_len * D;
+  const bf16* vbase = cache_v + (size_t)kh * max_len * D;
+  float qf[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) qf[e] = __bfloat162float(q[(size_t)h * D + lane * E + e]) * scale;
+  float m = -FLT_MAX, l = 0.f, acc[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) acc[e] = 0.f;
+  for (int j = warp; j < n; j += 8) {
+    const bf16* kr = kbase + (size_t)j * D + lane * E;
+    float s = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) s += qf[e] * __bfloat162float(kr[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mn = fmaxf(m, s);
+    const float corr = __expf(m - mn), pj = __expf(s - mn);
+    const bf16* vr = vbase + (size_t)j * D + lane * E;
+    l = l * corr + pj;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] = acc[e] * corr + pj * __bfloat162float(vr[e]);
+    m = mn;
+  }
+  if (lane == 0) {
+    s_m[warp] = m;
+    s_l[warp] = l;
+  }
+#pragma unroll
+  for (int e = 0; e < E; ++e) s_acc[warp][lane * E + e] = acc[e];
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float mm = -FLT_MAX;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) mm = fmaxf(mm, s_m[w]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const float f = s_m[w] == -FLT_MAX ? 0.f : __expf(s_m[w] - mm);
+      num += f * s_acc[w][threadIdx.x];
+      den += f * s_l[w];
+    }
+    out[(size_t)h * D + threadIdx.x] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+  }
+}
+
+// One block of 1024 threads: argmax over V logits (first index wins ties, as torch.argmax does), then the
+// chosen token is recorded, the position advances and the token's embedding row becomes the next input.
+__global__ void __launch_bounds__(1024) greedy_next_kernel(const bf16* __restrict__ logits, int V,
+                                                           const bf16* __restrict__ embed, int H, int* __restrict__ pos_ptr,
+                                                           long long* __restrict__ out_tokens, int* __restrict__ step_ptr,
+                                                           bf16* __restrict__ x_next) {
+  __shared__ float s_v[32];
+  __shared__ int s_i[32];
+  __shared__ int s_tok;
+  float best = -FLT_MAX;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = __bfloat162float(logits[i]);
+    if (v > best) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s_v[threadIdx.x >> 5] = best;
+    s_i[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = s_v[threadIdx.x];
+    bi = s_i[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (threadIdx.x == 0) {
+      if (bi < 0 || bi >= V) bi = 0;
+      s_tok = bi;
+      out_tokens[*step_ptr] = bi;
+      *step_ptr += 1;
+      *pos_ptr += 1;
+    }
+  }
+  __syncthreads();
+  const bf16* row = embed + (size_t)s_tok * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) x_next[i] = row[i];
+}
+
+}  // namespace
+
+extern "C" {
+
+int b2_rope_kv_store(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k, void* cache_v,
+                     int Hq, int Hk, int D, int max_len, void* stream) {
+  if (Hq < 1 || Hk < 1 || D < 2 || D % 2 || D / 2 > 1024 || max_len < 1) return b2::kErrBadShape;
+  if (!qkv || !inv_freq || !pos || !cache_k || !cache_v) return b2::kErrBadPointer;
+  rope_kv_store_kernel<<<Hq + 2 * Hk, D / 2, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<bf16*>(qkv), static_cast<const bf16*>(bias), static_cast<const float*>(inv_freq),
+      static_cast<const int*>(pos), static_cast<bf16*>(cache_k), static_cast<bf16*>(cache_v), Hq, Hk, D, max_len);
+  return (int)cudaGetLastError();
+}
+
+int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v, const void* pos, void* out, int Hq,
+                        int Hk, int D, int max_len, void* stream) {
+  if (Hq < 1 || Hk < 1 || Hq % Hk || max_len < 1) return b2::kErrBadShape;
+  if (D != 128 && D != 64) return b2::kErrNotImplemented;
+  if (!q || !cache_k || !cache_v || !pos || !out) return b2::kErrBadPointer;
+  const float scale = 1.f / sqrtf((float)D);
+  const auto st = static_cast<cudaStream_t>(stream);
+  if (D == 128)
+    decode_attention_kernel<128><<<Hq, 256, 0, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache_k),
+                                                     static_cast<const bf16*>(cache_v), static_cast<const int*>(pos),
+                                                     static_cast<bf16*>(out), Hq, Hk, max_len, scale);
+  else
+    decode_attention_kernel<64><<<Hq, 256, 0, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache_k),
+                                                    static_cast<const bf16*>(cache_v), static_cast<const int*>(pos),
+                                                    static_cast<bf16*>(out), Hq, Hk, max_len, scale);
+  return (int)cudaGetLastError();
+}
+
+int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* pos, void* out_tokens, void* step,
+                   void* x_next, void* stream) {
+  if (V < 1 || H < 1) return b2::kErrBadShape;
+  if (!logits || !embed || !pos || !out_tokens || !step || !x_next) return b2::kErrBadPointer;
+  greedy_next_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const bf16*>(logits), V, static_cast<const bf16*>(embed), H, static_cast<int*>(pos),
+      static_cast<long long*>(out_tokens), static_cast<int*>(step), static_cast<bf16*>(x_next));
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -37,6 +37,9 @@ SIGNATURES = {
     "b2_clear_status": ([], _i32),
     "b2_w4_gemv_scratch_bytes": ([_i32, _i32, _i32, _i32, _i32], ctypes.c_size_t),
     "b2_w4_gemv_noalloc": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
+    "b2_rope_kv_store": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
+    "b2_decode_attention": ([_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
+    "b2_greedy_next": ([_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp], _i32),
     "b2_version": ([], ctypes.c_char_p),
 }
 

@@ -1,0 +1,266 @@
+"""Shape-only Qwen2 (Llama-architecture) runner on the B200 library: random-init weights, greedy decode.
+
+Mirrors the reference's ``python/nanoserve/qwen.py`` (``Qwen2Runner.forward / generate``, lines 136-178) for the
+W4 configuration: every linear is int4 group-128 through ``ns_w4_linear``; embeddings and lm_head stay bf16.  There
+are no checkpoints offline, so weights are seeded random nibbles and scales with the benchmark's distributions.
+Differences from the reference, all on the host side of the boundary:
+  * q/k/v and gate/up are stored as one row-concatenated matrix each (one GEMV instead of three / two): rows of
+    ``Wq``/``S`` are independent, so this is the same arithmetic in fewer launches.
+  * One decode step is captured in a CUDA graph; the position lives in device memory (``b2_rope_kv_store``,
+    ``b2_decode_attention``, ``b2_greedy_next``), so the same graph is replayed for every token.  The reference runs
+    ~400 eager launches per token (README.md:227-228).
+  * Tensor parallel: every matrix is sharded by output rows over the ranks, outputs are all-gathered at the four
+    layer boundaries; attention, norms and RoPE run replicated on the gathered activations.
+Batch size 1, as in the reference (qwen.py:12).
+"""
+import ctypes
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from .ops import Kernels
+
+
+@dataclass
+class Qwen2Config:
+    hidden: int = 3584
+    n_layers: int = 28
+    n_heads: int = 28
+    n_kv_heads: int = 4
+    head_dim: int = 128
+    intermediate: int = 18944
+    vocab: int = 152064
+    rope_theta: float = 1e6
+    rms_eps: float = 1e-6
+    group: int = 128
+
+    @classmethod
+    def qwen25_7b(cls):
+        return cls()
+
+
+def _rand_w4(N, K, G, gen, device):
+    """Random-init int4 weights with the benchmark's distributions: uniform nibbles, scales 0.005 + |N(0, 0.01)|."""
+    Wq = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, device=device, generator=gen)
+    S = (0.005 + (torch.randn(N, K // G, device=device, generator=gen) * 0.01).abs()).to(torch.bfloat16)
+    return Wq, S
+
+
+class Qwen2Runner:
+    def __init__(self, cfg: Qwen2Config, kernels: Kernels, device, rank: int = 0, world: int = 1, seed: int = 0,
+                 max_len: int = 1024, group=None):
+        self.cfg, self.k, self.dev = cfg, kernels, device
+        self.rank, self.world, self.group = rank, world, group
+        self.max_len = max_len
+        H, D = cfg.hidden, cfg.head_dim
+        self.nq, self.nkv, self.I = cfg.n_heads * D, cfg.n_kv_heads * D, cfg.intermediate
+        for n in (self.nq, self.nkv, self.I, H, cfg.vocab):
+            if n % world:
+                raise ValueError(f"{n} rows do not split evenly over {world} ranks")
+        gen = torch.Generator(device=device).manual_seed(seed)
+
+        def shard(t):  # rows [rank * n / world, (rank + 1) * n / world)
+            n = t.shape[0] // world
+            return t[rank * n:(rank + 1) * n].contiguous()
+
+        def w4(N, K):
+            Wq, S = _rand_w4(N, K, cfg.group, gen, device)  # same seed on every rank, then each keeps its rows
+            return shard(Wq), shard(S)
+
+        self.layers = []
+        for _ in range(cfg.n_layers):
+            q, k, v = w4(self.nq, H), w4(self.nkv, H), w4(self.nkv, H)
+            o = w4(H, self.nq)
+            g, u = w4(self.I, H), w4(self.I, H)
+            d = w4(H, self.I)
+            bias = (torch.randn(self.nq + 2 * self.nkv, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+            self.layers.append({
+                "qkv": (torch.cat([q[0], k[0], v[0]]), torch.cat([q[1], k[1], v[1]])),
+                "o": o, "gu": (torch.cat([g[0], u[0]]), torch.cat([g[1], u[1]])), "d": d,
+                "bias": bias,  # full-width: applied after the gather (Qwen2 has q/k/v biases, qwen.py:76,147-148)
+                "ln_in": (1 + 0.02 * torch.randn(H, device=device, generator=gen)).to(torch.bfloat16),
+                "ln_post": (1 + 0.02 * torch.randn(H, device=device, generator=gen)).to(torch.bfloat16),
+            })
+        self.final_norm = (1 + 0.02 * torch.randn(H, device=device, generator=gen)).to(torch.bfloat16)
+        self.embed = (torch.randn(cfg.vocab, H, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+        self.lm_head = shard((torch.randn(cfg.vocab, H, device=device, generator=gen) * 0.02).to(torch.bfloat16))
+        self.inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2, dtype=torch.int64, device=device).float() / D))
+        self.cache_k = torch.zeros(cfg.n_layers, cfg.n_kv_heads, max_len, D, dtype=torch.bfloat16, device=device)
+        self.cache_v = torch.zeros_like(self.cache_k)
+        # decode state on the device
+        self.pos = torch.zeros(1, dtype=torch.int32, device=device)
+        self.step = torch.zeros(1, dtype=torch.int32, device=device)
+        self.tokens = torch.zeros(max_len, dtype=torch.int64, device=device)
+        self.x = torch.zeros(1, H, dtype=torch.bfloat16, device=device)  # residual stream of the current token
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.stream = torch.cuda.Stream(device=device)
+        kernels.init()
+
+    # ------------------------------------------------------------------ helpers
+    def weight_bytes_per_token(self) -> int:
+        """Bytes of weights one decode step streams on this rank (packed + scales + bf16 lm_head shard)."""
+        n = 0
+        for L in self.layers:
+            for name in ("qkv", "o", "gu", "d"):
+                Wq, S = L[name]
+                n += Wq.numel() * 4 + S.numel() * 2
+        return n + self.lm_head.numel() * 2
+
+    def _st(self):
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _gather(self, local: torch.Tensor) -> torch.Tensor:
+        """[T, n / world] -> [T, n] (rank-major along the feature axis)."""
+        if self.world == 1:
+            return local
+        T, n = local.shape
+        out = torch.empty(self.world, T, n, dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local.contiguous(), group=self.group)
+        return out.permute(1, 0, 2).reshape(T, self.world * n)
+
+    def _gather_parts(self, local: torch.Tensor, widths: List[int]) -> torch.Tensor:
+        """Local output of a row-concatenated matrix ([T, sum(w_i / world)]) -> full [T, sum(w_i)] with each part
+        contiguous (q | k | v order)."""
+        if self.world == 1:
+            return local
+        T = local.shape[0]
+        out = torch.empty(self.world, T, local.shape[1], dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local.contiguous(), group=self.group)
+        parts, off = [], 0
+        for w in widths:
+            wl = w // self.world
+            parts.append(out[:, :, off:off + wl].permute(1, 0, 2).reshape(T, w))
+            off += wl
+        return torch.cat(parts, dim=1)
+
+    def linear(self, x, wt):
+        return self.k.w4_linear(x, wt[0], wt[1], self.cfg.group)
+
+    # ------------------------------------------------------------------ prompt (eager, GEMM path)
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """Runs the prompt, fills the KV cache, leaves the device state ready for decoding.  Returns the first
+        generated token (tensor on the device)."""
+        cfg, k = self.cfg, self.k
+        T, D = ids.shape[0], cfg.head_dim
+        assert T < self.max_len
+        x = F.embedding(ids, self.embed).contiguous()
+        h = k.rmsnorm(x, None, self.layers[0]["ln_in"], cfg.rms_eps)
+        for li, L in enumerate(self.layers):
+            qkv = self._gather_parts(self.linear(h, L["qkv"]), [self.nq, self.nkv, self.nkv])
+            qkv = qkv + L["bias"]
+            q, kk, v = qkv[:, :self.nq], qkv[:, self.nq:self.nq + self.nkv], qkv[:, self.nq + self.nkv:]
+            k.rope(q, kk, self.inv_freq, cfg.n_heads, cfg.n_kv_heads, D, 0)
+            self.cache_k[li, :, :T] = kk.reshape(T, cfg.n_kv_heads, D).transpose(0, 1)
+            self.cache_v[li, :, :T] = v.reshape(T, cfg.n_kv_heads, D).transpose(0, 1)
+            qh = q.reshape(T, cfg.n_heads, D).transpose(0, 1)[None]
+            kh = kk.reshape(T, cfg.n_kv_heads, D).transpose(0, 1)[None]
+            vh = v.reshape(T, cfg.n_kv_heads, D).transpose(0, 1)[None]
+            a = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, enable_gqa=True)
+            a = a[0].transpose(0, 1).reshape(T, self.nq).contiguous()
+            h = k.rmsnorm(x, self._gather(self.linear(a, L["o"])), L["ln_post"], cfg.rms_eps)
+            gu = self.linear(h, L["gu"])
+            il = self.I // self.world
+            act = self._gather(k.swiglu(gu[:, :il].contiguous(), gu[:, il:].contiguous()))
+            nxt = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
+            h = k.rmsnorm(x, self._gather(self.linear(act, L["d"])), nxt, cfg.rms_eps)
+        logits = self._gather(F.linear(h[-1:], self.lm_head))
+        self.pos.fill_(T - 1)  # greedy_next advances it to T, the position of the first generated token
+        self.step.zero_()
+        self._greedy_next(logits)
+        return self.tokens[0]
+
+    def _greedy_next(self, logits):
+        rc = self.k.lib.b2_greedy_next(logits.data_ptr(), self.cfg.vocab, self.embed.data_ptr(), self.cfg.hidden,
+                                       self.pos.data_ptr(), self.tokens.data_ptr(), self.step.data_ptr(),
+                                       self.x.data_ptr(), self._st())
+        self.k._check(rc, "b2_greedy_next")
+
+    # ------------------------------------------------------------------ one decode step (graph-capturable)
+    @torch.no_grad()
+    def decode_step(self):
+        cfg, k, lib = self.cfg, self.k, self.k.lib
+        D, x = cfg.head_dim, self.x
+        h = k.rmsnorm(x, None, self.layers[0]["ln_in"], cfg.rms_eps)
+        for li, L in enumerate(self.layers):
+            qkv = self._gather_parts(self.linear(h, L["qkv"]), [self.nq, self.nkv, self.nkv]).contiguous()
+            rc = lib.b2_rope_kv_store(qkv.data_ptr(), L["bias"].data_ptr(), self.inv_freq.data_ptr(),
+                                      self.pos.data_ptr(), self.cache_k[li].data_ptr(), self.cache_v[li].data_ptr(),
+                                      cfg.n_heads, cfg.n_kv_heads, D, self.max_len, self._st())
+            k._check(rc, "b2_rope_kv_store")
+            a = torch.empty(1, self.nq, dtype=torch.bfloat16, device=self.dev)
+            rc = lib.b2_decode_attention(qkv.data_ptr(), self.cache_k[li].data_ptr(), self.cache_v[li].data_ptr(),
+                                         self.pos.data_ptr(), a.data_ptr(), cfg.n_heads, cfg.n_kv_heads, D,
+                                         self.max_len, self._st())
+            k._check(rc, "b2_decode_attention")
+            h = k.rmsnorm(x, self._gather(self.linear(a, L["o"])), L["ln_post"], cfg.rms_eps)
+            gu = self.linear(h, L["gu"])
+            il = self.I // self.world
+            act = self._gather(k.swiglu(gu[:, :il], gu[:, il:]))  # T = 1: both halves are contiguous
+            nxt = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
+            h = k.rmsnorm(x, self._gather(self.linear(act, L["d"])), nxt, cfg.rms_eps)
+        logits = self._gather(F.linear(h, self.lm_head))
+        self._greedy_next(logits)
+        return logits
+
+    def capture(self):
+        """Warms up and captures one decode step.  The warm-up steps advance the device state; callers that
+        need clean state re-run prefill afterwards."""
+        with torch.cuda.stream(self.stream):
+            for _ in range(2):
+                self.decode_step()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream):
+                self.decode_step()
+        self.graph = g
+
+    @torch.no_grad()
+    def generate(self, prompt_ids: torch.Tensor, n_new: int, use_graph: bool = True) -> List[int]:
+        """Greedy decoding.  Returns the generated ids (list), as the reference's generate does (qwen.py:166-178)."""
+        assert prompt_ids.shape[0] + n_new <= self.max_len
+        if use_graph and self.graph is None:
+            self.prefill(prompt_ids)
+            self.capture()
+        with torch.cuda.stream(self.stream):
+            self.prefill(prompt_ids)
+            for _ in range(n_new - 1):
+                if use_graph:
+                    self.graph.replay()
+                else:
+                    self.decode_step()
+        torch.cuda.synchronize()
+        return self.tokens[:n_new].tolist()
+
+
+def decode_rate(kernels: Kernels, device, rank: int = 0, world: int = 1, cfg: Optional[Qwen2Config] = None,
+                prompt_len: int = 512, n_new: int = 256, seed: int = 0) -> dict:
+    """Greedy decode of `n_new` tokens after a `prompt_len`-token prompt of uniform random ids, batch 1: the
+    reference's decode-rate measurement ((G - 1) tokens over the time after the first one, python/bench_e2e.py:210-213)
+    with CUDA events around the G - 1 graph replays.  Every rank must call it; returns the numbers of this rank."""
+    cfg = cfg or Qwen2Config.qwen25_7b()
+    r = Qwen2Runner(cfg, kernels, device, rank=rank, world=world, seed=seed, max_len=prompt_len + n_new + 8)
+    gen = torch.Generator(device=device).manual_seed(4)
+    prompt = torch.randint(0, cfg.vocab, (prompt_len,), device=device, generator=gen)
+    r.generate(prompt, 4)  # warms every kernel variant and captures the decode graph
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(r.stream):
+        e0.record(r.stream)
+        r.prefill(prompt)
+        e1.record(r.stream)
+        for _ in range(n_new - 1):
+            r.graph.replay()
+        e2.record(r.stream)
+    torch.cuda.synchronize()
+    t_prefill, t_decode = e0.elapsed_time(e1) * 1e-3, e1.elapsed_time(e2) * 1e-3
+    tokens = r.tokens[:n_new].tolist()
+    return {"tok_s": (n_new - 1) / t_decode, "ms_per_token": t_decode / (n_new - 1) * 1e3,
+            "prefill_tok_s": prompt_len / t_prefill, "prompt_len": prompt_len, "n_new": n_new,
+            "weight_bytes_per_token_per_rank": r.weight_bytes_per_token(), "first_tokens": tokens[:8],
+            "launches_per_token": "10 per layer + lm_head + argmax, one CUDA graph"}
