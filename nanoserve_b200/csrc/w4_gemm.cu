@@ -173,11 +173,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const __nv_bfloat16* s_row = p.S + (size_t)(n < p.N ? n : 0) * p.KG;
       int s = 0, b = 0;
       uint32_t ph = 0, bph = 0;
-      for (int kb = 0; kb < p.nkb; ++kb) {
+      // the scale of K block kb + 1 is fetched while block kb is unpacked: the L2 round trip stays off the
+      // critical path of the hand-off to the MMA
+      auto load_scale = [&](int kb) {
         const int k0 = kb * kBK + hf * 32;
         __nv_bfloat16 sv = __float2bfloat16(0.f);
         if (n < p.N && k0 < p.K) sv = __ldg(s_row + k0 / p.G);
-        const uint32_t s2 = bf16_dup(sv);
+        return bf16_dup(sv);
+      };
+      uint32_t s2_next = load_scale(0);
+      for (int kb = 0; kb < p.nkb; ++kb) {
+        const uint32_t s2 = s2_next;
+        if (kb + 1 < p.nkb) s2_next = load_scale(kb + 1);
 
         // one lane per warp polls: many threads spinning on a shared-memory barrier slow the copies down
         if (lane == 0) mbar_wait(bar_full + 8 * s, ph, abort_flag);

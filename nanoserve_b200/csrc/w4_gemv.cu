@@ -250,6 +250,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
     fence_mbar_init();
   }
   __syncthreads();
+  pdl_launch_dependents();  // let the next kernel in the stream begin its own prologue as SMs free up
 
   if (warp == NCW) {
     // ------------------------------------------------------------ producer warp
@@ -282,6 +283,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
     // Sums the per-warp partial sums of a finished tile while the consumer warps are already on the
     // next one; owns the output stores and the cross-CTA (split-K) reduction.
     int tcount = 0;
+    pdl_wait_prior_grid();  // Y, the scratch and the counters may still be in use by the previous kernel
     for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
       const int sl = tile / p.nrg, rg = tile - sl * p.nrg;
       const int row0 = rg * kRowsPerGroup;
@@ -342,6 +344,10 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
     uint32_t k_r16 = 0x2C002C00u;    // fp16 1/16 twice
     asm volatile("" : "+r"(k_mask_lo), "+r"(k_mask_hi), "+r"(k_magic), "+r"(k_n1032), "+r"(k_n72), "+r"(k_r16));
     const int nstages = p.nstages, gdiv = p.gdiv;
+    // Launched with programmatic stream serialization this kernel may start while the previous one is still
+    // running: the weight stream (constant data) is already flowing; X, produced upstream, is touched only
+    // after the previous grid has completed and flushed.
+    pdl_wait_prior_grid();
 
     int s = 0;
     uint32_t ph = 0;
@@ -585,6 +591,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
 // ------------------------------------------------------------------ host side
 struct GemvPlan {
   int mt, ncw, mode, nslices, cps, nstages, grid;
+  bool pdl;
   size_t smem;
   int xs_m_stride;
   double cost;
@@ -670,6 +677,7 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
   if (!have) have = plan_for_width(M, N, K, 8, mt, flags, sm_count, partial_cap, counters_cap, &best);
   if (!have) return false;
   best.mode = mode;
+  best.pdl = (flags & kFlagPdl) != 0;
   *out = best;
   return true;
 }
@@ -681,8 +689,18 @@ int launch_variant(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan&
   // the call correct on every device of a multi-GPU process without per-device bookkeeping.
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
   if (e != cudaSuccess) return (int)e;
-  kernel<<<pl.grid, (NCW + 2) * 32, pl.smem, stream>>>(tmap, p);
-  return (int)cudaGetLastError();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(pl.grid);
+  cfg.blockDim = dim3((NCW + 2) * 32);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pl.pdl ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kernel, tmap, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 template <int MT, int NCW>

@@ -43,6 +43,7 @@ enum : int {
                            // bf16x2 subtract per weight pair (fewer ALU ops, fp32-level cancellation)
   kFlagForceNoSplitK = 2,  // GEMV: never use split-K (no scratch needed)
   kFlagNarrowCta = 4,      // GEMV: use the 8-consumer-warp CTA even when the 16-warp one applies
+  kFlagPdl = 8,            // GEMV: launch with programmatic stream serialization (overlap with the previous kernel)
 };
 
 int gemv_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,

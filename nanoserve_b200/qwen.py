@@ -264,3 +264,17 @@ def decode_rate(kernels: Kernels, device, rank: int = 0, world: int = 1, cfg: Op
             "prefill_tok_s": prompt_len / t_prefill, "prompt_len": prompt_len, "n_new": n_new,
             "weight_bytes_per_token_per_rank": r.weight_bytes_per_token(), "first_tokens": tokens[:8],
             "launches_per_token": "10 per layer + lm_head + argmax, one CUDA graph"}
+
+
+if __name__ == "__main__":
+    import argparse
+    import json
+
+    ap = argparse.ArgumentParser(description="greedy-decode rate of a random-init Qwen2.5-7B-shaped W4 model, one GPU")
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--new", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=28)
+    a = ap.parse_args()
+    c = Qwen2Config.qwen25_7b()
+    c.n_layers = a.layers
+    print(json.dumps(decode_rate(Kernels(), torch.device("cuda"), cfg=c, prompt_len=a.prompt, n_new=a.new)))
