@@ -86,6 +86,23 @@ int b2_w4_linear(const void* X, const void* Wq, const void* S, void* Y, int M, i
                  int flags, void* stream);
 
 /*
+ * Decode GEMV (1 <= M <= 16, G % 128 == 0) with the operator that precedes the linear folded into the kernel, so a
+ * decoder layer needs fewer launches.  No counterpart in the reference library (it runs ns_rmsnorm / ns_swiglu
+ * as separate kernels before ns_w4_linear, python/nanoserve/qwen.py:158-161).  Results equal the two-kernel
+ * sequence up to the rounding of the norm's sum of squares.
+ *   prologue 0: none (same as b2_w4_linear).
+ *   prologue 1: add + RMSNorm (semantics of ns_rmsnorm): the product's input is rmsnorm(bf16(X + R)) * Wn with
+ *               X, R [M, K], Wn [K]; R may be NULL (plain norm).  If Xout is not NULL, bf16(X + R) is stored there
+ *               (Xout must not alias X: other CTAs are still reading X).
+ *   prologue 2: SwiGLU (semantics of ns_swiglu): X is [M, 2K] = gate | up; the input is bf16(silu(gate) * up).
+ */
+#define B2_PROLOGUE_NONE 0
+#define B2_PROLOGUE_ADD_RMSNORM 1
+#define B2_PROLOGUE_SWIGLU 2
+int b2_w4_linear_fused(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G, int prologue,
+                       const void* R, const void* Wn, float eps, void* Xout, int flags, void* stream);
+
+/*
  * Synchronises the current device and returns its status word: 0, or B2_ERR_DEVICE if a kernel gave up
  * on a bounded wait since the last b2_clear_status.  A non-zero status makes later launches return at
  * once on the device, so the error cannot be missed.
@@ -115,16 +132,19 @@ int b2_w4_gemv_noalloc(const void* X, const void* Wq, const void* S, void* Y, in
  * a host-side position (python/nanoserve/qwen.py:119-133,147-151,174-177).
  *   b2_rope_kv_store: qkv [(Hq+2Hk)*D] bf16 of the new token, in place: += bias (may be NULL), rotate-half RoPE on
  *     the q and k heads at position *pos, k and v written to cache_k / cache_v [Hk, max_len, D] at that position.
- *   b2_decode_attention: out [Hq*D] = softmax(q K^T / sqrt(D)) V over cache positions 0..*pos (D = 64 or 128).
+ *   b2_decode_attention: out [Hq*D] = softmax(q K^T / sqrt(D)) V over cache positions 0..*pos (D = 64 or 128);
+ *     two launches (32 key slices per KV head, then a merge).
  *   b2_greedy_next: token = argmax(logits[0..V)) (lowest index on ties); out_tokens[*step] = token; *step += 1;
  *     *pos += 1; x_next[0..H) = embed[token].  pos, step: int32 on the device; out_tokens: int64 on the device.
  */
 int b2_rope_kv_store(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k, void* cache_v,
                      int Hq, int Hk, int D, int max_len, void* stream);
-int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v, const void* pos, void* out, int Hq,
-                        int Hk, int D, int max_len, void* stream);
+int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v, const void* pos, void* out,
+                        void* workspace, int Hq, int Hk, int D, int max_len, void* stream);
 int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* pos, void* out_tokens, void* step,
-                   void* x_next, void* stream);
+                   void* x_next, void* workspace, void* stream);
+/* Bytes of caller-owned device scratch (`workspace`) the two calls above need (split partials; Hq / Hk <= 8). */
+size_t b2_decode_workspace_bytes(int Hq, int D);
 
 /* Library identification: "nanoserve-b200 <version> sm_100a". */
 const char* b2_version(void);

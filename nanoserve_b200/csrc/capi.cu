@@ -78,6 +78,22 @@ int b2_w4_linear(const void* X, const void* Wq, const void* S, void* Y, int M, i
   return linear_dispatch(X, Wq, S, Y, M, N, K, G, flags, stream);
 }
 
+int b2_w4_linear_fused(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G, int prologue,
+                       const void* R, const void* Wn, float eps, void* Xout, int flags, void* stream) {
+  if (M < 1 || M > 16) return b2::kErrUnsupportedM;
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return rc;
+  b2::GemvPrologue pro;
+  pro.kind = prologue;
+  pro.R = R;
+  pro.Wn = Wn;
+  pro.Xout = Xout;
+  pro.eps = eps;
+  return b2::gemv_launch_ex(X, Wq, S, Y, M, N, K, G, pro, st->ws, flags, st->sm_count,
+                            static_cast<cudaStream_t>(stream));
+}
+
 int ns_w4_quantize(const void* W, void* Wq, void* S, int N, int K, int G, void* stream) {
   return b2::quantize_launch(W, Wq, S, N, K, G, static_cast<cudaStream_t>(stream));
 }

@@ -50,19 +50,25 @@ __global__ void rope_kv_store_kernel(bf16* __restrict__ qkv, const bf16* __restr
   }
 }
 
-// grid: Hq blocks, block: 256 threads (8 warps).  Each warp walks keys j = warp, warp+8, ... with an online
-// softmax; lanes split the head dimension (D = 128: 4 elements per lane).  Partial (max, sum, acc) of the
-// warps are merged through shared memory.
+// Decode attention in two launches.  Pass 1, grid (Hk, kSplits): a CTA takes one KV head and one slice of the
+// cached positions; warp w serves query head w of the group (Hq / Hk <= 8 heads share a KV head, so K and V rows
+// are read once per CTA, not once per query head); lanes split the head dimension; online softmax per warp.
+// It writes un-normalised partials (max, sum, acc[D]) per (query head, split).  Pass 2, grid Hq: merges the
+// splits.  With 4 KV heads x 32 splits the first pass fills 128 SMs however long the cache is.
+constexpr int kSplits = 32;
+
 template <int D>
-__global__ void __launch_bounds__(256) decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache_k,
-                                                               const bf16* __restrict__ cache_v,
-                                                               const int* __restrict__ pos_ptr, bf16* __restrict__ out,
-                                                               int Hq, int Hk, int max_len, float scale) {
+__global__ void __launch_bounds__(256) decode_attention_partial_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ cache_k, const bf16* __restrict__ cache_v,
+    const int* __restrict__ pos_ptr, float* __restrict__ part, int Hq, int Hk, int max_len, float scale) {
   constexpr int E = D / 32;  // elements per lane
-  __shared__ float s_m[8], s_l[8], s_acc[8][D];
-  const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kh = blockIdx.x, sp = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rep = Hq / Hk;
+  if (warp >= rep) return;
+  const int h = kh * rep + warp;
   const int n = min(*pos_ptr + 1, max_len);
-  const int kh = h / (Hq / Hk);
+  const int per = (n + kSplits - 1) / kSplits;
+  const int j0 = sp * per, j1 = min(n, j0 + per);
   const bf16* kbase = cache_k + (size_t)kh * max_len * D;
   const bf16* vbase = cache_v + (size_t)kh * max_len * D;
   float qf[E];
@@ -71,7 +77,7 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const bf16* __res
   float m = -FLT_MAX, l = 0.f, acc[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) acc[e] = 0.f;
-  for (int j = warp; j < n; j += 8) {
+  for (int j = j0; j < j1; ++j) {
     const bf16* kr = kbase + (size_t)j * D + lane * E;
     float s = 0.f;
 #pragma unroll
@@ -86,79 +92,98 @@ __global__ void __launch_bounds__(256) decode_attention_kernel(const bf16* __res
     for (int e = 0; e < E; ++e) acc[e] = acc[e] * corr + pj * __bfloat162float(vr[e]);
     m = mn;
   }
+  float* out = part + ((size_t)h * kSplits + sp) * (D + 2);
   if (lane == 0) {
-    s_m[warp] = m;
-    s_l[warp] = l;
+    out[0] = m;
+    out[1] = l;
   }
 #pragma unroll
-  for (int e = 0; e < E; ++e) s_acc[warp][lane * E + e] = acc[e];
-  __syncthreads();
-  if (threadIdx.x < D) {
-    float mm = -FLT_MAX;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) mm = fmaxf(mm, s_m[w]);
-    float num = 0.f, den = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      const float f = s_m[w] == -FLT_MAX ? 0.f : __expf(s_m[w] - mm);
-      num += f * s_acc[w][threadIdx.x];
-      den += f * s_l[w];
-    }
-    out[(size_t)h * D + threadIdx.x] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+  for (int e = 0; e < E; ++e) out[2 + lane * E + e] = acc[e];
+}
+
+template <int D>
+__global__ void decode_attention_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out) {
+  const int h = blockIdx.x, d = threadIdx.x;  // block: D threads
+  const float* p = part + (size_t)h * kSplits * (D + 2);
+  float mm = -FLT_MAX;
+#pragma unroll 4
+  for (int s = 0; s < kSplits; ++s) mm = fmaxf(mm, p[s * (D + 2)]);
+  float num = 0.f, den = 0.f;
+#pragma unroll 4
+  for (int s = 0; s < kSplits; ++s) {
+    const float ms = p[s * (D + 2)];
+    const float f = ms == -FLT_MAX ? 0.f : __expf(ms - mm);
+    num += f * p[s * (D + 2) + 2 + d];
+    den += f * p[s * (D + 2) + 1];
+  }
+  out[(size_t)h * D + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+}
+
+// Greedy choice in two launches.  Pass 1, kArgBlocks CTAs: each scans a slice of the logits and writes its best
+// (value, index).  Pass 2, one CTA: picks the best of those (lowest index on ties, as torch.argmax returns the
+// first occurrence), records the token, advances step and position, and copies the token's embedding row.
+constexpr int kArgBlocks = 148;
+
+__device__ __forceinline__ void argmax_merge(float& best, int& bi, float ov, int oi) {
+  if (ov > best || (ov == best && oi < bi)) {
+    best = ov;
+    bi = oi;
   }
 }
 
-// One block of 1024 threads: argmax over V logits (first index wins ties, as torch.argmax does), then the
-// chosen token is recorded, the position advances and the token's embedding row becomes the next input.
-__global__ void __launch_bounds__(1024) greedy_next_kernel(const bf16* __restrict__ logits, int V,
-                                                           const bf16* __restrict__ embed, int H, int* __restrict__ pos_ptr,
-                                                           long long* __restrict__ out_tokens, int* __restrict__ step_ptr,
-                                                           bf16* __restrict__ x_next) {
-  __shared__ float s_v[32];
-  __shared__ int s_i[32];
-  __shared__ int s_tok;
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const bf16* __restrict__ logits, int V,
+                                                             float* __restrict__ pv, int* __restrict__ pi) {
+  __shared__ float s_v[8];
+  __shared__ int s_i[8];
   float best = -FLT_MAX;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < V; i += gridDim.x * blockDim.x) {
     const float v = __bfloat162float(logits[i]);
-    if (v > best) {
+    if (v > best) {  // indices ascend within a thread, so the first occurrence is kept
       best = v;
       bi = i;
     }
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) {
-      best = ov;
-      bi = oi;
-    }
-  }
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
   if ((threadIdx.x & 31) == 0) {
     s_v[threadIdx.x >> 5] = best;
     s_i[threadIdx.x >> 5] = bi;
   }
   __syncthreads();
-  if (threadIdx.x < 32) {
-    best = s_v[threadIdx.x];
-    bi = s_i[threadIdx.x];
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) argmax_merge(best, bi, s_v[w], s_i[w]);
+    pv[blockIdx.x] = best;
+    pi[blockIdx.x] = bi;
+  }
+}
+
+__global__ void __launch_bounds__(256) greedy_finish_kernel(const float* __restrict__ pv, const int* __restrict__ pi,
+                                                            int nparts, int V, const bf16* __restrict__ embed, int H,
+                                                            int* __restrict__ pos_ptr, long long* __restrict__ out_tokens,
+                                                            int* __restrict__ step_ptr, bf16* __restrict__ x_next) {
+  __shared__ float s_v[8];
+  __shared__ int s_i[8];
+  __shared__ int s_tok;
+  float best = -FLT_MAX;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) argmax_merge(best, bi, pv[i], pi[i]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) {
-        best = ov;
-        bi = oi;
-      }
-    }
-    if (threadIdx.x == 0) {
-      if (bi < 0 || bi >= V) bi = 0;
-      s_tok = bi;
-      out_tokens[*step_ptr] = bi;
-      *step_ptr += 1;
-      *pos_ptr += 1;
-    }
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if ((threadIdx.x & 31) == 0) {
+    s_v[threadIdx.x >> 5] = best;
+    s_i[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) argmax_merge(best, bi, s_v[w], s_i[w]);
+    if (bi < 0 || bi >= V) bi = 0;
+    s_tok = bi;
+    out_tokens[*step_ptr] = bi;
+    *step_ptr += 1;
+    *pos_ptr += 1;
   }
   __syncthreads();
   const bf16* row = embed + (size_t)s_tok * H;
@@ -179,31 +204,46 @@ int b2_rope_kv_store(void* qkv, const void* bias, const void* inv_freq, const vo
   return (int)cudaGetLastError();
 }
 
-int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v, const void* pos, void* out, int Hq,
-                        int Hk, int D, int max_len, void* stream) {
-  if (Hq < 1 || Hk < 1 || Hq % Hk || max_len < 1) return b2::kErrBadShape;
+size_t b2_decode_workspace_bytes(int Hq, int D) {
+  const size_t attn = (size_t)Hq * kSplits * (D + 2) * sizeof(float);
+  const size_t arg = (size_t)kArgBlocks * (sizeof(float) + sizeof(int));
+  return attn > arg ? attn : arg;
+}
+
+int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v, const void* pos, void* out,
+                        void* workspace, int Hq, int Hk, int D, int max_len, void* stream) {
+  if (Hq < 1 || Hk < 1 || Hq % Hk || Hq / Hk > 8 || max_len < 1) return b2::kErrBadShape;
   if (D != 128 && D != 64) return b2::kErrNotImplemented;
-  if (!q || !cache_k || !cache_v || !pos || !out) return b2::kErrBadPointer;
+  if (!q || !cache_k || !cache_v || !pos || !out || !workspace) return b2::kErrBadPointer;
   const float scale = 1.f / sqrtf((float)D);
   const auto st = static_cast<cudaStream_t>(stream);
-  if (D == 128)
-    decode_attention_kernel<128><<<Hq, 256, 0, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache_k),
-                                                     static_cast<const bf16*>(cache_v), static_cast<const int*>(pos),
-                                                     static_cast<bf16*>(out), Hq, Hk, max_len, scale);
-  else
-    decode_attention_kernel<64><<<Hq, 256, 0, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache_k),
-                                                    static_cast<const bf16*>(cache_v), static_cast<const int*>(pos),
-                                                    static_cast<bf16*>(out), Hq, Hk, max_len, scale);
+  float* part = static_cast<float*>(workspace);
+  const dim3 grid(Hk, kSplits);
+  if (D == 128) {
+    decode_attention_partial_kernel<128><<<grid, 256, 0, st>>>(
+        static_cast<const bf16*>(q), static_cast<const bf16*>(cache_k), static_cast<const bf16*>(cache_v),
+        static_cast<const int*>(pos), part, Hq, Hk, max_len, scale);
+    decode_attention_merge_kernel<128><<<Hq, 128, 0, st>>>(part, static_cast<bf16*>(out));
+  } else {
+    decode_attention_partial_kernel<64><<<grid, 256, 0, st>>>(
+        static_cast<const bf16*>(q), static_cast<const bf16*>(cache_k), static_cast<const bf16*>(cache_v),
+        static_cast<const int*>(pos), part, Hq, Hk, max_len, scale);
+    decode_attention_merge_kernel<64><<<Hq, 64, 0, st>>>(part, static_cast<bf16*>(out));
+  }
   return (int)cudaGetLastError();
 }
 
 int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* pos, void* out_tokens, void* step,
-                   void* x_next, void* stream) {
+                   void* x_next, void* workspace, void* stream) {
   if (V < 1 || H < 1) return b2::kErrBadShape;
-  if (!logits || !embed || !pos || !out_tokens || !step || !x_next) return b2::kErrBadPointer;
-  greedy_next_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const bf16*>(logits), V, static_cast<const bf16*>(embed), H, static_cast<int*>(pos),
-      static_cast<long long*>(out_tokens), static_cast<int*>(step), static_cast<bf16*>(x_next));
+  if (!logits || !embed || !pos || !out_tokens || !step || !x_next || !workspace) return b2::kErrBadPointer;
+  const auto st = static_cast<cudaStream_t>(stream);
+  float* pv = static_cast<float*>(workspace);
+  int* pi = reinterpret_cast<int*>(pv + kArgBlocks);
+  argmax_partial_kernel<<<kArgBlocks, 256, 0, st>>>(static_cast<const bf16*>(logits), V, pv, pi);
+  greedy_finish_kernel<<<1, 256, 0, st>>>(pv, pi, kArgBlocks, V, static_cast<const bf16*>(embed), H,
+                                          static_cast<int*>(pos), static_cast<long long*>(out_tokens),
+                                          static_cast<int*>(step), static_cast<bf16*>(x_next));
   return (int)cudaGetLastError();
 }
 

@@ -55,10 +55,14 @@ constexpr int kChunkK = 128;           // K elements per consumer-warp work item
 constexpr int kRedPitch = 36;          // floats per (warp, token) row of the reduction buffer: 32 + 4 pad
 constexpr int kMaxStages = 8;
 constexpr int kSmemLimit = 232448;     // 227 KB opt-in maximum per CTA on sm_100
-constexpr int kHeaderBytes = 512;      // flags + barriers (first 256 B), a 256-byte block of zeros
+constexpr int kHeaderBytes = 2048;     // flags + barriers (256 B), 256 B of zeros, RMSNorm partial sums and factors
+constexpr int kNormSsOffset = 512;     // float [16 tokens][16 warps]
+constexpr int kNormInvOffset = 1536;   // float [16 tokens]
 constexpr int kBoxBytes = kRowsPerGroup * 128;  // 32 rows x 128 B (two chunks), swizzled
 
 enum : int { kModeGeneric = 0, kModeExact = 1, kModeFold = 2 };
+// What the kernel does to its input before the product (the operators that precede a linear in a decoder layer)
+enum : int { kProNone = 0, kProAddRmsNorm = 1, kProSwiglu = 2 };
 
 struct GemvParams {
   const __nv_bfloat16* X;
@@ -77,9 +81,16 @@ struct GemvParams {
   float* partial;   // [nslices][M][N]
   int* counters;    // [nrg]
   int* status;
+  // prologue (fast path only)
+  int pro;                    // kPro*
+  const __nv_bfloat16* R;     // add + RMSNorm: residual to add to X first (may be null)
+  const __nv_bfloat16* Wn;    // add + RMSNorm: norm weights [K]
+  __nv_bfloat16* Xout;        // add + RMSNorm: where X + R is stored (may be null)
+  float eps;
 };
 
-__host__ __device__ constexpr int red_bytes(int ncw, int mt) { return 2 * ncw * mt * 8 * kRedPitch * 4; }
+// two buffers of [consumer warp][token < M][kRedPitch] floats
+__host__ __device__ constexpr int red_bytes(int ncw, int m) { return (2 * ncw * m * kRedPitch * 4 + 127) & ~127; }
 
 __device__ __forceinline__ void consumer_sync(int nthreads) {
   asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
@@ -146,13 +157,89 @@ __device__ __forceinline__ void stage_x_bf16(const GemvParams& p, uint32_t xs_ba
   }
 }
 
+__device__ __forceinline__ void unpack8_bf16(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack8_bf16(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+// The eight input values x[m, k0..k0+8) as the product sees them, as bf16 bits.  With a prologue they are
+// what the separate operator would have stored in bf16: RMSNorm of the (bf16-rounded) sum X + R times the norm
+// weight (semantics of ns_rmsnorm), or silu(gate) * up of a [M, 2K] gate|up row (semantics of ns_swiglu).
+__device__ __forceinline__ uint4 load_x_unit(const GemvParams& p, int m, int k0, const float* inv) {
+  if (p.pro == kProNone) return __ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + k0));
+  float a[8], b[8];
+  if (p.pro == kProSwiglu) {
+    unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * 2 * p.K + k0)), a);
+    unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * 2 * p.K + p.K + k0)), b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = a[e] / (1.f + __expf(-a[e])) * b[e];
+    return pack8_bf16(a);
+  }
+  unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + k0)), a);
+  if (p.R != nullptr) {
+    unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.R + (size_t)m * p.K + k0)), b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = __bfloat162float(__float2bfloat16(a[e] + b[e]));
+  }
+  unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.Wn + k0)), b);
+  const float s = inv[m];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) a[e] = a[e] * s * b[e];
+  return pack8_bf16(a);
+}
+
+// add + RMSNorm prologue, first pass: every CTA computes 1 / rms of each token's full row of X + R (the row is a
+// few KB; recomputing it per CTA is cheaper than another launch); CTA 0 also stores X + R to Xout.
+template <int CT>
+__device__ __forceinline__ void rmsnorm_factors(const GemvParams& p, float* ss, float* inv, int ctid) {
+  const int warp = ctid >> 5, lane = ctid & 31, nw = CT / 32;
+  const int units = p.K / 8;
+  for (int m = 0; m < p.M; ++m) {
+    float acc = 0.f;
+    for (int u = ctid; u < units; u += CT) {
+      float a[8], b[8];
+      unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + u * 8)), a);
+      if (p.R != nullptr) {
+        unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.R + (size_t)m * p.K + u * 8)), b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] = __bfloat162float(__float2bfloat16(a[e] + b[e]));
+        if (blockIdx.x == 0 && p.Xout != nullptr)
+          *reinterpret_cast<uint4*>(p.Xout + (size_t)m * p.K + u * 8) = pack8_bf16(a);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc += a[e] * a[e];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) ss[m * 16 + warp] = acc;
+  }
+  consumer_sync(CT);
+  if (ctid < p.M) {
+    float t = 0.f;
+    for (int w = 0; w < nw; ++w) t += ss[ctid * 16 + w];
+    inv[ctid] = rsqrtf(t / p.K + p.eps);
+  }
+  consumer_sync(CT);
+}
+
 // fp16 staging for the fast path.  Per (token, chunk): e = biased exponent of the largest |x| (clamped),
 // x is multiplied by 2^(141 - e) (largest magnitude lands in [2^14, 2^15)) and converted to fp16;
 // xinfo[token][chunk] = { 2^(e - 141), correction }.  FOLD: the odd in-word positions are stored
 // divided by 16 (their weights arrive as 1024 + 16 q) and correction = sum of offset * stored value.
 template <int CT, bool FOLD>
-__device__ __forceinline__ void stage_x_f16(const GemvParams& p, uint32_t xs_base, float2* xinfo, int cb, int ce,
-                                            int ctid) {
+__device__ __forceinline__ void stage_x_f16(const GemvParams& p, uint32_t xs_base, float2* xinfo, const float* inv,
+                                            int cb, int ce, int ctid) {
   const int nch = ce - cb;
   const int units = p.M * nch * 16;
   const int units_pad = (units + 31) & ~31;
@@ -166,7 +253,7 @@ __device__ __forceinline__ void stage_x_f16(const GemvParams& p, uint32_t xs_bas
       ch = r >> 4;
       jt = r & 15;
       const int k0 = (cb + ch) * kChunkK + 32 * (jt & 3) + 8 * (jt >> 2);
-      if (k0 < p.K) v = __ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + k0));
+      if (k0 < p.K) v = load_x_unit(p, m, k0, inv);
     }
     // largest magnitude of the chunk: bf16 magnitudes order like their 15-bit patterns
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -216,7 +303,7 @@ __device__ __forceinline__ void stage_x_f16(const GemvParams& p, uint32_t xs_bas
 
 // MT: token tiles of 8 (1 or 2).  NCW: consumer warps (= chunks per stage, even).  MODE: see kMode*.
 template <int MT, int NCW, int MODE>
-__global__ void __launch_bounds__((NCW + 2) * 32, 1)
+__global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1)
     w4_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemvParams p) {
   constexpr int kStageBytes = (NCW / 2) * kBoxBytes;
   constexpr int kConsumerThreads = NCW * 32;
@@ -229,9 +316,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
   const uint32_t bar_red_empty = bar_red_full + 16;           // [2] the reducer has consumed them
   const uint32_t zero_base = smem_u32(smem + 256);
   float* red = reinterpret_cast<float*>(smem + kHeaderBytes);
-  float2* xinfo = reinterpret_cast<float2*>(smem + kHeaderBytes + red_bytes(NCW, MT));
+  float2* xinfo = reinterpret_cast<float2*>(smem + kHeaderBytes + red_bytes(NCW, p.M));
   const int xinfo_bytes = (p.M * p.cps * 8 + 127) & ~127;
-  const uint32_t xs_base = smem_u32(smem + kHeaderBytes + red_bytes(NCW, MT) + xinfo_bytes);
+  const uint32_t xs_base = smem_u32(smem + kHeaderBytes + red_bytes(NCW, p.M) + xinfo_bytes);
   const int xs_bytes = (p.M * p.xs_m_stride + 127) & ~127;
   const uint32_t ring_base = (xs_base + xs_bytes + 1023) & ~1023u;  // swizzled boxes: 1024-byte aligned
 
@@ -288,14 +375,14 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
       const int sl = tile / p.nrg, rg = tile - sl * p.nrg;
       const int row0 = rg * kRowsPerGroup;
       const int b = tcount & 1;
-      const float* rbuf = red + b * (NCW * MT * 8 * kRedPitch);
+      const float* rbuf = red + b * (NCW * p.M * kRedPitch);
       if (lane == 0) mbar_wait(bar_red_full + 8 * b, (tcount >> 1) & 1, abort_flag);
       __syncwarp();
       const int n = row0 + lane;
       for (int tok = 0; tok < p.M; ++tok) {
         float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < NCW; ++w) sum += rbuf[(w * MT * 8 + tok) * kRedPitch + lane];
+        for (int w = 0; w < NCW; ++w) sum += rbuf[(w * p.M + tok) * kRedPitch + lane];
         if (n < p.N) {
           if (p.nslices == 1)
             p.Y[(size_t)tok * p.N + n] = __float2bfloat16(sum);
@@ -359,10 +446,13 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
       const int row0 = rg * kRowsPerGroup;
       if (sl != staged_slice) {
         if (staged_slice >= 0) consumer_sync(kConsumerThreads);  // all done with the old slice
-        if constexpr (kHalf)
-          stage_x_f16<kConsumerThreads, MODE == kModeFold>(p, xs_base, xinfo, cb, ce, ctid);
-        else
-          stage_x_bf16<kConsumerThreads>(p, xs_base, cb, ce, ctid);
+        if constexpr (kHalf) {
+          float* inv = reinterpret_cast<float*>(smem + kNormInvOffset);
+          if (p.pro == kProAddRmsNorm && staged_slice < 0)
+            rmsnorm_factors<kConsumerThreads>(p, reinterpret_cast<float*>(smem + kNormSsOffset), inv, ctid);
+          stage_x_f16<kConsumerThreads, MODE == kModeFold>(p, xs_base, xinfo, inv, cb, ce, ctid);
+        }
+        if constexpr (!kHalf) stage_x_bf16<kConsumerThreads>(p, xs_base, cb, ce, ctid);
         if (ctid < 16) sts128(zero_base + ctid * 16, make_uint4(0u, 0u, 0u, 0u));
         consumer_sync(kConsumerThreads);
         staged_slice = sl;
@@ -562,18 +652,23 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
 
       // ---- hand the per-warp partial sums of this tile to the reducer warp (two buffers in rotation)
       const int b = tcount & 1;
-      float* rbuf = red + b * (NCW * MT * 8 * kRedPitch);
+      float* rbuf = red + b * (NCW * p.M * kRedPitch);
       if (lane == 0) mbar_wait(bar_red_empty + 8 * b, ((tcount >> 1) & 1) ^ 1, abort_flag);
       __syncwarp();
 #pragma unroll
       for (int rb = 0; rb < 2; ++rb)
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-          float* r0 = rbuf + (warp * MT * 8 + mt * 8 + 2 * t) * kRedPitch + rb * 16 + gr;
-          r0[0] = fin[rb][mt][0];
-          r0[kRedPitch] = fin[rb][mt][1];
-          r0[8] = fin[rb][mt][2];
-          r0[kRedPitch + 8] = fin[rb][mt][3];
+          const int tok = mt * 8 + 2 * t;  // accumulator columns 2t, 2t+1 of this tile; padding tokens are dropped
+          float* r0 = rbuf + (warp * p.M + tok) * kRedPitch + rb * 16 + gr;
+          if (tok < p.M) {
+            r0[0] = fin[rb][mt][0];
+            r0[8] = fin[rb][mt][2];
+          }
+          if (tok + 1 < p.M) {
+            r0[kRedPitch] = fin[rb][mt][1];
+            r0[kRedPitch + 8] = fin[rb][mt][3];
+          }
         }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_red_full + 8 * b);
@@ -592,16 +687,18 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
 struct GemvPlan {
   int mt, ncw, mode, nslices, cps, nstages, grid;
   bool pdl;
+  int ctas_per_sm;
   size_t smem;
   int xs_m_stride;
   double cost;
 };
 
 size_t smem_without_ring(int M, int mt, int ncw, int cps) {
+  (void)mt;
   const int xs_m_stride = cps * 256 + 64;
   const size_t xinfo_bytes = ((size_t)M * cps * 8 + 127) & ~(size_t)127;
   const size_t xs_bytes = ((size_t)M * xs_m_stride + 127) & ~(size_t)127;
-  return kHeaderBytes + red_bytes(ncw, mt) + xinfo_bytes + xs_bytes + 1024;
+  return kHeaderBytes + red_bytes(ncw, M) + xinfo_bytes + xs_bytes + 1024;
 }
 
 // Plan for a fixed CTA width.  Cost model in units of "one chunk of one row group" (2 KB of weights): a
@@ -617,27 +714,42 @@ bool plan_for_width(int M, int N, int K, int ncw, int mt, int flags, int sm_coun
   const int nrg = (N + kRowsPerGroup - 1) / kRowsPerGroup;
   const int stage_bytes = (ncw / 2) * kBoxBytes;
   const int grid = std::max(1, sm_count);
+  // Two CTAs per SM when both fit (shared memory: half of 227 KB minus the per-CTA reserve; registers: the narrow
+  // MT == 1 kernels are compiled for it): more warps to hide latency, and one CTA's tail overlaps the other's
+  // streaming.  Otherwise one CTA with a deeper ring.
+  constexpr size_t kHalfSmem = 113 * 1024;
   double best = 1e30;
-  int best_ns = 0, best_cps = 0;
+  int best_ns = 0, best_cps = 0, best_ctas = 1;
   const int max_ns = (flags & kFlagForceNoSplitK) ? 1 : std::min(nchunks, 64);
   for (int ns = 1; ns <= max_ns; ++ns) {
     const int cps = (nchunks + ns - 1) / ns;
     if ((nchunks + cps - 1) / cps != ns) continue;
-    if (smem_without_ring(M, mt, ncw, cps) + 3 * (size_t)stage_bytes > (size_t)kSmemLimit) continue;
     if (ns > 1) {
       if ((size_t)ns * M * N * sizeof(float) > partial_cap) continue;
       if (nrg > counters_cap) continue;
     }
+    const size_t fixed = smem_without_ring(M, mt, ncw, cps);
     const long tiles = (long)nrg * ns;
-    const long per_cta = (tiles + grid - 1) / grid;
     const int stage_chunks = ((cps + ncw - 1) / ncw) * ncw;
     // the memory system moves only real bytes, the warps pay for padded stages: weigh them equally
+    // fixed cost of a tile (hand-off to the reducer) and of a split-K tile (scratch round trip, measured to be
+    // dear: splitting the 3584 x 18944 projection five ways was slower than leaving 36 SMs idle)
     const double tile_cost = 0.5 * (cps + stage_chunks) + 4.0 + (ns > 1 ? 12.0 : 0.0);
-    const double cost = per_cta * tile_cost;
-    if (cost < best) {
-      best = cost;
-      best_ns = ns;
-      best_cps = cps;
+    for (int ctas = 2; ctas >= 1; --ctas) {
+      if (ctas == 2 && !(mt == 1 && ncw <= 12 && fixed + 2 * (size_t)stage_bytes <= kHalfSmem)) continue;
+      if (ctas == 1 && fixed + 2 * (size_t)stage_bytes > (size_t)kSmemLimit) continue;
+      const long slots = (long)grid * ctas;
+      const long rounds = (tiles + slots - 1) / slots;
+      const long active = std::min<long>(ctas, (tiles + grid - 1) / grid);  // CTAs that share the busiest SM
+      double cost = rounds * tile_cost * active;
+      if (active == 2) cost *= 0.9;                             // measured: tails overlap
+      if (active == 1 && ncw <= 12) cost *= 1.0 + (16 - ncw) / 20.0;  // measured: too few warps on the SM
+      if (cost < best) {
+        best = cost;
+        best_ns = ns;
+        best_cps = cps;
+        best_ctas = ctas;
+      }
     }
   }
   if (best_ns == 0) return false;
@@ -646,12 +758,19 @@ bool plan_for_width(int M, int N, int K, int ncw, int mt, int flags, int sm_coun
   pl.xs_m_stride = pl.cps * 256 + 64;
   pl.cost = best;
   const size_t fixed = smem_without_ring(M, mt, ncw, pl.cps);
-  int stages = (int)(((size_t)kSmemLimit - fixed) / stage_bytes);
-  stages = std::min(stages, ncw >= 14 ? 5 : kMaxStages);
+  const long tiles = (long)nrg * pl.nslices;
+  int stages;
+  if (best_ctas == 2) {
+    stages = std::min<int>(4, (int)((kHalfSmem - fixed) / stage_bytes));
+  } else {
+    stages = (int)(((size_t)kSmemLimit - fixed) / stage_bytes);
+    stages = std::min(stages, ncw >= 14 ? 5 : kMaxStages);
+  }
   if (stages < 2) return false;
   pl.nstages = stages;
   pl.smem = fixed + (size_t)stages * stage_bytes;
-  pl.grid = (int)std::min<long>(grid, (long)nrg * pl.nslices);
+  pl.grid = (int)std::min<long>((long)grid * best_ctas, tiles);
+  pl.ctas_per_sm = best_ctas;
   *out = pl;
   return true;
 }
@@ -662,10 +781,14 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
   const int mode = (G % 128) ? kModeGeneric : ((flags & kFlagFoldZeroPoint) ? kModeFold : kModeExact);
   GemvPlan best{};
   bool have = false;
-  // wide CTAs (16 or 14 consumer warps) for one token tile; the narrow one otherwise or as a fallback
-  const int widths_wide[2] = {16, 14};
+  // One token tile: candidates are the wide CTAs (16 or 14 consumer warps, one per SM) and the narrow one
+  // (8 consumer warps, two per SM when they fit); the cost model picks.  Bits 4-7 of the flags force a
+  // width (diagnostics).  Two token tiles need the registers of the 8-warp CTA.
+  const int forced = ((flags >> 4) & 0xF) * 2;
   if (mt == 1 && !(flags & kFlagNarrowCta)) {
-    for (int w : widths_wide) {
+    const int widths[3] = {16, 14, 8};
+    for (int w : widths) {
+      if (forced && w != forced) continue;
       GemvPlan pl;
       if (plan_for_width(M, N, K, w, mt, flags, sm_count, partial_cap, counters_cap, &pl) &&
           (!have || pl.cost < best.cost)) {
@@ -688,6 +811,9 @@ int launch_variant(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan&
   // Raising the dynamic shared-memory limit is idempotent and cheap; doing it on every launch keeps
   // the call correct on every device of a multi-GPU process without per-device bookkeeping.
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+  if (e != cudaSuccess) return (int)e;
+  // ask for the largest shared-memory carve-out so that two CTAs of ~100 KB can be resident together
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return (int)e;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.grid);
@@ -722,7 +848,22 @@ size_t gemv_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, s
 
 int gemv_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
                 const Workspace& ws, int flags, int sm_count, cudaStream_t stream) {
+  return gemv_launch_ex(X, Wq, S, Y, M, N, K, G, GemvPrologue{}, ws, flags, sm_count, stream);
+}
+
+int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                   const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream) {
   if (M < 1 || M > 16) return kErrUnsupportedM;
+  if (pro.kind != kProNone) {
+    if (pro.kind != kProAddRmsNorm && pro.kind != kProSwiglu) return kErrBadShape;
+    if (G % 128) return kErrNotImplemented;  // prologues live in the fp16 staging of the fast path
+    if (pro.kind == kProAddRmsNorm) {
+      if (!pro.Wn) return kErrBadPointer;
+      if ((reinterpret_cast<uintptr_t>(pro.Wn) & 15) || (reinterpret_cast<uintptr_t>(pro.R) & 15) ||
+          (reinterpret_cast<uintptr_t>(pro.Xout) & 15))
+        return kErrBadPointer;
+    }
+  }
   if (N < 1 || K < 32 || G < 32 || K % 32 || G % 32 || K % G) return kErrBadShape;
   if (!X || !Wq || !S || !Y) return kErrBadPointer;
   if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(Wq) & 15) ||
@@ -758,6 +899,11 @@ int gemv_launch(const void* X, const void* Wq, const void* S, void* Y, int M, in
   p.partial = ws.partial;
   p.counters = ws.counters;
   p.status = ws.status;
+  p.pro = pro.kind;
+  p.R = static_cast<const __nv_bfloat16*>(pro.R);
+  p.Wn = static_cast<const __nv_bfloat16*>(pro.Wn);
+  p.Xout = static_cast<__nv_bfloat16*>(pro.Xout);
+  p.eps = pro.eps;
 
   if (pl.mt == 2) return launch_mode<2, 8>(tmap, p, pl, stream);
   switch (pl.ncw) {

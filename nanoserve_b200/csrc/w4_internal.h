@@ -46,6 +46,19 @@ enum : int {
   kFlagPdl = 8,            // GEMV: launch with programmatic stream serialization (overlap with the previous kernel)
 };
 
+// Optional prologue of the GEMV (G % 128 == 0 only): the operator that precedes the linear, folded into the
+// kernel's staging of X.  kind 0: none; 1: X <- bf16(X + R) (R may be null), input = RMSNorm(X) * Wn, X + R stored to
+// Xout (may be null); 2: X is a [M, 2K] gate|up row, input = silu(gate) * up.
+struct GemvPrologue {
+  int kind = 0;
+  const void* R = nullptr;
+  const void* Wn = nullptr;
+  void* Xout = nullptr;
+  float eps = 0.f;
+};
+
+int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                   const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream);
 int gemv_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
                 const Workspace& ws, int flags, int sm_count, cudaStream_t stream);
 int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,

@@ -34,13 +34,15 @@ SIGNATURES = {
     # additions
     "b2_init": ([], _i32),
     "b2_w4_linear": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp], _i32),
+    "b2_w4_linear_fused": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _f32, _vp, _i32, _vp], _i32),
     "b2_device_status": ([], _i32),
     "b2_clear_status": ([], _i32),
     "b2_w4_gemv_scratch_bytes": ([_i32, _i32, _i32, _i32, _i32], ctypes.c_size_t),
     "b2_w4_gemv_noalloc": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
     "b2_rope_kv_store": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
-    "b2_decode_attention": ([_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
-    "b2_greedy_next": ([_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp], _i32),
+    "b2_decode_attention": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
+    "b2_greedy_next": ([_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp], _i32),
+    "b2_decode_workspace_bytes": ([_i32, _i32], ctypes.c_size_t),
     "b2_version": ([], ctypes.c_char_p),
 }
 
@@ -147,6 +149,20 @@ class Kernels:
         return y
 
     # ---- additions
+    def w4_linear_fused(self, x, Wq, S, group=128, prologue=0, r=None, wn=None, eps=0.0, x_out=None, flags=0):
+        """Decode GEMV with the preceding operator folded in: prologue 1 = add + RMSNorm (x + r normalised with
+        weights wn; the sum goes to x_out), prologue 2 = SwiGLU (x is [M, 2K] gate | up)."""
+        self._cuda(x, Wq, S, r, wn, x_out)
+        M = x.shape[0]
+        N, K = Wq.shape[0], Wq.shape[1] * 8
+        assert x.is_contiguous() and x.shape[1] == (2 * K if prologue == 2 else K)
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        p = lambda t: None if t is None else t.data_ptr()
+        rc = self.lib.b2_w4_linear_fused(x.data_ptr(), Wq.data_ptr(), S.data_ptr(), y.data_ptr(), M, N, K, group,
+                                         prologue, p(r), p(wn), eps, p(x_out), flags, self._stream())
+        self._check(rc, "b2_w4_linear_fused")
+        return y
+
     def init(self):
         self._check(self.lib.b2_init(), "b2_init")
 

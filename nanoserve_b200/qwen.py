@@ -21,7 +21,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from .ops import Kernels
+from .ops import FLAG_PDL, Kernels
 
 
 @dataclass
@@ -95,8 +95,11 @@ class Qwen2Runner:
         self.step = torch.zeros(1, dtype=torch.int32, device=device)
         self.tokens = torch.zeros(max_len, dtype=torch.int64, device=device)
         self.x = torch.zeros(1, H, dtype=torch.bfloat16, device=device)  # residual stream of the current token
+        self.x_alt = torch.zeros_like(self.x)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.stream = torch.cuda.Stream(device=device)
+        self.scratch = torch.empty(int(kernels.lib.b2_decode_workspace_bytes(cfg.n_heads, D)), dtype=torch.uint8,
+                                   device=device)
         kernels.init()
 
     # ------------------------------------------------------------------ helpers
@@ -137,7 +140,8 @@ class Qwen2Runner:
         return torch.cat(parts, dim=1)
 
     def linear(self, x, wt):
-        return self.k.w4_linear(x, wt[0], wt[1], self.cfg.group)
+        # decode (one token) launches overlap their prologue with the previous kernel of the step
+        return self.k.w4_linear(x, wt[0], wt[1], self.cfg.group, flags=FLAG_PDL if x.shape[0] == 1 else 0)
 
     # ------------------------------------------------------------------ prompt (eager, GEMM path)
     @torch.no_grad()
@@ -176,32 +180,50 @@ class Qwen2Runner:
     def _greedy_next(self, logits):
         rc = self.k.lib.b2_greedy_next(logits.data_ptr(), self.cfg.vocab, self.embed.data_ptr(), self.cfg.hidden,
                                        self.pos.data_ptr(), self.tokens.data_ptr(), self.step.data_ptr(),
-                                       self.x.data_ptr(), self._st())
+                                       self.x.data_ptr(), self.scratch.data_ptr(), self._st())
         self.k._check(rc, "b2_greedy_next")
 
     # ------------------------------------------------------------------ one decode step (graph-capturable)
+    def _fused(self, x, wt, prologue, r=None, wn=None, x_out=None):
+        return self.k.w4_linear_fused(x, wt[0], wt[1], self.cfg.group, prologue=prologue, r=r, wn=wn,
+                                      eps=self.cfg.rms_eps, x_out=x_out, flags=FLAG_PDL)
+
     @torch.no_grad()
     def decode_step(self):
+        """One token.  Seven launches per layer on one GPU: qkv GEMV (residual add + RMSNorm folded in), RoPE + KV
+        store, attention (two passes), o GEMV, gate|up GEMV (add + norm folded in), down GEMV (SwiGLU folded in).
+        The residual stream alternates between two buffers because a fused GEMV may not overwrite the X other CTAs
+        are still reading; every step starts again from `self.x`, where b2_greedy_next puts the next embedding."""
         cfg, k, lib = self.cfg, self.k, self.k.lib
-        D, x = cfg.head_dim, self.x
-        h = k.rmsnorm(x, None, self.layers[0]["ln_in"], cfg.rms_eps)
+        D = cfg.head_dim
+        x, x_alt = self.x, self.x_alt
+        r, wn = None, self.layers[0]["ln_in"]  # pending residual and the norm that follows it
         for li, L in enumerate(self.layers):
-            qkv = self._gather_parts(self.linear(h, L["qkv"]), [self.nq, self.nkv, self.nkv]).contiguous()
+            y = self._fused(x, L["qkv"], 1, r=r, wn=wn, x_out=x_alt if r is not None else None)
+            if r is not None:
+                x, x_alt = x_alt, x
+            qkv = self._gather_parts(y, [self.nq, self.nkv, self.nkv]).contiguous()
             rc = lib.b2_rope_kv_store(qkv.data_ptr(), L["bias"].data_ptr(), self.inv_freq.data_ptr(),
                                       self.pos.data_ptr(), self.cache_k[li].data_ptr(), self.cache_v[li].data_ptr(),
                                       cfg.n_heads, cfg.n_kv_heads, D, self.max_len, self._st())
             k._check(rc, "b2_rope_kv_store")
             a = torch.empty(1, self.nq, dtype=torch.bfloat16, device=self.dev)
             rc = lib.b2_decode_attention(qkv.data_ptr(), self.cache_k[li].data_ptr(), self.cache_v[li].data_ptr(),
-                                         self.pos.data_ptr(), a.data_ptr(), cfg.n_heads, cfg.n_kv_heads, D,
-                                         self.max_len, self._st())
+                                         self.pos.data_ptr(), a.data_ptr(), self.scratch.data_ptr(), cfg.n_heads,
+                                         cfg.n_kv_heads, D, self.max_len, self._st())
             k._check(rc, "b2_decode_attention")
-            h = k.rmsnorm(x, self._gather(self.linear(a, L["o"])), L["ln_post"], cfg.rms_eps)
-            gu = self.linear(h, L["gu"])
-            il = self.I // self.world
-            act = self._gather(k.swiglu(gu[:, :il], gu[:, il:]))  # T = 1: both halves are contiguous
-            nxt = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
-            h = k.rmsnorm(x, self._gather(self.linear(act, L["d"])), nxt, cfg.rms_eps)
+            o = self._gather(self.linear(a, L["o"]))
+            gu = self._fused(x, L["gu"], 1, r=o, wn=L["ln_post"], x_out=x_alt)
+            x, x_alt = x_alt, x
+            if self.world == 1:
+                d = self._fused(gu, L["d"], 2)
+            else:  # the activation is gathered between SwiGLU and the down projection
+                il = self.I // self.world
+                d = self._gather(self.linear(self._gather(k.swiglu(gu[:, :il], gu[:, il:])), L["d"]))
+            r = d
+            wn = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
+        h = k.rmsnorm(x, r, wn, cfg.rms_eps)  # the stream is not needed after this: the next step starts from
+        # the embedding b2_greedy_next writes into self.x, whichever buffer the last layer ended on
         logits = self._gather(F.linear(h, self.lm_head))
         self._greedy_next(logits)
         return logits
@@ -263,7 +285,7 @@ def decode_rate(kernels: Kernels, device, rank: int = 0, world: int = 1, cfg: Op
     return {"tok_s": (n_new - 1) / t_decode, "ms_per_token": t_decode / (n_new - 1) * 1e3,
             "prefill_tok_s": prompt_len / t_prefill, "prompt_len": prompt_len, "n_new": n_new,
             "weight_bytes_per_token_per_rank": r.weight_bytes_per_token(), "first_tokens": tokens[:8],
-            "launches_per_token": "10 per layer + lm_head + argmax, one CUDA graph"}
+            "launches_per_token": "7 per layer (1 GPU) + final norm + lm_head + 2 for argmax, one CUDA graph"}
 
 
 if __name__ == "__main__":

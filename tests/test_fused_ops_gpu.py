@@ -80,8 +80,9 @@ def test_decode_attention_and_rope_kv_store(kernels):
     assert close(got, ref)
     assert torch.equal(ck[:, pos], got[Hq:Hq + Hk]) and torch.equal(cv[:, pos], got[Hq + Hk:])
     out = torch.empty(Hq * D, dtype=torch.bfloat16, device="cuda")
-    assert lib.b2_decode_attention(qkv.data_ptr(), ck.data_ptr(), cv.data_ptr(), p.data_ptr(), out.data_ptr(), Hq, Hk,
-                                   D, L, st) == 0
+    ws = torch.empty(int(lib.b2_decode_workspace_bytes(Hq, D)), dtype=torch.uint8, device="cuda")
+    assert lib.b2_decode_attention(qkv.data_ptr(), ck.data_ptr(), cv.data_ptr(), p.data_ptr(), out.data_ptr(),
+                                   ws.data_ptr(), Hq, Hk, D, L, st) == 0
     qh = got[:Hq].float()[None, :, None, :]
     ref_o = F.scaled_dot_product_attention(qh, ck[None, :, :pos + 1].float(), cv[None, :, :pos + 1].float(),
                                            enable_gqa=True)
@@ -101,7 +102,8 @@ def test_greedy_next(kernels):
     toks = torch.zeros(8, dtype=torch.int64, device="cuda")
     x = torch.zeros(H, dtype=torch.bfloat16, device="cuda")
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ws = torch.empty(int(lib.b2_decode_workspace_bytes(28, 128)), dtype=torch.uint8, device="cuda")
     assert lib.b2_greedy_next(logits.data_ptr(), V, embed.data_ptr(), H, pos.data_ptr(), toks.data_ptr(),
-                              step.data_ptr(), x.data_ptr(), st) == 0
+                              step.data_ptr(), x.data_ptr(), ws.data_ptr(), st) == 0
     torch.cuda.synchronize()
     assert int(toks[2]) == 777 and int(pos) == 12 and int(step) == 3 and torch.equal(x, embed[777])

@@ -1,0 +1,75 @@
+"""GPU tests of b2_w4_linear_fused: the GEMV with the preceding operator folded in must equal the two-kernel sequence
+(ns_rmsnorm or ns_swiglu, then ns_w4_linear) up to the rounding of the norm's sum of squares, and must match the CPU
+oracle applied to the operator's bf16 output."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests.util import bits_to_torch, check_bf16_output, torch_to_bits, u32_to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def agree(a, b, scale_slack=2e-3):
+    a, b = a.float(), b.float()
+    tol = torch.maximum(a.abs(), b.abs()) * 2.0**-7 + scale_slack * b.abs().max()
+    return bool(torch.all((a - b).abs() <= tol))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4608, 3584), (1, 512, 3584), (3, 256, 1024), (16, 448, 3584), (8, 64, 18944)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_add_rmsnorm_prologue(kernels, M, N, K, with_residual):
+    G = 128
+    _, Wq, S = oracle.synth_inputs(1, N, K, G, seed=41)
+    wq, s = u32_to_torch(Wq), bits_to_torch(S)
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    r = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16) if with_residual else None
+    wn = (1 + 0.1 * torch.randn(K, device="cuda", generator=g)).to(torch.bfloat16)
+    eps = 1e-6
+    # two-kernel sequence of the reference flow
+    x_seq = x.clone()
+    h = kernels.rmsnorm(x_seq, r, wn, eps)
+    y_seq = kernels.w4_linear(h, wq, s, G)
+    # fused
+    x_out = torch.full_like(x, 3.0) if with_residual else None
+    y = kernels.w4_linear_fused(x, wq, s, G, prologue=1, r=r, wn=wn, eps=eps, x_out=x_out)
+    torch.cuda.synchronize()
+    if with_residual:
+        assert torch.equal(x_out, x_seq)  # the updated residual stream, bit for bit
+    assert agree(y, y_seq)
+    # the norm output differs from the separate kernel's by at most a bf16 ulp where the factor rounds differently;
+    # against the oracle on the separate kernel's output the product stays within that plus the GEMV's own bound
+    ref = oracle.w4_linear_f32(torch_to_bits(h), Wq, S, G, threads=oracle.max_threads())
+    check_bf16_output(torch_to_bits(y), ref, 4e-3)
+    assert kernels.device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 3584, 18944), (4, 256, 512), (16, 448, 2304)])
+def test_swiglu_prologue(kernels, M, N, K):
+    G = 128
+    _, Wq, S = oracle.synth_inputs(1, N, K, G, seed=43)
+    wq, s = u32_to_torch(Wq), bits_to_torch(S)
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    gu = torch.randn(M, 2 * K, device="cuda", generator=g).to(torch.bfloat16)
+    act = kernels.swiglu(gu[:, :K].contiguous(), gu[:, K:].contiguous())
+    y_seq = kernels.w4_linear(act, wq, s, G)
+    y = kernels.w4_linear_fused(gu, wq, s, G, prologue=2)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y_seq)  # same element-wise arithmetic, same product: identical
+    check_bf16_output(torch_to_bits(y), oracle.w4_linear_f32(torch_to_bits(act), Wq, S, G, threads=oracle.max_threads()),
+                      3e-6)
+
+
+def test_prologue_error_codes(kernels):
+    x = torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda")
+    wq = torch.zeros(8, 32, dtype=torch.int32, device="cuda")
+    s = torch.ones(8, 8, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="code -3"):   # G = 32: prologues are fast-path only
+        kernels.w4_linear_fused(x, wq, s, 32, prologue=1, wn=x[0])
+    s = torch.ones(8, 2, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="code -4"):   # norm weights missing
+        kernels.w4_linear_fused(x, wq, s, 128, prologue=1)
+    with pytest.raises(RuntimeError, match="code -1"):
+        kernels.w4_linear_fused(x, wq, s, 128, prologue=7)
