@@ -69,8 +69,10 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
 #define B2_FLAG_FOLD_ZERO_POINT 1 /* GEMV: apply the -8 as one fp32 correction per 128-wide chunk */
 #define B2_FLAG_NO_SPLIT_K 2      /* GEMV: never split K across CTAs (uses no scratch memory) */
 #define B2_FLAG_NARROW_CTA 4      /* GEMV: 8 consumer warps per CTA instead of 16 */
-#define B2_FLAG_PDL 8             /* GEMV: programmatic dependent launch: the kernel may begin (weight prefetch only)
-                                     while the previous kernel of the stream is still running */
+#define B2_FLAG_NO_PDL 8          /* GEMV: plain launch.  By default the GEMV is launched with programmatic stream
+                                     serialization: it may begin (weight prefetch only) while the previous kernel of
+                                     the stream is still running, and touches X, Y and scratch only after that kernel
+                                     has completed */
 
 /*
  * Sets up the calling thread's current device: queries the SM count and allocates the per-device scratch

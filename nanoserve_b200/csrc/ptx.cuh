@@ -42,17 +42,16 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-// One try: the hardware suspends the thread until the phase completes or a time limit of about
-// `kSuspendHintNs` passes, so a waiting warp issues almost no instructions.
-constexpr uint32_t kSuspendHintNs = 20000;
+// One try: the hardware may suspend the thread for a short, implementation-defined time while the phase is
+// incomplete.  (An explicit long suspend-time hint was tried and measurably delayed the wake-up.)
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
+      : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }

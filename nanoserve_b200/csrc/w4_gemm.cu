@@ -84,8 +84,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + geo::kBarOffset + 27 * 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * kBN;
-  const int m0 = blockIdx.y * (128 * MI);
+  // token tiles vary fastest over the CTAs that run together: they then read many different X tiles and few
+  // weight tiles at a time, which spreads the L2 traffic (74 CTAs pulling the same X tile at once made a few L2
+  // slices the bottleneck)
+  const int m0 = blockIdx.x * (128 * MI);
+  const int n0 = blockIdx.y * kBN;
 
   if (tid == 0) {
     *abort_flag = 0;
@@ -280,7 +283,7 @@ int launch_gemm(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& 
   cudaError_t e =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmGeo<MI>::kSmemBytes);
   if (e != cudaSuccess) return (int)e;
-  const dim3 grid((p.N + kBN - 1) / kBN, (p.M + 128 * MI - 1) / (128 * MI));
+  const dim3 grid((p.M + 128 * MI - 1) / (128 * MI), (p.N + kBN - 1) / kBN);
   kernel<<<grid, kGemmThreads, GemmGeo<MI>::kSmemBytes, stream>>>(tx, tw, p);
   return (int)cudaGetLastError();
 }

@@ -800,7 +800,7 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
   if (!have) have = plan_for_width(M, N, K, 8, mt, flags, sm_count, partial_cap, counters_cap, &best);
   if (!have) return false;
   best.mode = mode;
-  best.pdl = (flags & kFlagPdl) != 0;
+  best.pdl = (flags & kFlagNoPdl) == 0;
   *out = best;
   return true;
 }

@@ -43,7 +43,8 @@ enum : int {
                            // bf16x2 subtract per weight pair (fewer ALU ops, fp32-level cancellation)
   kFlagForceNoSplitK = 2,  // GEMV: never use split-K (no scratch needed)
   kFlagNarrowCta = 4,      // GEMV: use the 8-consumer-warp CTA even when the 16-warp one applies
-  kFlagPdl = 8,            // GEMV: launch with programmatic stream serialization (overlap with the previous kernel)
+  kFlagNoPdl = 8,          // GEMV: do NOT launch with programmatic stream serialization (by default the kernel may
+                           // begin -- weight prefetch only -- while the previous kernel of the stream still runs)
 };
 
 // Optional prologue of the GEMV (G % 128 == 0 only): the operator that precedes the linear, folded into the

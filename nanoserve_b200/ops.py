@@ -19,7 +19,7 @@ _LIB_DEFAULT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "b
 FLAG_FOLD_ZERO_POINT = 1
 FLAG_NO_SPLIT_K = 2
 FLAG_NARROW_CTA = 4
-FLAG_PDL = 8
+FLAG_NO_PDL = 8
 
 # Every symbol include/nanoserve_b200.h declares, with its ctypes signature.
 _vp, _i32, _f32, _i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong

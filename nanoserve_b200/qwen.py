@@ -21,7 +21,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from .ops import FLAG_PDL, Kernels
+from .ops import Kernels
 
 
 @dataclass
@@ -140,8 +140,7 @@ class Qwen2Runner:
         return torch.cat(parts, dim=1)
 
     def linear(self, x, wt):
-        # decode (one token) launches overlap their prologue with the previous kernel of the step
-        return self.k.w4_linear(x, wt[0], wt[1], self.cfg.group, flags=FLAG_PDL if x.shape[0] == 1 else 0)
+        return self.k.w4_linear(x, wt[0], wt[1], self.cfg.group)
 
     # ------------------------------------------------------------------ prompt (eager, GEMM path)
     @torch.no_grad()
@@ -186,7 +185,7 @@ class Qwen2Runner:
     # ------------------------------------------------------------------ one decode step (graph-capturable)
     def _fused(self, x, wt, prologue, r=None, wn=None, x_out=None):
         return self.k.w4_linear_fused(x, wt[0], wt[1], self.cfg.group, prologue=prologue, r=r, wn=wn,
-                                      eps=self.cfg.rms_eps, x_out=x_out, flags=FLAG_PDL)
+                                      eps=self.cfg.rms_eps, x_out=x_out)
 
     @torch.no_grad()
     def decode_step(self):

@@ -67,7 +67,7 @@ SMALL_SHAPES = [(64, 128, 128), (96, 256, 128), (100, 384, 128), (33, 1024, 128)
 
 
 @pytest.mark.parametrize("N,K,G", SMALL_SHAPES)
-@pytest.mark.parametrize("flags", [0, ops.FLAG_FOLD_ZERO_POINT, ops.FLAG_PDL])
+@pytest.mark.parametrize("flags", [0, ops.FLAG_FOLD_ZERO_POINT, ops.FLAG_NO_PDL])
 def test_small_shapes_all_m(kernels, N, K, G, flags):
     for M in range(1, 17):
         X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=11)
