@@ -94,6 +94,21 @@ def test_prefill_shapes_sampled(kernels, M, N, K):
     assert kernels.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 3584, 18944), (64, 256, 4096), (300, 520, 8192)])
+def test_split_k_shapes(kernels, M, N, K):
+    """Few output tiles and a long K: the kernel splits K over CTAs and sums fp32 partials in fixed order."""
+    G = 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=12)
+    a = run(kernels, X, Wq, S, G)
+    b = run(kernels, X, Wq, S, G)
+    assert np.array_equal(a, b), "two identical launches differ: the split-K reduction is not deterministic"
+    rows = np.unique(np.concatenate([[0, M - 1], np.random.default_rng(1).integers(0, M, 6)]))
+    ref = oracle.w4_linear_f32(X[rows], Wq, S, G, threads=oracle.max_threads())
+    check_bf16_output(a[rows], ref, 1e-2)
+    check_bf16_output(a[rows], rounded_weight_reference(X[rows], Wq, S, G), 3e-5)
+    assert kernels.device_status() == 0
+
+
 def test_x_doubling_is_exact(kernels):
     M, N, K, G = 256, 512, 1024, 128
     X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=4)
