@@ -66,9 +66,14 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
 /* ---- additions (no counterpart in the reference library) --------------------------------------- */
 
 /* Flags for b2_w4_linear. */
-#define B2_FLAG_FOLD_ZERO_POINT 1 /* GEMV: apply the -8 as one fp32 correction per 128-wide chunk */
+#define B2_FLAG_FOLD_ZERO_POINT 1 /* GEMV with B2_FLAG_FLOAT_X: apply the -8 as one fp32 correction per 128-wide chunk */
 #define B2_FLAG_NO_SPLIT_K 2      /* GEMV: never split K across CTAs (uses no scratch memory) */
 #define B2_FLAG_NARROW_CTA 4      /* GEMV: 8 consumer warps per CTA instead of 16 */
+#define B2_FLAG_FLOAT_X 256       /* GEMV, G % 128 == 0: keep X in floating point (fp16 operands of a floating-point mma).
+                                     By default X is carried as 16-bit block fixed point per (token, 128-wide chunk of K)
+                                     -- every element is off by at most 2^-16 of its chunk's largest magnitude -- and the
+                                     nibbles feed an 8-bit integer mma without conversion */
+#define B2_FLAG_WIDE_X 512        /* GEMV, G % 128 == 0: 24-bit instead of 16-bit block fixed point for X */
 #define B2_FLAG_NO_PDL 8          /* GEMV: plain launch.  By default the GEMV is launched with programmatic stream
                                      serialization: it may begin (weight prefetch only) while the previous kernel of
                                      the stream is still running, and touches X, Y and scratch only after that kernel

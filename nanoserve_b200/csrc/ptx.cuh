@@ -79,6 +79,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same wait for warps that are off the critical path (a producer running several stages ahead, a reducer):
+// they sleep NS nanoseconds between tries, so their polling does not take issue slots from the warps doing the math.
+template <int NS>
+__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      __nanosleep(NS);
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ bulk-async copies (TMA)
 // Untiled copy global -> shared; both addresses 16-byte aligned, size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
@@ -96,6 +116,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap,
       "l"(tmap), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// Asynchronous BYTES-byte copy (4, 8 or 16) global -> shared by the calling thread (src_bytes < BYTES: the rest is
+// zero-filled; 0 reads nothing).  Both addresses BYTES-aligned.
+template <int BYTES>
+__device__ __forceinline__ void cp_async(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
+  static_assert(BYTES == 4 || BYTES == 8 || BYTES == 16, "cp.async copies 4, 8 or 16 bytes");
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;" ::"r"(dst_smem), "l"(src), "n"(BYTES), "r"(src_bytes)
+               : "memory");
+}
+// The mbarrier receives one arrival once all earlier cp.async copies of the calling thread have landed; the
+// arrival is one of those the barrier was initialised to expect (.noinc).
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

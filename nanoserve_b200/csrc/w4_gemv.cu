@@ -39,6 +39,7 @@
 //     result is deterministic).
 #include <algorithm>
 #include <cstdio>
+#include <type_traits>
 #include <cuda_fp16.h>
 
 #include "ptx.cuh"
@@ -55,12 +56,17 @@ constexpr int kChunkK = 128;           // K elements per consumer-warp work item
 constexpr int kRedPitch = 36;          // floats per (warp, token) row of the reduction buffer: 32 + 4 pad
 constexpr int kMaxStages = 8;
 constexpr int kSmemLimit = 232448;     // 227 KB opt-in maximum per CTA on sm_100
-constexpr int kHeaderBytes = 2048;     // flags + barriers (256 B), 256 B of zeros, RMSNorm partial sums and factors
-constexpr int kNormSsOffset = 512;     // float [16 tokens][16 warps]
-constexpr int kNormInvOffset = 1536;   // float [16 tokens]
+constexpr int kHeaderBytes = 2048;     // flags + barriers (256 B), 512 B of zeros, RMSNorm partial sums and factors
+constexpr int kZeroOffset = 256;       // 512 bytes of zeros: the staged X and info of padding tokens
+constexpr int kNormSsOffset = 768;     // float [16 tokens][16 warps]
+constexpr int kNormInvOffset = 1792;   // float [16 tokens]
 constexpr int kBoxBytes = kRowsPerGroup * 128;  // 32 rows x 128 B (two chunks), swizzled
 
-enum : int { kModeGeneric = 0, kModeExact = 1, kModeFold = 2 };
+enum : int { kModeGeneric = 0, kModeExact = 1, kModeFold = 2, kModeI8x2 = 3, kModeI8x3 = 4 };
+// bytes of one staged (token, 128-chunk) of X and of its info record
+__host__ __device__ constexpr int mode_limbs(int mode) { return mode == kModeI8x2 ? 2 : (mode == kModeI8x3 ? 3 : 0); }
+__host__ __device__ constexpr int x_chunk_bytes(int mode) { return mode_limbs(mode) ? 128 * mode_limbs(mode) : 256; }
+__host__ __device__ constexpr int x_info_bytes(int mode) { return mode_limbs(mode) ? 16 : 8; }
 // What the kernel does to its input before the product (the operators that precede a linear in a decoder layer)
 enum : int { kProNone = 0, kProAddRmsNorm = 1, kProSwiglu = 2 };
 
@@ -78,6 +84,8 @@ struct GemvParams {
   int ntiles;       // nrg * nslices
   int nstages;
   int xs_m_stride;  // bytes between tokens of the staged X
+  int sc_async;     // 0, or the width in bytes (4, 8, 16) of the cp.async copies with which the producer warp
+                    // stages the scales of every ring stage in shared memory
   float* partial;   // [nslices][M][N]
   int* counters;    // [nrg]
   int* status;
@@ -129,6 +137,46 @@ __device__ __forceinline__ void mma_16816_f16_zero(float (&d)[4], uint32_t a0, u
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+// D[16x8] = A[16x32] * B[32x8] + C, 8-bit integer inputs, 32-bit accumulate.  A is unsigned (nibbles, or nibbles
+// times 16); B is unsigned (a low byte of X) or signed (its top byte).
+// d = A * B + {c0, c1, c0, c1}: the first product of a chain takes its initial value without register moves.
+__device__ __forceinline__ void imma_16832_init(bool b_signed, int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                uint32_t a3, uint32_t b0, uint32_t b1, int c0, int c1) {
+  if (b_signed)
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
+  else
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
+}
+__device__ __forceinline__ void imma_16832(bool b_signed, int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                           uint32_t a3, uint32_t b0, uint32_t b1) {
+  if (b_signed)  // a compile-time constant at every call site after unrolling
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Loads of activations, scales and norm weights go to L2 (ld.global.cg), never through the non-coherent path: a
+// kernel launched with programmatic stream serialization becomes resident while earlier kernels still run, so the
+// SM's L1 is not invalidated between the producer of the data and this load, and a cached line can be stale
+// (observed: wrong scales after a library GEMV that triggers its dependents early).
+template <typename T>
+__device__ __forceinline__ T ld_l2(const T* p) {
+  return __ldcg(p);
+}
+
 // ---- staging of X -------------------------------------------------------------------------------
 // Every 16-byte unit holds the 8 values x[b..b+8) of one token as four pairs {x[b+p], x[b+p+4]},
 // p = 0..3 -- the pairing the unpack produces.  Unit (j, t) of a chunk (k = 128 c + 32 t + 8 j) sits at
@@ -147,7 +195,7 @@ __device__ __forceinline__ void stage_x_bf16(const GemvParams& p, uint32_t xs_ba
     const int j = jt >> 2, t = jt & 3;
     const int k0 = (cb + ch) * kChunkK + 32 * t + 8 * j;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (k0 < p.K) v = __ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + k0));
+    if (k0 < p.K) v = ld_l2(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + k0));
     uint4 o;
     o.x = __byte_perm(v.x, v.z, 0x5410);  // {x0, x4}
     o.y = __byte_perm(v.x, v.z, 0x7632);  // {x1, x5}
@@ -177,22 +225,22 @@ __device__ __forceinline__ uint4 pack8_bf16(const float (&f)[8]) {
 // what the separate operator would have stored in bf16: RMSNorm of the (bf16-rounded) sum X + R times the norm
 // weight (semantics of ns_rmsnorm), or silu(gate) * up of a [M, 2K] gate|up row (semantics of ns_swiglu).
 __device__ __forceinline__ uint4 load_x_unit(const GemvParams& p, int m, int k0, const float* inv) {
-  if (p.pro == kProNone) return __ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + k0));
+  if (p.pro == kProNone) return ld_l2(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + k0));
   float a[8], b[8];
   if (p.pro == kProSwiglu) {
-    unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * 2 * p.K + k0)), a);
-    unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * 2 * p.K + p.K + k0)), b);
+    unpack8_bf16(ld_l2(reinterpret_cast<const uint4*>(p.X + (size_t)m * 2 * p.K + k0)), a);
+    unpack8_bf16(ld_l2(reinterpret_cast<const uint4*>(p.X + (size_t)m * 2 * p.K + p.K + k0)), b);
 #pragma unroll
     for (int e = 0; e < 8; ++e) a[e] = a[e] / (1.f + __expf(-a[e])) * b[e];
     return pack8_bf16(a);
   }
-  unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + k0)), a);
+  unpack8_bf16(ld_l2(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + k0)), a);
   if (p.R != nullptr) {
-    unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.R + (size_t)m * p.K + k0)), b);
+    unpack8_bf16(ld_l2(reinterpret_cast<const uint4*>(p.R + (size_t)m * p.K + k0)), b);
 #pragma unroll
     for (int e = 0; e < 8; ++e) a[e] = __bfloat162float(__float2bfloat16(a[e] + b[e]));
   }
-  unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.Wn + k0)), b);
+  unpack8_bf16(ld_l2(reinterpret_cast<const uint4*>(p.Wn + k0)), b);
   const float s = inv[m];
 #pragma unroll
   for (int e = 0; e < 8; ++e) a[e] = a[e] * s * b[e];
@@ -209,9 +257,9 @@ __device__ __forceinline__ void rmsnorm_factors(const GemvParams& p, float* ss, 
     float acc = 0.f;
     for (int u = ctid; u < units; u += CT) {
       float a[8], b[8];
-      unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + u * 8)), a);
+      unpack8_bf16(ld_l2(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.K + u * 8)), a);
       if (p.R != nullptr) {
-        unpack8_bf16(__ldg(reinterpret_cast<const uint4*>(p.R + (size_t)m * p.K + u * 8)), b);
+        unpack8_bf16(ld_l2(reinterpret_cast<const uint4*>(p.R + (size_t)m * p.K + u * 8)), b);
 #pragma unroll
         for (int e = 0; e < 8; ++e) a[e] = __bfloat162float(__float2bfloat16(a[e] + b[e]));
         if (blockIdx.x == 0 && p.Xout != nullptr)
@@ -301,33 +349,123 @@ __device__ __forceinline__ void stage_x_f16(const GemvParams& p, uint32_t xs_bas
   }
 }
 
+// 8-bit staging for the integer path (L = 2 or 3 bytes per value).  Per (token, chunk): e = biased exponent of the
+// largest |x| (clamped); every x is multiplied by 2^(8L - 2 - (e - 127)) -- the largest magnitude lands in
+// [2^(8L-2), 2^(8L-1)) -- and rounded to an integer v of 8L bits (exact for every x within 2^(8L-9) of the largest:
+// bf16 has 8 significant bits).  Byte l of v's two's complement is "limb" l: the low limbs are unsigned, the top one
+// is signed, v = sum of 256^l limb_l.  A work item is 16 consecutive k of one token (two packed weight words of a
+// lane); it stores, per limb, one 16-byte unit { even k of word 0, even k of word 1, odd k of word 0, odd k of
+// word 1 }, four bytes each: the B fragments of one even-nibble and one odd-nibble mma.  Unit (jj, t)
+// (k = 128 c + 32 t + 16 jj) of limb l sits at byte l * 128 + (jj * 4 + t) * 16 of the chunk's 128 L bytes.
+// xinfo[token][chunk] = { bits of 2^(e - 127 - (8L - 2)) / 16, -128 * sum_k limb_l(v_k) for l = 0, 1, 2 }: the
+// zero-point 8, times the 16 that the nibble products carry, as the initial value of an accumulator.  A chunk that
+// holds an inf or a nan gets a nan factor (its integers are meaningless), so the outputs become nan.
+template <int CT, int L>
+__device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base, int4* xinfo, const float* inv,
+                                           int cb, int ce, int ctid) {
+  constexpr int B = 8 * L;
+  const int nch = ce - cb;
+  const int items = p.M * nch * 8;
+  const int items_pad = (items + 31) & ~31;
+  for (int it = ctid; it < items_pad; it += CT) {
+    const bool valid = it < items;
+    int m = 0, ch = 0, u = 0;
+    uint4 va = make_uint4(0u, 0u, 0u, 0u), vb = va;
+    if (valid) {
+      m = it / (nch * 8);
+      const int r = it - m * nch * 8;
+      ch = r >> 3;
+      u = r & 7;
+      const int k0 = (cb + ch) * kChunkK + 32 * (u & 3) + 16 * (u >> 2);
+      if (k0 < p.K) {
+        va = load_x_unit(p, m, k0, inv);
+        vb = load_x_unit(p, m, k0 + 8, inv);
+      }
+    }
+    const uint32_t w[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+    uint32_t mx = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    uint32_t eb = mx >> 7;
+    const bool bad = eb == 255u;
+    eb = min(254u, max(40u, eb));
+    const float down = __uint_as_float((uint32_t)(B + 252 - (int)eb) << 23);
+    const uint32_t up_bits = bad ? 0x7FC00000u : (uint32_t)((int)eb - B - 2) << 23;
+    int v[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[2 * i] = __float2int_rn(__uint_as_float(w[i] << 16) * down);
+      v[2 * i + 1] = __float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * down);
+    }
+    int csum[3] = {0, 0, 0};
+#pragma unroll
+    for (int l = 0; l < L; ++l) {
+      const uint32_t sel = (uint32_t)l | ((uint32_t)(4 + l) << 4);
+      auto pack = [&](int a, int b, int c, int d) {
+        return __byte_perm(__byte_perm((uint32_t)v[a], (uint32_t)v[b], sel),
+                           __byte_perm((uint32_t)v[c], (uint32_t)v[d], sel), 0x5410);
+      };
+      const uint4 o = make_uint4(pack(0, 2, 4, 6), pack(8, 10, 12, 14), pack(1, 3, 5, 7), pack(9, 11, 13, 15));
+      int c;
+      if (l == L - 1) {
+        c = __dp4a((int)o.x, 0x01010101, 0);
+        c = __dp4a((int)o.y, 0x01010101, c);
+        c = __dp4a((int)o.z, 0x01010101, c);
+        c = __dp4a((int)o.w, 0x01010101, c);
+      } else {
+        uint32_t cu = __dp4a(o.x, 0x01010101u, 0u);
+        cu = __dp4a(o.y, 0x01010101u, cu);
+        cu = __dp4a(o.z, 0x01010101u, cu);
+        cu = __dp4a(o.w, 0x01010101u, cu);
+        c = (int)cu;
+      }
+      c += __shfl_xor_sync(0xffffffffu, c, 4);
+      c += __shfl_xor_sync(0xffffffffu, c, 2);
+      c += __shfl_xor_sync(0xffffffffu, c, 1);
+      csum[l] = -128 * c;
+      if (valid) sts128(xs_base + m * p.xs_m_stride + ch * (128 * L) + l * 128 + u * 16, o);
+    }
+    if (valid && u == 0) xinfo[m * nch + ch] = make_int4((int)up_bits, csum[0], csum[1], csum[2]);
+  }
+}
+
 // MT: token tiles of 8 (1 or 2).  NCW: consumer warps (= chunks per stage, even).  MODE: see kMode*.
 template <int MT, int NCW, int MODE>
 __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1)
     w4_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemvParams p) {
   constexpr int kStageBytes = (NCW / 2) * kBoxBytes;
   constexpr int kConsumerThreads = NCW * 32;
-  constexpr bool kHalf = MODE != kModeGeneric;
+  constexpr bool kHalf = MODE != kModeGeneric;  // a chunk lies in one group: its sum is scaled once, in fp32
+  constexpr int L = mode_limbs(MODE);           // bytes per staged value of X on the integer path, else 0
+  constexpr bool kI8 = L > 0;
+  constexpr int kXChunk = x_chunk_bytes(MODE);
   extern __shared__ __align__(1024) unsigned char smem[];
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
   const uint32_t bar_full = smem_u32(smem + 64);
   const uint32_t bar_empty = bar_full + 8 * kMaxStages;
   const uint32_t bar_red_full = bar_empty + 8 * kMaxStages;  // [2] partial sums of a tile are in shared memory
   const uint32_t bar_red_empty = bar_red_full + 16;           // [2] the reducer has consumed them
-  const uint32_t zero_base = smem_u32(smem + 256);
+  const uint32_t zero_base = smem_u32(smem + kZeroOffset);
   float* red = reinterpret_cast<float*>(smem + kHeaderBytes);
   float2* xinfo = reinterpret_cast<float2*>(smem + kHeaderBytes + red_bytes(NCW, p.M));
-  const int xinfo_bytes = (p.M * p.cps * 8 + 127) & ~127;
+  const int xinfo_bytes = (p.M * p.cps * x_info_bytes(MODE) + 127) & ~127;
   const uint32_t xs_base = smem_u32(smem + kHeaderBytes + red_bytes(NCW, p.M) + xinfo_bytes);
   const int xs_bytes = (p.M * p.xs_m_stride + 127) & ~127;
+  // scales of each ring stage: [32 rows][NCW chunks] bf16, filled by the producer warp with cp.async
+  constexpr int kScStage = kHalf ? kRowsPerGroup * NCW * 2 : 0;
   const uint32_t ring_base = (xs_base + xs_bytes + 1023) & ~1023u;  // swizzled boxes: 1024-byte aligned
+  const uint32_t sc_base = ring_base + p.nstages * kStageBytes;
+  const bool sc_async = kHalf && p.sc_async;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
     *abort_flag = 0;
     for (int s = 0; s < p.nstages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, sc_async ? 33 : 1);  // the TMA issuer, and each lane's scale copies
       mbar_init(bar_empty + 8 * s, NCW);
     }
     for (int b = 0; b < 2; ++b) {
@@ -341,26 +479,51 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 
   if (warp == NCW) {
     // ------------------------------------------------------------ producer warp
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_w);
-      int s = 0;
-      uint32_t ph = 0;
-      for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
-        const int sl = tile / p.nrg, rg = tile - sl * p.nrg;
-        const int cb = sl * p.cps, ce = min(p.nchunks, cb + p.cps);
-        const int row0 = rg * kRowsPerGroup;
-        for (int c0 = cb; c0 < ce; c0 += NCW) {
-          const int nbox = (min(NCW, ce - c0) + 1) >> 1;
-          mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag);
+    // Lane 0 issues the TMA boxes of a stage; every lane copies the scales of one row of the stage (cp.async, two
+    // bf16 per copy), so the consumers never wait on a global load.
+    if (lane == 0) tma_prefetch_desc(&tmap_w);
+    int s = 0;
+    uint32_t ph = 0;
+    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+      const int sl = tile / p.nrg, rg = tile - sl * p.nrg;
+      const int cb = sl * p.cps, ce = min(p.nchunks, cb + p.cps);
+      const int row0 = rg * kRowsPerGroup;
+      const bool s_ok = row0 + lane < p.N;
+      const __nv_bfloat16* s_lane = p.S + (size_t)(s_ok ? row0 + lane : 0) * p.KG;
+      for (int c0 = cb; c0 < ce; c0 += NCW) {
+        const int nbox = (min(NCW, ce - c0) + 1) >> 1;
+        if (lane == 0) mbar_wait_backoff<100>(bar_empty + 8 * s, ph ^ 1, abort_flag);
+        __syncwarp();
+        if (lane == 0) {
           // out-of-range rows and K columns are zero-filled and still counted in the transaction bytes
           mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)(nbox * kBoxBytes));
           for (int b = 0; b < nbox; ++b)
             tma_load_2d(ring_base + s * kStageBytes + b * kBoxBytes, &tmap_w, (c0 + 2 * b) * 16, row0,
                         bar_full + 8 * s);
-          if (++s == p.nstages) {
-            s = 0;
-            ph ^= 1;
+        }
+        if (sc_async) {
+          const uint32_t dst = sc_base + s * kScStage + lane * (NCW * 2);
+          auto copy_row = [&](auto width) {  // the lane's NCW scales of this stage in copies of `width` bytes
+            constexpr int W = decltype(width)::value;
+#pragma unroll
+            for (int i = 0; i < NCW * 2 / W; ++i) {
+              const int c = c0 + i * (W / 2);
+              const int left = s_ok ? (ce - c) * 2 : 0;  // valid source bytes from this chunk on
+              cp_async<W>(dst + W * i, s_lane + (left > 0 ? c : cb), (uint32_t)min(W, max(0, left)));
+            }
+          };
+          if (p.sc_async == 16) {
+            if constexpr (NCW % 8 == 0) copy_row(std::integral_constant<int, 16>{});
+          } else if (p.sc_async == 8) {
+            if constexpr (NCW % 4 == 0) copy_row(std::integral_constant<int, 8>{});
+          } else {
+            copy_row(std::integral_constant<int, 4>{});
           }
+          cp_async_mbar_arrive_noinc(bar_full + 8 * s);
+        }
+        if (++s == p.nstages) {
+          s = 0;
+          ph ^= 1;
         }
       }
     }
@@ -376,7 +539,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       const int row0 = rg * kRowsPerGroup;
       const int b = tcount & 1;
       const float* rbuf = red + b * (NCW * p.M * kRedPitch);
-      if (lane == 0) mbar_wait(bar_red_full + 8 * b, (tcount >> 1) & 1, abort_flag);
+      if (lane == 0) mbar_wait_backoff<100>(bar_red_full + 8 * b, (tcount >> 1) & 1, abort_flag);
       __syncwarp();
       const int n = row0 + lane;
       for (int tok = 0; tok < p.M; ++tok) {
@@ -430,6 +593,11 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
     uint32_t k_n72 = 0xD480D480u;    // fp16 -72 twice
     uint32_t k_r16 = 0x2C002C00u;    // fp16 1/16 twice
     asm volatile("" : "+r"(k_mask_lo), "+r"(k_mask_hi), "+r"(k_magic), "+r"(k_n1032), "+r"(k_n72), "+r"(k_r16));
+    uint32_t k_nib_lo = 0x0F0F0F0Fu, k_nib_hi = 0xF0F0F0F0u;  // integer path: even / odd nibbles of a word as bytes
+    asm volatile("" : "+r"(k_nib_lo), "+r"(k_nib_hi));
+    const bool multi_token = p.M > 1;
+    // this lane's scales of a stage: rows gr (+8, +16, +24) of the stage's [32][NCW] block, column = its chunk
+    const uint32_t sc_lane = sc_base + gr * (NCW * 2) + warp * 2;
     const int nstages = p.nstages, gdiv = p.gdiv;
     // Launched with programmatic stream serialization this kernel may start while the previous one is still
     // running: the weight stream (constant data) is already flowing; X, produced upstream, is touched only
@@ -450,25 +618,31 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           float* inv = reinterpret_cast<float*>(smem + kNormInvOffset);
           if (p.pro == kProAddRmsNorm && staged_slice < 0)
             rmsnorm_factors<kConsumerThreads>(p, reinterpret_cast<float*>(smem + kNormSsOffset), inv, ctid);
-          stage_x_f16<kConsumerThreads, MODE == kModeFold>(p, xs_base, xinfo, inv, cb, ce, ctid);
+          if constexpr (kI8)
+            stage_x_i8<kConsumerThreads, L>(p, xs_base, reinterpret_cast<int4*>(xinfo), inv, cb, ce, ctid);
+          else
+            stage_x_f16<kConsumerThreads, MODE == kModeFold>(p, xs_base, xinfo, inv, cb, ce, ctid);
         }
         if constexpr (!kHalf) stage_x_bf16<kConsumerThreads>(p, xs_base, cb, ce, ctid);
-        if (ctid < 16) sts128(zero_base + ctid * 16, make_uint4(0u, 0u, 0u, 0u));
+        if (ctid < 32) sts128(zero_base + ctid * 16, make_uint4(0u, 0u, 0u, 0u));
         consumer_sync(kConsumerThreads);
         staged_slice = sl;
       }
       // B-fragment source of this lane: its token's staged X, or a block of zeros for padding tokens
       uint32_t xaddr[MT], xstep[MT];
+      bool xreal[MT];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const int m = mt * 8 + g;
         const bool real = m < p.M;
-        xaddr[mt] = real ? xs_base + m * p.xs_m_stride + warp * 256 + t * 16 : zero_base + t * 16;
-        xstep[mt] = real ? NCW * 256 : 0;
+        xreal[mt] = real;
+        xaddr[mt] = real ? xs_base + m * p.xs_m_stride + warp * kXChunk + t * 16 : zero_base + t * 16;
+        xstep[mt] = real ? NCW * kXChunk : 0;
       }
       // per-(token, chunk) info of the two accumulator columns (tokens mt*8 + 2t, +1) of this lane;
       // padding tokens read a zero pair (their accumulators are zero anyway)
       const float2* xi[MT][2];
+      const int4* xi8[MT][2];
       int xi_step[MT][2];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
@@ -476,7 +650,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         for (int q = 0; q < 2; ++q) {
           const int m = mt * 8 + 2 * t + q;
           const bool real = m < p.M;
-          xi[mt][q] = real ? xinfo + m * nch + warp : reinterpret_cast<const float2*>(smem + 256);
+          xi[mt][q] = real ? xinfo + m * nch + warp : reinterpret_cast<const float2*>(smem + kZeroOffset);
+          xi8[mt][q] = real ? reinterpret_cast<const int4*>(xinfo) + m * nch + warp
+                            : reinterpret_cast<const int4*>(smem + kZeroOffset);
           xi_step[mt][q] = real ? NCW : 0;
         }
       // fast path: lane i fetches the scale of row row0 + i; the quad layout is rebuilt with shuffles
@@ -495,7 +671,8 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       uint32_t srow_next = 0u;
       if constexpr (kHalf) {
         const int cf = cb + warp;
-        if (s_valid && cf < ce) srow_next = __bfloat16_as_ushort(__ldg(s_lane + (gdiv == 1 ? cf : cf / gdiv)));
+        if (!sc_async && s_valid && cf < ce)
+          srow_next = ld_l2(reinterpret_cast<const unsigned short*>(s_lane) + (gdiv == 1 ? cf : cf / gdiv));
       }
       for (int c = cb + warp, c0 = cb; c0 < ce; c0 += NCW, c += NCW) {
         const bool active = c < ce;
@@ -507,7 +684,8 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         if constexpr (kHalf) {
           const int cn = c + NCW;
           srow_next = 0u;
-          if (s_valid && cn < ce) srow_next = __bfloat16_as_ushort(__ldg(s_lane + (gdiv == 1 ? cn : cn / gdiv)));
+          if (!sc_async && s_valid && cn < ce)
+            srow_next = ld_l2(reinterpret_cast<const unsigned short*>(s_lane) + (gdiv == 1 ? cn : cn / gdiv));
         }
         if (active) {
           if constexpr (!kHalf) {
@@ -519,7 +697,8 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
               for (int hh = 0; hh < 2; ++hh) {
                 const int n = row0 + rb * 16 + gr + 8 * hh;
                 __nv_bfloat16 sv = __float2bfloat16(0.f);
-                if (n < p.N && grp >= 0) sv = __ldg(p.S + (size_t)n * p.KG + grp);
+                if (n < p.N && grp >= 0)
+                  sv = __ushort_as_bfloat16(ld_l2(reinterpret_cast<const unsigned short*>(p.S) + (size_t)n * p.KG + grp));
                 sc2[rb][hh] = bf16_dup(sv);
               }
           }
@@ -529,6 +708,97 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         __syncwarp();
 
         if (active) {
+          if constexpr (kI8) {
+          // ---- integer path: nibbles stay integers.  (w & 0x0F0F0F0F) holds the four even-k nibbles of a word as
+          // bytes, (w & 0xF0F0F0F0) the four odd-k nibbles times 16: both are ready-made u8 A fragments of
+          // mma.m16n8k32, so the unpack is two LOP3 per eight weights and no shift.  X arrives as L byte planes
+          // ("limbs"); every plane gets its own s32 accumulators, even and odd nibbles apart (the odd ones carry the
+          // factor 16), all combined once per chunk: T = sum_l 256^l (16 even_l + odd_l) = 16 sum_k (q_k - 8) v_k.
+          uint32_t xb[MT][L][8];
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int l = 0; l < L; ++l)
+#pragma unroll
+              for (int jj = 0; jj < 2; ++jj) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);  // padding tokens: no load at all (fewer wavefronts)
+                if (xreal[mt]) v = lds128(xaddr[mt] + l * 128 + jj * 64);
+                xb[mt][l][4 * jj + 0] = v.x;
+                xb[mt][l][4 * jj + 1] = v.y;
+                xb[mt][l][4 * jj + 2] = v.z;
+                xb[mt][l][4 * jj + 3] = v.w;
+              }
+          const uint32_t wa = w_lane_addr + s * kStageBytes;
+          uint4 wv[2][2];
+#pragma unroll
+          for (int rb = 0; rb < 2; ++rb) {
+            wv[rb][0] = lds128(wa + rb * 2048);
+            wv[rb][1] = lds128(wa + rb * 2048 + 1024);
+          }
+          int4 info[MT][2];
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            info[mt][0] = *xi8[mt][0];
+            info[mt][1] = *xi8[mt][1];
+          }
+          uint32_t scr[4] = {0u, 0u, 0u, 0u};  // scales of rows gr, gr + 8, gr + 16, gr + 24 of the stage
+          if (sc_async) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) scr[i] = lds_u16(sc_lane + s * kScStage + i * (8 * NCW * 2));
+          }
+#pragma unroll
+          for (int rb = 0; rb < 2; ++rb) {
+            const uint32_t wl[4] = {wv[rb][0].x, wv[rb][0].y, wv[rb][0].z, wv[rb][0].w};
+            const uint32_t wh[4] = {wv[rb][1].x, wv[rb][1].y, wv[rb][1].z, wv[rb][1].w};
+            int ae[MT][L][4], ao[MT][L][4];
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+              const uint32_t e0 = wl[2 * jj] & k_nib_lo, e1 = wh[2 * jj] & k_nib_lo;
+              const uint32_t e2 = wl[2 * jj + 1] & k_nib_lo, e3 = wh[2 * jj + 1] & k_nib_lo;
+              const uint32_t o0 = wl[2 * jj] & k_nib_hi, o1 = wh[2 * jj] & k_nib_hi;
+              const uint32_t o2 = wl[2 * jj + 1] & k_nib_hi, o3 = wh[2 * jj + 1] & k_nib_hi;
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int l = 0; l < L; ++l) {
+                  if (jj == 0) {
+                    // the odd chain starts from the zero-point term of its limb, the even chain from zero
+                    const int c0 = l == 0 ? info[mt][0].y : (l == 1 ? info[mt][0].z : info[mt][0].w);
+                    const int c1 = l == 0 ? info[mt][1].y : (l == 1 ? info[mt][1].z : info[mt][1].w);
+                    imma_16832_init(l == L - 1, ae[mt][l], e0, e1, e2, e3, xb[mt][l][0], xb[mt][l][1], 0, 0);
+                    imma_16832_init(l == L - 1, ao[mt][l], o0, o1, o2, o3, xb[mt][l][2], xb[mt][l][3], c0, c1);
+                  } else {
+                    imma_16832(l == L - 1, ae[mt][l], e0, e1, e2, e3, xb[mt][l][4 * jj], xb[mt][l][4 * jj + 1]);
+                    imma_16832(l == L - 1, ao[mt][l], o0, o1, o2, o3, xb[mt][l][4 * jj + 2], xb[mt][l][4 * jj + 3]);
+                  }
+                }
+            }
+            float s_lo, s_hi;
+            if (sc_async) {
+              s_lo = __uint_as_float(scr[2 * rb] << 16);
+              s_hi = __uint_as_float(scr[2 * rb + 1] << 16);
+            } else {
+              s_lo = __uint_as_float(__shfl_sync(0xffffffffu, srow, rb * 16 + gr) << 16);
+              s_hi = __uint_as_float(__shfl_sync(0xffffffffu, srow, rb * 16 + gr + 8) << 16);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const float up0 = __int_as_float(info[mt][0].x), up1 = __int_as_float(info[mt][1].x);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                if ((i & 1) && !multi_token) continue;  // one token: accumulator columns 1.. are padding
+                float f;
+                if constexpr (L == 2) {
+                  f = (float)((16 * ae[mt][1][i] + ao[mt][1][i]) * 256 + (16 * ae[mt][0][i] + ao[mt][0][i]));
+                } else {
+                  const int th = (16 * ae[mt][2][i] + ao[mt][2][i]) * 256 + (16 * ae[mt][1][i] + ao[mt][1][i]);
+                  f = fmaf((float)th, 256.f, (float)(16 * ae[mt][0][i] + ao[mt][0][i]));
+                }
+                fin[rb][mt][i] = fmaf((i < 2 ? s_lo : s_hi) * ((i & 1) ? up1 : up0), f, fin[rb][mt][i]);
+              }
+            }
+          }
+          } else {
           // all shared-memory loads of the stage first, then the math: the loads are ordered after the
           // barrier wait, the math is free to be scheduled around them
           uint32_t xf[MT][16];
@@ -557,6 +827,11 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
               info[mt][0] = *xi[mt][0];
               info[mt][1] = *xi[mt][1];
             }
+          }
+          uint32_t scr[4] = {0u, 0u, 0u, 0u};
+          if (sc_async) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) scr[i] = lds_u16(sc_lane + s * kScStage + i * (8 * NCW * 2));
           }
 #pragma unroll
           for (int rb = 0; rb < 2; ++rb) {
@@ -598,8 +873,14 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
                   }
               }
               // scale of rows gr and gr + 8 of this block, from the lanes that fetched them
-              const float s_lo = __uint_as_float(__shfl_sync(0xffffffffu, srow, rb * 16 + gr) << 16);
-              const float s_hi = __uint_as_float(__shfl_sync(0xffffffffu, srow, rb * 16 + gr + 8) << 16);
+              float s_lo, s_hi;
+              if (sc_async) {
+                s_lo = __uint_as_float(scr[2 * rb] << 16);
+                s_hi = __uint_as_float(scr[2 * rb + 1] << 16);
+              } else {
+                s_lo = __uint_as_float(__shfl_sync(0xffffffffu, srow, rb * 16 + gr) << 16);
+                s_hi = __uint_as_float(__shfl_sync(0xffffffffu, srow, rb * 16 + gr + 8) << 16);
+              }
 #pragma unroll
               for (int mt = 0; mt < MT; ++mt) {
                 float v0 = acc[mt][0][0] + acc[mt][1][0], v1 = acc[mt][0][1] + acc[mt][1][1];
@@ -635,6 +916,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
               }
             }
           }
+          }  // !kI8
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + 8 * s);
@@ -643,6 +925,8 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           xaddr[mt] += xstep[mt];
           xi[mt][0] += xi_step[mt][0];
           xi[mt][1] += xi_step[mt][1];
+          xi8[mt][0] += xi_step[mt][0];
+          xi8[mt][1] += xi_step[mt][1];
         }
         if (++s == nstages) {
           s = 0;
@@ -693,10 +977,9 @@ struct GemvPlan {
   double cost;
 };
 
-size_t smem_without_ring(int M, int mt, int ncw, int cps) {
-  (void)mt;
-  const int xs_m_stride = cps * 256 + 64;
-  const size_t xinfo_bytes = ((size_t)M * cps * 8 + 127) & ~(size_t)127;
+size_t smem_without_ring(int M, int mode, int ncw, int cps) {
+  const int xs_m_stride = cps * x_chunk_bytes(mode) + 64;
+  const size_t xinfo_bytes = ((size_t)M * cps * x_info_bytes(mode) + 127) & ~(size_t)127;
   const size_t xs_bytes = ((size_t)M * xs_m_stride + 127) & ~(size_t)127;
   return kHeaderBytes + red_bytes(ncw, M) + xinfo_bytes + xs_bytes + 1024;
 }
@@ -705,14 +988,16 @@ size_t smem_without_ring(int M, int mt, int ncw, int cps) {
 // tile costs its chunk count rounded up to whole stages (idle warps in a short last stage are lost
 // time), plus a fixed reduction overhead; split-K tiles pay the scratch round trip as well.  The slice
 // count with the smallest makespan over the persistent CTAs wins.
-bool plan_for_width(int M, int N, int K, int ncw, int mt, int flags, int sm_count, size_t partial_cap,
+bool plan_for_width(int M, int N, int K, int ncw, int mt, int mode, int flags, int sm_count, size_t partial_cap,
                     int counters_cap, GemvPlan* out) {
   GemvPlan pl{};
   pl.mt = mt;
+  pl.mode = mode;
   pl.ncw = ncw;
   const int nchunks = (K + kChunkK - 1) / kChunkK;
   const int nrg = (N + kRowsPerGroup - 1) / kRowsPerGroup;
-  const int stage_bytes = (ncw / 2) * kBoxBytes;
+  // a ring stage: the weight boxes plus (fast paths) the stage's scales, [32 rows][ncw] bf16
+  const int stage_bytes = (ncw / 2) * kBoxBytes + (mode == kModeGeneric ? 0 : kRowsPerGroup * ncw * 2);
   const int grid = std::max(1, sm_count);
   // Two CTAs per SM when both fit (shared memory: half of 227 KB minus the per-CTA reserve; registers: the narrow
   // MT == 1 kernels are compiled for it): more warps to hide latency, and one CTA's tail overlaps the other's
@@ -728,7 +1013,7 @@ bool plan_for_width(int M, int N, int K, int ncw, int mt, int flags, int sm_coun
       if ((size_t)ns * M * N * sizeof(float) > partial_cap) continue;
       if (nrg > counters_cap) continue;
     }
-    const size_t fixed = smem_without_ring(M, mt, ncw, cps);
+    const size_t fixed = smem_without_ring(M, mode, ncw, cps);
     const long tiles = (long)nrg * ns;
     const int stage_chunks = ((cps + ncw - 1) / ncw) * ncw;
     // the memory system moves only real bytes, the warps pay for padded stages: weigh them equally
@@ -755,9 +1040,9 @@ bool plan_for_width(int M, int N, int K, int ncw, int mt, int flags, int sm_coun
   if (best_ns == 0) return false;
   pl.nslices = best_ns;
   pl.cps = best_cps;
-  pl.xs_m_stride = pl.cps * 256 + 64;
+  pl.xs_m_stride = pl.cps * x_chunk_bytes(mode) + 64;
   pl.cost = best;
-  const size_t fixed = smem_without_ring(M, mt, ncw, pl.cps);
+  const size_t fixed = smem_without_ring(M, mode, ncw, pl.cps);
   const long tiles = (long)nrg * pl.nslices;
   int stages;
   if (best_ctas == 2) {
@@ -778,7 +1063,15 @@ bool plan_for_width(int M, int N, int K, int ncw, int mt, int flags, int sm_coun
 bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap,
                GemvPlan* out) {
   const int mt = M > 8 ? 2 : 1;
-  const int mode = (G % 128) ? kModeGeneric : ((flags & kFlagFoldZeroPoint) ? kModeFold : kModeExact);
+  // G % 128 == 0: the integer path with two bytes per value of X, or three (kFlagWideX), or X in floating point on
+  // the fp16 mma (kFlagFloatX; with kFlagFoldZeroPoint its cheaper variant)
+  int mode = kModeGeneric;
+  if (G % 128 == 0) {
+    if (flags & kFlagFloatX)
+      mode = (flags & kFlagFoldZeroPoint) ? kModeFold : kModeExact;
+    else
+      mode = (flags & kFlagWideX) ? kModeI8x3 : kModeI8x2;
+  }
   GemvPlan best{};
   bool have = false;
   // One token tile: candidates are the wide CTAs (16 or 14 consumer warps, one per SM) and the narrow one
@@ -790,14 +1083,14 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
     for (int w : widths) {
       if (forced && w != forced) continue;
       GemvPlan pl;
-      if (plan_for_width(M, N, K, w, mt, flags, sm_count, partial_cap, counters_cap, &pl) &&
+      if (plan_for_width(M, N, K, w, mt, mode, flags, sm_count, partial_cap, counters_cap, &pl) &&
           (!have || pl.cost < best.cost)) {
         best = pl;
         have = true;
       }
     }
   }
-  if (!have) have = plan_for_width(M, N, K, 8, mt, flags, sm_count, partial_cap, counters_cap, &best);
+  if (!have) have = plan_for_width(M, N, K, 8, mt, mode, flags, sm_count, partial_cap, counters_cap, &best);
   if (!have) return false;
   best.mode = mode;
   best.pdl = (flags & kFlagNoPdl) == 0;
@@ -834,6 +1127,8 @@ int launch_mode(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan& pl
   switch (pl.mode) {
     case kModeExact: return launch_variant<MT, NCW, kModeExact>(tmap, p, pl, stream);
     case kModeFold: return launch_variant<MT, NCW, kModeFold>(tmap, p, pl, stream);
+    case kModeI8x2: return launch_variant<MT, NCW, kModeI8x2>(tmap, p, pl, stream);
+    case kModeI8x3: return launch_variant<MT, NCW, kModeI8x3>(tmap, p, pl, stream);
     default: return launch_variant<MT, NCW, kModeGeneric>(tmap, p, pl, stream);
   }
 }
@@ -896,6 +1191,18 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
   p.ntiles = p.nrg * p.nslices;
   p.nstages = pl.nstages;
   p.xs_m_stride = pl.xs_m_stride;
+  // two scales per 4-byte copy: needs one scale per chunk, even element offsets and a 4-byte aligned base
+  p.sc_async = 0;
+  if (pl.mode != kModeGeneric && p.gdiv == 1) {
+    // every copy starts at element n * KG + slice * cps + i * ncw + j * (width / 2) of S: the widest width that
+    // keeps all of them aligned
+    for (int w = 16; w >= 4 && !p.sc_async; w >>= 1) {
+      const int e = w / 2;
+      if ((reinterpret_cast<uintptr_t>(S) % w) == 0 && p.KG % e == 0 && pl.ncw % e == 0 &&
+          (pl.nslices == 1 || pl.cps % e == 0))
+        p.sc_async = w;
+    }
+  }
   p.partial = ws.partial;
   p.counters = ws.counters;
   p.status = ws.status;

@@ -20,6 +20,8 @@ FLAG_FOLD_ZERO_POINT = 1
 FLAG_NO_SPLIT_K = 2
 FLAG_NARROW_CTA = 4
 FLAG_NO_PDL = 8
+FLAG_FLOAT_X = 256
+FLAG_WIDE_X = 512
 
 # Every symbol include/nanoserve_b200.h declares, with its ctypes signature.
 _vp, _i32, _f32, _i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong

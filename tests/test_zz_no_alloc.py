@@ -44,7 +44,7 @@ def test_matches_existing_entry_point_twice_in_a_row(kernels, M, N, K):
         tol = torch.maximum(a.abs(), b.abs()) * 2.0**-7 + 1e-5 * a.abs().max()
         assert torch.all((a - b).abs() <= tol)
     assert torch.equal(first, second), "the second call saw state left by the first"
-    check_bf16_output(torch_to_bits(second), oracle.w4_linear_f32(X, Wq, S, G, threads=oracle.max_threads()), 3e-6)
+    check_bf16_output(torch_to_bits(second), oracle.w4_linear_f32(X, Wq, S, G, threads=oracle.max_threads()), 2e-5)
 
 
 def test_rejects_sizes_beyond_the_fixed_scratch(kernels):
