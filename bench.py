@@ -161,6 +161,76 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------- sweep over the other configurations
+def run_sweep(k, dev, stream, flags):
+    """Decode GEMV at M in {1,2,4,8,16} over every 7B-shaped linear and the 70B-class gate/up and down, and the
+    prefill GEMM at M in {512,2048,8192} (4096 for the 70B-class shape), on one GPU.  Weights are random nibbles with
+    the benchmark's scale distribution, generated on the device; enough distinct copies are used in rotation that every
+    launch streams from HBM.  Each entry: microseconds per launch (CUDA events around a replayed CUDA graph), GB/s of
+    algorithmic bytes or TFLOP/s, and the fraction of the measured peak."""
+    import torch
+    peaks, which = measured_peaks()
+    gen = torch.Generator(device=dev).manual_seed(7)
+
+    def rand_w4(N, K):
+        Wq = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, device=dev, generator=gen)
+        S = (0.005 + (torch.randn(N, K // G, device=dev, generator=gen) * 0.01).abs()).to(torch.bfloat16)
+        return Wq, S
+
+    def time_graph(fns, reps):
+        with torch.cuda.stream(stream):
+            for f in fns[:2]:
+                f()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for f in fns:
+                    f()
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(stream)
+            for _ in range(reps):
+                g.replay()
+            ev1.record(stream)
+            torch.cuda.synchronize()
+        return ev0.elapsed_time(ev1) * 1e-3 / (reps * len(fns))
+
+    out = {"peak_source": which, "hbm_gbs_peak": peaks["hbm_gbs"], "bf16_tflops_peak": peaks["bf16_tflops"],
+           "gemv": [], "gemm": []}
+    gemv_shapes = [("q/o", 3584, 3584), ("k/v", 512, 3584), ("gate/up", 18944, 3584), ("down", 3584, 18944),
+                   ("70b gate/up", 28672, 8192), ("70b down", 8192, 28672)]
+    for name, N, K in gemv_shapes:
+        copies = max(4, min(32, (512 << 20) // (N * K // 2) + 1))
+        ws = [rand_w4(N, K) for _ in range(copies)]
+        for M in (1, 2, 4, 8, 16):
+            x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+            y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            t = time_graph([(lambda w=w: k.w4_linear(x, w[0], w[1], G, flags=flags, out=y)) for w in ws], 10)
+            nb = synth.gemv_bytes(M, N, K, G)
+            out["gemv"].append({"shape": name, "N": N, "K": K, "M": M, "us": round(t * 1e6, 2),
+                                "gbs": round(nb / t / 1e9, 1), "frac": round(nb / t / 1e9 / peaks["hbm_gbs"], 3)})
+        del ws
+        torch.cuda.empty_cache()
+    gemm_shapes = [("gate/up", 18944, 3584, (512, 2048, 8192)), ("down", 3584, 18944, (512, 2048, 8192)),
+                   ("70b gate/up", 28672, 8192, (4096,))]
+    for name, N, K, Ms in gemm_shapes:
+        ws = [rand_w4(N, K) for _ in range(2)]
+        for M in Ms:
+            x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+            y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            t = time_graph([(lambda w=w: k.w4_linear(x, w[0], w[1], G, out=y)) for w in ws], 5)
+            fl = 2.0 * M * N * K
+            out["gemm"].append({"shape": name, "N": N, "K": K, "M": M, "us": round(t * 1e6, 1),
+                                "tflops": round(fl / t / 1e12, 1),
+                                "frac": round(fl / t / 1e12 / peaks["bf16_tflops"], 3)})
+            del x, y
+        del ws
+        torch.cuda.empty_cache()
+    return out
+
+
 # ---------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -172,6 +242,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Qwen2.5-7B-shaped greedy-decode tokens/s leg")
     ap.add_argument("--flags", type=int, default=0, help="library flags for every launch (see include/nanoserve_b200.h)")
+    ap.add_argument("--no-sweep", action="store_true",
+                    help="skip the single-GPU sweep over the other benchmark configurations (decode GEMV at M = 1..16 over "
+                         "every 7B-shaped and 70B-class linear, prefill GEMM at M = 512..8192)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -322,6 +395,12 @@ def main():
             with open(traffic_file) as f:
                 roof["traffic"] = json.load(f).get("dram_bytes_per_launch_m%d" % M)
 
+    # ---- the other benchmark configurations on one GPU: every decode shape at M = 1..16, the prefill GEMMs
+    sweep = None
+    if world == 1 and not args.no_sweep:
+        del big, y_big
+        sweep = run_sweep(k, dev, stream, args.flags)
+
     # ---- second half of the headline metric: W4 greedy decode tokens/s of a Qwen2.5-7B-shaped model (512-token prompt,
     # 256 new tokens, batch 1, tensor parallel over the ranks); free the GEMV benchmark's weights first
     decode = None
@@ -374,6 +453,8 @@ def main():
         }
         if roof is not None:
             line["roofline"] = roof
+        if sweep is not None:
+            line["sweep"] = sweep
         if decode is not None:
             line["decode"] = decode
         if world == 1 and not args.no_cpu_baseline:
