@@ -242,6 +242,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Qwen2.5-7B-shaped greedy-decode tokens/s leg")
     ap.add_argument("--flags", type=int, default=0, help="library flags for every launch (see include/nanoserve_b200.h)")
+    ap.add_argument("--tp-collective", action="store_true",
+                    help="N > 1: all-gather the outputs with NCCL at the layer boundaries instead of fusing the gather "
+                         "into the GEMVs (peer stores + arrival counters)")
     ap.add_argument("--no-sweep", action="store_true",
                     help="skip the single-GPU sweep over the other benchmark configurations (decode GEMV at M = 1..16 over "
                          "every 7B-shaped and 70B-class linear, prefill GEMM at M = 512..8192)")
@@ -254,7 +257,7 @@ def main():
     import torch.distributed as dist
     from nanoserve_b200 import build as b2build
     from nanoserve_b200.ops import Kernels
-    from nanoserve_b200.tp import ShardedLayer
+    from nanoserve_b200.tp import PeerBuffers, ShardedLayer
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
@@ -283,6 +286,11 @@ def main():
     layers = [ShardedLayer.synthetic(k, LAYER, ORDER, G, seed=1000 + c, rank=rank, world=world, device=dev,
                                      flags=args.flags)
               for c in range(N_COPIES)]
+    fused_gather = world > 1 and not args.tp_collective
+    if fused_gather:
+        peer = PeerBuffers({name: M * LAYER[name][0] for name in ORDER}, len(ShardedLayer.BOUNDARIES), dev)
+        for l in layers:
+            l.attach_peer_buffers(peer, M)
     x_h = torch.from_numpy(synth.synth_x(M, 3584, 1).view(np.int16)).view(torch.bfloat16).pin_memory()
     a_h = torch.from_numpy(synth.synth_x(M, 18944, 2).view(np.int16)).view(torch.bfloat16).pin_memory()
     x_d, a_d = x_h.to(dev), a_h.to(dev)
@@ -409,7 +417,7 @@ def main():
         torch.cuda.empty_cache()
         try:
             from nanoserve_b200.qwen import decode_rate
-            d = decode_rate(k, dev, rank=rank, world=world)
+            d = decode_rate(k, dev, rank=rank, world=world, fused_gather=not args.tp_collective)
             t = torch.tensor([d["ms_per_token"]], dtype=torch.float64, device=dev)
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -440,7 +448,9 @@ def main():
             "vs_baseline": None, "dtype": "int4 weights x bf16 activations, fp32 accumulate", "data": "synthetic",
             "config": {
                 "workload": f"decode GEMV pass over the 7 linears of a Qwen2.5-7B-shaped layer, M={M}, int4 g128",
-                "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                "parallelism": (f"tp{world}, all-gather " + ("fused into the GEMVs (peer stores + arrival counters)"
+                                                             if fused_gather else "by NCCL at the 4 layer boundaries"))
+                if world > 1 else "single GPU",
                 "l2": f"weights rotate through {N_COPIES} layer copies ({resident * world / 1e6:.0f} MB) > 126 MB L2",
                 "bytes_per_step": nbytes, "launch": "one CUDA graph per layer copy, replayed in rotation",
                 "seeds": "X 1/2, layer copy c: 1000+c", "flags": args.flags,
@@ -448,7 +458,7 @@ def main():
             "e2e": {"value": nbytes * args.steps / t_e2e_wall / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e_wall / args.steps * 1e3,
                     "path": "Kernels.w4_linear per linear (ctypes -> C ABI), pinned host X in, all outputs out"},
-            "gpu_launches": launches_per_step * args.steps,
+            "gpu_launches": (launches_per_step + (len(ShardedLayer.BOUNDARIES) if fused_gather else 0)) * args.steps,
             "clocks": clocks,
         }
         if roof is not None:

@@ -153,6 +153,48 @@ int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* po
 /* Bytes of caller-owned device scratch (`workspace`) the two calls above need (split partials; Hq / Hk <= 8). */
 size_t b2_decode_workspace_bytes(int Hq, int D);
 
+/*
+ * Tensor parallelism over the output rows of a linear, one process per GPU, with the all-gather of the outputs fused
+ * into the decode GEMV.  No counterpart in the reference library (it has no multi-GPU code).  Rank r holds rows
+ * [r N/P, (r+1) N/P) of Wq and S (a zero-copy slice of the reference layout); X is replicated.
+ *   Producer side (world > 0): the GEMV stores every output value straight into the gathered row [M, ld] (bf16) of
+ *     EVERY rank through peer-mapped device pointers y_peer[0..world) (the caller maps them: CUDA IPC, symmetric
+ *     memory; its own rank included), and each CTA, after its last store, adds one to the arrival counter sig_peer[r]
+ *     (uint32, peer-mapped) of every rank.  The local shard may be up to three row-concatenated pieces (q | k | v,
+ *     gate | up) ending at local columns seg_end[0], seg_end[1], N; piece i lands at gathered column seg_dst[i].
+ *   Consumer side (wait_sig != NULL): before it reads X the GEMV waits until this rank's counter wait_sig has reached
+ *     (*epoch + 1) * wait_per_epoch: wait_per_epoch = ranks x b2_w4_gemv_grid(...) of the producing call, *epoch (int32
+ *     on the device) = completed uses of the counter, e.g. the decode step.  Counters only grow; zero them (all ranks,
+ *     with a host barrier) whenever *epoch restarts.  The wait is bounded (about half a second); a time-out shows in
+ *     b2_device_status().
+ * A call may be producer, consumer or both; with world == 0 the output goes to y_local.  The other arguments are those
+ * of b2_w4_linear_fused.  b2_rope_kv_store_tp is b2_rope_kv_store with the same wait in front.
+ */
+typedef struct b2_tp_desc {
+  int world;
+  void* y_peer[8];
+  void* sig_peer[8];
+  long long ld;
+  int seg_end[2];
+  int seg_dst[3];
+  void* y_local;
+  const void* wait_sig;
+  const void* epoch;
+  unsigned wait_per_epoch;
+} b2_tp_desc;
+int b2_w4_linear_tp(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, int prologue,
+                    const void* R, const void* Wn, float eps, void* Xout, const b2_tp_desc* tp, int flags,
+                    void* stream);
+/* CTAs the decode GEMV launches for this shape on the current device (0: not served by the GEMV). */
+size_t b2_w4_gemv_grid(int M, int N, int K, int G, int flags);
+int b2_rope_kv_store_tp(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
+                        void* cache_v, int Hq, int Hk, int D, int max_len, const void* wait_sig, const void* epoch,
+                        unsigned wait_per_epoch, void* stream);
+
+/* The consumer-side wait of b2_w4_linear_tp as a one-thread kernel of its own, for consumers that are not a GEMV
+ * (a norm, a sampler): kernels after it on the stream see the gathered rows complete. */
+int b2_tp_wait(const void* wait_sig, const void* epoch, unsigned wait_per_epoch, void* stream);
+
 /* Library identification: "nanoserve-b200 <version> sm_100a". */
 const char* b2_version(void);
 

@@ -94,6 +94,64 @@ int b2_w4_linear_fused(const void* X, const void* Wq, const void* S, void* Y, in
                             static_cast<cudaStream_t>(stream));
 }
 
+int b2_w4_linear_tp(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, int prologue,
+                    const void* R, const void* Wn, float eps, void* Xout, const b2_tp_desc* tp, int flags,
+                    void* stream) {
+  if (M < 1 || M > 16) return b2::kErrUnsupportedM;
+  if (!tp) return b2::kErrBadPointer;
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return rc;
+  b2::GemvPrologue pro;
+  pro.kind = prologue;
+  pro.R = R;
+  pro.Wn = Wn;
+  pro.Xout = Xout;
+  pro.eps = eps;
+  b2::GemvTp t;
+  if (tp->world < 0 || tp->world > b2::kMaxTpRanks) return b2::kErrBadShape;
+  if (tp->world == 0 && !tp->wait_sig) return b2::kErrBadShape;  // nothing tensor-parallel about this call
+  t.world = tp->world;
+  for (int r = 0; r < tp->world; ++r) {
+    t.y_peer[r] = tp->y_peer[r];
+    t.sig_peer[r] = static_cast<unsigned*>(tp->sig_peer[r]);
+  }
+  t.ld = tp->ld;
+  t.seg_end[0] = tp->seg_end[0];
+  t.seg_end[1] = tp->seg_end[1];
+  for (int i = 0; i < 3; ++i) t.seg_dst[i] = tp->seg_dst[i];
+  t.wait_sig = static_cast<const unsigned*>(tp->wait_sig);
+  t.epoch = static_cast<const int*>(tp->epoch);
+  t.wait_per_epoch = tp->wait_per_epoch;
+  void* y = tp->world > 0 ? tp->y_peer[0] : tp->y_local;
+  return b2::gemv_launch_ex(X, Wq, S, y, M, N, K, G, pro, st->ws, flags, st->sm_count,
+                            static_cast<cudaStream_t>(stream), &t);
+}
+
+size_t b2_w4_gemv_grid(int M, int N, int K, int G, int flags) {
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return 0;
+  return b2::gemv_grid(M, N, K, G, flags, st->sm_count, st->ws.partial_bytes, st->ws.n_counters);
+}
+
+int b2_tp_wait(const void* wait_sig, const void* epoch, unsigned wait_per_epoch, void* stream) {
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return rc;
+  return b2::tp_wait_launch(wait_sig, epoch, wait_per_epoch, st->ws.status, static_cast<cudaStream_t>(stream));
+}
+
+int b2_rope_kv_store_tp(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
+                        void* cache_v, int Hq, int Hk, int D, int max_len, const void* wait_sig, const void* epoch,
+                        unsigned wait_per_epoch, void* stream) {
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return rc;
+  return b2::rope_kv_store_launch(qkv, bias, inv_freq, pos, cache_k, cache_v, Hq, Hk, D, max_len, wait_sig, epoch,
+                                  wait_per_epoch, st->ws.status, static_cast<cudaStream_t>(stream));
+}
+
 int ns_w4_quantize(const void* W, void* Wq, void* S, int N, int K, int G, void* stream) {
   return b2::quantize_launch(W, Wq, S, N, K, G, static_cast<cudaStream_t>(stream));
 }

@@ -19,14 +19,35 @@ namespace {
 using bf16 = __nv_bfloat16;
 
 // grid: Hq + 2*Hk blocks (one per head of the fused qkv row), block: D/2 threads.
-__global__ void rope_kv_store_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ bias,
+// With wait_sig set, qkv is the gathered output of a tensor-parallel GEMV (b2_w4_linear_tp): every block first waits
+// (bounded) until all producing CTAs of all ranks have counted themselves in, then reads qkv from L2.
+__global__ void rope_kv_store_kernel(bf16* qkv, const bf16* __restrict__ bias,
                                      const float* __restrict__ inv_freq, const int* __restrict__ pos_ptr,
                                      bf16* __restrict__ cache_k, bf16* __restrict__ cache_v, int Hq, int Hk, int D,
-                                     int max_len) {
+                                     int max_len, const unsigned* wait_sig, const int* epoch, unsigned wait_per_epoch,
+                                     int* status) {
   const int h = blockIdx.x, i = threadIdx.x, half = D / 2;
+  if (wait_sig != nullptr) {
+    if (i == 0) {
+      const unsigned target = ((unsigned)*reinterpret_cast<const volatile int*>(epoch) + 1u) * wait_per_epoch;
+      const long long t0 = clock64();
+      for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wait_sig) : "memory");
+        if ((int)(v - target) >= 0) break;
+        if (clock64() - t0 > 1000000000LL) {  // about half a second: report and go on with what is there
+          if (status != nullptr) atomicCAS(status, 0, b2::kStatusGemvTimeout);
+          break;
+        }
+        __nanosleep(40);
+      }
+    }
+    __syncthreads();
+  }
   const int pos = *pos_ptr;
   bf16* x = qkv + (size_t)h * D;
-  float a = __bfloat162float(x[i]), b = __bfloat162float(x[i + half]);
+  float a = __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(x) + i)));
+  float b = __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(x) + i + half)));
   if (bias != nullptr) {  // the projection output is stored in bf16, then the bias is added in bf16 (q += bq)
     a = __bfloat162float(__float2bfloat16(a + __bfloat162float(bias[(size_t)h * D + i])));
     b = __bfloat162float(__float2bfloat16(b + __bfloat162float(bias[(size_t)h * D + i + half])));
@@ -192,16 +213,50 @@ __global__ void __launch_bounds__(256) greedy_finish_kernel(const float* __restr
 
 }  // namespace
 
+// One thread waits (bounded) for an arrival counter of a fused all-gather: kernels that follow on the stream may then
+// read the gathered rows without a wait of their own.
+__global__ void tp_wait_kernel(const unsigned* wait_sig, const int* epoch, unsigned wait_per_epoch, int* status) {
+  const unsigned target = ((unsigned)*reinterpret_cast<const volatile int*>(epoch) + 1u) * wait_per_epoch;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wait_sig) : "memory");
+    if ((int)(v - target) >= 0) break;
+    if (clock64() - t0 > 1000000000LL) {
+      if (status != nullptr) atomicCAS(status, 0, b2::kStatusGemvTimeout);
+      break;
+    }
+    __nanosleep(40);
+  }
+}
+
+namespace b2 {
+int tp_wait_launch(const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int* status, cudaStream_t stream) {
+  if (!wait_sig || !epoch) return kErrBadPointer;
+  tp_wait_kernel<<<1, 1, 0, stream>>>(static_cast<const unsigned*>(wait_sig), static_cast<const int*>(epoch),
+                                      wait_per_epoch, status);
+  return (int)cudaGetLastError();
+}
+int rope_kv_store_launch(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
+                         void* cache_v, int Hq, int Hk, int D, int max_len, const void* wait_sig, const void* epoch,
+                         unsigned wait_per_epoch, int* status, cudaStream_t stream) {
+  if (Hq < 1 || Hk < 1 || D < 2 || D % 2 || D / 2 > 1024 || max_len < 1) return kErrBadShape;
+  if (!qkv || !inv_freq || !pos || !cache_k || !cache_v) return kErrBadPointer;
+  if (wait_sig != nullptr && !epoch) return kErrBadPointer;
+  rope_kv_store_kernel<<<Hq + 2 * Hk, D / 2, 0, stream>>>(
+      static_cast<bf16*>(qkv), static_cast<const bf16*>(bias), static_cast<const float*>(inv_freq),
+      static_cast<const int*>(pos), static_cast<bf16*>(cache_k), static_cast<bf16*>(cache_v), Hq, Hk, D, max_len,
+      static_cast<const unsigned*>(wait_sig), static_cast<const int*>(epoch), wait_per_epoch, status);
+  return (int)cudaGetLastError();
+}
+}  // namespace b2
+
 extern "C" {
 
 int b2_rope_kv_store(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k, void* cache_v,
                      int Hq, int Hk, int D, int max_len, void* stream) {
-  if (Hq < 1 || Hk < 1 || D < 2 || D % 2 || D / 2 > 1024 || max_len < 1) return b2::kErrBadShape;
-  if (!qkv || !inv_freq || !pos || !cache_k || !cache_v) return b2::kErrBadPointer;
-  rope_kv_store_kernel<<<Hq + 2 * Hk, D / 2, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<bf16*>(qkv), static_cast<const bf16*>(bias), static_cast<const float*>(inv_freq),
-      static_cast<const int*>(pos), static_cast<bf16*>(cache_k), static_cast<bf16*>(cache_v), Hq, Hk, D, max_len);
-  return (int)cudaGetLastError();
+  return b2::rope_kv_store_launch(qkv, bias, inv_freq, pos, cache_k, cache_v, Hq, Hk, D, max_len, nullptr, nullptr, 0,
+                                  nullptr, static_cast<cudaStream_t>(stream));
 }
 
 size_t b2_decode_workspace_bytes(int Hq, int D) {

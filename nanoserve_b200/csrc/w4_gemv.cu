@@ -95,6 +95,7 @@ struct GemvParams {
   const __nv_bfloat16* Wn;    // add + RMSNorm: norm weights [K]
   __nv_bfloat16* Xout;        // add + RMSNorm: where X + R is stored (may be null)
   float eps;
+  GemvTp tp;                  // tensor-parallel epilogue / input wait (all zero: off)
 };
 
 // two buffers of [consumer warp][token < M][kRedPitch] floats
@@ -432,6 +433,47 @@ __device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base
   }
 }
 
+// ---- tensor parallelism: the all-gather of Y fused into the epilogue -------------------------------------
+// Global column of local output column n: the local shard is up to three row-concatenated pieces (q | k | v,
+// gate | up), each of which lands at its own offset of the gathered row.
+__device__ __forceinline__ int tp_column(const GemvTp& tp, int n) {
+  int c = tp.seg_dst[0] + n;
+  if (n >= tp.seg_end[0]) c = tp.seg_dst[1] + (n - tp.seg_end[0]);
+  if (n >= tp.seg_end[1]) c = tp.seg_dst[2] + (n - tp.seg_end[1]);
+  return c;
+}
+// One output value into the gathered row of every rank (plain stores through peer-mapped pointers).
+__device__ __forceinline__ void tp_store(const GemvTp& tp, int tok, int n, __nv_bfloat16 v) {
+  const size_t at = (size_t)tok * tp.ld + tp_column(tp, n);
+  for (int r = 0; r < tp.world; ++r) static_cast<__nv_bfloat16*>(tp.y_peer[r])[at] = v;
+}
+// Called by one warp when all of its CTA's outputs have been stored: makes them visible system-wide and counts
+// the CTA in on every rank.
+__device__ __forceinline__ void tp_signal(const GemvTp& tp, int lane) {
+  __threadfence_system();
+  __syncwarp();
+  if (lane < tp.world) {
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(tp.sig_peer[lane]) : "memory");
+  }
+}
+// Waits (bounded) until every CTA of every rank's producing kernel has counted itself in on this rank's counter
+// for the current epoch.  One thread polls; the caller synchronises the rest.  Returns false on time-out.
+__device__ __forceinline__ bool tp_wait(const GemvTp& tp, volatile int* abort_flag) {
+  const unsigned target = ((unsigned)*reinterpret_cast<const volatile int*>(tp.epoch) + 1u) * tp.wait_per_epoch;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(tp.wait_sig) : "memory");
+    if ((int)(v - target) >= 0) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+    __nanosleep(40);
+  }
+}
+
 // MT: token tiles of 8 (1 or 2).  NCW: consumer warps (= chunks per stage, even).  MODE: see kMode*.
 template <int MT, int NCW, int MODE>
 __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1)
@@ -547,10 +589,12 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 #pragma unroll
         for (int w = 0; w < NCW; ++w) sum += rbuf[(w * p.M + tok) * kRedPitch + lane];
         if (n < p.N) {
-          if (p.nslices == 1)
-            p.Y[(size_t)tok * p.N + n] = __float2bfloat16(sum);
-          else
+          if (p.nslices > 1)
             __stcg(p.partial + ((size_t)sl * p.M + tok) * p.N + n, sum);
+          else if (p.tp.world)
+            tp_store(p.tp, tok, n, __float2bfloat16(sum));
+          else
+            p.Y[(size_t)tok * p.N + n] = __float2bfloat16(sum);
         }
       }
       __syncwarp();
@@ -572,11 +616,15 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
             for (int tok = 0; tok < p.M; ++tok) {
               float sum = 0.f;
               for (int q = 0; q < p.nslices; ++q) sum += __ldcg(p.partial + ((size_t)q * p.M + tok) * p.N + n);
-              p.Y[(size_t)tok * p.N + n] = __float2bfloat16(sum);
+              if (p.tp.world)
+                tp_store(p.tp, tok, n, __float2bfloat16(sum));
+              else
+                p.Y[(size_t)tok * p.N + n] = __float2bfloat16(sum);
             }
         }
       }
     }
+    if (p.tp.world) tp_signal(p.tp, lane);  // every CTA counts itself in once, after its last store
   } else {
     // ------------------------------------------------------------ consumer warps
     const int g = lane >> 2, t = lane & 3;
@@ -603,6 +651,12 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
     // running: the weight stream (constant data) is already flowing; X, produced upstream, is touched only
     // after the previous grid has completed and flushed.
     pdl_wait_prior_grid();
+    if (p.tp.wait_sig != nullptr) {
+      // the input is the gathered output of the producing kernels of every rank: wait until all their CTAs have
+      // counted themselves in (their stores are visible by then)
+      if (ctid == 0) tp_wait(p.tp, abort_flag);
+      consumer_sync(kConsumerThreads);
+    }
 
     int s = 0;
     uint32_t ph = 0;
@@ -1146,9 +1200,23 @@ int gemv_launch(const void* X, const void* Wq, const void* S, void* Y, int M, in
   return gemv_launch_ex(X, Wq, S, Y, M, N, K, G, GemvPrologue{}, ws, flags, sm_count, stream);
 }
 
+size_t gemv_grid(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap) {
+  GemvPlan pl;
+  if (!make_plan(M, N, K, G, flags, sm_count, partial_cap, counters_cap, &pl)) return 0;
+  return (size_t)pl.grid;
+}
+
 int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
-                   const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream) {
+                   const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream,
+                   const GemvTp* tp) {
   if (M < 1 || M > 16) return kErrUnsupportedM;
+  if (tp != nullptr && tp->world > 0) {
+    if (tp->world > kMaxTpRanks || tp->ld < N || tp->seg_end[0] < 0 || tp->seg_end[1] < tp->seg_end[0]) return kErrBadShape;
+    for (int r = 0; r < tp->world; ++r)
+      if (!tp->y_peer[r] || !tp->sig_peer[r] || (reinterpret_cast<uintptr_t>(tp->sig_peer[r]) & 3)) return kErrBadPointer;
+    Y = tp->y_peer[0];  // the plain output pointer is not used
+  }
+  if (tp != nullptr && tp->wait_sig != nullptr && !tp->epoch) return kErrBadPointer;
   if (pro.kind != kProNone) {
     if (pro.kind != kProAddRmsNorm && pro.kind != kProSwiglu) return kErrBadShape;
     if (G % 128) return kErrNotImplemented;  // prologues live in the fp16 staging of the fast path
@@ -1211,6 +1279,7 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
   p.Wn = static_cast<const __nv_bfloat16*>(pro.Wn);
   p.Xout = static_cast<__nv_bfloat16*>(pro.Xout);
   p.eps = pro.eps;
+  if (tp != nullptr) p.tp = *tp;
 
   if (pl.mt == 2) return launch_mode<2, 8>(tmap, p, pl, stream);
   switch (pl.ncw) {

@@ -60,13 +60,43 @@ struct GemvPrologue {
   float eps = 0.f;
 };
 
+// Tensor parallelism over the output rows, with the all-gather fused into the GEMV (all fields zero: off).
+// Producer side (world > 0): every output value is stored into the gathered row [M, ld] of EVERY rank through
+// peer-mapped pointers -- local column n goes to column seg_dst[i] + (n - start of piece i), the local shard being up
+// to three row-concatenated pieces ending at seg_end[0], seg_end[1], N -- and each CTA, after its last store, adds one
+// to an arrival counter on every rank (release, system scope).
+// Consumer side (wait_sig != null): before it reads X the kernel waits (bounded; a time-out sets the device status)
+// until its own rank's counter has reached (*epoch + 1) * wait_per_epoch, where wait_per_epoch is the number of CTAs
+// that count in per use (ranks x grid of the producing launch) and *epoch counts completed uses (the decode step).
+// Counters only ever grow.
+constexpr int kMaxTpRanks = 8;
+struct GemvTp {
+  int world = 0;
+  void* y_peer[kMaxTpRanks] = {};
+  unsigned* sig_peer[kMaxTpRanks] = {};
+  long long ld = 0;
+  int seg_end[2] = {0x7fffffff, 0x7fffffff};
+  int seg_dst[3] = {0, 0, 0};
+  const unsigned* wait_sig = nullptr;
+  const int* epoch = nullptr;
+  unsigned wait_per_epoch = 0;
+};
+
 int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
-                   const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream);
+                   const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream,
+                   const GemvTp* tp = nullptr);
+// CTAs gemv_launch_ex launches for this shape (what a consumer of its fused all-gather has to wait for, per rank).
+size_t gemv_grid(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap);
 int gemv_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
                 const Workspace& ws, int flags, int sm_count, cudaStream_t stream);
 int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
                 const Workspace& ws, int flags, int sm_count, cudaStream_t stream);
 int quantize_launch(const void* W, void* Wq, void* S, int N, int K, int G, cudaStream_t stream);
+
+int tp_wait_launch(const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int* status, cudaStream_t stream);
+int rope_kv_store_launch(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
+                         void* cache_v, int Hq, int Hk, int D, int max_len, const void* wait_sig, const void* epoch,
+                         unsigned wait_per_epoch, int* status, cudaStream_t stream);
 
 // Scratch bytes gemv_launch would use for this shape (0 when it runs without split-K).
 size_t gemv_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);

@@ -45,8 +45,39 @@ SIGNATURES = {
     "b2_decode_attention": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
     "b2_greedy_next": ([_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp], _i32),
     "b2_decode_workspace_bytes": ([_i32, _i32], ctypes.c_size_t),
+    "b2_w4_linear_tp": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _f32, _vp, _vp, _i32, _vp], _i32),
+    "b2_w4_gemv_grid": ([_i32, _i32, _i32, _i32, _i32], ctypes.c_size_t),
+    "b2_rope_kv_store_tp": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_uint, _vp], _i32),
+    "b2_tp_wait": ([_vp, _vp, ctypes.c_uint, _vp], _i32),
     "b2_version": ([], ctypes.c_char_p),
 }
+
+
+class TpDesc(ctypes.Structure):
+    """struct b2_tp_desc of include/nanoserve_b200.h."""
+    _fields_ = [("world", _i32), ("y_peer", _vp * 8), ("sig_peer", _vp * 8), ("ld", _i64), ("seg_end", _i32 * 2),
+                ("seg_dst", _i32 * 3), ("y_local", _vp), ("wait_sig", _vp), ("epoch", _vp),
+                ("wait_per_epoch", ctypes.c_uint)]
+
+
+def make_tp_desc(y_peers=(), sig_peers=(), ld=0, pieces=None, y_local=None, wait_sig=None, epoch=None,
+                 wait_per_epoch=0) -> TpDesc:
+    """pieces: [(local_width, gathered_column), ...] of the row-concatenated local shard (at most three)."""
+    d = TpDesc()
+    d.world = len(y_peers)
+    for r, (y, sg) in enumerate(zip(y_peers, sig_peers)):
+        d.y_peer[r], d.sig_peer[r] = y, sg
+    d.ld = ld
+    ends, dst, acc = [0x7FFFFFFF, 0x7FFFFFFF], [0, 0, 0], 0
+    for i, (w, col) in enumerate(pieces or []):
+        acc += w
+        dst[i] = col
+        if i < 2 and i + 1 < len(pieces):
+            ends[i] = acc
+    d.seg_end[0], d.seg_end[1] = ends
+    d.seg_dst[0], d.seg_dst[1], d.seg_dst[2] = dst
+    d.y_local, d.wait_sig, d.epoch, d.wait_per_epoch = y_local, wait_sig, epoch, wait_per_epoch
+    return d
 
 
 def load_library(path: str = _LIB_DEFAULT) -> ctypes.CDLL:
@@ -164,6 +195,25 @@ class Kernels:
                                          prologue, p(r), p(wn), eps, p(x_out), flags, self._stream())
         self._check(rc, "b2_w4_linear_fused")
         return y
+
+    def w4_linear_tp(self, x, Wq, S, desc: "TpDesc", group=128, prologue=0, r=None, wn=None, eps=0.0, x_out=None,
+                     flags=0):
+        """Decode GEMV of a tensor-parallel shard with the all-gather fused in (see b2_w4_linear_tp); the outputs
+        go where `desc` says."""
+        self._cuda(x, Wq, S, r, wn, x_out)
+        M = x.shape[0]
+        N, K = Wq.shape[0], Wq.shape[1] * 8
+        assert x.is_contiguous() and x.shape[1] == (2 * K if prologue == 2 else K)
+        p = lambda t: None if t is None else t.data_ptr()
+        rc = self.lib.b2_w4_linear_tp(x.data_ptr(), Wq.data_ptr(), S.data_ptr(), M, N, K, group, prologue, p(r), p(wn),
+                                      eps, p(x_out), ctypes.byref(desc), flags, self._stream())
+        self._check(rc, "b2_w4_linear_tp")
+
+    def tp_wait(self, wait_sig: int, epoch: int, wait_per_epoch: int):
+        self._check(self.lib.b2_tp_wait(wait_sig, epoch, wait_per_epoch, self._stream()), "b2_tp_wait")
+
+    def gemv_grid(self, M, N, K, group=128, flags=0) -> int:
+        return int(self.lib.b2_w4_gemv_grid(M, N, K, group, flags))
 
     def init(self):
         self._check(self.lib.b2_init(), "b2_init")

@@ -10,7 +10,9 @@ Differences from the reference, all on the host side of the boundary:
     ``b2_decode_attention``, ``b2_greedy_next``), so the same graph is replayed for every token.  The reference runs
     ~400 eager launches per token (README.md:227-228).
   * Tensor parallel: every matrix is sharded by output rows over the ranks, outputs are all-gathered at the four
-    layer boundaries; attention, norms and RoPE run replicated on the gathered activations.
+    layer boundaries; attention, norms and RoPE run replicated on the gathered activations.  In the decode step the
+    gather is fused into the GEMVs (``b2_w4_linear_tp``: peer stores into every rank's gathered row + arrival
+    counters, the consumer waits on the counter); the prompt and the lm_head use NCCL.
 Batch size 1, as in the reference (qwen.py:12).
 """
 import ctypes
@@ -21,7 +23,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from .ops import Kernels
+from .ops import Kernels, make_tp_desc
 
 
 @dataclass
@@ -51,7 +53,7 @@ def _rand_w4(N, K, G, gen, device):
 
 class Qwen2Runner:
     def __init__(self, cfg: Qwen2Config, kernels: Kernels, device, rank: int = 0, world: int = 1, seed: int = 0,
-                 max_len: int = 1024, group=None):
+                 max_len: int = 1024, group=None, fused_gather: bool = True):
         self.cfg, self.k, self.dev = cfg, kernels, device
         self.rank, self.world, self.group = rank, world, group
         self.max_len = max_len
@@ -101,6 +103,42 @@ class Qwen2Runner:
         self.scratch = torch.empty(int(kernels.lib.b2_decode_workspace_bytes(cfg.n_heads, D)), dtype=torch.uint8,
                                    device=device)
         kernels.init()
+        self.peer = None
+        if world > 1 and fused_gather:
+            self._setup_fused_gather()
+
+    def _setup_fused_gather(self):
+        """Symmetric buffers for the four gathered rows of a layer (shared by all layers: a rank cannot pass a wait
+        before every rank has delivered, so it is never more than one boundary ahead of the slowest rank and a buffer
+        is consumed everywhere before anyone overwrites it), four arrival counters per layer, and the descriptors of
+        every tensor-parallel launch."""
+        from .tp import PeerBuffers
+        cfg, k, P, r = self.cfg, self.k, self.world, self.rank
+        H, I, nq, nkv, G = cfg.hidden, self.I, self.nq, self.nkv, cfg.group
+        self.peer = peer = PeerBuffers({"qkv": nq + 2 * nkv, "o": H, "gu": 2 * I, "d": H}, 4 * cfg.n_layers,
+                                       self.dev, self.group)
+        ep = peer.epoch.data_ptr()
+        g_qkv = P * k.gemv_grid(1, (nq + 2 * nkv) // P, H, G)
+        g_o = P * k.gemv_grid(1, H // P, nq, G)
+        g_gu = P * k.gemv_grid(1, 2 * I // P, H, G)
+        g_d = P * k.gemv_grid(1, H // P, I, G)
+        self.tp_wait_d = g_d
+        self.tp_wait_qkv = g_qkv
+        self.tp_desc = []
+        for li in range(cfg.n_layers):
+            c = 4 * li
+            wait_prev = dict(wait_sig=peer.counter(c - 1), epoch=ep, wait_per_epoch=g_d) if li > 0 else {}
+            self.tp_desc.append({
+                "qkv": make_tp_desc(peer.peers("qkv"), peer.counter_peers(c), ld=nq + 2 * nkv,
+                                    pieces=[(nq // P, r * nq // P), (nkv // P, nq + r * nkv // P),
+                                            (nkv // P, nq + nkv + r * nkv // P)], **wait_prev),
+                "o": make_tp_desc(peer.peers("o"), peer.counter_peers(c + 1), ld=H, pieces=[(H // P, r * H // P)]),
+                "gu": make_tp_desc(peer.peers("gu"), peer.counter_peers(c + 2), ld=2 * I,
+                                   pieces=[(I // P, r * I // P), (I // P, I + r * I // P)],
+                                   wait_sig=peer.counter(c + 1), epoch=ep, wait_per_epoch=g_o),
+                "d": make_tp_desc(peer.peers("d"), peer.counter_peers(c + 3), ld=H, pieces=[(H // P, r * H // P)],
+                                  wait_sig=peer.counter(c + 2), epoch=ep, wait_per_epoch=g_gu),
+            })
 
     # ------------------------------------------------------------------ helpers
     def weight_bytes_per_token(self) -> int:
@@ -173,6 +211,8 @@ class Qwen2Runner:
         logits = self._gather(F.linear(h[-1:], self.lm_head))
         self.pos.fill_(T - 1)  # greedy_next advances it to T, the position of the first generated token
         self.step.zero_()
+        if self.peer is not None:
+            self.peer.reset()  # counters and epoch restart together, on every rank
         self._greedy_next(logits)
         return self.tokens[0]
 
@@ -193,6 +233,8 @@ class Qwen2Runner:
         store, attention (two passes), o GEMV, gate|up GEMV (add + norm folded in), down GEMV (SwiGLU folded in).
         The residual stream alternates between two buffers because a fused GEMV may not overwrite the X other CTAs
         are still reading; every step starts again from `self.x`, where b2_greedy_next puts the next embedding."""
+        if self.peer is not None:
+            return self._decode_step_fused_gather()
         cfg, k, lib = self.cfg, self.k, self.k.lib
         D = cfg.head_dim
         x, x_alt = self.x, self.x_alt
@@ -227,6 +269,47 @@ class Qwen2Runner:
         self._greedy_next(logits)
         return logits
 
+    @torch.no_grad()
+    def _decode_step_fused_gather(self):
+        """The decode step on more than one GPU with the all-gathers inside the GEMVs: the same seven launches per
+        layer as on one GPU, no collective.  Every GEMV stores its rows into the gathered row of every rank and counts
+        itself in; the kernel that consumes the row (the next GEMV, or the RoPE kernel) waits on the counter."""
+        cfg, k, lib, peer = self.cfg, self.k, self.k.lib, self.peer
+        D, G, eps = cfg.head_dim, cfg.group, cfg.rms_eps
+        ep = peer.epoch.data_ptr()
+        qkv_buf, o_buf = peer.local("qkv", 1), peer.local("o", 1)
+        gu_buf, d_buf = peer.local("gu", 1), peer.local("d", 1)
+        x, x_alt = self.x, self.x_alt
+        for li, L in enumerate(self.layers):
+            dsc = self.tp_desc[li]
+            if li == 0:
+                k.w4_linear_tp(x, L["qkv"][0], L["qkv"][1], dsc["qkv"], G, prologue=1, wn=L["ln_in"], eps=eps)
+            else:
+                k.w4_linear_tp(x, L["qkv"][0], L["qkv"][1], dsc["qkv"], G, prologue=1, r=d_buf, wn=L["ln_in"], eps=eps,
+                               x_out=x_alt)
+                x, x_alt = x_alt, x
+            rc = lib.b2_rope_kv_store_tp(qkv_buf.data_ptr(), L["bias"].data_ptr(), self.inv_freq.data_ptr(),
+                                         self.pos.data_ptr(), self.cache_k[li].data_ptr(),
+                                         self.cache_v[li].data_ptr(), cfg.n_heads, cfg.n_kv_heads, D, self.max_len,
+                                         peer.counter(4 * li), ep, self.tp_wait_qkv, self._st())
+            k._check(rc, "b2_rope_kv_store_tp")
+            a = torch.empty(1, self.nq, dtype=torch.bfloat16, device=self.dev)
+            rc = lib.b2_decode_attention(qkv_buf.data_ptr(), self.cache_k[li].data_ptr(), self.cache_v[li].data_ptr(),
+                                         self.pos.data_ptr(), a.data_ptr(), self.scratch.data_ptr(), cfg.n_heads,
+                                         cfg.n_kv_heads, D, self.max_len, self._st())
+            k._check(rc, "b2_decode_attention")
+            k.w4_linear_tp(a, L["o"][0], L["o"][1], dsc["o"], G)
+            k.w4_linear_tp(x, L["gu"][0], L["gu"][1], dsc["gu"], G, prologue=1, r=o_buf, wn=L["ln_post"], eps=eps,
+                           x_out=x_alt)
+            x, x_alt = x_alt, x
+            k.w4_linear_tp(gu_buf, L["d"][0], L["d"][1], dsc["d"], G, prologue=2)
+        k.tp_wait(peer.counter(4 * cfg.n_layers - 1), ep, self.tp_wait_d)
+        h = k.rmsnorm(x, d_buf, self.final_norm, eps)
+        logits = self._gather(F.linear(h, self.lm_head))
+        self._greedy_next(logits)
+        peer.epoch.add_(1)
+        return logits
+
     def capture(self):
         """Warms up and captures one decode step.  The warm-up steps advance the device state; callers that
         need clean state re-run prefill afterwards."""
@@ -258,12 +341,13 @@ class Qwen2Runner:
 
 
 def decode_rate(kernels: Kernels, device, rank: int = 0, world: int = 1, cfg: Optional[Qwen2Config] = None,
-                prompt_len: int = 512, n_new: int = 256, seed: int = 0) -> dict:
+                prompt_len: int = 512, n_new: int = 256, seed: int = 0, fused_gather: bool = True) -> dict:
     """Greedy decode of `n_new` tokens after a `prompt_len`-token prompt of uniform random ids, batch 1: the
     reference's decode-rate measurement ((G - 1) tokens over the time after the first one, python/bench_e2e.py:210-213)
     with CUDA events around the G - 1 graph replays.  Every rank must call it; returns the numbers of this rank."""
     cfg = cfg or Qwen2Config.qwen25_7b()
-    r = Qwen2Runner(cfg, kernels, device, rank=rank, world=world, seed=seed, max_len=prompt_len + n_new + 8)
+    r = Qwen2Runner(cfg, kernels, device, rank=rank, world=world, seed=seed, max_len=prompt_len + n_new + 8,
+                    fused_gather=fused_gather)
     gen = torch.Generator(device=device).manual_seed(4)
     prompt = torch.randint(0, cfg.vocab, (prompt_len,), device=device, generator=gen)
     r.generate(prompt, 4)  # warms every kernel variant and captures the decode graph
@@ -284,7 +368,9 @@ def decode_rate(kernels: Kernels, device, rank: int = 0, world: int = 1, cfg: Op
     return {"tok_s": (n_new - 1) / t_decode, "ms_per_token": t_decode / (n_new - 1) * 1e3,
             "prefill_tok_s": prompt_len / t_prefill, "prompt_len": prompt_len, "n_new": n_new,
             "weight_bytes_per_token_per_rank": r.weight_bytes_per_token(), "first_tokens": tokens[:8],
-            "launches_per_token": "7 per layer (1 GPU) + final norm + lm_head + 2 for argmax, one CUDA graph"}
+            "launches_per_token": "7 per layer + final norm + lm_head + 2 for argmax, one CUDA graph; " +
+                                  ("all-gathers fused into the GEMVs" if r.peer is not None else
+                                   "NCCL all-gathers at the layer boundaries" if world > 1 else "one GPU")}
 
 
 if __name__ == "__main__":

@@ -3,8 +3,12 @@
 The reference is single-GPU (python/nanoserve/qwen.py:12); this is new.  Rows of ``Wq [N, K/8]`` and
 ``S [N, K/G]`` are independent, so rank r of P keeps the contiguous row block [r*N/P, (r+1)*N/P) of every
 matrix -- a zero-copy slice of the reference layout -- with K, and therefore every quantization group, whole.
-X is replicated.  The only exchange is an all-gather of Y at a layer boundary (NCCL over NVLink on GPUs,
-gloo in the CPU tests).  One process per GPU.
+X is replicated.  The only exchange is an all-gather of Y at a layer boundary.  Two ways to do it:
+  * a collective (NCCL over NVLink on GPUs, gloo in the CPU tests): ``gather_rows``;
+  * fused into the decode GEMV (``b2_w4_linear_tp``): the kernel stores its outputs straight into the gathered row of
+    every rank through peer-mapped memory (``PeerBuffers``) and counts itself in; the consumer waits on the counter.
+    At decode sizes a gathered row is a few KB and a collective costs more than the GEMV it follows.
+One process per GPU.
 """
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
@@ -42,6 +46,55 @@ def gather_rows(parts: Sequence[torch.Tensor], world: int, group=None) -> List[t
     return full
 
 
+class PeerBuffers:
+    """Gathered-output rows and arrival counters of a tensor-parallel group, allocated as symmetric memory so that
+    every rank holds a device pointer to every other rank's copy (plain peer loads/stores over NVLink; no multicast
+    object is used).  ``rows``: name -> elements (bf16) of one gathered buffer; ``n_counters`` uint32 counters."""
+
+    def __init__(self, rows: Dict[str, int], n_counters: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.offsets, off = {}, 0
+        for name, n in rows.items():
+            self.offsets[name] = (off, n)
+            off += (n * 2 + 255) & ~255
+        self.counter_off = off
+        nbytes = off + ((n_counters * 4 + 255) & ~255) + 256
+        self.mem = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.mem.zero_()
+        self.handle = symm.rendezvous(self.mem, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.n_counters = n_counters
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.reset()
+
+    def local(self, name: str, M: int) -> torch.Tensor:
+        """This rank's gathered buffer ``[M, n / M]`` (bf16 view of the symmetric allocation)."""
+        off, n = self.offsets[name]
+        return self.mem[off:off + n * 2].view(torch.bfloat16).view(M, n // M)
+
+    def peers(self, name: str) -> List[int]:
+        off, _ = self.offsets[name]
+        return [p + off for p in self.ptrs]
+
+    def counter(self, i: int, rank: Optional[int] = None) -> int:
+        base = self.ptrs[self.rank if rank is None else rank]
+        return base + self.counter_off + 4 * i
+
+    def counter_peers(self, i: int) -> List[int]:
+        return [self.counter(i, r) for r in range(self.world)]
+
+    def reset(self):
+        """Zeroes the counters and the epoch on every rank; nothing of the group may be in flight."""
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        self.mem[self.counter_off:].zero_()
+        self.epoch.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+
+
 class ShardedLayer:
     """The seven quantized linears of one decoder layer, sharded by output rows."""
 
@@ -53,6 +106,8 @@ class ShardedLayer:
         self.linear, self.shards, self.G = linear, shards, G
         self.rank, self.world, self.group = rank, world, group
         self.full = full if full is not None else (shards if world == 1 else None)
+        self.kernels = None
+        self.peer: Optional[PeerBuffers] = None
 
     @classmethod
     def synthetic(cls, kernels, shapes, order, G, seed, rank, world, device, flags=0):
@@ -70,7 +125,26 @@ class ShardedLayer:
         def linear(x, Wq, S, G):
             return kernels.w4_linear(x, Wq, S, G, flags=flags)
 
-        return cls(linear, shards, G, rank, world)
+        layer = cls(linear, shards, G, rank, world)
+        layer.kernels, layer.flags, layer.shapes = kernels, flags, dict(shapes)
+        return layer
+
+    def attach_peer_buffers(self, peer: "PeerBuffers", M: int):
+        """Switches decode_pass to the fused all-gather: one gathered buffer per matrix (names of `shapes`, M rows
+        each), one counter per layer boundary, shared by every layer that uses the same PeerBuffers (a boundary's
+        buffers are consumed before the next pass reaches it: see decode_pass)."""
+        from .ops import make_tp_desc
+        self.peer, self.M = peer, M
+        self.descs, self.waits = {}, []
+        for b, names in enumerate(self.BOUNDARIES):
+            per_epoch = 0
+            for name in names:
+                N, K = self.shapes[name]
+                nl = N // self.world
+                self.descs[name] = make_tp_desc(y_peers=peer.peers(name), sig_peers=peer.counter_peers(b), ld=N,
+                                                pieces=[(nl, self.rank * nl)])
+                per_epoch += self.world * self.kernels.gemv_grid(M, nl, K, self.G, self.flags)
+            self.waits.append((peer.counter(b), per_epoch))
 
     def resident_bytes(self) -> int:
         return sum(w.numel() * 4 + s.numel() * 2 for w, s in self.shards.values())
@@ -78,6 +152,8 @@ class ShardedLayer:
     def decode_pass(self, x: torch.Tensor, act: torch.Tensor) -> List[torch.Tensor]:
         """One pass over the seven linears: q, k, v, o, gate, up take ``x [M, hidden]``; down takes
         ``act [M, intermediate]``.  Returns the seven full-width outputs in that order."""
+        if self.peer is not None:
+            return self._decode_pass_fused(x, act)
         outs = []
         for names in self.BOUNDARIES:
             local = []
@@ -86,4 +162,22 @@ class ShardedLayer:
                 inp = act if Wq.shape[1] * 8 == act.shape[1] and name == "down" else x
                 local.append(self.linear(inp, Wq, S, self.G))
             outs.extend(gather_rows(local, self.world, self.group))
+        return outs
+
+    def _decode_pass_fused(self, x: torch.Tensor, act: torch.Tensor) -> List[torch.Tensor]:
+        """The same pass with the all-gather inside the GEMVs: every launch stores its rows into every rank's gathered
+        buffer; at each boundary a one-thread kernel waits until all ranks' launches have counted themselves in.  The
+        epoch advances once per pass.  A rank can run at most one boundary ahead of the slowest one (it needs
+        everybody's rows to pass a wait), so a buffer is never overwritten while another rank still reads it."""
+        k, peer = self.kernels, self.peer
+        outs = []
+        for b, names in enumerate(self.BOUNDARIES):
+            for name in names:
+                Wq, S = self.shards[name]
+                inp = act if name == "down" else x
+                k.w4_linear_tp(inp, Wq, S, self.descs[name], self.G, flags=self.flags)
+                outs.append(peer.local(name, self.M))
+            sig, per_epoch = self.waits[b]
+            k.tp_wait(sig, peer.epoch.data_ptr(), per_epoch)
+        peer.epoch.add_(1)
         return outs

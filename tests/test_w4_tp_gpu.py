@@ -1,0 +1,125 @@
+"""GPU tests of the tensor-parallel GEMV entry point (b2_w4_linear_tp) on ONE GPU: the "ranks" are row shards of one
+matrix launched one after the other on one stream, every rank's gathered buffer lives on the same device, so the peer
+stores, the piece-wise column mapping, the arrival counters and the consumer-side wait are all exercised without a
+second GPU.  (The launches are stream-ordered: a consumer never spins on a kernel that has not finished.)
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from nanoserve_b200 import ops
+from tests.util import bits_to_torch, check_bf16_output, torch_to_bits, u32_to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _shards(Wq, S, world, pieces):
+    """Row shards of a row-concatenated matrix: rank r gets rows [r w/P, (r+1) w/P) of every piece."""
+    out = []
+    for r in range(world):
+        rows, off = [], 0
+        for w in pieces:
+            wl = w // world
+            rows.append(torch.arange(off + r * wl, off + (r + 1) * wl))
+            off += w
+        idx = torch.cat(rows).to(Wq.device)
+        out.append((Wq[idx].contiguous(), S[idx].contiguous()))
+    return out
+
+
+@pytest.mark.parametrize("M", [1, 4])
+@pytest.mark.parametrize("world,pieces,K", [(1, [512], 512), (2, [256, 128, 128], 1024), (4, [1024, 1024], 512),
+                                            (2, [3584], 3584)])
+def test_fused_all_gather_matches_single_gpu(kernels, M, world, pieces, K):
+    G, N = 128, sum(pieces)
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=61)
+    x, wq, s = bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S)
+    want = kernels.w4_linear(x, wq, s, G).float()
+    gathered = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    sig = torch.zeros(world, dtype=torch.int32, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    grids = []
+    for r, (wq_r, s_r) in enumerate(_shards(wq, s, world, pieces)):
+        n_local = wq_r.shape[0]
+        cols, off = [], 0
+        for w in pieces:
+            cols.append((w // world, off + r * (w // world)))
+            off += w
+        d = ops.make_tp_desc(y_peers=[g.data_ptr() for g in gathered],
+                             sig_peers=[sig[i:].data_ptr() for i in range(world)], ld=N, pieces=cols)
+        kernels.w4_linear_tp(x, wq_r, s_r, d, G)
+        grids.append(kernels.gemv_grid(M, n_local, K, G))
+    torch.cuda.synchronize()
+    assert kernels.device_status() == 0
+    assert sig.tolist() == [sum(grids)] * world  # every CTA of every launch counted itself in on every rank
+    # rows are independent, but a shard may be planned with another K split than the whole matrix: the fp32 sums are
+    # taken in another order, so the bound is one bf16 rounding plus summation noise; all ranks hold the same bits
+    tol = want.abs() * 2.0**-7 + 1e-5 * want.abs().max()
+    for g in gathered:
+        assert torch.all((g.float() - want).abs() <= tol)
+        assert torch.equal(g, gathered[0])
+    check_bf16_output(torch_to_bits(gathered[0]), oracle.w4_linear_f32(X, Wq, S, G, threads=oracle.max_threads()), 2e-5)
+
+
+def test_consumer_waits_on_the_counter_and_reads_the_gathered_row(kernels):
+    """Producer -> consumer chain through a gathered buffer: the second GEMV (SwiGLU prologue) waits on the counter
+    of the first and must reproduce the two-call result."""
+    G, M, K1, I = 128, 2, 512, 1024
+    _, Wa, Sa = oracle.synth_inputs(1, 2 * I, K1, G, seed=71)  # gate | up
+    _, Wb, Sb = oracle.synth_inputs(1, 384, I, G, seed=72)     # down
+    wa, sa, wb, sb = u32_to_torch(Wa), bits_to_torch(Sa), u32_to_torch(Wb), bits_to_torch(Sb)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(M, K1, device="cuda", generator=g).to(torch.bfloat16)
+    gu = kernels.w4_linear(x, wa, sa, G)
+    want = kernels.w4_linear_fused(gu, wb, sb, G, prologue=2)
+
+    buf = torch.zeros(M, 2 * I, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(M, 384, dtype=torch.bfloat16, device="cuda")
+    sig = torch.zeros(2, dtype=torch.int32, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for step in range(3):  # counters only grow: the target follows the epoch
+        epoch.fill_(step)
+        buf.zero_()
+        prod = ops.make_tp_desc(y_peers=[buf.data_ptr()], sig_peers=[sig.data_ptr()], ld=2 * I, pieces=[(2 * I, 0)])
+        kernels.w4_linear_tp(x, wa, sa, prod, G)
+        cons = ops.make_tp_desc(y_local=out.data_ptr(), wait_sig=sig.data_ptr(), epoch=epoch.data_ptr(),
+                                wait_per_epoch=kernels.gemv_grid(M, 2 * I, K1, G))
+        kernels.w4_linear_tp(buf, wb, sb, cons, G, prologue=2)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), step
+    assert kernels.device_status() == 0
+
+
+def test_bounded_wait_reports_a_time_out(kernels):
+    """A counter nobody bumps: the consumer gives up after its bounded wait and the device status says so; the
+    context stays usable."""
+    G, M, N, K = 128, 1, 64, 256
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=81)
+    x, wq, s = bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    sig = torch.zeros(1, dtype=torch.int32, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cons = ops.make_tp_desc(y_local=out.data_ptr(), wait_sig=sig.data_ptr(), epoch=epoch.data_ptr(), wait_per_epoch=1)
+    kernels.w4_linear_tp(x, wq, s, cons, G)
+    torch.cuda.synchronize()
+    assert kernels.device_status() != 0
+    kernels.clear_status()
+    assert kernels.device_status() == 0
+    y = kernels.w4_linear(x, wq, s, G)  # the library still works
+    check_bf16_output(torch_to_bits(y), oracle.w4_linear_f32(X, Wq, S, G), 2e-5)
+
+
+def test_tp_error_codes(kernels):
+    x = torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda")
+    wq = torch.zeros(64, 32, dtype=torch.int32, device="cuda")
+    s = torch.ones(64, 2, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="code -1"):  # neither producer nor consumer
+        kernels.w4_linear_tp(x, wq, s, ops.make_tp_desc(), 128)
+    buf = torch.zeros(1, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="code -4"):  # a peer without a counter
+        kernels.w4_linear_tp(x, wq, s, ops.make_tp_desc(y_peers=[buf.data_ptr()], sig_peers=[None], ld=64,
+                                                          pieces=[(64, 0)]), 128)
+    with pytest.raises(RuntimeError, match="code -1"):  # gathered row narrower than the shard
+        kernels.w4_linear_tp(x, wq, s, ops.make_tp_desc(y_peers=[buf.data_ptr()], sig_peers=[buf.data_ptr()], ld=32,
+                                                          pieces=[(64, 0)]), 128)
