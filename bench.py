@@ -242,6 +242,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the Qwen2.5-7B-shaped greedy-decode tokens/s leg")
     ap.add_argument("--flags", type=int, default=0, help="library flags for every launch (see include/nanoserve_b200.h)")
+    ap.add_argument("--layer", default="7b", choices=["7b", "70b"],
+                    help="shapes of the layer pass: the Qwen2.5-7B-shaped layer of the headline metric, or the 70B-class "
+                         "layer (hidden 8192, intermediate 28672) of the multi-GPU configuration")
     ap.add_argument("--tp-collective", action="store_true",
                     help="N > 1: all-gather the outputs with NCCL at the layer boundaries instead of fusing the gather "
                          "into the GEMVs (peer stores + arrival counters)")
@@ -252,6 +255,9 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args)
         return
+    global LAYER, N_COPIES
+    if args.layer == "70b":
+        LAYER, N_COPIES = synth.CLASS_70B_LAYER, 4
 
     import torch
     import torch.distributed as dist
@@ -291,8 +297,9 @@ def main():
         peer = PeerBuffers({name: M * LAYER[name][0] for name in ORDER}, len(ShardedLayer.BOUNDARIES), dev)
         for l in layers:
             l.attach_peer_buffers(peer, M)
-    x_h = torch.from_numpy(synth.synth_x(M, 3584, 1).view(np.int16)).view(torch.bfloat16).pin_memory()
-    a_h = torch.from_numpy(synth.synth_x(M, 18944, 2).view(np.int16)).view(torch.bfloat16).pin_memory()
+    hidden, inter = LAYER["q"][1], LAYER["down"][1]
+    x_h = torch.from_numpy(synth.synth_x(M, hidden, 1).view(np.int16)).view(torch.bfloat16).pin_memory()
+    a_h = torch.from_numpy(synth.synth_x(M, inter, 2).view(np.int16)).view(torch.bfloat16).pin_memory()
     x_d, a_d = x_h.to(dev), a_h.to(dev)
     resident = sum(l.resident_bytes() for l in layers)
 
@@ -371,7 +378,7 @@ def main():
 
     # ---- the dominant kernel alone: the 18944 x 3584 GEMV over 16 distinct matrices (gate and up of 8 copies)
     roof = None
-    if world == 1:
+    if world == 1 and args.layer == "7b":
         big = [(l.full["gate"]) for l in layers] + [(l.full["up"]) for l in layers]
         y_big = torch.empty(M, 18944, dtype=torch.bfloat16, device=dev)
         with torch.cuda.stream(stream):
@@ -405,14 +412,14 @@ def main():
 
     # ---- the other benchmark configurations on one GPU: every decode shape at M = 1..16, the prefill GEMMs
     sweep = None
-    if world == 1 and not args.no_sweep:
+    if world == 1 and not args.no_sweep and args.layer == "7b":
         del big, y_big
         sweep = run_sweep(k, dev, stream, args.flags)
 
     # ---- second half of the headline metric: W4 greedy decode tokens/s of a Qwen2.5-7B-shaped model (512-token prompt,
     # 256 new tokens, batch 1, tensor parallel over the ranks); free the GEMV benchmark's weights first
     decode = None
-    if not args.no_decode:
+    if not args.no_decode and args.layer == "7b":
         del graphs, layers
         torch.cuda.empty_cache()
         try:
@@ -447,7 +454,9 @@ def main():
             "ms_per_step": t_dev / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int4 weights x bf16 activations, fp32 accumulate", "data": "synthetic",
             "config": {
-                "workload": f"decode GEMV pass over the 7 linears of a Qwen2.5-7B-shaped layer, M={M}, int4 g128",
+                "workload": "decode GEMV pass over the 7 linears of a " +
+                            ("Qwen2.5-7B-shaped" if args.layer == "7b" else "70B-class (hidden 8192, intermediate 28672)") +
+                            f" layer, M={M}, int4 g128",
                 "parallelism": (f"tp{world}, all-gather " + ("fused into the GEMVs (peer stores + arrival counters)"
                                                              if fused_gather else "by NCCL at the 4 layer boundaries"))
                 if world > 1 else "single GPU",

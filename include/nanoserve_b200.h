@@ -159,12 +159,12 @@ size_t b2_decode_workspace_bytes(int Hq, int D);
  * [r N/P, (r+1) N/P) of Wq and S (a zero-copy slice of the reference layout); X is replicated.
  *   Producer side (world > 0): the GEMV stores every output value straight into the gathered row [M, ld] (bf16) of
  *     EVERY rank through peer-mapped device pointers y_peer[0..world) (the caller maps them: CUDA IPC, symmetric
- *     memory; its own rank included), and each CTA, after its last store, adds one to the arrival counter sig_peer[r]
- *     (uint32, peer-mapped) of every rank.  The local shard may be up to three row-concatenated pieces (q | k | v,
+ *     memory; its own rank included), and the launch, after its last store, adds one to the arrival counter
+ *     sig_peer[r] (uint32, peer-mapped) of every rank.  The local shard may be up to three row-concatenated pieces (q | k | v,
  *     gate | up) ending at local columns seg_end[0], seg_end[1], N; piece i lands at gathered column seg_dst[i].
  *   Consumer side (wait_sig != NULL): before it reads X the GEMV waits until this rank's counter wait_sig has reached
- *     (*epoch + 1) * wait_per_epoch: wait_per_epoch = ranks x b2_w4_gemv_grid(...) of the producing call, *epoch (int32
- *     on the device) = completed uses of the counter, e.g. the decode step.  Counters only grow; zero them (all ranks,
+ *     (*epoch + 1) * wait_per_epoch: wait_per_epoch = ranks x producing launches per use, *epoch (int32 on the
+ *     device) = completed uses of the counter, e.g. the decode step.  Counters only grow; zero them (all ranks,
  *     with a host barrier) whenever *epoch restarts.  The wait is bounded (about half a second); a time-out shows in
  *     b2_device_status().
  * A call may be producer, consumer or both; with world == 0 the output goes to y_local.  The other arguments are those

@@ -447,17 +447,29 @@ __device__ __forceinline__ void tp_store(const GemvTp& tp, int tok, int n, __nv_
   const size_t at = (size_t)tok * tp.ld + tp_column(tp, n);
   for (int r = 0; r < tp.world; ++r) static_cast<__nv_bfloat16*>(tp.y_peer[r])[at] = v;
 }
-// Called by one warp when all of its CTA's outputs have been stored: makes them visible system-wide and counts
-// the CTA in on every rank.
+// Called by one warp of every CTA when all of the CTA's outputs have been stored.  System-scope releases are dear
+// (a release per CTA cost 6 us per launch, an explicit system fence on top of it 13 us), so the CTAs first count
+// themselves in on a device-scope counter of their own GPU; the last one to arrive -- which has thereby observed the
+// stores of all the others -- resets that counter and adds one, with release at system scope, to the arrival counter
+// of every rank: one signal per launch and rank.
 __device__ __forceinline__ void tp_signal(const GemvTp& tp, int lane) {
-  __threadfence_system();
   __syncwarp();
-  if (lane < tp.world) {
+  int last = 0;
+  if (lane == 0) {
+    __threadfence();
+    last = atomicAdd(tp.local_count, 1) == (int)gridDim.x - 1;
+    if (last) {
+      *tp.local_count = 0;  // ready for the next launch (launches sharing the counter are stream-ordered)
+      __threadfence();
+    }
+  }
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (last && lane < tp.world) {
     asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(tp.sig_peer[lane]) : "memory");
   }
 }
-// Waits (bounded) until every CTA of every rank's producing kernel has counted itself in on this rank's counter
-// for the current epoch.  One thread polls; the caller synchronises the rest.  Returns false on time-out.
+// Waits (bounded) until every producing launch of every rank has counted itself in on this rank's counter for the
+// current epoch.  One thread polls; the caller synchronises the rest.  Returns false on time-out.
 __device__ __forceinline__ bool tp_wait(const GemvTp& tp, volatile int* abort_flag) {
   const unsigned target = ((unsigned)*reinterpret_cast<const volatile int*>(tp.epoch) + 1u) * tp.wait_per_epoch;
   const long long t0 = clock64();
@@ -1235,8 +1247,9 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
   if (!ws.status) return kErrWorkspace;
   const bool have_scratch = ws.partial && ws.counters;
   GemvPlan pl;
+  // the last counter is kept for the tensor-parallel epilogue's CTA count
   if (!make_plan(M, N, K, G, have_scratch ? flags : (flags | kFlagForceNoSplitK), sm_count,
-                 ws.partial_bytes, ws.n_counters, &pl))
+                 ws.partial_bytes, ws.n_counters - 1, &pl))
     return kErrTooLarge;
 
   // Wq as a 2-D tensor of 32-bit words [N rows, K/8 columns]; boxes of 32 words (two chunks) x 32 rows
@@ -1279,7 +1292,13 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
   p.Wn = static_cast<const __nv_bfloat16*>(pro.Wn);
   p.Xout = static_cast<__nv_bfloat16*>(pro.Xout);
   p.eps = pro.eps;
-  if (tp != nullptr) p.tp = *tp;
+  if (tp != nullptr) {
+    p.tp = *tp;
+    if (tp->world > 0) {
+      if (!ws.counters || ws.n_counters < 2) return kErrWorkspace;
+      p.tp.local_count = ws.counters + ws.n_counters - 1;  // the last counter is never used by split-K (see make_plan)
+    }
+  }
 
   if (pl.mt == 2) return launch_mode<2, 8>(tmap, p, pl, stream);
   switch (pl.ncw) {

@@ -80,6 +80,7 @@ struct GemvTp {
   const unsigned* wait_sig = nullptr;
   const int* epoch = nullptr;
   unsigned wait_per_epoch = 0;
+  int* local_count = nullptr;
 };
 
 int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,

@@ -118,10 +118,7 @@ class Qwen2Runner:
         self.peer = peer = PeerBuffers({"qkv": nq + 2 * nkv, "o": H, "gu": 2 * I, "d": H}, 4 * cfg.n_layers,
                                        self.dev, self.group)
         ep = peer.epoch.data_ptr()
-        g_qkv = P * k.gemv_grid(1, (nq + 2 * nkv) // P, H, G)
-        g_o = P * k.gemv_grid(1, H // P, nq, G)
-        g_gu = P * k.gemv_grid(1, 2 * I // P, H, G)
-        g_d = P * k.gemv_grid(1, H // P, I, G)
+        g_qkv = g_o = g_gu = g_d = P  # signals per use of a counter: one per producing launch and rank
         self.tp_wait_d = g_d
         self.tp_wait_qkv = g_qkv
         self.tp_desc = []
