@@ -111,8 +111,9 @@ int b2_w4_linear_fused(const void* X, const void* Wq, const void* S, void* Y, in
 
 /*
  * Synchronises the current device and returns its status word: 0, or B2_ERR_DEVICE if a kernel gave up
- * on a bounded wait since the last b2_clear_status.  A non-zero status makes later launches return at
- * once on the device, so the error cannot be missed.
+ * on a bounded wait since the last b2_clear_status (an mbarrier of its pipeline, or a tensor-parallel arrival
+ * counter).  The outputs of that launch are undefined.  While the word is set, GEMM launches return at once on the
+ * device; b2_clear_status also clears arrival counters a time-out may have left half counted.
  */
 int b2_device_status(void);
 int b2_clear_status(void);

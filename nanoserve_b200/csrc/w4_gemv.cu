@@ -3,40 +3,52 @@
 // Replaces the reference's w4a16_gemv_kernel / w4a16_gemv (kernels/quant/w4a16.cuh:42-115), which
 // serves M in {1,2,4,8} only on CUDA cores.  Same operands, same weight format, fp32 accumulation.
 //
-// Design (HBM-bound: every weight byte is read exactly once, X is tiny and lives in shared memory):
-//   * One persistent CTA per SM.  A producer lane streams the packed weights of a 32-row group into a
-//     shared-memory ring with tiled TMA loads through a tensor map over Wq: boxes of 32 rows x 128 bytes
-//     (two K chunks) with the 128-byte swizzle, NCW/2 boxes per stage, completion counted on an
-//     mbarrier; several stages are in flight from the first instruction.  (Per-row untiled bulk copies
-//     were measured first: the TMA unit retires about one copy per 70 cycles whatever its size, so 1 KB
-//     row segments cap near 4 TB/s; tiled boxes reach the copy-kernel bandwidth.)
-//   * NCW consumer warps each take one 128-wide K chunk of the stage for both 16-row blocks.  A lane
-//     reads 16 bytes (32 nibbles) per row with one 128-bit shared load; the swizzle plus a fixed
-//     permutation of which tile row feeds which mma row makes those loads bank-conflict free.
-//   * Unpack for G % 128 == 0 (the fast path): one shift and four LOP3 per word turn eight nibbles into
-//     four fp16x2 registers {1024 + q[p], 1024 + q[p+4]} (nibbles at bits 0-3 of a half) or
-//     {1024 + 16 q[p], 1024 + 16 q[p+4]} (nibbles at bits 4-7: the fp16 mantissa has room, so no shift).
-//     One packed-half FMA per register gives q - 8 exactly (x 1 - 1032, or x 1/16 - 72); these feed the
-//     A operand of mma.sync.m16n8k16 (f16 inputs, fp32 accumulate).  The integer/logic pipe runs at half
-//     rate on this SM and is the scarce resource, so the unpack is kept to five such instructions per
-//     eight weights and the loop bookkeeping is pared down.
-//   * X is staged once per CTA as fp16: each (token, 128-chunk) is scaled by an exact power of two so
-//     that its largest magnitude sits in [2^14, 2^15) -- bf16 mantissas fit fp16 exactly, and anything the
-//     conversion could lose is below 2^-29 of the chunk's largest term.  The power of two is multiplied
-//     back in fp32 together with the group scale.  The contraction index of an mma is a dummy, so the
-//     pairing {p, p+4} the unpack produces is matched by permuting X when it is staged; the weights are
-//     never shuffled.  Tokens sit on the n-side of the mma (8 per tile, two tiles for M > 8).
-//   * Scale: a chunk lies in one group, so the exact integer-valued partial sum of the chunk is scaled
-//     once in fp32 (more exact than rounding (q - 8) * s per weight).  Optionally the -8 is folded into one
-//     fp32 correction per chunk instead of the per-register FMA (fewer instructions, fp32 cancellation).
-//     For G < 128 each lane scales its own words in bf16 (the rounding the reference's tensor-core path
+// Structure (HBM-bound: every weight byte is read exactly once, X is tiny and lives in shared memory):
+//   * Persistent CTAs: two half-SM CTAs per SM where they fit (8 consumer warps + producer + reducer), else one wide
+//     CTA (14 or 16 consumer warps); the host picks with a cost model.  Lane 0 of the producer warp streams the
+//     packed weights of a 32-row group into a shared-memory ring with tiled TMA loads through a tensor map over Wq:
+//     boxes of 32 rows x 128 bytes (two K chunks) with the 128-byte swizzle, NCW/2 boxes per stage, completion counted
+//     on an mbarrier; several stages are in flight from the first instruction.  (Per-row untiled bulk copies were
+//     measured first: the TMA unit retires about one copy per 70 cycles whatever its size, so 1 KB row segments cap
+//     near 4 TB/s; tiled boxes reach the copy-kernel bandwidth.)  The other producer lanes copy the stage's scales
+//     with cp.async (8 or 16 bytes per copy) onto the same mbarrier: under the weight stream a dependent global load
+//     costs a microsecond or more, so the consumers never issue one.
+//   * NCW consumer warps each take one 128-wide K chunk of the stage for both 16-row blocks.  A lane reads 16 bytes
+//     (32 nibbles) per row with one 128-bit shared load; the swizzle plus a fixed permutation of which tile row feeds
+//     which mma row makes those loads bank-conflict free.
+//   * Launched with programmatic stream serialization: the weight stream starts while the previous kernel of the
+//     stream drains; X, Y and scratch are touched only after griddepcontrol.wait.  Every load of activations, scales
+//     and norm weights goes to L2 (ld.global.cg): under such a launch the SM's L1 is not invalidated between the
+//     producer of the data and the load.
+//   * K reduction: inside the mma across the four lanes of a quad, then across warps through shared memory: the
+//     consumer warps drop their partial sums of a finished row group into one of two buffers and move on, a reducer
+//     warp sums them and stores Y (mbarrier hand-off, nobody blocks).  Only when K is split across CTAs to fill the
+//     machine, fp32 partials go through scratch memory and are summed in fixed order by the last CTA to arrive (an
+//     atomic counter per row group; nobody waits on anybody, the result is deterministic).
+//   * Optional prologue: the operator that precedes the linear (add + RMSNorm, SwiGLU) is evaluated while X is staged.
+//   * Optional tensor-parallel epilogue: outputs go straight into the gathered row of every rank (peer stores), one
+//     arrival signal per launch and rank; the consumer side waits on its rank's counter before it reads X.
+//
+// Arithmetic, by mode:
+//   * integer (default for G % 128 == 0): (w & 0x0F0F0F0F) holds the four even-k nibbles of a word as bytes,
+//     (w & 0xF0F0F0F0) the four odd-k nibbles times 16: ready-made unsigned A fragments of mma.sync.m16n8k32 (s32
+//     accumulate), two LOP3 per eight weights, no shift, no conversion.  X is staged as block fixed point: per
+//     (token, 128-chunk) scaled by a power of two so that the largest magnitude lands in [2^14, 2^15) (or [2^22, 2^23)),
+//     rounded to an integer and split into 2 (or 3) byte planes, the low ones unsigned, the top one signed.  Every
+//     plane has its own accumulators, even and odd nibbles apart; one combination per chunk gives
+//     16 sum_k (q_k - 8) v_k exactly -- the zero-point is the initial value of an accumulator -- then one
+//     int-to-float conversion, times group scale and the chunk's power of two, fp32 accumulation over the chunks.
+//   * fp16 (kFlagFloatX): one shift and four LOP3 per word turn eight nibbles into four fp16x2 registers
+//     {1024 + q[p], 1024 + q[p+4]} / {1024 + 16 q[p], 1024 + 16 q[p+4]}; one packed-half FMA per register gives q - 8
+//     exactly; mma.sync.m16n8k16 (f16 inputs, fp32 accumulate).  X is staged as fp16 after an exact power-of-two
+//     normalisation per (token, chunk).  With kFlagFoldZeroPoint the -8 is one fp32 correction per chunk instead.
+//     The contraction index of an mma is a dummy, so the pairing {p, p+4} the unpack produces is matched by permuting
+//     X when it is staged; the weights are never shuffled.
+//   * generic (G < 128): each lane scales its own words in bf16 (the rounding the reference's tensor-core path
 //     applies) on a bf16 mma.
-//   * K reduction: inside the mma across the four lanes of a quad, then across warps through shared
-//     memory: the consumer warps drop their partial sums of a finished row group into one of two buffers
-//     and move on, a reducer warp sums them and stores Y (mbarrier hand-off, nobody blocks).  Only when K
-//     is split across CTAs to fill the machine, fp32 partials go through scratch memory and are summed in
-//     fixed order by the last CTA to arrive (an atomic counter per row group; nobody waits on anybody, the
-//     result is deterministic).
+//   Tokens sit on the n-side of the mma (8 per tile, two tiles for M > 8).  The integer/logic pipe runs at half rate
+//   on this SM and a warp issues about one instruction per ten cycles at the occupancy this kernel reaches, so the
+//   instruction count on a warp's path, not the issue-slot utilisation, sets the run time.
 #include <algorithm>
 #include <cstdio>
 #include <type_traits>

@@ -90,3 +90,41 @@ def test_shard_rows_partition():
 def test_gather_rows_single_rank_is_identity():
     t = [torch.arange(6.0).view(2, 3)]
     assert gather_rows(t, 1)[0] is t[0]
+
+
+def test_tp_descriptor_column_mapping():
+    """make_tp_desc against the kernel's rule (tp_column in csrc/w4_gemv.cu): local column n of a shard made of up to
+    three row-concatenated pieces goes to seg_dst[i] + (n - start of piece i).  Reassembling every rank's columns
+    must give each gathered column exactly once, in q | k | v order."""
+    from nanoserve_b200.ops import make_tp_desc
+
+    def column(d, n):
+        c = d.seg_dst[0] + n
+        if n >= d.seg_end[0]:
+            c = d.seg_dst[1] + (n - d.seg_end[0])
+        if n >= d.seg_end[1]:
+            c = d.seg_dst[2] + (n - d.seg_end[1])
+        return c
+
+    for world, widths in [(1, [64]), (2, [3584, 512, 512]), (4, [18944, 18944]), (8, [3584])]:
+        total, seen = sum(widths), {}
+        for r in range(world):
+            pieces, off = [], 0
+            for w in widths:
+                pieces.append((w // world, off + r * (w // world)))
+                off += w
+            d = make_tp_desc(y_peers=[1] * world, sig_peers=[1] * world, ld=total, pieces=pieces)
+            assert d.world == world and d.ld == total
+            n_local = sum(w // world for w in widths)
+            for n in range(n_local):
+                c = column(d, n)
+                assert c not in seen, (world, widths, r, n)
+                seen[c] = (r, n)
+        assert sorted(seen) == list(range(total))
+        # piece i of rank r is contiguous and starts where the gathered piece starts plus r shards
+        off = 0
+        for i, w in enumerate(widths):
+            for r in range(world):
+                start_local = sum(x // world for x in widths[:i])
+                assert seen[off + r * (w // world)] == (r, start_local)
+            off += w
