@@ -499,14 +499,19 @@ __device__ __forceinline__ bool tp_wait(const GemvTp& tp, volatile int* abort_fl
 }
 
 // MT: token tiles of 8 (1 or 2).  NCW: consumer warps (= chunks per stage, even).  MODE: see kMode*.
-template <int MT, int NCW, int MODE>
+// CPW: K chunks a consumer warp takes per ring stage (2: a whole 128-byte box; integer modes with staged scales only).
+// An iteration of the consumer loop costs about a quarter of a microsecond of latency whatever it contains, so
+// fewer, fatter iterations are cheaper.
+template <int MT, int NCW, int MODE, int CPW>
 __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1)
     w4_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemvParams p) {
-  constexpr int kStageBytes = (NCW / 2) * kBoxBytes;
+  constexpr int kSC = NCW * CPW;  // chunks per stage
+  constexpr int kStageBytes = (kSC / 2) * kBoxBytes;
   constexpr int kConsumerThreads = NCW * 32;
   constexpr bool kHalf = MODE != kModeGeneric;  // a chunk lies in one group: its sum is scaled once, in fp32
   constexpr int L = mode_limbs(MODE);           // bytes per staged value of X on the integer path, else 0
   constexpr bool kI8 = L > 0;
+  static_assert(CPW == 1 || (CPW == 2 && kI8), "two chunks per warp: integer modes only");
   constexpr int kXChunk = x_chunk_bytes(MODE);
   extern __shared__ __align__(1024) unsigned char smem[];
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
@@ -521,7 +526,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
   const uint32_t xs_base = smem_u32(smem + kHeaderBytes + red_bytes(NCW, p.M) + xinfo_bytes);
   const int xs_bytes = (p.M * p.xs_m_stride + 127) & ~127;
   // scales of each ring stage: [32 rows][NCW chunks] bf16, filled by the producer warp with cp.async
-  constexpr int kScStage = kHalf ? kRowsPerGroup * NCW * 2 : 0;
+  constexpr int kScStage = kHalf ? kRowsPerGroup * kSC * 2 : 0;
   const uint32_t ring_base = (xs_base + xs_bytes + 1023) & ~1023u;  // swizzled boxes: 1024-byte aligned
   const uint32_t sc_base = ring_base + p.nstages * kStageBytes;
   const bool sc_async = kHalf && p.sc_async;
@@ -556,8 +561,8 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       const int row0 = rg * kRowsPerGroup;
       const bool s_ok = row0 + lane < p.N;
       const __nv_bfloat16* s_lane = p.S + (size_t)(s_ok ? row0 + lane : 0) * p.KG;
-      for (int c0 = cb; c0 < ce; c0 += NCW) {
-        const int nbox = (min(NCW, ce - c0) + 1) >> 1;
+      for (int c0 = cb; c0 < ce; c0 += kSC) {
+        const int nbox = (min(kSC, ce - c0) + 1) >> 1;
         if (lane == 0) mbar_wait_backoff<100>(bar_empty + 8 * s, ph ^ 1, abort_flag);
         __syncwarp();
         if (lane == 0) {
@@ -568,20 +573,20 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
                         bar_full + 8 * s);
         }
         if (sc_async) {
-          const uint32_t dst = sc_base + s * kScStage + lane * (NCW * 2);
+          const uint32_t dst = sc_base + s * kScStage + lane * (kSC * 2);
           auto copy_row = [&](auto width) {  // the lane's NCW scales of this stage in copies of `width` bytes
             constexpr int W = decltype(width)::value;
 #pragma unroll
-            for (int i = 0; i < NCW * 2 / W; ++i) {
+            for (int i = 0; i < kSC * 2 / W; ++i) {
               const int c = c0 + i * (W / 2);
               const int left = s_ok ? (ce - c) * 2 : 0;  // valid source bytes from this chunk on
               cp_async<W>(dst + W * i, s_lane + (left > 0 ? c : cb), (uint32_t)min(W, max(0, left)));
             }
           };
           if (p.sc_async == 16) {
-            if constexpr (NCW % 8 == 0) copy_row(std::integral_constant<int, 16>{});
+            if constexpr (kSC % 8 == 0) copy_row(std::integral_constant<int, 16>{});
           } else if (p.sc_async == 8) {
-            if constexpr (NCW % 4 == 0) copy_row(std::integral_constant<int, 8>{});
+            if constexpr (kSC % 4 == 0) copy_row(std::integral_constant<int, 8>{});
           } else {
             copy_row(std::integral_constant<int, 4>{});
           }
@@ -656,9 +661,11 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
     // memory access phase land in opposite halves of the swizzled 128-byte rows (no bank conflicts)
     const int gr = (g >> 1) | ((g & 1) << 2);
     const int ctid = tid;  // consumer warps are warps 0..NCW-1
-    // chunk `warp` of a stage sits in box warp/2, 64-byte half warp%2; 16-byte unit index XOR (row % 8 = gr)
-    const uint32_t w_lane_addr = ring_base + (warp >> 1) * kBoxBytes + gr * 128 +
-                                 ((uint32_t(((warp & 1) << 2) | t) ^ uint32_t(gr)) << 4);
+    // chunk j of a stage sits in box j / 2, 64-byte half j % 2; 16-byte unit index XOR (row % 8 = gr).  With one
+    // chunk per warp j = warp; with two, the warp owns box `warp` and takes half 0 then half 1.
+    const uint32_t w_lane_addr = ring_base + (CPW == 2 ? warp : (warp >> 1)) * kBoxBytes + gr * 128;
+    const uint32_t w_unit0 = (uint32_t(((CPW == 2 ? 0 : (warp & 1)) << 2) | t) ^ uint32_t(gr)) << 4;
+    const uint32_t w_unit1 = (uint32_t(4 | t) ^ uint32_t(gr)) << 4;  // second half of the box (CPW == 2)
     // unpack constants, pinned in registers so that every (x & mask) | magic is a single LOP3
     uint32_t k_mask_lo = 0x000F000Fu, k_mask_hi = 0x00F000F0u, k_magic = 0x64006400u;
     uint32_t k_n1032 = 0xE408E408u;  // fp16 -1032 twice
@@ -668,8 +675,8 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
     uint32_t k_nib_lo = 0x0F0F0F0Fu, k_nib_hi = 0xF0F0F0F0u;  // integer path: even / odd nibbles of a word as bytes
     asm volatile("" : "+r"(k_nib_lo), "+r"(k_nib_hi));
     const bool multi_token = p.M > 1;
-    // this lane's scales of a stage: rows gr (+8, +16, +24) of the stage's [32][NCW] block, column = its chunk
-    const uint32_t sc_lane = sc_base + gr * (NCW * 2) + warp * 2;
+    // this lane's scales of a stage: rows gr (+8, +16, +24) of the stage's [32][chunks] block, column = its chunk
+    const uint32_t sc_lane = sc_base + gr * (kSC * 2) + (CPW * warp) * 2;
     const int nstages = p.nstages, gdiv = p.gdiv;
     // Launched with programmatic stream serialization this kernel may start while the previous one is still
     // running: the weight stream (constant data) is already flowing; X, produced upstream, is touched only
@@ -714,8 +721,8 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         const int m = mt * 8 + g;
         const bool real = m < p.M;
         xreal[mt] = real;
-        xaddr[mt] = real ? xs_base + m * p.xs_m_stride + warp * kXChunk + t * 16 : zero_base + t * 16;
-        xstep[mt] = real ? NCW * kXChunk : 0;
+        xaddr[mt] = real ? xs_base + m * p.xs_m_stride + (CPW * warp) * kXChunk + t * 16 : zero_base + t * 16;
+        xstep[mt] = real ? kSC * kXChunk : 0;
       }
       // per-(token, chunk) info of the two accumulator columns (tokens mt*8 + 2t, +1) of this lane;
       // padding tokens read a zero pair (their accumulators are zero anyway)
@@ -728,10 +735,10 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         for (int q = 0; q < 2; ++q) {
           const int m = mt * 8 + 2 * t + q;
           const bool real = m < p.M;
-          xi[mt][q] = real ? xinfo + m * nch + warp : reinterpret_cast<const float2*>(smem + kZeroOffset);
-          xi8[mt][q] = real ? reinterpret_cast<const int4*>(xinfo) + m * nch + warp
+          xi[mt][q] = real ? xinfo + m * nch + CPW * warp : reinterpret_cast<const float2*>(smem + kZeroOffset);
+          xi8[mt][q] = real ? reinterpret_cast<const int4*>(xinfo) + m * nch + CPW * warp
                             : reinterpret_cast<const int4*>(smem + kZeroOffset);
-          xi_step[mt][q] = real ? NCW : 0;
+          xi_step[mt][q] = real ? kSC : 0;
         }
       // fast path: lane i fetches the scale of row row0 + i; the quad layout is rebuilt with shuffles
       const int n_lane = row0 + lane;
@@ -752,7 +759,8 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         if (!sc_async && s_valid && cf < ce)
           srow_next = ld_l2(reinterpret_cast<const unsigned short*>(s_lane) + (gdiv == 1 ? cf : cf / gdiv));
       }
-      for (int c = cb + warp, c0 = cb; c0 < ce; c0 += NCW, c += NCW) {
+      for (int c0 = cb; c0 < ce; c0 += kSC) {
+        const int c = c0 + CPW * warp;  // this warp's (first) chunk of the stage
         const bool active = c < ce;
 
         // scales: the fast path fetched this stage's scale one stage ago and now fetches the next one, so
@@ -760,7 +768,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         uint32_t sc2[2][2] = {{0u, 0u}, {0u, 0u}};
         const uint32_t srow = srow_next;
         if constexpr (kHalf) {
-          const int cn = c + NCW;
+          const int cn = c + kSC;
           srow_next = 0u;
           if (!sc_async && s_valid && cn < ce)
             srow_next = ld_l2(reinterpret_cast<const unsigned short*>(s_lane) + (gdiv == 1 ? cn : cn / gdiv));
@@ -785,7 +793,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         if (lane == 0) mbar_wait(bar_full + 8 * s, ph, abort_flag);
         __syncwarp();
 
-        if (active) {
+#pragma unroll
+        for (int h = 0; h < CPW; ++h)
+        if (c + h < ce) {
           if constexpr (kI8) {
           // ---- integer path: nibbles stay integers.  (w & 0x0F0F0F0F) holds the four even-k nibbles of a word as
           // bytes, (w & 0xF0F0F0F0) the four odd-k nibbles times 16: both are ready-made u8 A fragments of
@@ -800,13 +810,13 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 #pragma unroll
               for (int jj = 0; jj < 2; ++jj) {
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);  // padding tokens: no load at all (fewer wavefronts)
-                if (xreal[mt]) v = lds128(xaddr[mt] + l * 128 + jj * 64);
+                if (xreal[mt]) v = lds128(xaddr[mt] + h * kXChunk + l * 128 + jj * 64);
                 xb[mt][l][4 * jj + 0] = v.x;
                 xb[mt][l][4 * jj + 1] = v.y;
                 xb[mt][l][4 * jj + 2] = v.z;
                 xb[mt][l][4 * jj + 3] = v.w;
               }
-          const uint32_t wa = w_lane_addr + s * kStageBytes;
+          const uint32_t wa = w_lane_addr + s * kStageBytes + (h ? w_unit1 : w_unit0);
           uint4 wv[2][2];
 #pragma unroll
           for (int rb = 0; rb < 2; ++rb) {
@@ -816,13 +826,13 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           int4 info[MT][2];
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            info[mt][0] = *xi8[mt][0];
-            info[mt][1] = *xi8[mt][1];
+            info[mt][0] = *(xi8[mt][0] + (xi_step[mt][0] ? h : 0));
+            info[mt][1] = *(xi8[mt][1] + (xi_step[mt][1] ? h : 0));
           }
           uint32_t scr[4] = {0u, 0u, 0u, 0u};  // scales of rows gr, gr + 8, gr + 16, gr + 24 of the stage
           if (sc_async) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) scr[i] = lds_u16(sc_lane + s * kScStage + i * (8 * NCW * 2));
+            for (int i = 0; i < 4; ++i) scr[i] = lds_u16(sc_lane + h * 2 + s * kScStage + i * (8 * kSC * 2));
           }
 #pragma unroll
           for (int rb = 0; rb < 2; ++rb) {
@@ -891,7 +901,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
               xf[mt][4 * j + 3] = v.w;
             }
           }
-          const uint32_t wa = w_lane_addr + s * kStageBytes;
+          const uint32_t wa = w_lane_addr + s * kStageBytes + w_unit0;
           uint4 wv[2][2];
 #pragma unroll
           for (int rb = 0; rb < 2; ++rb) {
@@ -909,7 +919,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           uint32_t scr[4] = {0u, 0u, 0u, 0u};
           if (sc_async) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) scr[i] = lds_u16(sc_lane + s * kScStage + i * (8 * NCW * 2));
+            for (int i = 0; i < 4; ++i) scr[i] = lds_u16(sc_lane + s * kScStage + i * (8 * kSC * 2));
           }
 #pragma unroll
           for (int rb = 0; rb < 2; ++rb) {
@@ -1047,7 +1057,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 
 // ------------------------------------------------------------------ host side
 struct GemvPlan {
-  int mt, ncw, mode, nslices, cps, nstages, grid;
+  int mt, ncw, cpw, mode, nslices, cps, nstages, grid;
   bool pdl;
   int ctas_per_sm;
   size_t smem;
@@ -1066,16 +1076,18 @@ size_t smem_without_ring(int M, int mode, int ncw, int cps) {
 // tile costs its chunk count rounded up to whole stages (idle warps in a short last stage are lost
 // time), plus a fixed reduction overhead; split-K tiles pay the scratch round trip as well.  The slice
 // count with the smallest makespan over the persistent CTAs wins.
-bool plan_for_width(int M, int N, int K, int ncw, int mt, int mode, int flags, int sm_count, size_t partial_cap,
-                    int counters_cap, GemvPlan* out) {
+bool plan_for_width(int M, int N, int K, int ncw, int cpw, int mt, int mode, int flags, int sm_count,
+                    size_t partial_cap, int counters_cap, GemvPlan* out) {
   GemvPlan pl{};
   pl.mt = mt;
   pl.mode = mode;
   pl.ncw = ncw;
+  pl.cpw = cpw;
+  const int sc = ncw * cpw;  // chunks per stage
   const int nchunks = (K + kChunkK - 1) / kChunkK;
   const int nrg = (N + kRowsPerGroup - 1) / kRowsPerGroup;
   // a ring stage: the weight boxes plus (fast paths) the stage's scales, [32 rows][ncw] bf16
-  const int stage_bytes = (ncw / 2) * kBoxBytes + (mode == kModeGeneric ? 0 : kRowsPerGroup * ncw * 2);
+  const int stage_bytes = (sc / 2) * kBoxBytes + (mode == kModeGeneric ? 0 : kRowsPerGroup * sc * 2);
   const int grid = std::max(1, sm_count);
   // Two CTAs per SM when both fit (shared memory: half of 227 KB minus the per-CTA reserve; registers: the narrow
   // MT == 1 kernels are compiled for it): more warps to hide latency, and one CTA's tail overlaps the other's
@@ -1087,17 +1099,20 @@ bool plan_for_width(int M, int N, int K, int ncw, int mt, int mode, int flags, i
   for (int ns = 1; ns <= max_ns; ++ns) {
     const int cps = (nchunks + ns - 1) / ns;
     if ((nchunks + cps - 1) / cps != ns) continue;
+    if (cpw == 2 && ns > 1 && (cps & 1)) continue;  // slices start on a box boundary, scale copies stay aligned
     if (ns > 1) {
       if ((size_t)ns * M * N * sizeof(float) > partial_cap) continue;
       if (nrg > counters_cap) continue;
     }
     const size_t fixed = smem_without_ring(M, mode, ncw, cps);
     const long tiles = (long)nrg * ns;
-    const int stage_chunks = ((cps + ncw - 1) / ncw) * ncw;
+    const int iters = (cps + sc - 1) / sc;  // ring stages per tile
+    const int stage_chunks = iters * sc;
     // the memory system moves only real bytes, the warps pay for padded stages: weigh them equally
     // fixed cost of a tile (hand-off to the reducer) and of a split-K tile (scratch round trip, measured to be
     // dear: splitting the 3584 x 18944 projection five ways was slower than leaving 36 SMs idle)
-    const double tile_cost = 0.5 * (cps + stage_chunks) + 4.0 + (ns > 1 ? 12.0 : 0.0);
+    // ... and of an iteration of the consumer loop (wait, release, bookkeeping: 0.24 us measured, about two chunks)
+    const double tile_cost = 0.5 * (cps + stage_chunks) + 2.0 * iters + (ns > 1 ? 12.0 : 0.0);
     for (int ctas = 2; ctas >= 1; --ctas) {
       if (ctas == 2 && !(mt == 1 && ncw <= 12 && fixed + 2 * (size_t)stage_bytes <= kHalfSmem)) continue;
       if (ctas == 1 && fixed + 2 * (size_t)stage_bytes > (size_t)kSmemLimit) continue;
@@ -1156,19 +1171,27 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
   // (8 consumer warps, two per SM when they fit); the cost model picks.  Bits 4-7 of the flags force a
   // width (diagnostics).  Two token tiles need the registers of the 8-warp CTA.
   const int forced = ((flags >> 4) & 0xF) * 2;
+  // Two chunks per warp and stage: integer modes whose scales can be staged with aligned copies (one scale per chunk,
+  // an even number of scales per row).  Bits 10 / 11 of the flags force two / one (diagnostics).
+  const bool cpw2_ok = mode_limbs(mode) > 0 && mt == 1 && G == 128 && (K / G) % 2 == 0 && !(flags & 0x800) &&
+                       (flags & 0x400);  // opt-in until measured on every shape
   if (mt == 1 && !(flags & kFlagNarrowCta)) {
     const int widths[3] = {16, 14, 8};
     for (int w : widths) {
       if (forced && w != forced) continue;
-      GemvPlan pl;
-      if (plan_for_width(M, N, K, w, mt, mode, flags, sm_count, partial_cap, counters_cap, &pl) &&
-          (!have || pl.cost < best.cost)) {
-        best = pl;
-        have = true;
+      for (int cpw = cpw2_ok ? 2 : 1; cpw >= 1; --cpw) {
+        if (cpw == 1 && cpw2_ok && (flags & 0x400)) continue;
+        if (cpw == 2 && w == 16) continue;  // not instantiated: 14 x 2 covers the wide case
+        GemvPlan pl;
+        if (plan_for_width(M, N, K, w, cpw, mt, mode, flags, sm_count, partial_cap, counters_cap, &pl) &&
+            (!have || pl.cost < best.cost)) {
+          best = pl;
+          have = true;
+        }
       }
     }
   }
-  if (!have) have = plan_for_width(M, N, K, 8, mt, mode, flags, sm_count, partial_cap, counters_cap, &best);
+  if (!have) have = plan_for_width(M, N, K, 8, 1, mt, mode, flags, sm_count, partial_cap, counters_cap, &best);
   if (!have) return false;
   best.mode = mode;
   best.pdl = (flags & kFlagNoPdl) == 0;
@@ -1176,9 +1199,9 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
   return true;
 }
 
-template <int MT, int NCW, int MODE>
+template <int MT, int NCW, int MODE, int CPW>
 int launch_variant(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan& pl, cudaStream_t stream) {
-  auto kernel = w4_gemv_kernel<MT, NCW, MODE>;
+  auto kernel = w4_gemv_kernel<MT, NCW, MODE, CPW>;
   // Raising the dynamic shared-memory limit is idempotent and cheap; doing it on every launch keeps
   // the call correct on every device of a multi-GPU process without per-device bookkeeping.
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
@@ -1203,11 +1226,17 @@ int launch_variant(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan&
 template <int MT, int NCW>
 int launch_mode(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan& pl, cudaStream_t stream) {
   switch (pl.mode) {
-    case kModeExact: return launch_variant<MT, NCW, kModeExact>(tmap, p, pl, stream);
-    case kModeFold: return launch_variant<MT, NCW, kModeFold>(tmap, p, pl, stream);
-    case kModeI8x2: return launch_variant<MT, NCW, kModeI8x2>(tmap, p, pl, stream);
-    case kModeI8x3: return launch_variant<MT, NCW, kModeI8x3>(tmap, p, pl, stream);
-    default: return launch_variant<MT, NCW, kModeGeneric>(tmap, p, pl, stream);
+    case kModeExact: return launch_variant<MT, NCW, kModeExact, 1>(tmap, p, pl, stream);
+    case kModeFold: return launch_variant<MT, NCW, kModeFold, 1>(tmap, p, pl, stream);
+    case kModeI8x2:
+      if constexpr (MT == 1 && NCW != 16)
+        if (pl.cpw == 2) return launch_variant<MT, NCW, kModeI8x2, 2>(tmap, p, pl, stream);
+      return launch_variant<MT, NCW, kModeI8x2, 1>(tmap, p, pl, stream);
+    case kModeI8x3:
+      if constexpr (MT == 1 && NCW != 16)
+        if (pl.cpw == 2) return launch_variant<MT, NCW, kModeI8x3, 2>(tmap, p, pl, stream);
+      return launch_variant<MT, NCW, kModeI8x3, 1>(tmap, p, pl, stream);
+    default: return launch_variant<MT, NCW, kModeGeneric, 1>(tmap, p, pl, stream);
   }
 }
 
@@ -1259,6 +1288,7 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
   if (!ws.status) return kErrWorkspace;
   const bool have_scratch = ws.partial && ws.counters;
   GemvPlan pl;
+  if (reinterpret_cast<uintptr_t>(S) & 3) flags |= 0x800;  // scale copies need a 4-byte aligned base: one chunk per warp
   // the last counter is kept for the tensor-parallel epilogue's CTA count
   if (!make_plan(M, N, K, G, have_scratch ? flags : (flags | kFlagForceNoSplitK), sm_count,
                  ws.partial_bytes, ws.n_counters - 1, &pl))
@@ -1291,7 +1321,7 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
     // keeps all of them aligned
     for (int w = 16; w >= 4 && !p.sc_async; w >>= 1) {
       const int e = w / 2;
-      if ((reinterpret_cast<uintptr_t>(S) % w) == 0 && p.KG % e == 0 && pl.ncw % e == 0 &&
+      if ((reinterpret_cast<uintptr_t>(S) % w) == 0 && p.KG % e == 0 && (pl.ncw * pl.cpw) % e == 0 &&
           (pl.nslices == 1 || pl.cps % e == 0))
         p.sc_async = w;
     }
