@@ -74,9 +74,17 @@ constexpr int kNormSsOffset = 768;     // float [16 tokens][16 warps]
 constexpr int kNormInvOffset = 1792;   // float [16 tokens]
 constexpr int kBoxBytes = kRowsPerGroup * 128;  // 32 rows x 128 B (two chunks), swizzled
 
-enum : int { kModeGeneric = 0, kModeExact = 1, kModeFold = 2, kModeI8x2 = 3, kModeI8x3 = 4 };
+// kModeI8c3: the integer path with the three byte planes of X as COLUMNS of the mma's B operand instead of three
+// mma's per fragment: with M <= 2 the eight columns hold (token, plane) pairs that would otherwise be padding, so
+// 22-bit fixed point costs half the tensor instructions of the 16-bit two-plane form.  Planes are balanced base-256
+// digits (all signed).
+enum : int { kModeGeneric = 0, kModeExact = 1, kModeFold = 2, kModeI8x2 = 3, kModeI8x3 = 4, kModeI8c3 = 5 };
 // bytes of one staged (token, 128-chunk) of X and of its info record
-__host__ __device__ constexpr int mode_limbs(int mode) { return mode == kModeI8x2 ? 2 : (mode == kModeI8x3 ? 3 : 0); }
+__host__ __device__ constexpr int mode_limbs(int mode) {
+  return mode == kModeI8x2 ? 2 : ((mode == kModeI8x3 || mode == kModeI8c3) ? 3 : 0);
+}
+// columns of partial sums a warp hands to the reducer: tokens, or (token, plane) pairs
+__host__ __device__ constexpr int mode_cols(int mode, int M) { return mode == kModeI8c3 ? 3 * M : M; }
 __host__ __device__ constexpr int x_chunk_bytes(int mode) { return mode_limbs(mode) ? 128 * mode_limbs(mode) : 256; }
 __host__ __device__ constexpr int x_info_bytes(int mode) { return mode_limbs(mode) ? 16 : 8; }
 // What the kernel does to its input before the product (the operators that precede a linear in a decoder layer)
@@ -373,10 +381,14 @@ __device__ __forceinline__ void stage_x_f16(const GemvParams& p, uint32_t xs_bas
 // xinfo[token][chunk] = { bits of 2^(e - 127 - (8L - 2)) / 16, -128 * sum_k limb_l(v_k) for l = 0, 1, 2 }: the
 // zero-point 8, times the 16 that the nibble products carry, as the initial value of an accumulator.  A chunk that
 // holds an inf or a nan gets a nan factor (its integers are meaningless), so the outputs become nan.
-template <int CT, int L>
+// COL (kModeI8c3): one bit less of range (largest magnitude in [2^(8L-3), 2^(8L-2))) and balanced digits in
+// [-128, 127] for every plane -- bytes of (v + 0x808080) ^ 0x808080 -- so that all planes are signed operands of one
+// mma; the two 64-byte halves of a plane are swapped for odd planes, which puts the planes of neighbouring columns into
+// different shared-memory banks.
+template <int CT, int L, bool COL>
 __device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base, int4* xinfo, const float* inv,
                                            int cb, int ce, int ctid) {
-  constexpr int B = 8 * L;
+  constexpr int B = 8 * L - (COL ? 1 : 0);
   const int nch = ce - cb;
   const int items = p.M * nch * 8;
   const int items_pad = (items + 31) & ~31;
@@ -412,6 +424,10 @@ __device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base
     for (int i = 0; i < 8; ++i) {
       v[2 * i] = __float2int_rn(__uint_as_float(w[i] << 16) * down);
       v[2 * i + 1] = __float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * down);
+      if constexpr (COL) {
+        v[2 * i] = (int)(((uint32_t)v[2 * i] + 0x00808080u) ^ 0x00808080u);
+        v[2 * i + 1] = (int)(((uint32_t)v[2 * i + 1] + 0x00808080u) ^ 0x00808080u);
+      }
     }
     int csum[3] = {0, 0, 0};
 #pragma unroll
@@ -423,7 +439,7 @@ __device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base
       };
       const uint4 o = make_uint4(pack(0, 2, 4, 6), pack(8, 10, 12, 14), pack(1, 3, 5, 7), pack(9, 11, 13, 15));
       int c;
-      if (l == L - 1) {
+      if (COL || l == L - 1) {
         c = __dp4a((int)o.x, 0x01010101, 0);
         c = __dp4a((int)o.y, 0x01010101, c);
         c = __dp4a((int)o.z, 0x01010101, c);
@@ -439,7 +455,8 @@ __device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base
       c += __shfl_xor_sync(0xffffffffu, c, 2);
       c += __shfl_xor_sync(0xffffffffu, c, 1);
       csum[l] = -128 * c;
-      if (valid) sts128(xs_base + m * p.xs_m_stride + ch * (128 * L) + l * 128 + u * 16, o);
+      const int uu = COL ? (u ^ ((l & 1) << 2)) : u;
+      if (valid) sts128(xs_base + m * p.xs_m_stride + ch * (128 * L) + l * 128 + uu * 16, o);
     }
     if (valid && u == 0) xinfo[m * nch + ch] = make_int4((int)up_bits, csum[0], csum[1], csum[2]);
   }
@@ -511,6 +528,10 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
   constexpr bool kHalf = MODE != kModeGeneric;  // a chunk lies in one group: its sum is scaled once, in fp32
   constexpr int L = mode_limbs(MODE);           // bytes per staged value of X on the integer path, else 0
   constexpr bool kI8 = L > 0;
+  constexpr bool kCol = MODE == kModeI8c3;      // planes as columns of B: one plane per lane
+  constexpr int LP = kCol ? 1 : L;              // planes a lane holds per fragment
+  static_assert(!kCol || MT == 1, "planes as columns: at most 8 columns");
+  const int ncols = mode_cols(MODE, p.M);       // columns of partial sums per warp
   static_assert(CPW == 1 || (CPW == 2 && kI8), "two chunks per warp: integer modes only");
   constexpr int kXChunk = x_chunk_bytes(MODE);
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -521,9 +542,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
   const uint32_t bar_red_empty = bar_red_full + 16;           // [2] the reducer has consumed them
   const uint32_t zero_base = smem_u32(smem + kZeroOffset);
   float* red = reinterpret_cast<float*>(smem + kHeaderBytes);
-  float2* xinfo = reinterpret_cast<float2*>(smem + kHeaderBytes + red_bytes(NCW, p.M));
+  float2* xinfo = reinterpret_cast<float2*>(smem + kHeaderBytes + red_bytes(NCW, ncols));
   const int xinfo_bytes = (p.M * p.cps * x_info_bytes(MODE) + 127) & ~127;
-  const uint32_t xs_base = smem_u32(smem + kHeaderBytes + red_bytes(NCW, p.M) + xinfo_bytes);
+  const uint32_t xs_base = smem_u32(smem + kHeaderBytes + red_bytes(NCW, ncols) + xinfo_bytes);
   const int xs_bytes = (p.M * p.xs_m_stride + 127) & ~127;
   // scales of each ring stage: [32 rows][NCW chunks] bf16, filled by the producer warp with cp.async
   constexpr int kScStage = kHalf ? kRowsPerGroup * kSC * 2 : 0;
@@ -609,14 +630,24 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       const int sl = tile / p.nrg, rg = tile - sl * p.nrg;
       const int row0 = rg * kRowsPerGroup;
       const int b = tcount & 1;
-      const float* rbuf = red + b * (NCW * p.M * kRedPitch);
+      const float* rbuf = red + b * (NCW * ncols * kRedPitch);
       if (lane == 0) mbar_wait_backoff<100>(bar_red_full + 8 * b, (tcount >> 1) & 1, abort_flag);
       __syncwarp();
       const int n = row0 + lane;
       for (int tok = 0; tok < p.M; ++tok) {
         float sum = 0.f;
+        if constexpr (kCol) {
+          // columns 3 tok .. 3 tok + 2 are the byte planes of the token: sum over the warps, then recombine
+          float pl[3] = {0.f, 0.f, 0.f};
 #pragma unroll
-        for (int w = 0; w < NCW; ++w) sum += rbuf[(w * p.M + tok) * kRedPitch + lane];
+          for (int w = 0; w < NCW; ++w)
+#pragma unroll
+            for (int l = 0; l < 3; ++l) pl[l] += rbuf[(w * ncols + 3 * tok + l) * kRedPitch + lane];
+          sum = fmaf(fmaf(pl[2], 256.f, pl[1]), 256.f, pl[0]);
+        } else {
+#pragma unroll
+          for (int w = 0; w < NCW; ++w) sum += rbuf[(w * ncols + tok) * kRedPitch + lane];
+        }
         if (n < p.N) {
           if (p.nslices > 1)
             __stcg(p.partial + ((size_t)sl * p.M + tok) * p.N + n, sum);
@@ -704,7 +735,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           if (p.pro == kProAddRmsNorm && staged_slice < 0)
             rmsnorm_factors<kConsumerThreads>(p, reinterpret_cast<float*>(smem + kNormSsOffset), inv, ctid);
           if constexpr (kI8)
-            stage_x_i8<kConsumerThreads, L>(p, xs_base, reinterpret_cast<int4*>(xinfo), inv, cb, ce, ctid);
+            stage_x_i8<kConsumerThreads, L, kCol>(p, xs_base, reinterpret_cast<int4*>(xinfo), inv, cb, ce, ctid);
           else
             stage_x_f16<kConsumerThreads, MODE == kModeFold>(p, xs_base, xinfo, inv, cb, ce, ctid);
         }
@@ -716,12 +747,23 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       // B-fragment source of this lane: its token's staged X, or a block of zeros for padding tokens
       uint32_t xaddr[MT], xstep[MT];
       bool xreal[MT];
+      uint32_t jj_flip = 0;  // planes as columns: odd planes have their 64-byte halves swapped
+      int sel_a[2] = {0, 0};  // ... and the plane of accumulator columns 2t, 2t + 1
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        const int m = mt * 8 + g;
-        const bool real = m < p.M;
+        int m = mt * 8 + g;
+        bool real = m < p.M;
+        uint32_t plane_off = 0;
+        if constexpr (kCol) {  // column g of B is plane g % 3 of token g / 3
+          real = m < ncols;
+          const int tok = m / 3, l = m - 3 * tok;
+          m = tok;
+          plane_off = l * 128;
+          jj_flip = (l & 1) * 64;
+        }
         xreal[mt] = real;
-        xaddr[mt] = real ? xs_base + m * p.xs_m_stride + (CPW * warp) * kXChunk + t * 16 : zero_base + t * 16;
+        xaddr[mt] = real ? xs_base + m * p.xs_m_stride + (CPW * warp) * kXChunk + plane_off + t * 16
+                         : zero_base + t * 16;
         xstep[mt] = real ? kSC * kXChunk : 0;
       }
       // per-(token, chunk) info of the two accumulator columns (tokens mt*8 + 2t, +1) of this lane;
@@ -733,8 +775,14 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          const int m = mt * 8 + 2 * t + q;
-          const bool real = m < p.M;
+          int m = mt * 8 + 2 * t + q;
+          bool real = m < p.M;
+          if constexpr (kCol) {
+            real = m < ncols;
+            const int tok = m / 3;
+            sel_a[q] = m - 3 * tok;
+            m = tok;
+          }
           xi[mt][q] = real ? xinfo + m * nch + CPW * warp : reinterpret_cast<const float2*>(smem + kZeroOffset);
           xi8[mt][q] = real ? reinterpret_cast<const int4*>(xinfo) + m * nch + CPW * warp
                             : reinterpret_cast<const int4*>(smem + kZeroOffset);
@@ -802,15 +850,15 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           // mma.m16n8k32, so the unpack is two LOP3 per eight weights and no shift.  X arrives as L byte planes
           // ("limbs"); every plane gets its own s32 accumulators, even and odd nibbles apart (the odd ones carry the
           // factor 16), all combined once per chunk: T = sum_l 256^l (16 even_l + odd_l) = 16 sum_k (q_k - 8) v_k.
-          uint32_t xb[MT][L][8];
+          uint32_t xb[MT][LP][8];
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int l = 0; l < L; ++l)
+            for (int l = 0; l < LP; ++l)
 #pragma unroll
               for (int jj = 0; jj < 2; ++jj) {
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);  // padding tokens: no load at all (fewer wavefronts)
-                if (xreal[mt]) v = lds128(xaddr[mt] + h * kXChunk + l * 128 + jj * 64);
+                if (xreal[mt]) v = lds128(xaddr[mt] + h * kXChunk + l * 128 + ((jj * 64) ^ jj_flip));
                 xb[mt][l][4 * jj + 0] = v.x;
                 xb[mt][l][4 * jj + 1] = v.y;
                 xb[mt][l][4 * jj + 2] = v.z;
@@ -838,7 +886,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           for (int rb = 0; rb < 2; ++rb) {
             const uint32_t wl[4] = {wv[rb][0].x, wv[rb][0].y, wv[rb][0].z, wv[rb][0].w};
             const uint32_t wh[4] = {wv[rb][1].x, wv[rb][1].y, wv[rb][1].z, wv[rb][1].w};
-            int ae[MT][L][4], ao[MT][L][4];
+            int ae[MT][LP][4], ao[MT][LP][4];
 #pragma unroll
             for (int jj = 0; jj < 2; ++jj) {
               const uint32_t e0 = wl[2 * jj] & k_nib_lo, e1 = wh[2 * jj] & k_nib_lo;
@@ -848,16 +896,18 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 #pragma unroll
               for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int l = 0; l < L; ++l) {
+                for (int l = 0; l < LP; ++l) {
+                  const bool sgn = kCol || l == L - 1;  // signed planes: all balanced digits, or the top byte
                   if (jj == 0) {
-                    // the odd chain starts from the zero-point term of its limb, the even chain from zero
-                    const int c0 = l == 0 ? info[mt][0].y : (l == 1 ? info[mt][0].z : info[mt][0].w);
-                    const int c1 = l == 0 ? info[mt][1].y : (l == 1 ? info[mt][1].z : info[mt][1].w);
-                    imma_16832_init(l == L - 1, ae[mt][l], e0, e1, e2, e3, xb[mt][l][0], xb[mt][l][1], 0, 0);
-                    imma_16832_init(l == L - 1, ao[mt][l], o0, o1, o2, o3, xb[mt][l][2], xb[mt][l][3], c0, c1);
+                    // the odd chain starts from the zero-point term of its plane, the even chain from zero
+                    const int pa = kCol ? sel_a[0] : l, pb = kCol ? sel_a[1] : l;
+                    const int c0 = pa == 0 ? info[mt][0].y : (pa == 1 ? info[mt][0].z : info[mt][0].w);
+                    const int c1 = pb == 0 ? info[mt][1].y : (pb == 1 ? info[mt][1].z : info[mt][1].w);
+                    imma_16832_init(sgn, ae[mt][l], e0, e1, e2, e3, xb[mt][l][0], xb[mt][l][1], 0, 0);
+                    imma_16832_init(sgn, ao[mt][l], o0, o1, o2, o3, xb[mt][l][2], xb[mt][l][3], c0, c1);
                   } else {
-                    imma_16832(l == L - 1, ae[mt][l], e0, e1, e2, e3, xb[mt][l][4 * jj], xb[mt][l][4 * jj + 1]);
-                    imma_16832(l == L - 1, ao[mt][l], o0, o1, o2, o3, xb[mt][l][4 * jj + 2], xb[mt][l][4 * jj + 3]);
+                    imma_16832(sgn, ae[mt][l], e0, e1, e2, e3, xb[mt][l][4 * jj], xb[mt][l][4 * jj + 1]);
+                    imma_16832(sgn, ao[mt][l], o0, o1, o2, o3, xb[mt][l][4 * jj + 2], xb[mt][l][4 * jj + 3]);
                   }
                 }
             }
@@ -874,9 +924,11 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
               const float up0 = __int_as_float(info[mt][0].x), up1 = __int_as_float(info[mt][1].x);
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                if ((i & 1) && !multi_token) continue;  // one token: accumulator columns 1.. are padding
+                if (!kCol && (i & 1) && !multi_token) continue;  // one token: accumulator columns 1.. are padding
                 float f;
-                if constexpr (L == 2) {
+                if constexpr (kCol) {
+                  f = (float)(16 * ae[mt][0][i] + ao[mt][0][i]);  // this column's plane; planes meet in the reducer
+                } else if constexpr (L == 2) {
                   f = (float)((16 * ae[mt][1][i] + ao[mt][1][i]) * 256 + (16 * ae[mt][0][i] + ao[mt][0][i]));
                 } else {
                   const int th = (16 * ae[mt][2][i] + ao[mt][2][i]) * 256 + (16 * ae[mt][1][i] + ao[mt][1][i]);
@@ -1024,7 +1076,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 
       // ---- hand the per-warp partial sums of this tile to the reducer warp (two buffers in rotation)
       const int b = tcount & 1;
-      float* rbuf = red + b * (NCW * p.M * kRedPitch);
+      float* rbuf = red + b * (NCW * ncols * kRedPitch);
       if (lane == 0) mbar_wait(bar_red_empty + 8 * b, ((tcount >> 1) & 1) ^ 1, abort_flag);
       __syncwarp();
 #pragma unroll
@@ -1032,12 +1084,12 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const int tok = mt * 8 + 2 * t;  // accumulator columns 2t, 2t+1 of this tile; padding tokens are dropped
-          float* r0 = rbuf + (warp * p.M + tok) * kRedPitch + rb * 16 + gr;
-          if (tok < p.M) {
+          float* r0 = rbuf + (warp * ncols + tok) * kRedPitch + rb * 16 + gr;
+          if (tok < ncols) {
             r0[0] = fin[rb][mt][0];
             r0[8] = fin[rb][mt][2];
           }
-          if (tok + 1 < p.M) {
+          if (tok + 1 < ncols) {
             r0[kRedPitch] = fin[rb][mt][1];
             r0[kRedPitch + 8] = fin[rb][mt][3];
           }
@@ -1069,7 +1121,7 @@ size_t smem_without_ring(int M, int mode, int ncw, int cps) {
   const int xs_m_stride = cps * x_chunk_bytes(mode) + 64;
   const size_t xinfo_bytes = ((size_t)M * cps * x_info_bytes(mode) + 127) & ~(size_t)127;
   const size_t xs_bytes = ((size_t)M * xs_m_stride + 127) & ~(size_t)127;
-  return kHeaderBytes + red_bytes(ncw, M) + xinfo_bytes + xs_bytes + 1024;
+  return kHeaderBytes + red_bytes(ncw, mode_cols(mode, M)) + xinfo_bytes + xs_bytes + 1024;
 }
 
 // Plan for a fixed CTA width.  Cost model in units of "one chunk of one row group" (2 KB of weights): a
@@ -1164,6 +1216,7 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
       mode = (flags & kFlagFoldZeroPoint) ? kModeFold : kModeExact;
     else
       mode = (flags & kFlagWideX) ? kModeI8x3 : kModeI8x2;
+    if (mode == kModeI8x2 && M <= 2 && (flags & 0x1000)) mode = kModeI8c3;  // opt-in until measured
   }
   GemvPlan best{};
   bool have = false;
@@ -1236,6 +1289,13 @@ int launch_mode(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan& pl
       if constexpr (MT == 1 && NCW != 16)
         if (pl.cpw == 2) return launch_variant<MT, NCW, kModeI8x3, 2>(tmap, p, pl, stream);
       return launch_variant<MT, NCW, kModeI8x3, 1>(tmap, p, pl, stream);
+    case kModeI8c3:
+      if constexpr (MT == 1) {
+        if constexpr (NCW != 16)
+          if (pl.cpw == 2) return launch_variant<MT, NCW, kModeI8c3, 2>(tmap, p, pl, stream);
+        return launch_variant<MT, NCW, kModeI8c3, 1>(tmap, p, pl, stream);
+      }
+      return kErrNotImplemented;
     default: return launch_variant<MT, NCW, kModeGeneric, 1>(tmap, p, pl, stream);
   }
 }
