@@ -74,6 +74,12 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
                                      -- every element is off by at most 2^-16 of its chunk's largest magnitude -- and the
                                      nibbles feed an 8-bit integer mma without conversion */
 #define B2_FLAG_WIDE_X 512        /* GEMV, G % 128 == 0: 24-bit instead of 16-bit block fixed point for X */
+#define B2_FLAG_NO_AUTOTUNE 4096  /* GEMV (M <= 8): the first launch of a shape on a device, when its stream is not being
+                                     captured, times the five CTA shapes (8 / 14 / 16 consumer warps, one or two K chunks
+                                     per warp and stage) on the caller's operands -- under a millisecond, one stream
+                                     synchronisation -- and later launches use the fastest.  With this flag (or
+                                     B2_GEMV_AUTOTUNE=0 in the environment) the built-in cost model decides.  Warm a shape
+                                     up once before capturing it in a CUDA graph */
 #define B2_FLAG_NO_PDL 8          /* GEMV: plain launch.  By default the GEMV is launched with programmatic stream
                                      serialization: it may begin (weight prefetch only) while the previous kernel of
                                      the stream is still running, and touches X, Y and scratch only after that kernel

@@ -18,6 +18,49 @@ namespace {
 
 using bf16 = __nv_bfloat16;
 
+// The small kernels of a decode step are launched with programmatic stream serialization, like the GEMVs around them:
+// they become resident while the previous kernel drains and start the moment it has completed, which takes the
+// launch latency off the step's critical path.  Under such a launch the SM's L1 is not invalidated between the
+// producer of the inputs and the loads, so everything a previous kernel may have written is read with
+// ld.global.cg (L2), never through the non-coherent path.
+__device__ __forceinline__ void pdl_begin() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ float ld_bf16(const bf16* p) {
+  return __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(p))));
+}
+// E (2 or 4) consecutive bf16 as floats with one L2 load.
+template <int E>
+__device__ __forceinline__ void ld_row(const bf16* p, float (&f)[E]) {
+  static_assert(E == 2 || E == 4, "head dimension 64 or 128");
+  if constexpr (E == 4) {
+    const uint2 v = __ldcg(reinterpret_cast<const uint2*>(p));
+    f[0] = __uint_as_float(v.x << 16);
+    f[1] = __uint_as_float(v.x & 0xFFFF0000u);
+    f[2] = __uint_as_float(v.y << 16);
+    f[3] = __uint_as_float(v.y & 0xFFFF0000u);
+  } else {
+    const unsigned v = __ldcg(reinterpret_cast<const unsigned*>(p));
+    f[0] = __uint_as_float(v << 16);
+    f[1] = __uint_as_float(v & 0xFFFF0000u);
+  }
+}
+template <typename... Args>
+cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 // grid: Hq + 2*Hk blocks (one per head of the fused qkv row), block: D/2 threads.
 // With wait_sig set, qkv is the gathered output of a tensor-parallel GEMV (b2_w4_linear_tp): every block first waits
 // (bounded) until all producing CTAs of all ranks have counted themselves in, then reads qkv from L2.
@@ -27,6 +70,7 @@ __global__ void rope_kv_store_kernel(bf16* qkv, const bf16* __restrict__ bias,
                                      int max_len, const unsigned* wait_sig, const int* epoch, unsigned wait_per_epoch,
                                      int* status) {
   const int h = blockIdx.x, i = threadIdx.x, half = D / 2;
+  pdl_begin();
   if (wait_sig != nullptr) {
     if (i == 0) {
       const unsigned target = ((unsigned)*reinterpret_cast<const volatile int*>(epoch) + 1u) * wait_per_epoch;
@@ -44,7 +88,7 @@ __global__ void rope_kv_store_kernel(bf16* qkv, const bf16* __restrict__ bias,
     }
     __syncthreads();
   }
-  const int pos = *pos_ptr;
+  const int pos = __ldcg(pos_ptr);
   bf16* x = qkv + (size_t)h * D;
   float a = __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(x) + i)));
   float b = __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(x) + i + half)));
@@ -80,37 +124,42 @@ constexpr int kSplits = 32;
 
 template <int D>
 __global__ void __launch_bounds__(256) decode_attention_partial_kernel(
-    const bf16* __restrict__ q, const bf16* __restrict__ cache_k, const bf16* __restrict__ cache_v,
-    const int* __restrict__ pos_ptr, float* __restrict__ part, int Hq, int Hk, int max_len, float scale) {
+    const bf16* q, const bf16* cache_k, const bf16* cache_v, const int* pos_ptr, float* part, int Hq, int Hk,
+    int max_len, float scale) {
   constexpr int E = D / 32;  // elements per lane
   const int kh = blockIdx.x, sp = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rep = Hq / Hk;
+  pdl_begin();
   if (warp >= rep) return;
   const int h = kh * rep + warp;
-  const int n = min(*pos_ptr + 1, max_len);
+  const int n = min(__ldcg(pos_ptr) + 1, max_len);
   const int per = (n + kSplits - 1) / kSplits;
   const int j0 = sp * per, j1 = min(n, j0 + per);
   const bf16* kbase = cache_k + (size_t)kh * max_len * D;
   const bf16* vbase = cache_v + (size_t)kh * max_len * D;
   float qf[E];
 #pragma unroll
-  for (int e = 0; e < E; ++e) qf[e] = __bfloat162float(q[(size_t)h * D + lane * E + e]) * scale;
+  for (int e = 0; e < E; ++e) qf[e] = 0.f;
+  ld_row<E>(q + (size_t)h * D + lane * E, qf);
+#pragma unroll
+  for (int e = 0; e < E; ++e) qf[e] *= scale;
   float m = -FLT_MAX, l = 0.f, acc[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) acc[e] = 0.f;
   for (int j = j0; j < j1; ++j) {
     const bf16* kr = kbase + (size_t)j * D + lane * E;
-    float s = 0.f;
+    float s = 0.f, kf[E], vf[E];
+    ld_row<E>(kr, kf);
+    ld_row<E>(vbase + (size_t)j * D + lane * E, vf);
 #pragma unroll
-    for (int e = 0; e < E; ++e) s += qf[e] * __bfloat162float(kr[e]);
+    for (int e = 0; e < E; ++e) s += qf[e] * kf[e];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     const float mn = fmaxf(m, s);
     const float corr = __expf(m - mn), pj = __expf(s - mn);
-    const bf16* vr = vbase + (size_t)j * D + lane * E;
     l = l * corr + pj;
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[e] = acc[e] * corr + pj * __bfloat162float(vr[e]);
+    for (int e = 0; e < E; ++e) acc[e] = acc[e] * corr + pj * vf[e];
     m = mn;
   }
   float* out = part + ((size_t)h * kSplits + sp) * (D + 2);
@@ -123,19 +172,20 @@ __global__ void __launch_bounds__(256) decode_attention_partial_kernel(
 }
 
 template <int D>
-__global__ void decode_attention_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out) {
+__global__ void decode_attention_merge_kernel(const float* part, bf16* out) {
   const int h = blockIdx.x, d = threadIdx.x;  // block: D threads
+  pdl_begin();
   const float* p = part + (size_t)h * kSplits * (D + 2);
   float mm = -FLT_MAX;
 #pragma unroll 4
-  for (int s = 0; s < kSplits; ++s) mm = fmaxf(mm, p[s * (D + 2)]);
+  for (int s = 0; s < kSplits; ++s) mm = fmaxf(mm, __ldcg(p + s * (D + 2)));
   float num = 0.f, den = 0.f;
 #pragma unroll 4
   for (int s = 0; s < kSplits; ++s) {
-    const float ms = p[s * (D + 2)];
+    const float ms = __ldcg(p + s * (D + 2));
     const float f = ms == -FLT_MAX ? 0.f : __expf(ms - mm);
-    num += f * p[s * (D + 2) + 2 + d];
-    den += f * p[s * (D + 2) + 1];
+    num += f * __ldcg(p + s * (D + 2) + 2 + d);
+    den += f * __ldcg(p + s * (D + 2) + 1);
   }
   out[(size_t)h * D + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
 }
@@ -243,11 +293,13 @@ int rope_kv_store_launch(void* qkv, const void* bias, const void* inv_freq, cons
   if (Hq < 1 || Hk < 1 || D < 2 || D % 2 || D / 2 > 1024 || max_len < 1) return kErrBadShape;
   if (!qkv || !inv_freq || !pos || !cache_k || !cache_v) return kErrBadPointer;
   if (wait_sig != nullptr && !epoch) return kErrBadPointer;
-  rope_kv_store_kernel<<<Hq + 2 * Hk, D / 2, 0, stream>>>(
-      static_cast<bf16*>(qkv), static_cast<const bf16*>(bias), static_cast<const float*>(inv_freq),
-      static_cast<const int*>(pos), static_cast<bf16*>(cache_k), static_cast<bf16*>(cache_v), Hq, Hk, D, max_len,
-      static_cast<const unsigned*>(wait_sig), static_cast<const int*>(epoch), wait_per_epoch, status);
-  return (int)cudaGetLastError();
+  const cudaError_t e = launch_pdl(rope_kv_store_kernel, dim3(Hq + 2 * Hk), dim3(D / 2), stream,
+                                   static_cast<bf16*>(qkv), static_cast<const bf16*>(bias),
+                                   static_cast<const float*>(inv_freq), static_cast<const int*>(pos),
+                                   static_cast<bf16*>(cache_k), static_cast<bf16*>(cache_v), Hq, Hk, D, max_len,
+                                   static_cast<const unsigned*>(wait_sig), static_cast<const int*>(epoch),
+                                   wait_per_epoch, status);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 }  // namespace b2
 
@@ -275,15 +327,17 @@ int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v,
   float* part = static_cast<float*>(workspace);
   const dim3 grid(Hk, kSplits);
   if (D == 128) {
-    decode_attention_partial_kernel<128><<<grid, 256, 0, st>>>(
-        static_cast<const bf16*>(q), static_cast<const bf16*>(cache_k), static_cast<const bf16*>(cache_v),
-        static_cast<const int*>(pos), part, Hq, Hk, max_len, scale);
-    decode_attention_merge_kernel<128><<<Hq, 128, 0, st>>>(part, static_cast<bf16*>(out));
+    launch_pdl(decode_attention_partial_kernel<128>, grid, dim3(256), st, static_cast<const bf16*>(q),
+               static_cast<const bf16*>(cache_k), static_cast<const bf16*>(cache_v), static_cast<const int*>(pos), part,
+               Hq, Hk, max_len, scale);
+    launch_pdl(decode_attention_merge_kernel<128>, dim3(Hq), dim3(128), st, static_cast<const float*>(part),
+               static_cast<bf16*>(out));
   } else {
-    decode_attention_partial_kernel<64><<<grid, 256, 0, st>>>(
-        static_cast<const bf16*>(q), static_cast<const bf16*>(cache_k), static_cast<const bf16*>(cache_v),
-        static_cast<const int*>(pos), part, Hq, Hk, max_len, scale);
-    decode_attention_merge_kernel<64><<<Hq, 64, 0, st>>>(part, static_cast<bf16*>(out));
+    launch_pdl(decode_attention_partial_kernel<64>, grid, dim3(256), st, static_cast<const bf16*>(q),
+               static_cast<const bf16*>(cache_k), static_cast<const bf16*>(cache_v), static_cast<const int*>(pos), part,
+               Hq, Hk, max_len, scale);
+    launch_pdl(decode_attention_merge_kernel<64>, dim3(Hq), dim3(64), st, static_cast<const float*>(part),
+               static_cast<bf16*>(out));
   }
   return (int)cudaGetLastError();
 }

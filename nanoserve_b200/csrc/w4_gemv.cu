@@ -51,6 +51,10 @@
 //   instruction count on a warp's path, not the issue-slot utilisation, sets the run time.
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <tuple>
 #include <type_traits>
 #include <cuda_fp16.h>
 
@@ -74,17 +78,9 @@ constexpr int kNormSsOffset = 768;     // float [16 tokens][16 warps]
 constexpr int kNormInvOffset = 1792;   // float [16 tokens]
 constexpr int kBoxBytes = kRowsPerGroup * 128;  // 32 rows x 128 B (two chunks), swizzled
 
-// kModeI8c3: the integer path with the three byte planes of X as COLUMNS of the mma's B operand instead of three
-// mma's per fragment: with M <= 2 the eight columns hold (token, plane) pairs that would otherwise be padding, so
-// 22-bit fixed point costs half the tensor instructions of the 16-bit two-plane form.  Planes are balanced base-256
-// digits (all signed).
-enum : int { kModeGeneric = 0, kModeExact = 1, kModeFold = 2, kModeI8x2 = 3, kModeI8x3 = 4, kModeI8c3 = 5 };
+enum : int { kModeGeneric = 0, kModeExact = 1, kModeFold = 2, kModeI8x2 = 3, kModeI8x3 = 4 };
 // bytes of one staged (token, 128-chunk) of X and of its info record
-__host__ __device__ constexpr int mode_limbs(int mode) {
-  return mode == kModeI8x2 ? 2 : ((mode == kModeI8x3 || mode == kModeI8c3) ? 3 : 0);
-}
-// columns of partial sums a warp hands to the reducer: tokens, or (token, plane) pairs
-__host__ __device__ constexpr int mode_cols(int mode, int M) { return mode == kModeI8c3 ? 3 * M : M; }
+__host__ __device__ constexpr int mode_limbs(int mode) { return mode == kModeI8x2 ? 2 : (mode == kModeI8x3 ? 3 : 0); }
 __host__ __device__ constexpr int x_chunk_bytes(int mode) { return mode_limbs(mode) ? 128 * mode_limbs(mode) : 256; }
 __host__ __device__ constexpr int x_info_bytes(int mode) { return mode_limbs(mode) ? 16 : 8; }
 // What the kernel does to its input before the product (the operators that precede a linear in a decoder layer)
@@ -381,14 +377,10 @@ __device__ __forceinline__ void stage_x_f16(const GemvParams& p, uint32_t xs_bas
 // xinfo[token][chunk] = { bits of 2^(e - 127 - (8L - 2)) / 16, -128 * sum_k limb_l(v_k) for l = 0, 1, 2 }: the
 // zero-point 8, times the 16 that the nibble products carry, as the initial value of an accumulator.  A chunk that
 // holds an inf or a nan gets a nan factor (its integers are meaningless), so the outputs become nan.
-// COL (kModeI8c3): one bit less of range (largest magnitude in [2^(8L-3), 2^(8L-2))) and balanced digits in
-// [-128, 127] for every plane -- bytes of (v + 0x808080) ^ 0x808080 -- so that all planes are signed operands of one
-// mma; the two 64-byte halves of a plane are swapped for odd planes, which puts the planes of neighbouring columns into
-// different shared-memory banks.
-template <int CT, int L, bool COL>
+template <int CT, int L>
 __device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base, int4* xinfo, const float* inv,
                                            int cb, int ce, int ctid) {
-  constexpr int B = 8 * L - (COL ? 1 : 0);
+  constexpr int B = 8 * L;
   const int nch = ce - cb;
   const int items = p.M * nch * 8;
   const int items_pad = (items + 31) & ~31;
@@ -424,10 +416,6 @@ __device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base
     for (int i = 0; i < 8; ++i) {
       v[2 * i] = __float2int_rn(__uint_as_float(w[i] << 16) * down);
       v[2 * i + 1] = __float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * down);
-      if constexpr (COL) {
-        v[2 * i] = (int)(((uint32_t)v[2 * i] + 0x00808080u) ^ 0x00808080u);
-        v[2 * i + 1] = (int)(((uint32_t)v[2 * i + 1] + 0x00808080u) ^ 0x00808080u);
-      }
     }
     int csum[3] = {0, 0, 0};
 #pragma unroll
@@ -439,7 +427,7 @@ __device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base
       };
       const uint4 o = make_uint4(pack(0, 2, 4, 6), pack(8, 10, 12, 14), pack(1, 3, 5, 7), pack(9, 11, 13, 15));
       int c;
-      if (COL || l == L - 1) {
+      if (l == L - 1) {
         c = __dp4a((int)o.x, 0x01010101, 0);
         c = __dp4a((int)o.y, 0x01010101, c);
         c = __dp4a((int)o.z, 0x01010101, c);
@@ -455,8 +443,7 @@ __device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base
       c += __shfl_xor_sync(0xffffffffu, c, 2);
       c += __shfl_xor_sync(0xffffffffu, c, 1);
       csum[l] = -128 * c;
-      const int uu = COL ? (u ^ ((l & 1) << 2)) : u;
-      if (valid) sts128(xs_base + m * p.xs_m_stride + ch * (128 * L) + l * 128 + uu * 16, o);
+      if (valid) sts128(xs_base + m * p.xs_m_stride + ch * (128 * L) + l * 128 + u * 16, o);
     }
     if (valid && u == 0) xinfo[m * nch + ch] = make_int4((int)up_bits, csum[0], csum[1], csum[2]);
   }
@@ -528,10 +515,6 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
   constexpr bool kHalf = MODE != kModeGeneric;  // a chunk lies in one group: its sum is scaled once, in fp32
   constexpr int L = mode_limbs(MODE);           // bytes per staged value of X on the integer path, else 0
   constexpr bool kI8 = L > 0;
-  constexpr bool kCol = MODE == kModeI8c3;      // planes as columns of B: one plane per lane
-  constexpr int LP = kCol ? 1 : L;              // planes a lane holds per fragment
-  static_assert(!kCol || MT == 1, "planes as columns: at most 8 columns");
-  const int ncols = mode_cols(MODE, p.M);       // columns of partial sums per warp
   static_assert(CPW == 1 || (CPW == 2 && kI8), "two chunks per warp: integer modes only");
   constexpr int kXChunk = x_chunk_bytes(MODE);
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -542,9 +525,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
   const uint32_t bar_red_empty = bar_red_full + 16;           // [2] the reducer has consumed them
   const uint32_t zero_base = smem_u32(smem + kZeroOffset);
   float* red = reinterpret_cast<float*>(smem + kHeaderBytes);
-  float2* xinfo = reinterpret_cast<float2*>(smem + kHeaderBytes + red_bytes(NCW, ncols));
+  float2* xinfo = reinterpret_cast<float2*>(smem + kHeaderBytes + red_bytes(NCW, p.M));
   const int xinfo_bytes = (p.M * p.cps * x_info_bytes(MODE) + 127) & ~127;
-  const uint32_t xs_base = smem_u32(smem + kHeaderBytes + red_bytes(NCW, ncols) + xinfo_bytes);
+  const uint32_t xs_base = smem_u32(smem + kHeaderBytes + red_bytes(NCW, p.M) + xinfo_bytes);
   const int xs_bytes = (p.M * p.xs_m_stride + 127) & ~127;
   // scales of each ring stage: [32 rows][NCW chunks] bf16, filled by the producer warp with cp.async
   constexpr int kScStage = kHalf ? kRowsPerGroup * kSC * 2 : 0;
@@ -630,24 +613,14 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       const int sl = tile / p.nrg, rg = tile - sl * p.nrg;
       const int row0 = rg * kRowsPerGroup;
       const int b = tcount & 1;
-      const float* rbuf = red + b * (NCW * ncols * kRedPitch);
+      const float* rbuf = red + b * (NCW * p.M * kRedPitch);
       if (lane == 0) mbar_wait_backoff<100>(bar_red_full + 8 * b, (tcount >> 1) & 1, abort_flag);
       __syncwarp();
       const int n = row0 + lane;
       for (int tok = 0; tok < p.M; ++tok) {
         float sum = 0.f;
-        if constexpr (kCol) {
-          // columns 3 tok .. 3 tok + 2 are the byte planes of the token: sum over the warps, then recombine
-          float pl[3] = {0.f, 0.f, 0.f};
 #pragma unroll
-          for (int w = 0; w < NCW; ++w)
-#pragma unroll
-            for (int l = 0; l < 3; ++l) pl[l] += rbuf[(w * ncols + 3 * tok + l) * kRedPitch + lane];
-          sum = fmaf(fmaf(pl[2], 256.f, pl[1]), 256.f, pl[0]);
-        } else {
-#pragma unroll
-          for (int w = 0; w < NCW; ++w) sum += rbuf[(w * ncols + tok) * kRedPitch + lane];
-        }
+        for (int w = 0; w < NCW; ++w) sum += rbuf[(w * p.M + tok) * kRedPitch + lane];
         if (n < p.N) {
           if (p.nslices > 1)
             __stcg(p.partial + ((size_t)sl * p.M + tok) * p.N + n, sum);
@@ -735,7 +708,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           if (p.pro == kProAddRmsNorm && staged_slice < 0)
             rmsnorm_factors<kConsumerThreads>(p, reinterpret_cast<float*>(smem + kNormSsOffset), inv, ctid);
           if constexpr (kI8)
-            stage_x_i8<kConsumerThreads, L, kCol>(p, xs_base, reinterpret_cast<int4*>(xinfo), inv, cb, ce, ctid);
+            stage_x_i8<kConsumerThreads, L>(p, xs_base, reinterpret_cast<int4*>(xinfo), inv, cb, ce, ctid);
           else
             stage_x_f16<kConsumerThreads, MODE == kModeFold>(p, xs_base, xinfo, inv, cb, ce, ctid);
         }
@@ -747,23 +720,12 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       // B-fragment source of this lane: its token's staged X, or a block of zeros for padding tokens
       uint32_t xaddr[MT], xstep[MT];
       bool xreal[MT];
-      uint32_t jj_flip = 0;  // planes as columns: odd planes have their 64-byte halves swapped
-      int sel_a[2] = {0, 0};  // ... and the plane of accumulator columns 2t, 2t + 1
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        int m = mt * 8 + g;
-        bool real = m < p.M;
-        uint32_t plane_off = 0;
-        if constexpr (kCol) {  // column g of B is plane g % 3 of token g / 3
-          real = m < ncols;
-          const int tok = m / 3, l = m - 3 * tok;
-          m = tok;
-          plane_off = l * 128;
-          jj_flip = (l & 1) * 64;
-        }
+        const int m = mt * 8 + g;
+        const bool real = m < p.M;
         xreal[mt] = real;
-        xaddr[mt] = real ? xs_base + m * p.xs_m_stride + (CPW * warp) * kXChunk + plane_off + t * 16
-                         : zero_base + t * 16;
+        xaddr[mt] = real ? xs_base + m * p.xs_m_stride + (CPW * warp) * kXChunk + t * 16 : zero_base + t * 16;
         xstep[mt] = real ? kSC * kXChunk : 0;
       }
       // per-(token, chunk) info of the two accumulator columns (tokens mt*8 + 2t, +1) of this lane;
@@ -775,14 +737,8 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          int m = mt * 8 + 2 * t + q;
-          bool real = m < p.M;
-          if constexpr (kCol) {
-            real = m < ncols;
-            const int tok = m / 3;
-            sel_a[q] = m - 3 * tok;
-            m = tok;
-          }
+          const int m = mt * 8 + 2 * t + q;
+          const bool real = m < p.M;
           xi[mt][q] = real ? xinfo + m * nch + CPW * warp : reinterpret_cast<const float2*>(smem + kZeroOffset);
           xi8[mt][q] = real ? reinterpret_cast<const int4*>(xinfo) + m * nch + CPW * warp
                             : reinterpret_cast<const int4*>(smem + kZeroOffset);
@@ -850,15 +806,15 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           // mma.m16n8k32, so the unpack is two LOP3 per eight weights and no shift.  X arrives as L byte planes
           // ("limbs"); every plane gets its own s32 accumulators, even and odd nibbles apart (the odd ones carry the
           // factor 16), all combined once per chunk: T = sum_l 256^l (16 even_l + odd_l) = 16 sum_k (q_k - 8) v_k.
-          uint32_t xb[MT][LP][8];
+          uint32_t xb[MT][L][8];
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int l = 0; l < LP; ++l)
+            for (int l = 0; l < L; ++l)
 #pragma unroll
               for (int jj = 0; jj < 2; ++jj) {
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);  // padding tokens: no load at all (fewer wavefronts)
-                if (xreal[mt]) v = lds128(xaddr[mt] + h * kXChunk + l * 128 + ((jj * 64) ^ jj_flip));
+                if (xreal[mt]) v = lds128(xaddr[mt] + h * kXChunk + l * 128 + jj * 64);
                 xb[mt][l][4 * jj + 0] = v.x;
                 xb[mt][l][4 * jj + 1] = v.y;
                 xb[mt][l][4 * jj + 2] = v.z;
@@ -886,7 +842,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           for (int rb = 0; rb < 2; ++rb) {
             const uint32_t wl[4] = {wv[rb][0].x, wv[rb][0].y, wv[rb][0].z, wv[rb][0].w};
             const uint32_t wh[4] = {wv[rb][1].x, wv[rb][1].y, wv[rb][1].z, wv[rb][1].w};
-            int ae[MT][LP][4], ao[MT][LP][4];
+            int ae[MT][L][4], ao[MT][L][4];
 #pragma unroll
             for (int jj = 0; jj < 2; ++jj) {
               const uint32_t e0 = wl[2 * jj] & k_nib_lo, e1 = wh[2 * jj] & k_nib_lo;
@@ -896,18 +852,16 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 #pragma unroll
               for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int l = 0; l < LP; ++l) {
-                  const bool sgn = kCol || l == L - 1;  // signed planes: all balanced digits, or the top byte
+                for (int l = 0; l < L; ++l) {
                   if (jj == 0) {
-                    // the odd chain starts from the zero-point term of its plane, the even chain from zero
-                    const int pa = kCol ? sel_a[0] : l, pb = kCol ? sel_a[1] : l;
-                    const int c0 = pa == 0 ? info[mt][0].y : (pa == 1 ? info[mt][0].z : info[mt][0].w);
-                    const int c1 = pb == 0 ? info[mt][1].y : (pb == 1 ? info[mt][1].z : info[mt][1].w);
-                    imma_16832_init(sgn, ae[mt][l], e0, e1, e2, e3, xb[mt][l][0], xb[mt][l][1], 0, 0);
-                    imma_16832_init(sgn, ao[mt][l], o0, o1, o2, o3, xb[mt][l][2], xb[mt][l][3], c0, c1);
+                    // the odd chain starts from the zero-point term of its limb, the even chain from zero
+                    const int c0 = l == 0 ? info[mt][0].y : (l == 1 ? info[mt][0].z : info[mt][0].w);
+                    const int c1 = l == 0 ? info[mt][1].y : (l == 1 ? info[mt][1].z : info[mt][1].w);
+                    imma_16832_init(l == L - 1, ae[mt][l], e0, e1, e2, e3, xb[mt][l][0], xb[mt][l][1], 0, 0);
+                    imma_16832_init(l == L - 1, ao[mt][l], o0, o1, o2, o3, xb[mt][l][2], xb[mt][l][3], c0, c1);
                   } else {
-                    imma_16832(sgn, ae[mt][l], e0, e1, e2, e3, xb[mt][l][4 * jj], xb[mt][l][4 * jj + 1]);
-                    imma_16832(sgn, ao[mt][l], o0, o1, o2, o3, xb[mt][l][4 * jj + 2], xb[mt][l][4 * jj + 3]);
+                    imma_16832(l == L - 1, ae[mt][l], e0, e1, e2, e3, xb[mt][l][4 * jj], xb[mt][l][4 * jj + 1]);
+                    imma_16832(l == L - 1, ao[mt][l], o0, o1, o2, o3, xb[mt][l][4 * jj + 2], xb[mt][l][4 * jj + 3]);
                   }
                 }
             }
@@ -924,11 +878,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
               const float up0 = __int_as_float(info[mt][0].x), up1 = __int_as_float(info[mt][1].x);
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                if (!kCol && (i & 1) && !multi_token) continue;  // one token: accumulator columns 1.. are padding
+                if ((i & 1) && !multi_token) continue;  // one token: accumulator columns 1.. are padding
                 float f;
-                if constexpr (kCol) {
-                  f = (float)(16 * ae[mt][0][i] + ao[mt][0][i]);  // this column's plane; planes meet in the reducer
-                } else if constexpr (L == 2) {
+                if constexpr (L == 2) {
                   f = (float)((16 * ae[mt][1][i] + ao[mt][1][i]) * 256 + (16 * ae[mt][0][i] + ao[mt][0][i]));
                 } else {
                   const int th = (16 * ae[mt][2][i] + ao[mt][2][i]) * 256 + (16 * ae[mt][1][i] + ao[mt][1][i]);
@@ -1076,7 +1028,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 
       // ---- hand the per-warp partial sums of this tile to the reducer warp (two buffers in rotation)
       const int b = tcount & 1;
-      float* rbuf = red + b * (NCW * ncols * kRedPitch);
+      float* rbuf = red + b * (NCW * p.M * kRedPitch);
       if (lane == 0) mbar_wait(bar_red_empty + 8 * b, ((tcount >> 1) & 1) ^ 1, abort_flag);
       __syncwarp();
 #pragma unroll
@@ -1084,12 +1036,12 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const int tok = mt * 8 + 2 * t;  // accumulator columns 2t, 2t+1 of this tile; padding tokens are dropped
-          float* r0 = rbuf + (warp * ncols + tok) * kRedPitch + rb * 16 + gr;
-          if (tok < ncols) {
+          float* r0 = rbuf + (warp * p.M + tok) * kRedPitch + rb * 16 + gr;
+          if (tok < p.M) {
             r0[0] = fin[rb][mt][0];
             r0[8] = fin[rb][mt][2];
           }
-          if (tok + 1 < ncols) {
+          if (tok + 1 < p.M) {
             r0[kRedPitch] = fin[rb][mt][1];
             r0[kRedPitch + 8] = fin[rb][mt][3];
           }
@@ -1121,7 +1073,7 @@ size_t smem_without_ring(int M, int mode, int ncw, int cps) {
   const int xs_m_stride = cps * x_chunk_bytes(mode) + 64;
   const size_t xinfo_bytes = ((size_t)M * cps * x_info_bytes(mode) + 127) & ~(size_t)127;
   const size_t xs_bytes = ((size_t)M * xs_m_stride + 127) & ~(size_t)127;
-  return kHeaderBytes + red_bytes(ncw, mode_cols(mode, M)) + xinfo_bytes + xs_bytes + 1024;
+  return kHeaderBytes + red_bytes(ncw, M) + xinfo_bytes + xs_bytes + 1024;
 }
 
 // Plan for a fixed CTA width.  Cost model in units of "one chunk of one row group" (2 KB of weights): a
@@ -1163,16 +1115,24 @@ bool plan_for_width(int M, int N, int K, int ncw, int cpw, int mt, int mode, int
     // the memory system moves only real bytes, the warps pay for padded stages: weigh them equally
     // fixed cost of a tile (hand-off to the reducer) and of a split-K tile (scratch round trip, measured to be
     // dear: splitting the 3584 x 18944 projection five ways was slower than leaving 36 SMs idle)
-    // ... and of an iteration of the consumer loop (wait, release, bookkeeping: 0.24 us measured, about two chunks)
-    const double tile_cost = 0.5 * (cps + stage_chunks) + 2.0 * iters + (ns > 1 ? 12.0 : 0.0);
+    // ... and of an iteration of the consumer loop (wait, release, bookkeeping: 0.23 us measured, just under three
+    // chunks), which is what two chunks per warp and stage save
+    // split-K tiles pay the scratch round trip, the counter and the final sum (1 to 3 us measured; whether a split pays
+    // is one of the things the first-launch measurement settles)
+    const double tile_cost = 0.5 * (cps + stage_chunks) + 2.85 * iters + 3.0 + (ns > 1 ? 12.0 : 0.0);
+    // staging of X: once per CTA and slice, spread over the consumer threads
+    const double stage_cost = 0.5 * M * cps * (8.0 / ncw);
     for (int ctas = 2; ctas >= 1; --ctas) {
       if (ctas == 2 && !(mt == 1 && ncw <= 12 && fixed + 2 * (size_t)stage_bytes <= kHalfSmem)) continue;
       if (ctas == 1 && fixed + 2 * (size_t)stage_bytes > (size_t)kSmemLimit) continue;
       const long slots = (long)grid * ctas;
       const long rounds = (tiles + slots - 1) / slots;
       const long active = std::min<long>(ctas, (tiles + grid - 1) / grid);  // CTAs that share the busiest SM
-      double cost = rounds * tile_cost * active;
-      if (active == 2) cost *= 0.9;                             // measured: tails overlap
+      double cost = (rounds * tile_cost + stage_cost * std::min<long>(rounds, ns)) * active;
+      if (active == 2) cost *= 0.78;  // measured: one CTA's staging and tail overlap the other's streaming
+      // a ring of two stages lets the producer run only one stage ahead
+      const size_t cap = ctas == 2 ? kHalfSmem : (size_t)kSmemLimit;
+      if ((cap - fixed) / stage_bytes < 3) cost *= 1.25;
       if (active == 1 && ncw <= 12) cost *= 1.0 + (16 - ncw) / 20.0;  // measured: too few warps on the SM
       if (cost < best) {
         best = cost;
@@ -1216,7 +1176,6 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
       mode = (flags & kFlagFoldZeroPoint) ? kModeFold : kModeExact;
     else
       mode = (flags & kFlagWideX) ? kModeI8x3 : kModeI8x2;
-    if (mode == kModeI8x2 && M <= 2 && (flags & 0x1000)) mode = kModeI8c3;  // opt-in until measured
   }
   GemvPlan best{};
   bool have = false;
@@ -1226,8 +1185,7 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
   const int forced = ((flags >> 4) & 0xF) * 2;
   // Two chunks per warp and stage: integer modes whose scales can be staged with aligned copies (one scale per chunk,
   // an even number of scales per row).  Bits 10 / 11 of the flags force two / one (diagnostics).
-  const bool cpw2_ok = mode_limbs(mode) > 0 && mt == 1 && G == 128 && (K / G) % 2 == 0 && !(flags & 0x800) &&
-                       (flags & 0x400);  // opt-in until measured on every shape
+  const bool cpw2_ok = mode_limbs(mode) > 0 && mt == 1 && G == 128 && (K / G) % 2 == 0 && !(flags & 0x800);
   if (mt == 1 && !(flags & kFlagNarrowCta)) {
     const int widths[3] = {16, 14, 8};
     for (int w : widths) {
@@ -1289,13 +1247,6 @@ int launch_mode(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan& pl
       if constexpr (MT == 1 && NCW != 16)
         if (pl.cpw == 2) return launch_variant<MT, NCW, kModeI8x3, 2>(tmap, p, pl, stream);
       return launch_variant<MT, NCW, kModeI8x3, 1>(tmap, p, pl, stream);
-    case kModeI8c3:
-      if constexpr (MT == 1) {
-        if constexpr (NCW != 16)
-          if (pl.cpw == 2) return launch_variant<MT, NCW, kModeI8c3, 2>(tmap, p, pl, stream);
-        return launch_variant<MT, NCW, kModeI8c3, 1>(tmap, p, pl, stream);
-      }
-      return kErrNotImplemented;
     default: return launch_variant<MT, NCW, kModeGeneric, 1>(tmap, p, pl, stream);
   }
 }
@@ -1319,9 +1270,133 @@ size_t gemv_grid(int M, int N, int K, int G, int flags, int sm_count, size_t par
   return (size_t)pl.grid;
 }
 
+namespace {
+
+// ---- choice of the CTA shape by measurement ---------------------------------------------------------------
+// The cost model ranks the five CTA shapes (8, 14 or 16 consumer warps x one or two chunks per warp and stage) well
+// enough for the shapes it was fitted on and misses by 20-60 % elsewhere (long K with few rows, tensor-parallel
+// shards, M = 4..8).  So the first launch of a shape on a device, when the stream is not being captured, times
+// every shape of CTA on the caller's own operands (a few launches each with the matrix pushed out of L2 in between,
+// about a millisecond in all, a handful of stream synchronisations) and remembers the fastest; later launches, and launches under capture, use the remembered
+// choice or, failing that, the model.  Trial launches are plain GEMVs: they never signal a tensor-parallel counter
+// and, for a tensor-parallel call, write to the tail of the scratch area instead of the gathered rows.
+constexpr int kShapeFlagMask = 0xCF0;         // forced width (bits 4-7), forced chunks per warp (bits 10, 11)
+// (a remembered choice may also carry kFlagForceNoSplitK)
+constexpr size_t kTrialBytes = 2u << 20;      // tail of the split-K scratch kept for trial outputs (>= 16 x 65536 bf16)
+struct TuneKey {
+  int dev, M, N, K, G, flags, pro;
+  bool operator<(const TuneKey& o) const {
+    return std::tie(dev, M, N, K, G, flags, pro) < std::tie(o.dev, o.M, o.N, o.K, o.G, o.flags, o.pro);
+  }
+};
+std::map<TuneKey, int> g_tuned;  // -> shape flags of the fastest candidate
+std::mutex g_tune_mu;
+
+int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                        const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream,
+                        const GemvTp* tp);
+
+bool autotune_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("B2_GEMV_AUTOTUNE");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+}  // namespace
+
 int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
-                   const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream,
+                   const GemvPrologue& pro, const Workspace& ws_in, int flags, int sm_count, cudaStream_t stream,
                    const GemvTp* tp) {
+  Workspace ws = ws_in;
+  if (ws.partial && ws.partial_bytes > 2 * kTrialBytes) ws.partial_bytes -= kTrialBytes;  // trial outputs live there
+  const bool tunable = !(flags & (kShapeFlagMask | kFlagNarrowCta | kFlagNoAutotune)) && autotune_enabled() &&
+                       ws.partial && ws_in.partial_bytes > 2 * kTrialBytes && (size_t)M * N * 2 <= kTrialBytes;
+  if (!tunable) return gemv_launch_planned(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const TuneKey key{dev, M, N, K, G, flags, pro.kind};
+  {
+    std::lock_guard<std::mutex> lock(g_tune_mu);
+    auto it = g_tuned.find(key);
+    if (it != g_tuned.end())
+      return gemv_launch_planned(X, Wq, S, Y, M, N, K, G, pro, ws, flags | it->second, sm_count, stream, tp);
+  }
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)
+    return gemv_launch_planned(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
+
+  // ---- time the candidates
+  const bool is_tp = tp != nullptr && (tp->world > 0 || tp->wait_sig != nullptr);
+  void* y_trial = is_tp ? static_cast<void*>(reinterpret_cast<unsigned char*>(ws_in.partial) + ws.partial_bytes) : Y;
+  if (!is_tp && !Y) return kErrBadPointer;
+  // candidates: the CTA shapes (one token tile; two token tiles have one shape), each with the model's K split and,
+  // where the model splits, without a split
+  const int shapes[5] = {(4 << 4) | 0x800, (7 << 4) | 0x800, (8 << 4) | 0x800, (4 << 4) | 0x400, (7 << 4) | 0x400};
+  int cand[10], ncand = 0;
+  for (int c = 0; c < (M > 8 ? 1 : 5); ++c) {
+    const int shape = M > 8 ? 0 : shapes[c];
+    GemvPlan pl;
+    if (!make_plan(M, N, K, G, flags | shape, sm_count, ws.partial_bytes, ws.n_counters - 1, &pl)) continue;
+    cand[ncand++] = shape;
+    if (pl.nslices > 1) cand[ncand++] = shape | kFlagForceNoSplitK;
+  }
+  cudaEvent_t e0, e1;
+  if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess)
+    return gemv_launch_planned(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
+  int best = 0;
+  float best_ms = 1e30f;
+  for (int c = 0; c < ncand; ++c) {
+    const int f = flags | cand[c];
+    if (gemv_launch_planned(X, Wq, S, y_trial, M, N, K, G, pro, ws, f, sm_count, stream, nullptr) != 0) continue;
+    // In use the weights come from HBM (a model's matrices do not fit the 126 MB L2 together), so every timed launch
+    // is preceded by a write over the scratch area that pushes the matrix out of L2.
+    bool ok = true;
+    float cold[6];
+    for (int i = 0; i < 6 && ok; ++i) {
+      cudaMemsetAsync(ws.partial, 0, ws.partial_bytes, stream);
+      cudaEventRecord(e0, stream);
+      ok = gemv_launch_planned(X, Wq, S, y_trial, M, N, K, G, pro, ws, f, sm_count, stream, nullptr) == 0;
+      cudaEventRecord(e1, stream);
+      cold[i] = 0.f;
+      ok = ok && cudaEventSynchronize(e1) == cudaSuccess && cudaEventElapsedTime(&cold[i], e0, e1) == cudaSuccess;
+    }
+    if (!ok) continue;
+    std::sort(cold, cold + 6);  // the three fastest count: other work on the GPU only ever adds time
+    // ... and a dependent chain of launches, as in a decode step, where one launch's fixed costs overlap the weight
+    // stream of its neighbours (the matrix may sit in L2 here; the sum of the two views ranks the shapes best)
+    float chain = 1e30f;
+    for (int rep = 0; rep < 2 && ok; ++rep) {
+      cudaEventRecord(e0, stream);
+      for (int i = 0; i < 8 && ok; ++i)
+        ok = gemv_launch_planned(X, Wq, S, y_trial, M, N, K, G, pro, ws, f, sm_count, stream, nullptr) == 0;
+      cudaEventRecord(e1, stream);
+      float t = 0.f;
+      ok = ok && cudaEventSynchronize(e1) == cudaSuccess && cudaEventElapsedTime(&t, e0, e1) == cudaSuccess;
+      chain = std::min(chain, t);
+    }
+    if (!ok) continue;
+    const float ms = (cold[0] + cold[1] + cold[2]) / 3.f + chain / 8.f;
+    if (ms < best_ms) {
+      best_ms = ms;
+      best = cand[c];
+    }
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  {
+    std::lock_guard<std::mutex> lock(g_tune_mu);
+    g_tuned[key] = best;  // 0 if every trial failed: the model decides
+  }
+  return gemv_launch_planned(X, Wq, S, Y, M, N, K, G, pro, ws, flags | best, sm_count, stream, tp);
+}
+
+namespace {
+
+int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                        const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream,
+                        const GemvTp* tp) {
   if (M < 1 || M > 16) return kErrUnsupportedM;
   if (tp != nullptr && tp->world > 0) {
     if (tp->world > kMaxTpRanks || tp->ld < N || tp->seg_end[0] < 0 || tp->seg_end[1] < tp->seg_end[0]) return kErrBadShape;
@@ -1409,5 +1484,7 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
     default: return launch_mode<1, 8>(tmap, p, pl, stream);
   }
 }
+
+}  // namespace
 
 }  // namespace b2

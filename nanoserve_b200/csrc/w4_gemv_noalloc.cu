@@ -79,5 +79,5 @@ extern "C" int b2_w4_gemv_noalloc(const void* X, const void* Wq, const void* S, 
   ws.status = reinterpret_cast<int*>(slot.base + kStatusOffset);
   e = cudaMemsetAsync(ws.counters, 0, kCounters * sizeof(int), st);
   if (e != cudaSuccess) return (int)e;
-  return b2::gemv_launch(X, Wq, S, Y, M, N, K, G, ws, 0, slot.sm_count, st);
+  return b2::gemv_launch(X, Wq, S, Y, M, N, K, G, ws, b2::kFlagNoAutotune, slot.sm_count, st);  // no events, no sync
 }

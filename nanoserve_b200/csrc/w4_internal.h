@@ -44,6 +44,7 @@ enum : int {
   kFlagForceNoSplitK = 2,  // GEMV: never use split-K (no scratch needed)
   kFlagNarrowCta = 4,      // GEMV: use the 8-consumer-warp CTA even when the 16-warp one applies
   kFlagFloatX = 256,       // GEMV: keep X in floating point (fp16 mma path) instead of 16-bit block fixed point
+  kFlagNoAutotune = 4096,  // GEMV: never time CTA shapes on the first launch of a shape; the cost model decides
   kFlagWideX = 512,        // GEMV: 24-bit instead of 16-bit block fixed point for X (three byte planes)
   kFlagNoPdl = 8,          // GEMV: do NOT launch with programmatic stream serialization (by default the kernel may
                            // begin -- weight prefetch only -- while the previous kernel of the stream still runs)
