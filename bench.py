@@ -231,6 +231,79 @@ def run_sweep(k, dev, stream, flags):
     return out
 
 
+# ---------------------------------------------------------------------------- 70B-class prefill GEMM over the ranks
+def run_prefill_tp(k, dev, stream, rank, world, M=4096, N=28672, K=8192, reps=6):
+    """Prefill GEMM of the 70B-class gate/up shape with the output features sharded over the ranks (rank r holds rows
+    [r N/P, (r+1) N/P) of the weight) and the outputs all-gathered by NCCL: once as GEMM then gather, once with M cut
+    into chunks so the gather of one chunk runs on a second stream under the GEMM of the next.  Times are CUDA events
+    on the compute stream between barriers, max over ranks; TFLOP/s is 2 M N K over that time (the whole job)."""
+    import torch
+    import torch.distributed as dist
+    gen = torch.Generator(device=dev).manual_seed(21 + rank)
+    nl = N // world
+    ws = []
+    for _ in range(2):
+        Wq = torch.randint(-2**31, 2**31 - 1, (nl, K // 8), dtype=torch.int32, device=dev, generator=gen)
+        S = (0.005 + (torch.randn(nl, K // G, device=dev, generator=gen) * 0.01).abs()).to(torch.bfloat16)
+        ws.append((Wq, S))
+    x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+    comm = torch.cuda.Stream(device=dev)
+
+    def make(chunks, gather):
+        mc = M // chunks
+        ys = [torch.empty(mc, nl, dtype=torch.bfloat16, device=dev) for _ in range(chunks)]
+        gs = [torch.empty(world, mc, nl, dtype=torch.bfloat16, device=dev) for _ in range(chunks)]
+        evs = [torch.cuda.Event() for _ in range(chunks)]
+
+        def step(w):
+            for c in range(chunks):
+                k.w4_linear(x[c * mc:(c + 1) * mc], w[0], w[1], G, out=ys[c])
+                if gather and world > 1:
+                    if chunks == 1:
+                        dist.all_gather_into_tensor(gs[c], ys[c])
+                    else:
+                        evs[c].record(stream)
+                        with torch.cuda.stream(comm):
+                            comm.wait_event(evs[c])
+                            dist.all_gather_into_tensor(gs[c], ys[c])
+            if gather and world > 1 and chunks > 1:
+                stream.wait_stream(comm)
+        return step
+
+    def timed(step):
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                step(ws[i % 2])
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(stream)
+            for i in range(reps):
+                step(ws[i % 2])
+            ev1.record(stream)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+        t = torch.tensor([ev0.elapsed_time(ev1) * 1e-3 / reps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    peaks, which = measured_peaks()
+    fl = 2.0 * M * N * K
+    out = {"M": M, "N": N, "K": K, "rows_per_rank": nl, "gathered_bytes_per_rank": M * N * 2,
+           "peak_source": which, "bf16_tflops_peak_per_gpu": peaks["bf16_tflops"]}
+    legs = [("gemm_only", 1, False)]
+    if world > 1:
+        legs += [("gemm_then_all_gather", 1, True), ("overlapped_2_chunks", 2, True), ("overlapped_4_chunks", 4, True)]
+    for name, chunks, gather in legs:
+        t = timed(make(chunks, gather))
+        out[name] = {"ms": round(t * 1e3, 4), "tflops_aggregate": round(fl / t / 1e12, 1),
+                     "frac_of_peak_x_gpus": round(fl / t / 1e12 / (peaks["bf16_tflops"] * world), 3)}
+    return out
+
+
 # ---------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -250,7 +323,8 @@ def main():
                          "into the GEMVs (peer stores + arrival counters)")
     ap.add_argument("--no-sweep", action="store_true",
                     help="skip the single-GPU sweep over the other benchmark configurations (decode GEMV at M = 1..16 over "
-                         "every 7B-shaped and 70B-class linear, prefill GEMM at M = 512..8192)")
+                         "every 7B-shaped and 70B-class linear, prefill GEMM at M = 512..8192) and, with --layer 70b, the "
+                         "70B-class prefill GEMM sharded over the ranks")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -416,6 +490,11 @@ def main():
         del big, y_big
         sweep = run_sweep(k, dev, stream, args.flags)
 
+    # ---- 70B-class prefill GEMM, output features sharded over the ranks, outputs all-gathered
+    prefill = None
+    if args.layer == "70b" and not args.no_sweep:
+        prefill = run_prefill_tp(k, dev, stream, rank, world)
+
     # ---- second half of the headline metric: W4 greedy decode tokens/s of a Qwen2.5-7B-shaped model (512-token prompt,
     # 256 new tokens, batch 1, tensor parallel over the ranks); free the GEMV benchmark's weights first
     decode = None
@@ -476,6 +555,8 @@ def main():
             line["sweep"] = sweep
         if decode is not None:
             line["decode"] = decode
+        if prefill is not None:
+            line["prefill_tp"] = prefill
         if world == 1 and not args.no_cpu_baseline:
             one, _ = cpu_layer_pass(1, 1)
             n = max(1, min(8, int(15.0 / max(one, 1e-3))))
