@@ -80,6 +80,13 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
                                      synchronisation -- and later launches use the fastest.  With this flag (or
                                      B2_GEMV_AUTOTUNE=0 in the environment) the built-in cost model decides.  Warm a shape
                                      up once before capturing it in a CUDA graph */
+#define B2_FLAG_PRE_STAGE_X 8192  /* GEMV, integer path: convert X to its fixed-point form once, in a small kernel launched in
+                                     front of the GEMV, and let every CTA copy its slice (default from M = 8 on, from M = 4 where
+                                     K >= 8192, and one of
+                                     the things the first-launch measurement tries from M = 2 on); ignored where it does
+                                     not apply (RMSNorm prologue, tensor-parallel consumer, B2_FLAG_FLOAT_X, M * K beyond
+                                     the staging area) */
+#define B2_FLAG_NO_PRE_STAGE_X 16384 /* GEMV: every CTA converts the slice of X it needs itself, at every M */
 #define B2_FLAG_NO_PDL 8          /* GEMV: plain launch.  By default the GEMV is launched with programmatic stream
                                      serialization: it may begin (weight prefetch only) while the previous kernel of
                                      the stream is still running, and touches X, Y and scratch only after that kernel
@@ -87,7 +94,7 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
 
 /*
  * Sets up the calling thread's current device: queries the SM count and allocates the per-device scratch
- * (split-K partial sums, arrival counters, a status word; 64 MiB + 256 KiB).  ns_w4_linear does this on
+ * (split-K partial sums, arrival counters, the staged X of a launch, a status word; 68 MiB + 256 KiB).  ns_w4_linear does this on
  * its first call on a device; call b2_init first when that first call would fall inside a CUDA-graph
  * capture.  Launches on different streams of one device share the scratch: split-K launches that overlap
  * in time race (shapes that fill the GPU without split-K never touch it).

@@ -14,6 +14,7 @@ namespace {
 constexpr int kMaxDevices = 64;
 constexpr size_t kPartialBytes = 64ull << 20;  // split-K partial sums
 constexpr int kCounters = 1 << 16;             // one per 32-row group: N up to 2 M rows
+constexpr size_t kXStageBytes = 4ull << 20;    // X of a GEMV launch in its staged form: M * K up to 1.8 M values
 
 struct DeviceState {
   bool ready = false;
@@ -36,7 +37,7 @@ DeviceState* device_state(int* rc) {
   e = cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) { *rc = (int)e; return nullptr; }
   void *partial = nullptr, *small = nullptr;
-  e = cudaMalloc(&partial, kPartialBytes);
+  e = cudaMalloc(&partial, kPartialBytes + kXStageBytes);
   if (e != cudaSuccess) { *rc = b2::kErrWorkspace; return nullptr; }
   e = cudaMalloc(&small, (kCounters + 64) * sizeof(int));
   if (e != cudaSuccess) { cudaFree(partial); *rc = b2::kErrWorkspace; return nullptr; }
@@ -45,6 +46,8 @@ DeviceState* device_state(int* rc) {
   if (e != cudaSuccess) { cudaFree(partial); cudaFree(small); *rc = (int)e; return nullptr; }
   st.ws.partial = static_cast<float*>(partial);
   st.ws.partial_bytes = kPartialBytes;
+  st.ws.xstage = static_cast<unsigned char*>(partial) + kPartialBytes;
+  st.ws.xstage_bytes = kXStageBytes;
   st.ws.status = static_cast<int*>(small);          // word 0
   st.ws.counters = static_cast<int*>(small) + 64;   // 256-byte offset
   st.ws.n_counters = kCounters;

@@ -124,6 +124,13 @@ __device__ __forceinline__ void cp_async(uint32_t dst_smem, const void* src, uin
   asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;" ::"r"(dst_smem), "l"(src), "n"(BYTES), "r"(src_bytes)
                : "memory");
 }
+// 16 bytes through L2 only (.cg): for data another kernel has just written (the L1 may hold a stale line when this
+// kernel started, under programmatic launch, before that kernel had finished).
+__device__ __forceinline__ void cp_async_cg16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+// Waits until all cp.async copies of the calling thread have landed.
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 // The mbarrier receives one arrival once all earlier cp.async copies of the calling thread have landed; the
 // arrival is one of those the barrier was initialised to expect (.noinc).
 __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
@@ -132,6 +139,17 @@ __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
 
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// Two fp32 additions in one instruction (sm_100: add.f32x2), each rounded to nearest like a scalar add.
+__device__ __forceinline__ float2 add_f32x2(float2 a, float2 b) {
+  unsigned long long ra, rb, rd;
+  float2 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
 }
 
 // ------------------------------------------------------------------ programmatic dependent launch

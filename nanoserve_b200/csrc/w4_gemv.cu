@@ -112,6 +112,10 @@ struct GemvParams {
   __nv_bfloat16* Xout;        // add + RMSNorm: where X + R is stored (may be null)
   float eps;
   GemvTp tp;                  // tensor-parallel epilogue / input wait (all zero: off)
+  // integer path, optional: X staged once by w4_stage_x_kernel ([M][nchunks] chunks of 128 L bytes, and the
+  // per-(token, chunk) info) instead of by every CTA; null = every CTA converts its own slice
+  const unsigned char* pre_x;
+  const int4* pre_info;
 };
 
 // two buffers of [consumer warp][token < M][kRedPitch] floats
@@ -377,76 +381,128 @@ __device__ __forceinline__ void stage_x_f16(const GemvParams& p, uint32_t xs_bas
 // xinfo[token][chunk] = { bits of 2^(e - 127 - (8L - 2)) / 16, -128 * sum_k limb_l(v_k) for l = 0, 1, 2 }: the
 // zero-point 8, times the 16 that the nibble products carry, as the initial value of an accumulator.  A chunk that
 // holds an inf or a nan gets a nan factor (its integers are meaningless), so the outputs become nan.
-template <int CT, int L>
+// GLOBAL: the same bytes go to global memory (gx: [M][nch] chunks of 128 L bytes, xinfo: [M][nch]) for every CTA of a
+// later kernel to copy; `ctid` / `nthreads` are then grid-wide.
+template <int L, bool GLOBAL>
 __device__ __forceinline__ void stage_x_i8(const GemvParams& p, uint32_t xs_base, int4* xinfo, const float* inv,
-                                           int cb, int ce, int ctid) {
+                                           int cb, int ce, int ctid, int nthreads, unsigned char* gx = nullptr) {
   constexpr int B = 8 * L;
+  // items in flight per thread: a load from L2 takes a microsecond under the weight stream, so the loads of several
+  // items are issued before the first is converted
+  constexpr int UN = GLOBAL ? 1 : 4;
   const int nch = ce - cb;
   const int items = p.M * nch * 8;
   const int items_pad = (items + 31) & ~31;
-  for (int it = ctid; it < items_pad; it += CT) {
-    const bool valid = it < items;
-    int m = 0, ch = 0, u = 0;
-    uint4 va = make_uint4(0u, 0u, 0u, 0u), vb = va;
-    if (valid) {
-      m = it / (nch * 8);
-      const int r = it - m * nch * 8;
-      ch = r >> 3;
-      u = r & 7;
-      const int k0 = (cb + ch) * kChunkK + 32 * (u & 3) + 16 * (u >> 2);
-      if (k0 < p.K) {
-        va = load_x_unit(p, m, k0, inv);
-        vb = load_x_unit(p, m, k0 + 8, inv);
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  for (int it0 = ctid; it0 < items_pad; it0 += nthreads * UN) {
+    uint4 va[UN], vb[UN];
+#pragma unroll
+    for (int q = 0; q < UN; ++q) {
+      va[q] = zero4;
+      vb[q] = zero4;
+      const int it = it0 + q * nthreads;
+      if (it < items) {
+        const int m = it / (nch * 8);
+        const int r = it - m * nch * 8;
+        const int k0 = (cb + (r >> 3)) * kChunkK + 32 * (r & 3) + 16 * ((r & 7) >> 2);
+        if (k0 < p.K) {
+          va[q] = load_x_unit(p, m, k0, inv);
+          vb[q] = load_x_unit(p, m, k0 + 8, inv);
+        }
       }
     }
-    const uint32_t w[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-    uint32_t mx = 0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
-    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    uint32_t eb = mx >> 7;
-    const bool bad = eb == 255u;
-    eb = min(254u, max(40u, eb));
-    const float down = __uint_as_float((uint32_t)(B + 252 - (int)eb) << 23);
-    const uint32_t up_bits = bad ? 0x7FC00000u : (uint32_t)((int)eb - B - 2) << 23;
-    int v[16];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      v[2 * i] = __float2int_rn(__uint_as_float(w[i] << 16) * down);
-      v[2 * i + 1] = __float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * down);
-    }
-    int csum[3] = {0, 0, 0};
-#pragma unroll
-    for (int l = 0; l < L; ++l) {
-      const uint32_t sel = (uint32_t)l | ((uint32_t)(4 + l) << 4);
-      auto pack = [&](int a, int b, int c, int d) {
-        return __byte_perm(__byte_perm((uint32_t)v[a], (uint32_t)v[b], sel),
-                           __byte_perm((uint32_t)v[c], (uint32_t)v[d], sel), 0x5410);
-      };
-      const uint4 o = make_uint4(pack(0, 2, 4, 6), pack(8, 10, 12, 14), pack(1, 3, 5, 7), pack(9, 11, 13, 15));
-      int c;
-      if (l == L - 1) {
-        c = __dp4a((int)o.x, 0x01010101, 0);
-        c = __dp4a((int)o.y, 0x01010101, c);
-        c = __dp4a((int)o.z, 0x01010101, c);
-        c = __dp4a((int)o.w, 0x01010101, c);
-      } else {
-        uint32_t cu = __dp4a(o.x, 0x01010101u, 0u);
-        cu = __dp4a(o.y, 0x01010101u, cu);
-        cu = __dp4a(o.z, 0x01010101u, cu);
-        cu = __dp4a(o.w, 0x01010101u, cu);
-        c = (int)cu;
+    for (int q = 0; q < UN; ++q) {
+      const int it = it0 + q * nthreads;
+      if (it >= items_pad) break;  // whole warps leave together: the shuffles below stay converged
+      const bool valid = it < items;
+      int m = 0, ch = 0, u = 0;
+      if (valid) {
+        m = it / (nch * 8);
+        const int r = it - m * nch * 8;
+        ch = r >> 3;
+        u = r & 7;
       }
-      c += __shfl_xor_sync(0xffffffffu, c, 4);
-      c += __shfl_xor_sync(0xffffffffu, c, 2);
-      c += __shfl_xor_sync(0xffffffffu, c, 1);
-      csum[l] = -128 * c;
-      if (valid) sts128(xs_base + m * p.xs_m_stride + ch * (128 * L) + l * 128 + u * 16, o);
+      const uint32_t w[8] = {va[q].x, va[q].y, va[q].z, va[q].w, vb[q].x, vb[q].y, vb[q].z, vb[q].w};
+      uint32_t mx = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      uint32_t eb = mx >> 7;
+      const bool bad = eb == 255u;
+      eb = min(254u, max(40u, eb));
+      const float down = __uint_as_float((uint32_t)(B + 252 - (int)eb) << 23);
+      const uint32_t up_bits = bad ? 0x7FC00000u : (uint32_t)((int)eb - B - 2) << 23;
+      int v[16];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[2 * i] = __float2int_rn(__uint_as_float(w[i] << 16) * down);
+        v[2 * i + 1] = __float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * down);
+      }
+      int csum[3] = {0, 0, 0};
+#pragma unroll
+      for (int l = 0; l < L; ++l) {
+        const uint32_t sel = (uint32_t)l | ((uint32_t)(4 + l) << 4);
+        auto pack = [&](int a, int b, int c, int d) {
+          return __byte_perm(__byte_perm((uint32_t)v[a], (uint32_t)v[b], sel),
+                             __byte_perm((uint32_t)v[c], (uint32_t)v[d], sel), 0x5410);
+        };
+        const uint4 o = make_uint4(pack(0, 2, 4, 6), pack(8, 10, 12, 14), pack(1, 3, 5, 7), pack(9, 11, 13, 15));
+        int c;
+        if (l == L - 1) {
+          c = __dp4a((int)o.x, 0x01010101, 0);
+          c = __dp4a((int)o.y, 0x01010101, c);
+          c = __dp4a((int)o.z, 0x01010101, c);
+          c = __dp4a((int)o.w, 0x01010101, c);
+        } else {
+          uint32_t cu = __dp4a(o.x, 0x01010101u, 0u);
+          cu = __dp4a(o.y, 0x01010101u, cu);
+          cu = __dp4a(o.z, 0x01010101u, cu);
+          cu = __dp4a(o.w, 0x01010101u, cu);
+          c = (int)cu;
+        }
+        c += __shfl_xor_sync(0xffffffffu, c, 4);
+        c += __shfl_xor_sync(0xffffffffu, c, 2);
+        c += __shfl_xor_sync(0xffffffffu, c, 1);
+        csum[l] = -128 * c;
+        if constexpr (GLOBAL) {
+          if (valid) __stcg(reinterpret_cast<uint4*>(gx + ((size_t)m * nch + ch) * (128 * L) + l * 128 + u * 16), o);
+        } else {
+          if (valid) sts128(xs_base + m * p.xs_m_stride + ch * (128 * L) + l * 128 + u * 16, o);
+        }
+      }
+      if (valid && u == 0) {
+        const int4 info = make_int4((int)up_bits, csum[0], csum[1], csum[2]);
+        if constexpr (GLOBAL)
+          __stcg(xinfo + m * nch + ch, info);
+        else
+          xinfo[m * nch + ch] = info;
+      }
     }
-    if (valid && u == 0) xinfo[m * nch + ch] = make_int4((int)up_bits, csum[0], csum[1], csum[2]);
   }
+}
+
+// Copy of a slice [cb, ce) of the pre-staged X and its info into the CTA's shared memory with 16-byte asynchronous
+// copies through L2 (the staging kernel may have finished only just before, under programmatic launch).
+template <int L>
+__device__ __forceinline__ void copy_staged_x(const GemvParams& p, uint32_t xs_base, uint32_t xinfo_base, int cb, int ce,
+                                              int ctid, int nthreads) {
+  const int nch = ce - cb;
+  const int nx = nch * (8 * L);  // 16-byte units of X per token
+  const int per = nx + nch;      // ... plus one unit of info per chunk
+  const int total = p.M * per;
+  const uint4* gx = reinterpret_cast<const uint4*>(p.pre_x);
+  const uint4* gi = reinterpret_cast<const uint4*>(p.pre_info);
+  for (int it = ctid; it < total; it += nthreads) {
+    const int m = it / per, r = it - m * per;
+    const bool is_x = r < nx;
+    const uint4* src = is_x ? gx + ((size_t)m * p.nchunks + cb) * (8 * L) + r : gi + (size_t)m * p.nchunks + cb + (r - nx);
+    const uint32_t dst = is_x ? xs_base + m * p.xs_m_stride + r * 16 : xinfo_base + (m * nch + (r - nx)) * 16;
+    cp_async_cg16(dst, src);  // all copies of a thread are in flight together
+  }
+  cp_async_wait_all();
 }
 
 // ---- tensor parallelism: the all-gather of Y fused into the epilogue -------------------------------------
@@ -462,6 +518,39 @@ __device__ __forceinline__ int tp_column(const GemvTp& tp, int n) {
 __device__ __forceinline__ void tp_store(const GemvTp& tp, int tok, int n, __nv_bfloat16 v) {
   const size_t at = (size_t)tok * tp.ld + tp_column(tp, n);
   for (int r = 0; r < tp.world; ++r) static_cast<__nv_bfloat16*>(tp.y_peer[r])[at] = v;
+}
+// Four consecutive outputs of one token (n0 a multiple of 4) rounded to bf16: into Y or, tensor parallel, into the
+// gathered row of every rank.  One 8-byte store where the four land side by side on an 8-byte boundary.
+__device__ __forceinline__ void store_out4(const GemvParams& p, int tok, int n0, const float4& v) {
+  if (n0 >= p.N) return;
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  const uint2 pk = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+  const __nv_bfloat16 e[4] = {lo.x, lo.y, hi.x, hi.y};
+  const bool whole = n0 + 3 < p.N;
+  if (p.tp.world) {
+    const int c0 = tp_column(p.tp, n0);
+    const size_t at = (size_t)tok * p.tp.ld + c0;
+    const bool side_by_side = whole && tp_column(p.tp, n0 + 3) == c0 + 3;
+    for (int r = 0; r < p.tp.world; ++r) {
+      __nv_bfloat16* y = static_cast<__nv_bfloat16*>(p.tp.y_peer[r]);
+      if (side_by_side && (reinterpret_cast<uintptr_t>(y + at) & 7) == 0) {
+        *reinterpret_cast<uint2*>(y + at) = pk;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (n0 + i < p.N) y[(size_t)tok * p.tp.ld + tp_column(p.tp, n0 + i)] = e[i];
+      }
+    }
+    return;
+  }
+  __nv_bfloat16* y = p.Y + (size_t)tok * p.N + n0;
+  if (whole && (reinterpret_cast<uintptr_t>(y) & 7) == 0) {
+    *reinterpret_cast<uint2*>(y) = pk;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (n0 + i < p.N) y[i] = e[i];
+  }
 }
 // Called by one warp of every CTA when all of the CTA's outputs have been stored.  System-scope releases are dear
 // (a release per CTA cost 6 us per launch, an explicit system fence on top of it 13 us), so the CTAs first count
@@ -500,6 +589,18 @@ __device__ __forceinline__ bool tp_wait(const GemvTp& tp, volatile int* abort_fl
     }
     __nanosleep(40);
   }
+}
+
+// X of a launch staged once for all CTAs (integer path, M >= 2 or so: converting M x K values in every CTA costs more
+// than one small kernel in front).  One thread per 16 values; launched in front of the GEMV on the same stream.
+constexpr int kStageXThreads = 128;
+template <int L>
+__global__ void __launch_bounds__(kStageXThreads) w4_stage_x_kernel(const GemvParams p) {
+  pdl_launch_dependents();  // the GEMV behind may start its weight stream
+  pdl_wait_prior_grid();    // X is the previous kernel's output; the staging area may still be read by the previous GEMV
+  stage_x_i8<L, true>(p, 0u, const_cast<int4*>(p.pre_info), nullptr, 0, p.nchunks,
+                      blockIdx.x * kStageXThreads + threadIdx.x, gridDim.x * kStageXThreads,
+                      const_cast<unsigned char*>(p.pre_x));
 }
 
 // MT: token tiles of 8 (1 or 2).  NCW: consumer warps (= chunks per stage, even).  MODE: see kMode*.
@@ -607,6 +708,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
     // ------------------------------------------------------------ reducer warp
     // Sums the per-warp partial sums of a finished tile while the consumer warps are already on the
     // next one; owns the output stores and the cross-CTA (split-K) reduction.
+    constexpr int kRedUnits = 2 * MT;  // (token, four rows) units per lane: 8 MT tokens x 8 row quads / 32 lanes
     int tcount = 0;
     pdl_wait_prior_grid();  // Y, the scratch and the counters may still be in use by the previous kernel
     for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++tcount) {
@@ -616,22 +718,92 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       const float* rbuf = red + b * (NCW * p.M * kRedPitch);
       if (lane == 0) mbar_wait_backoff<100>(bar_red_full + 8 * b, (tcount >> 1) & 1, abort_flag);
       __syncwarp();
-      const int n = row0 + lane;
-      for (int tok = 0; tok < p.M; ++tok) {
+      // A unit is four consecutive rows of one token; lane takes units lane, lane + 32, ...  The warp competes for
+      // issue slots with all the consumer warps (an instruction every ten cycles or so), so what counts is its
+      // instruction count: 16-byte loads, paired adds, 8-byte stores.  Sums run over the warps in ascending order.
+      if (p.M == 1) {
+        // one token: a row per lane is the shortest instruction sequence
         float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < NCW; ++w) sum += rbuf[(w * p.M + tok) * kRedPitch + lane];
+        for (int w = 0; w < NCW; ++w) sum += rbuf[w * kRedPitch + lane];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_red_empty + 8 * b);
+        const int n = row0 + lane;
         if (n < p.N) {
           if (p.nslices > 1)
-            __stcg(p.partial + ((size_t)sl * p.M + tok) * p.N + n, sum);
+            __stcg(p.partial + (size_t)sl * p.N + n, sum);
           else if (p.tp.world)
-            tp_store(p.tp, tok, n, __float2bfloat16(sum));
+            tp_store(p.tp, 0, n, __float2bfloat16(sum));
           else
-            p.Y[(size_t)tok * p.N + n] = __float2bfloat16(sum);
+            p.Y[n] = __float2bfloat16(sum);
+        }
+        if (p.nslices > 1) {
+          __threadfence();
+          __syncwarp();
+          int last = 0;
+          if (lane == 0) {
+            const int old = atomicAdd(p.counters + rg, 1);
+            last = old == p.nslices - 1;
+            if (last) p.counters[rg] = 0;  // ready for the next launch
+          }
+          last = __shfl_sync(0xffffffffu, last, 0);
+          if (last) {
+            __threadfence();
+            if (n < p.N) {
+              float total = 0.f;
+              for (int q = 0; q < p.nslices; ++q) total += __ldcg(p.partial + (size_t)q * p.N + n);
+              if (p.tp.world)
+                tp_store(p.tp, 0, n, __float2bfloat16(total));
+              else
+                p.Y[n] = __float2bfloat16(total);
+            }
+          }
+        }
+        continue;
+      }
+      const int nunits = p.M * 8;
+      float4 acc[kRedUnits];
+      const float* src[kRedUnits];
+#pragma unroll
+      for (int j = 0; j < kRedUnits; ++j) {
+        const int u = min(lane + 32 * j, nunits - 1);
+        acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        src[j] = rbuf + (u >> 3) * kRedPitch + (u & 7) * 4;
+      }
+      const int wstride = p.M * kRedPitch;
+#pragma unroll
+      for (int w = 0; w < NCW; ++w)
+#pragma unroll
+        for (int j = 0; j < kRedUnits; ++j)
+          if (j == 0 || lane + 32 * j < nunits) {
+            const float4 v = *reinterpret_cast<const float4*>(src[j] + w * wstride);
+            const float2 lo = add_f32x2(make_float2(acc[j].x, acc[j].y), make_float2(v.x, v.y));
+            const float2 hi = add_f32x2(make_float2(acc[j].z, acc[j].w), make_float2(v.z, v.w));
+            acc[j] = make_float4(lo.x, lo.y, hi.x, hi.y);
+          }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_red_empty + 8 * b);  // the sums are in registers: the buffer is free again
+      const bool rows_aligned = (p.N & 3) == 0;
+#pragma unroll
+      for (int j = 0; j < kRedUnits; ++j) {
+        const int u = lane + 32 * j;
+        if (u < nunits) {
+          const int tok = u >> 3, n0 = row0 + (u & 7) * 4;
+          if (p.nslices > 1) {
+            float* d = p.partial + ((size_t)sl * p.M + tok) * p.N + n0;
+            const float f[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w};
+            if (rows_aligned && n0 + 3 < p.N) {
+              __stcg(reinterpret_cast<float4*>(d), acc[j]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                if (n0 + i < p.N) __stcg(d + i, f[i]);
+            }
+          } else {
+            store_out4(p, tok, n0, acc[j]);
+          }
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_red_empty + 8 * b);
       if (p.nslices > 1) {
         // the last slice of this row group to arrive sums all partials in slice order
         __threadfence();
@@ -645,15 +817,41 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {
           __threadfence();
-          if (n < p.N)
-            for (int tok = 0; tok < p.M; ++tok) {
-              float sum = 0.f;
-              for (int q = 0; q < p.nslices; ++q) sum += __ldcg(p.partial + ((size_t)q * p.M + tok) * p.N + n);
-              if (p.tp.world)
-                tp_store(p.tp, tok, n, __float2bfloat16(sum));
-              else
-                p.Y[(size_t)tok * p.N + n] = __float2bfloat16(sum);
+#pragma unroll
+          for (int j = 0; j < kRedUnits; ++j) {
+            const int u = lane + 32 * j;
+            const int tok = u >> 3, n0 = row0 + (u & 7) * 4;
+            if (u < nunits && n0 < p.N) {
+              const float* s0 = p.partial + (size_t)tok * p.N + n0;
+              const size_t qstride = (size_t)p.M * p.N;
+              float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (rows_aligned && n0 + 3 < p.N) {
+                // four slices' loads in flight together (an L2 round trip takes a microsecond under the weight stream)
+                for (int q0 = 0; q0 < p.nslices; q0 += 4) {
+                  float4 v[4];
+#pragma unroll
+                  for (int i = 0; i < 4; ++i)
+                    if (q0 + i < p.nslices) v[i] = __ldcg(reinterpret_cast<const float4*>(s0 + (q0 + i) * qstride));
+#pragma unroll
+                  for (int i = 0; i < 4; ++i)
+                    if (q0 + i < p.nslices) {
+                      sum.x += v[i].x;
+                      sum.y += v[i].y;
+                      sum.z += v[i].z;
+                      sum.w += v[i].w;
+                    }
+                }
+              } else {
+                float f[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int q = 0; q < p.nslices; ++q)
+#pragma unroll
+                  for (int i = 0; i < 4; ++i)
+                    if (n0 + i < p.N) f[i] += __ldcg(s0 + q * qstride + i);
+                sum = make_float4(f[0], f[1], f[2], f[3]);
+              }
+              store_out4(p, tok, n0, sum);
             }
+          }
         }
       }
     }
@@ -707,9 +905,12 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           float* inv = reinterpret_cast<float*>(smem + kNormInvOffset);
           if (p.pro == kProAddRmsNorm && staged_slice < 0)
             rmsnorm_factors<kConsumerThreads>(p, reinterpret_cast<float*>(smem + kNormSsOffset), inv, ctid);
-          if constexpr (kI8)
-            stage_x_i8<kConsumerThreads, L>(p, xs_base, reinterpret_cast<int4*>(xinfo), inv, cb, ce, ctid);
-          else
+          if constexpr (kI8) {
+            if (p.pre_x != nullptr)
+              copy_staged_x<L>(p, xs_base, smem_u32(xinfo), cb, ce, ctid, kConsumerThreads);
+            else
+              stage_x_i8<L, false>(p, xs_base, reinterpret_cast<int4*>(xinfo), inv, cb, ce, ctid, kConsumerThreads);
+          } else
             stage_x_f16<kConsumerThreads, MODE == kModeFold>(p, xs_base, xinfo, inv, cb, ce, ctid);
         }
         if constexpr (!kHalf) stage_x_bf16<kConsumerThreads>(p, xs_base, cb, ce, ctid);
@@ -1062,7 +1263,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 // ------------------------------------------------------------------ host side
 struct GemvPlan {
   int mt, ncw, cpw, mode, nslices, cps, nstages, grid;
-  bool pdl;
+  bool pdl, prestage;
   int ctas_per_sm;
   size_t smem;
   int xs_m_stride;
@@ -1080,9 +1281,10 @@ size_t smem_without_ring(int M, int mode, int ncw, int cps) {
 // tile costs its chunk count rounded up to whole stages (idle warps in a short last stage are lost
 // time), plus a fixed reduction overhead; split-K tiles pay the scratch round trip as well.  The slice
 // count with the smallest makespan over the persistent CTAs wins.
-bool plan_for_width(int M, int N, int K, int ncw, int cpw, int mt, int mode, int flags, int sm_count,
+bool plan_for_width(int M, int N, int K, int ncw, int cpw, int mt, int mode, int flags, bool prestage, int sm_count,
                     size_t partial_cap, int counters_cap, GemvPlan* out) {
   GemvPlan pl{};
+  pl.prestage = prestage;
   pl.mt = mt;
   pl.mode = mode;
   pl.ncw = ncw;
@@ -1100,7 +1302,9 @@ bool plan_for_width(int M, int N, int K, int ncw, int cpw, int mt, int mode, int
   double best = 1e30;
   int best_ns = 0, best_cps = 0, best_ctas = 1;
   const int max_ns = (flags & kFlagForceNoSplitK) ? 1 : std::min(nchunks, 64);
+  const int forced_ns = (flags >> 16) & 0x3F;  // bits 16-21 of the flags: this many K slices or none (diagnostics)
   for (int ns = 1; ns <= max_ns; ++ns) {
+    if (forced_ns && ns != forced_ns) continue;
     const int cps = (nchunks + ns - 1) / ns;
     if ((nchunks + cps - 1) / cps != ns) continue;
     if (cpw == 2 && ns > 1 && (cps & 1)) continue;  // slices start on a box boundary, scale copies stay aligned
@@ -1121,7 +1325,8 @@ bool plan_for_width(int M, int N, int K, int ncw, int cpw, int mt, int mode, int
     // is one of the things the first-launch measurement settles)
     const double tile_cost = 0.5 * (cps + stage_chunks) + 2.85 * iters + 3.0 + (ns > 1 ? 12.0 : 0.0);
     // staging of X: once per CTA and slice, spread over the consumer threads
-    const double stage_cost = 0.5 * M * cps * (8.0 / ncw);
+    // (pre-staged X: a plain copy of the slice, about a tenth of the conversion)
+    const double stage_cost = (prestage ? 0.05 : 0.5) * M * cps * (8.0 / ncw);
     for (int ctas = 2; ctas >= 1; --ctas) {
       if (ctas == 2 && !(mt == 1 && ncw <= 12 && fixed + 2 * (size_t)stage_bytes <= kHalfSmem)) continue;
       if (ctas == 1 && fixed + 2 * (size_t)stage_bytes > (size_t)kSmemLimit) continue;
@@ -1177,6 +1382,9 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
     else
       mode = (flags & kFlagWideX) ? kModeI8x3 : kModeI8x2;
   }
+  // X staged by a kernel in front: integer modes; by default from eight tokens on, from four where K is long
+  const bool prestage = mode_limbs(mode) > 0 && !(flags & kFlagNoPreStageX) &&
+                        ((flags & kFlagPreStageX) || M >= 8 || (M >= 4 && K >= 8192));
   GemvPlan best{};
   bool have = false;
   // One token tile: candidates are the wide CTAs (16 or 14 consumer warps, one per SM) and the narrow one
@@ -1185,7 +1393,7 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
   const int forced = ((flags >> 4) & 0xF) * 2;
   // Two chunks per warp and stage: integer modes whose scales can be staged with aligned copies (one scale per chunk,
   // an even number of scales per row).  Bits 10 / 11 of the flags force two / one (diagnostics).
-  const bool cpw2_ok = mode_limbs(mode) > 0 && mt == 1 && G == 128 && (K / G) % 2 == 0 && !(flags & 0x800);
+  const bool cpw2_ok = mode_limbs(mode) > 0 && G == 128 && (K / G) % 2 == 0 && !(flags & 0x800);
   if (mt == 1 && !(flags & kFlagNarrowCta)) {
     const int widths[3] = {16, 14, 8};
     for (int w : widths) {
@@ -1194,7 +1402,7 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
         if (cpw == 1 && cpw2_ok && (flags & 0x400)) continue;
         if (cpw == 2 && w == 16) continue;  // not instantiated: 14 x 2 covers the wide case
         GemvPlan pl;
-        if (plan_for_width(M, N, K, w, cpw, mt, mode, flags, sm_count, partial_cap, counters_cap, &pl) &&
+        if (plan_for_width(M, N, K, w, cpw, mt, mode, flags, prestage, sm_count, partial_cap, counters_cap, &pl) &&
             (!have || pl.cost < best.cost)) {
           best = pl;
           have = true;
@@ -1202,7 +1410,18 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
       }
     }
   }
-  if (!have) have = plan_for_width(M, N, K, 8, 1, mt, mode, flags, sm_count, partial_cap, counters_cap, &best);
+  if (!have && mt == 2) {  // two token tiles: the 8-warp CTA, two chunks per warp and stage or one
+    for (int cpw = cpw2_ok ? 2 : 1; cpw >= 1; --cpw) {
+      if (cpw == 1 && cpw2_ok && (flags & 0x400)) continue;
+      GemvPlan pl;
+      if (plan_for_width(M, N, K, 8, cpw, mt, mode, flags, prestage, sm_count, partial_cap, counters_cap, &pl) &&
+          (!have || pl.cost < best.cost)) {
+        best = pl;
+        have = true;
+      }
+    }
+  }
+  if (!have) have = plan_for_width(M, N, K, 8, 1, mt, mode, flags, prestage, sm_count, partial_cap, counters_cap, &best);
   if (!have) return false;
   best.mode = mode;
   best.pdl = (flags & kFlagNoPdl) == 0;
@@ -1240,11 +1459,11 @@ int launch_mode(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan& pl
     case kModeExact: return launch_variant<MT, NCW, kModeExact, 1>(tmap, p, pl, stream);
     case kModeFold: return launch_variant<MT, NCW, kModeFold, 1>(tmap, p, pl, stream);
     case kModeI8x2:
-      if constexpr (MT == 1 && NCW != 16)
+      if constexpr (NCW != 16)
         if (pl.cpw == 2) return launch_variant<MT, NCW, kModeI8x2, 2>(tmap, p, pl, stream);
       return launch_variant<MT, NCW, kModeI8x2, 1>(tmap, p, pl, stream);
     case kModeI8x3:
-      if constexpr (MT == 1 && NCW != 16)
+      if constexpr (NCW != 16)
         if (pl.cpw == 2) return launch_variant<MT, NCW, kModeI8x3, 2>(tmap, p, pl, stream);
       return launch_variant<MT, NCW, kModeI8x3, 1>(tmap, p, pl, stream);
     default: return launch_variant<MT, NCW, kModeGeneric, 1>(tmap, p, pl, stream);
@@ -1334,13 +1553,20 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
   // candidates: the CTA shapes (one token tile; two token tiles have one shape), each with the model's K split and,
   // where the model splits, without a split
   const int shapes[5] = {(4 << 4) | 0x800, (7 << 4) | 0x800, (8 << 4) | 0x800, (4 << 4) | 0x400, (7 << 4) | 0x400};
-  int cand[10], ncand = 0;
-  for (int c = 0; c < (M > 8 ? 1 : 5); ++c) {
-    const int shape = M > 8 ? 0 : shapes[c];
-    GemvPlan pl;
-    if (!make_plan(M, N, K, G, flags | shape, sm_count, ws.partial_bytes, ws.n_counters - 1, &pl)) continue;
-    cand[ncand++] = shape;
-    if (pl.nslices > 1) cand[ncand++] = shape | kFlagForceNoSplitK;
+  // ... and, from two tokens on, with X converted in every CTA or once by a kernel in front (a caller's flag for
+  // either stands; launches that cannot use the kernel in front ignore the flag)
+  int cand[20], ncand = 0;
+  const bool pre_open = M >= 2 && G % 128 == 0 && !(flags & (kFlagFloatX | kFlagPreStageX | kFlagNoPreStageX)) &&
+                        pro.kind != kProAddRmsNorm && !(tp != nullptr && tp->wait_sig != nullptr);
+  const int shapes2[2] = {0x800, 0x400};  // two token tiles: 8 consumer warps, one or two chunks per warp and stage
+  for (int c = 0; c < (M > 8 ? 2 : 5); ++c) {
+    for (int pre = 0; pre < (pre_open ? 2 : 1); ++pre) {
+      const int shape = (M > 8 ? shapes2[c] : shapes[c]) | (pre_open ? (pre ? kFlagPreStageX : kFlagNoPreStageX) : 0);
+      GemvPlan pl;
+      if (!make_plan(M, N, K, G, flags | shape, sm_count, ws.partial_bytes, ws.n_counters - 1, &pl)) continue;
+      cand[ncand++] = shape;
+      if (pl.nslices > 1) cand[ncand++] = shape | kFlagForceNoSplitK;
+    }
   }
   cudaEvent_t e0, e1;
   if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess)
@@ -1424,6 +1650,14 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
   const bool have_scratch = ws.partial && ws.counters;
   GemvPlan pl;
   if (reinterpret_cast<uintptr_t>(S) & 3) flags |= 0x800;  // scale copies need a 4-byte aligned base: one chunk per warp
+  // X staged by a kernel in front: not with the RMSNorm prologue (its factors need the whole row first), not for a
+  // tensor-parallel consumer (the wait on the arrival counter happens inside the GEMV), and only while it fits
+  const int nchunks_all = (K + kChunkK - 1) / kChunkK;
+  const size_t pre_x_bytes = ((size_t)M * nchunks_all * 128 * ((flags & kFlagWideX) ? 3 : 2) + 255) & ~(size_t)255;
+  const size_t pre_bytes = pre_x_bytes + (size_t)M * nchunks_all * sizeof(int4);
+  if (pro.kind == kProAddRmsNorm || (tp != nullptr && tp->wait_sig != nullptr) || !ws.xstage ||
+      pre_bytes > ws.xstage_bytes)
+    flags = (flags & ~kFlagPreStageX) | kFlagNoPreStageX;
   // the last counter is kept for the tensor-parallel epilogue's CTA count
   if (!make_plan(M, N, K, G, have_scratch ? flags : (flags | kFlagForceNoSplitK), sm_count,
                  ws.partial_bytes, ws.n_counters - 1, &pl))
@@ -1475,6 +1709,24 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
       if (!ws.counters || ws.n_counters < 2) return kErrWorkspace;
       p.tp.local_count = ws.counters + ws.n_counters - 1;  // the last counter is never used by split-K (see make_plan)
     }
+  }
+
+  if (pl.prestage) {
+    p.pre_x = ws.xstage;
+    p.pre_info = reinterpret_cast<const int4*>(ws.xstage + pre_x_bytes);
+    const int items = M * p.nchunks * 8;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((items + kStageXThreads - 1) / kStageXThreads);
+    cfg.blockDim = dim3(kStageXThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pl.pdl ? 1 : 0;
+    const cudaError_t e = pl.mode == kModeI8x3 ? cudaLaunchKernelEx(&cfg, w4_stage_x_kernel<3>, p)
+                                               : cudaLaunchKernelEx(&cfg, w4_stage_x_kernel<2>, p);
+    if (e != cudaSuccess) return (int)e;
   }
 
   if (pl.mt == 2) return launch_mode<2, 8>(tmap, p, pl, stream);

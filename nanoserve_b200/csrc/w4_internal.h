@@ -35,6 +35,8 @@ struct Workspace {
   int* counters = nullptr;
   int n_counters = 0;
   int* status = nullptr;
+  unsigned char* xstage = nullptr;  // GEMV: X of a launch staged once for all CTAs (optional)
+  size_t xstage_bytes = 0;
 };
 
 // Flags for the linear launches.
@@ -46,6 +48,9 @@ enum : int {
   kFlagFloatX = 256,       // GEMV: keep X in floating point (fp16 mma path) instead of 16-bit block fixed point
   kFlagNoAutotune = 4096,  // GEMV: never time CTA shapes on the first launch of a shape; the cost model decides
   kFlagWideX = 512,        // GEMV: 24-bit instead of 16-bit block fixed point for X (three byte planes)
+  kFlagPreStageX = 8192,   // GEMV, integer path: convert X once in a small kernel in front and let every CTA copy its
+                           // slice, instead of converting in every CTA (default: for M >= 4)
+  kFlagNoPreStageX = 16384,  // GEMV: never do that
   kFlagNoPdl = 8,          // GEMV: do NOT launch with programmatic stream serialization (by default the kernel may
                            // begin -- weight prefetch only -- while the previous kernel of the stream still runs)
 };

@@ -6,6 +6,7 @@ import pytest
 import torch
 
 import oracle
+from nanoserve_b200 import ops
 from tests.util import bits_to_torch, check_bf16_output, torch_to_bits, u32_to_torch
 
 pytestmark = pytest.mark.gpu
@@ -54,10 +55,14 @@ def test_swiglu_prologue(kernels, M, N, K):
     g = torch.Generator(device="cuda").manual_seed(M + K)
     gu = torch.randn(M, 2 * K, device="cuda", generator=g).to(torch.bfloat16)
     act = kernels.swiglu(gu[:, :K].contiguous(), gu[:, K:].contiguous())
-    y_seq = kernels.w4_linear(act, wq, s, G)
-    y = kernels.w4_linear_fused(gu, wq, s, G, prologue=2)
-    torch.cuda.synchronize()
-    assert torch.equal(y, y_seq)  # same element-wise arithmetic, same product: identical
+    # the CTA shape and K split come from the cost model here, so that both calls sum in the same order; X converted in
+    # every CTA, or once by the kernel in front of the GEMV
+    for flags in (ops.FLAG_NO_AUTOTUNE, ops.FLAG_NO_AUTOTUNE | ops.FLAG_PRE_STAGE_X,
+                  ops.FLAG_NO_AUTOTUNE | ops.FLAG_NO_PRE_STAGE_X):
+        y_seq = kernels.w4_linear(act, wq, s, G, flags=flags)
+        y = kernels.w4_linear_fused(gu, wq, s, G, prologue=2, flags=flags)
+        torch.cuda.synchronize()
+        assert torch.equal(y, y_seq), flags  # same element-wise arithmetic, same product: identical
     # SwiGLU outputs have heavy tails: the 16-bit fixed-point staging of X is coarser where a chunk holds an outlier
     check_bf16_output(torch_to_bits(y), oracle.w4_linear_f32(torch_to_bits(act), Wq, S, G, threads=oracle.max_threads()),
                       5e-5)

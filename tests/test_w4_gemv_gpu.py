@@ -39,7 +39,8 @@ def slack_for(G, flags):
     return SLACK_EXACT if flags & ops.FLAG_WIDE_X else SLACK_DEFAULT
 
 
-@pytest.mark.parametrize("flags", [0, ops.FLAG_WIDE_X, ops.FLAG_FLOAT_X, FLOAT_FOLD, ops.FLAG_NARROW_CTA])
+@pytest.mark.parametrize("flags", [0, ops.FLAG_WIDE_X, ops.FLAG_FLOAT_X, FLOAT_FOLD, ops.FLAG_NARROW_CTA,
+                                   ops.FLAG_PRE_STAGE_X, ops.FLAG_NO_PRE_STAGE_X, ops.FLAG_PRE_STAGE_X | ops.FLAG_WIDE_X])
 @pytest.mark.parametrize("G", [128, 32])
 def test_unpack_is_bit_exact(kernels, flags, G):
     """S == 1 and one-hot X rows make Y[m, n] = q[n, k_m] - 8: every nibble value in every in-word
@@ -73,7 +74,9 @@ SMALL_SHAPES = [(64, 128, 128), (96, 256, 128), (100, 384, 128), (33, 1024, 128)
 
 
 @pytest.mark.parametrize("N,K,G", SMALL_SHAPES)
-@pytest.mark.parametrize("flags", [0, ops.FLAG_WIDE_X, ops.FLAG_FLOAT_X, FLOAT_FOLD, ops.FLAG_NO_PDL])
+@pytest.mark.parametrize("flags", [0, ops.FLAG_WIDE_X, ops.FLAG_FLOAT_X, FLOAT_FOLD, ops.FLAG_NO_PDL,
+                                   ops.FLAG_PRE_STAGE_X, ops.FLAG_NO_PRE_STAGE_X, ops.FLAG_PRE_STAGE_X | ops.FLAG_WIDE_X,
+                                   ops.FLAG_PRE_STAGE_X | ops.FLAG_NO_PDL])
 def test_small_shapes_all_m(kernels, N, K, G, flags):
     for M in range(1, 17):
         X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=11)
@@ -112,6 +115,27 @@ def test_split_k_matches_single_pass_and_is_deterministic(kernels, N, K):
     assert np.array_equal(a, b), "two identical launches differ: the K reduction is not deterministic"
     check_bf16_output(a, ref, SLACK_DEFAULT)
     check_bf16_output(c, ref, SLACK_DEFAULT)
+    assert kernels.device_status() == 0
+
+
+@pytest.mark.parametrize("N,K", [(96, 4096), (512, 3584), (18944, 3584), (100, 384)])  # K that fits one CTA unsplit
+@pytest.mark.parametrize("M", [1, 3, 8, 16])
+def test_x_staged_in_front_gives_the_same_bits(kernels, N, K, M):
+    """The kernel in front of the GEMV writes the bytes a CTA would have produced itself: with the CTA shape and the
+    K split pinned, the outputs are bit-identical, launch after launch (the staging area is reused)."""
+    G = 128
+    pin = ops.FLAG_NO_SPLIT_K | (4 << 4) | 0x800  # 8 consumer warps, one chunk per warp and stage
+    for wide in (0, ops.FLAG_WIDE_X):
+        if wide and M * K * 3 > 150000:
+            continue  # three bytes per value of X: the unsplit K no longer fits one CTA's shared memory
+        X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=31)
+        a = run(kernels, X, Wq, S, G, pin | wide | ops.FLAG_NO_PRE_STAGE_X)
+        for _ in range(3):
+            b = run(kernels, X, Wq, S, G, pin | wide | ops.FLAG_PRE_STAGE_X)
+            assert np.array_equal(a, b)
+        X2, _, _ = oracle.synth_inputs(M, N, K, G, seed=32)  # another X through the same staging area
+        a2 = run(kernels, X2, Wq, S, G, pin | wide | ops.FLAG_NO_PRE_STAGE_X)
+        assert np.array_equal(a2, run(kernels, X2, Wq, S, G, pin | wide | ops.FLAG_PRE_STAGE_X))
     assert kernels.device_status() == 0
 
 
