@@ -87,6 +87,11 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
                                      not apply (RMSNorm prologue, tensor-parallel consumer, B2_FLAG_FLOAT_X, M * K beyond
                                      the staging area) */
 #define B2_FLAG_NO_PRE_STAGE_X 16384 /* GEMV: every CTA converts the slice of X it needs itself, at every M */
+#define B2_FLAG_SPLIT_SUM_KERNEL 32768   /* GEMV with K split across CTAs: a small kernel behind the GEMV adds up the slices'
+                                           partial sums (the default where no measurement has decided; never for
+                                           tensor-parallel producers) */
+#define B2_FLAG_NO_SPLIT_SUM_KERNEL 65536 /* GEMV: the last CTA of a row group to arrive adds them up (a hand-shake of three
+                                           L2 round trips per tile, but no second kernel) */
 #define B2_FLAG_NO_PDL 8          /* GEMV: plain launch.  By default the GEMV is launched with programmatic stream
                                      serialization: it may begin (weight prefetch only) while the previous kernel of
                                      the stream is still running, and touches X, Y and scratch only after that kernel

@@ -116,6 +116,7 @@ struct GemvParams {
   // per-(token, chunk) info) instead of by every CTA; null = every CTA converts its own slice
   const unsigned char* pre_x;
   const int4* pre_info;
+  int sum_kernel;  // split-K: the partial sums are added up by w4_sum_slices_kernel behind this kernel, not by the last CTA
 };
 
 // two buffers of [consumer warp][token < M][kRedPitch] floats
@@ -552,6 +553,37 @@ __device__ __forceinline__ void store_out4(const GemvParams& p, int tok, int n0,
       if (n0 + i < p.N) y[i] = e[i];
   }
 }
+// Split-K: the partial sums of all slices for four consecutive outputs of one token, added in slice order.
+__device__ __forceinline__ float4 sum_slices4(const GemvParams& p, int tok, int n0) {
+  const float* s0 = p.partial + (size_t)tok * p.N + n0;
+  const size_t qstride = (size_t)p.M * p.N;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  if ((p.N & 3) == 0 && n0 + 3 < p.N) {
+    // four slices' loads in flight together (an L2 round trip takes a microsecond under the weight stream)
+    for (int q0 = 0; q0 < p.nslices; q0 += 4) {
+      float4 v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (q0 + i < p.nslices) v[i] = __ldcg(reinterpret_cast<const float4*>(s0 + (q0 + i) * qstride));
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (q0 + i < p.nslices) {
+          sum.x += v[i].x;
+          sum.y += v[i].y;
+          sum.z += v[i].z;
+          sum.w += v[i].w;
+        }
+    }
+  } else {
+    float f[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int q = 0; q < p.nslices; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (n0 + i < p.N) f[i] += __ldcg(s0 + q * qstride + i);
+    sum = make_float4(f[0], f[1], f[2], f[3]);
+  }
+  return sum;
+}
 // Called by one warp of every CTA when all of the CTA's outputs have been stored.  System-scope releases are dear
 // (a release per CTA cost 6 us per launch, an explicit system fence on top of it 13 us), so the CTAs first count
 // themselves in on a device-scope counter of their own GPU; the last one to arrive -- which has thereby observed the
@@ -601,6 +633,23 @@ __global__ void __launch_bounds__(kStageXThreads) w4_stage_x_kernel(const GemvPa
   stage_x_i8<L, true>(p, 0u, const_cast<int4*>(p.pre_info), nullptr, 0, p.nchunks,
                       blockIdx.x * kStageXThreads + threadIdx.x, gridDim.x * kStageXThreads,
                       const_cast<unsigned char*>(p.pre_x));
+}
+
+// Split-K without the per-tile hand-shake: behind a GEMV launched with `sum_kernel` set, adds up the partial sums of
+// the slices and stores the outputs.  (In the GEMV itself a split tile costs the reducer warp a store, a fence and an
+// atomic whose answer it needs: three L2 round trips, 3.5 us per tile measured, one after the other.)
+// Small CTAs: launched programmatically, they become resident beside the GEMV's CTAs (which leave few registers
+// free) and only then let the next kernel of the stream start its weight stream.
+constexpr int kSumThreads = 64;
+__global__ void __launch_bounds__(kSumThreads) w4_sum_slices_kernel(const GemvParams p) {
+  pdl_launch_dependents();
+  pdl_wait_prior_grid();  // all partial sums are in memory once the GEMV has completed
+  const int quads = (p.N + 3) >> 2;
+  const int total = p.M * quads;
+  for (int u = blockIdx.x * kSumThreads + threadIdx.x; u < total; u += gridDim.x * kSumThreads) {
+    const int tok = u / quads, n0 = (u - tok * quads) * 4;
+    store_out4(p, tok, n0, sum_slices4(p, tok, n0));
+  }
 }
 
 // MT: token tiles of 8 (1 or 2).  NCW: consumer warps (= chunks per stage, even).  MODE: see kMode*.
@@ -718,9 +767,6 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
       const float* rbuf = red + b * (NCW * p.M * kRedPitch);
       if (lane == 0) mbar_wait_backoff<100>(bar_red_full + 8 * b, (tcount >> 1) & 1, abort_flag);
       __syncwarp();
-      // A unit is four consecutive rows of one token; lane takes units lane, lane + 32, ...  The warp competes for
-      // issue slots with all the consumer warps (an instruction every ten cycles or so), so what counts is its
-      // instruction count: 16-byte loads, paired adds, 8-byte stores.  Sums run over the warps in ascending order.
       if (p.M == 1) {
         // one token: a row per lane is the shortest instruction sequence
         float sum = 0.f;
@@ -737,7 +783,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           else
             p.Y[n] = __float2bfloat16(sum);
         }
-        if (p.nslices > 1) {
+        if (p.nslices > 1 && !p.sum_kernel) {
           __threadfence();
           __syncwarp();
           int last = 0;
@@ -761,6 +807,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         }
         continue;
       }
+      // A unit is four consecutive rows of one token; lane takes units lane, lane + 32, ...  The warp competes for
+      // issue slots with all the consumer warps (an instruction every ten cycles or so), so what counts is its
+      // instruction count: 16-byte loads, paired adds, 8-byte stores.  Sums run over the warps in ascending order.
       const int nunits = p.M * 8;
       float4 acc[kRedUnits];
       const float* src[kRedUnits];
@@ -804,7 +853,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           }
         }
       }
-      if (p.nslices > 1) {
+      if (p.nslices > 1 && !p.sum_kernel) {
         // the last slice of this row group to arrive sums all partials in slice order
         __threadfence();
         __syncwarp();
@@ -821,36 +870,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
           for (int j = 0; j < kRedUnits; ++j) {
             const int u = lane + 32 * j;
             const int tok = u >> 3, n0 = row0 + (u & 7) * 4;
-            if (u < nunits && n0 < p.N) {
-              const float* s0 = p.partial + (size_t)tok * p.N + n0;
-              const size_t qstride = (size_t)p.M * p.N;
-              float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (rows_aligned && n0 + 3 < p.N) {
-                // four slices' loads in flight together (an L2 round trip takes a microsecond under the weight stream)
-                for (int q0 = 0; q0 < p.nslices; q0 += 4) {
-                  float4 v[4];
-#pragma unroll
-                  for (int i = 0; i < 4; ++i)
-                    if (q0 + i < p.nslices) v[i] = __ldcg(reinterpret_cast<const float4*>(s0 + (q0 + i) * qstride));
-#pragma unroll
-                  for (int i = 0; i < 4; ++i)
-                    if (q0 + i < p.nslices) {
-                      sum.x += v[i].x;
-                      sum.y += v[i].y;
-                      sum.z += v[i].z;
-                      sum.w += v[i].w;
-                    }
-                }
-              } else {
-                float f[4] = {0.f, 0.f, 0.f, 0.f};
-                for (int q = 0; q < p.nslices; ++q)
-#pragma unroll
-                  for (int i = 0; i < 4; ++i)
-                    if (n0 + i < p.N) f[i] += __ldcg(s0 + q * qstride + i);
-                sum = make_float4(f[0], f[1], f[2], f[3]);
-              }
-              store_out4(p, tok, n0, sum);
-            }
+            if (u < nunits && n0 < p.N) store_out4(p, tok, n0, sum_slices4(p, tok, n0));
           }
         }
       }
@@ -1263,7 +1283,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
 // ------------------------------------------------------------------ host side
 struct GemvPlan {
   int mt, ncw, cpw, mode, nslices, cps, nstages, grid;
-  bool pdl, prestage;
+  bool pdl, prestage, sum_kernel;
   int ctas_per_sm;
   size_t smem;
   int xs_m_stride;
@@ -1302,7 +1322,7 @@ bool plan_for_width(int M, int N, int K, int ncw, int cpw, int mt, int mode, int
   double best = 1e30;
   int best_ns = 0, best_cps = 0, best_ctas = 1;
   const int max_ns = (flags & kFlagForceNoSplitK) ? 1 : std::min(nchunks, 64);
-  const int forced_ns = (flags >> 16) & 0x3F;  // bits 16-21 of the flags: this many K slices or none (diagnostics)
+  const int forced_ns = (flags >> 24) & 0x3F;  // bits 24-29 of the flags: this many K slices or none (diagnostics)
   for (int ns = 1; ns <= max_ns; ++ns) {
     if (forced_ns && ns != forced_ns) continue;
     const int cps = (nchunks + ns - 1) / ns;
@@ -1323,7 +1343,11 @@ bool plan_for_width(int M, int N, int K, int ncw, int cpw, int mt, int mode, int
     // chunks), which is what two chunks per warp and stage save
     // split-K tiles pay the scratch round trip, the counter and the final sum (1 to 3 us measured; whether a split pays
     // is one of the things the first-launch measurement settles)
-    const double tile_cost = 0.5 * (cps + stage_chunks) + 2.85 * iters + 3.0 + (ns > 1 ? 12.0 : 0.0);
+    // (with the sums left to the kernel behind, a split tile costs a 16-byte store more than a whole one, and the
+    // launch pays for that kernel once)
+    const bool sum_kernel = (flags & kFlagSplitSumKernel) != 0;
+    const double tile_cost = 0.5 * (cps + stage_chunks) + 2.85 * iters + 3.0 + (ns > 1 ? (sum_kernel ? 1.0 : 12.0) : 0.0);
+    const double launch_cost = ns > 1 && sum_kernel ? 20.0 : 0.0;
     // staging of X: once per CTA and slice, spread over the consumer threads
     // (pre-staged X: a plain copy of the slice, about a tenth of the conversion)
     const double stage_cost = (prestage ? 0.05 : 0.5) * M * cps * (8.0 / ncw);
@@ -1335,6 +1359,7 @@ bool plan_for_width(int M, int N, int K, int ncw, int cpw, int mt, int mode, int
       const long active = std::min<long>(ctas, (tiles + grid - 1) / grid);  // CTAs that share the busiest SM
       double cost = (rounds * tile_cost + stage_cost * std::min<long>(rounds, ns)) * active;
       if (active == 2) cost *= 0.78;  // measured: one CTA's staging and tail overlap the other's streaming
+      cost += launch_cost;
       // a ring of two stages lets the producer run only one stage ahead
       const size_t cap = ctas == 2 ? kHalfSmem : (size_t)kSmemLimit;
       if ((cap - fixed) / stage_bytes < 3) cost *= 1.25;
@@ -1372,6 +1397,8 @@ bool plan_for_width(int M, int N, int K, int ncw, int cpw, int mt, int mode, int
 
 bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap,
                GemvPlan* out) {
+  // split K: the slices are summed by a kernel behind the GEMV unless the caller (or a tensor-parallel launch) says no
+  flags = (flags & kFlagNoSplitSumKernel) ? (flags & ~kFlagSplitSumKernel) : (flags | kFlagSplitSumKernel);
   const int mt = M > 8 ? 2 : 1;
   // G % 128 == 0: the integer path with two bytes per value of X, or three (kFlagWideX), or X in floating point on
   // the fp16 mma (kFlagFloatX; with kFlagFoldZeroPoint its cheaper variant)
@@ -1424,6 +1451,7 @@ bool make_plan(int M, int N, int K, int G, int flags, int sm_count, size_t parti
   if (!have) have = plan_for_width(M, N, K, 8, 1, mt, mode, flags, prestage, sm_count, partial_cap, counters_cap, &best);
   if (!have) return false;
   best.mode = mode;
+  best.sum_kernel = best.nslices > 1 && (flags & kFlagSplitSumKernel);
   best.pdl = (flags & kFlagNoPdl) == 0;
   *out = best;
   return true;
@@ -1555,27 +1583,33 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
   const int shapes[5] = {(4 << 4) | 0x800, (7 << 4) | 0x800, (8 << 4) | 0x800, (4 << 4) | 0x400, (7 << 4) | 0x400};
   // ... and, from two tokens on, with X converted in every CTA or once by a kernel in front (a caller's flag for
   // either stands; launches that cannot use the kernel in front ignore the flag)
-  int cand[20], ncand = 0;
+  int cand[32], ncand = 0;
   const bool pre_open = M >= 2 && G % 128 == 0 && !(flags & (kFlagFloatX | kFlagPreStageX | kFlagNoPreStageX)) &&
                         pro.kind != kProAddRmsNorm && !(tp != nullptr && tp->wait_sig != nullptr);
+  // ... and, where K is split, with the slices added up by the last CTA to arrive or by a kernel behind (which may
+  // change the split the model picks)
+  const bool sum_open = !(flags & (kFlagSplitSumKernel | kFlagNoSplitSumKernel | kFlagForceNoSplitK)) &&
+                        !(tp != nullptr && tp->world > 0);
   const int shapes2[2] = {0x800, 0x400};  // two token tiles: 8 consumer warps, one or two chunks per warp and stage
   for (int c = 0; c < (M > 8 ? 2 : 5); ++c) {
     for (int pre = 0; pre < (pre_open ? 2 : 1); ++pre) {
       const int shape = (M > 8 ? shapes2[c] : shapes[c]) | (pre_open ? (pre ? kFlagPreStageX : kFlagNoPreStageX) : 0);
       GemvPlan pl;
-      if (!make_plan(M, N, K, G, flags | shape, sm_count, ws.partial_bytes, ws.n_counters - 1, &pl)) continue;
-      cand[ncand++] = shape;
+      const int in_kernel = sum_open ? kFlagNoSplitSumKernel : 0;
+      if (!make_plan(M, N, K, G, flags | shape | in_kernel, sm_count, ws.partial_bytes, ws.n_counters - 1, &pl)) continue;
+      cand[ncand++] = shape | in_kernel;
       if (pl.nslices > 1) cand[ncand++] = shape | kFlagForceNoSplitK;
+      if (sum_open && make_plan(M, N, K, G, flags | shape | kFlagSplitSumKernel, sm_count, ws.partial_bytes,
+                                ws.n_counters - 1, &pl) && pl.nslices > 1)
+        cand[ncand++] = shape | kFlagSplitSumKernel;
     }
   }
   cudaEvent_t e0, e1;
   if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess)
     return gemv_launch_planned(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
-  int best = 0;
-  float best_ms = 1e30f;
-  for (int c = 0; c < ncand; ++c) {
-    const int f = flags | cand[c];
-    if (gemv_launch_planned(X, Wq, S, y_trial, M, N, K, G, pro, ws, f, sm_count, stream, nullptr) != 0) continue;
+  // score of a candidate in milliseconds (1e30 if a launch failed)
+  auto measure = [&](int f) -> float {
+    if (gemv_launch_planned(X, Wq, S, y_trial, M, N, K, G, pro, ws, f, sm_count, stream, nullptr) != 0) return 1e30f;
     // In use the weights come from HBM (a model's matrices do not fit the 126 MB L2 together), so every timed launch
     // is preceded by a write over the scratch area that pushes the matrix out of L2.
     bool ok = true;
@@ -1588,7 +1622,7 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
       cold[i] = 0.f;
       ok = ok && cudaEventSynchronize(e1) == cudaSuccess && cudaEventElapsedTime(&cold[i], e0, e1) == cudaSuccess;
     }
-    if (!ok) continue;
+    if (!ok) return 1e30f;
     std::sort(cold, cold + 6);  // the three fastest count: other work on the GPU only ever adds time
     // ... and a dependent chain of launches, as in a decode step, where one launch's fixed costs overlap the weight
     // stream of its neighbours (the matrix may sit in L2 here; the sum of the two views ranks the shapes best)
@@ -1602,13 +1636,28 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
       ok = ok && cudaEventSynchronize(e1) == cudaSuccess && cudaEventElapsedTime(&t, e0, e1) == cudaSuccess;
       chain = std::min(chain, t);
     }
-    if (!ok) continue;
-    const float ms = (cold[0] + cold[1] + cold[2]) / 3.f + chain / 8.f;
-    if (ms < best_ms) {
-      best_ms = ms;
-      best = cand[c];
-    }
+    if (!ok) return 1e30f;
+    return (cold[0] + cold[1] + cold[2]) / 3.f + chain / 8.f;
+  };
+  float score[32];
+  int order[32];
+  for (int c = 0; c < ncand; ++c) {
+    score[c] = measure(flags | cand[c]);
+    order[c] = c;
   }
+  std::sort(order, order + ncand, [&](int a, int b) { return score[a] < score[b]; });
+  // the leaders are often within the noise of one another: a second look at the best three
+  for (int r = 0; r < std::min(3, ncand); ++r) {
+    const int c = order[r];
+    if (score[c] < 1e29f) score[c] = std::min(score[c], measure(flags | cand[c])) ;
+  }
+  int best = 0;
+  float best_ms = 1e30f;
+  for (int r = 0; r < std::min(3, ncand); ++r)
+    if (score[order[r]] < best_ms) {
+      best_ms = score[order[r]];
+      best = cand[order[r]];
+    }
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
   {
@@ -1658,6 +1707,9 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
   if (pro.kind == kProAddRmsNorm || (tp != nullptr && tp->wait_sig != nullptr) || !ws.xstage ||
       pre_bytes > ws.xstage_bytes)
     flags = (flags & ~kFlagPreStageX) | kFlagNoPreStageX;
+  // split-K sums by a kernel behind (the default): not for a tensor-parallel producer, whose CTAs signal the peers
+  // after their stores
+  if (tp != nullptr && tp->world > 0) flags |= kFlagNoSplitSumKernel;
   // the last counter is kept for the tensor-parallel epilogue's CTA count
   if (!make_plan(M, N, K, G, have_scratch ? flags : (flags | kFlagForceNoSplitK), sm_count,
                  ws.partial_bytes, ws.n_counters - 1, &pl))
@@ -1729,12 +1781,30 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
     if (e != cudaSuccess) return (int)e;
   }
 
-  if (pl.mt == 2) return launch_mode<2, 8>(tmap, p, pl, stream);
-  switch (pl.ncw) {
-    case 16: return launch_mode<1, 16>(tmap, p, pl, stream);
-    case 14: return launch_mode<1, 14>(tmap, p, pl, stream);
-    default: return launch_mode<1, 8>(tmap, p, pl, stream);
+  p.sum_kernel = pl.sum_kernel ? 1 : 0;
+  int rc;
+  if (pl.mt == 2) {
+    rc = launch_mode<2, 8>(tmap, p, pl, stream);
+  } else {
+    switch (pl.ncw) {
+      case 16: rc = launch_mode<1, 16>(tmap, p, pl, stream); break;
+      case 14: rc = launch_mode<1, 14>(tmap, p, pl, stream); break;
+      default: rc = launch_mode<1, 8>(tmap, p, pl, stream); break;
+    }
   }
+  if (rc != 0 || !p.sum_kernel) return rc;
+  const int units = M * ((N + 3) / 4);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(std::min((units + kSumThreads - 1) / kSumThreads, 4 * sm_count));
+  cfg.blockDim = dim3(kSumThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pl.pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, w4_sum_slices_kernel, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 }  // namespace

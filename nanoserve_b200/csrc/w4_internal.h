@@ -51,6 +51,9 @@ enum : int {
   kFlagPreStageX = 8192,   // GEMV, integer path: convert X once in a small kernel in front and let every CTA copy its
                            // slice, instead of converting in every CTA (default: for M >= 4)
   kFlagNoPreStageX = 16384,  // GEMV: never do that
+  kFlagSplitSumKernel = 32768,    // GEMV, split K: the slices' partial sums are added up by a small kernel behind the GEMV
+                                  // instead of by the last CTA of a row group to arrive (not for tensor-parallel producers)
+  kFlagNoSplitSumKernel = 65536,  // GEMV: never do that
   kFlagNoPdl = 8,          // GEMV: do NOT launch with programmatic stream serialization (by default the kernel may
                            // begin -- weight prefetch only -- while the previous kernel of the stream still runs)
 };

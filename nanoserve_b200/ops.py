@@ -25,6 +25,8 @@ FLAG_WIDE_X = 512
 FLAG_NO_AUTOTUNE = 4096
 FLAG_PRE_STAGE_X = 8192
 FLAG_NO_PRE_STAGE_X = 16384
+FLAG_SPLIT_SUM_KERNEL = 32768
+FLAG_NO_SPLIT_SUM_KERNEL = 65536
 
 # Every symbol include/nanoserve_b200.h declares, with its ctypes signature.
 _vp, _i32, _f32, _i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong

@@ -76,7 +76,8 @@ SMALL_SHAPES = [(64, 128, 128), (96, 256, 128), (100, 384, 128), (33, 1024, 128)
 @pytest.mark.parametrize("N,K,G", SMALL_SHAPES)
 @pytest.mark.parametrize("flags", [0, ops.FLAG_WIDE_X, ops.FLAG_FLOAT_X, FLOAT_FOLD, ops.FLAG_NO_PDL,
                                    ops.FLAG_PRE_STAGE_X, ops.FLAG_NO_PRE_STAGE_X, ops.FLAG_PRE_STAGE_X | ops.FLAG_WIDE_X,
-                                   ops.FLAG_PRE_STAGE_X | ops.FLAG_NO_PDL])
+                                   ops.FLAG_PRE_STAGE_X | ops.FLAG_NO_PDL, ops.FLAG_SPLIT_SUM_KERNEL,
+                                   ops.FLAG_SPLIT_SUM_KERNEL | ops.FLAG_NO_AUTOTUNE | ops.FLAG_PRE_STAGE_X])
 def test_small_shapes_all_m(kernels, N, K, G, flags):
     for M in range(1, 17):
         X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=11)
@@ -115,6 +116,13 @@ def test_split_k_matches_single_pass_and_is_deterministic(kernels, N, K):
     assert np.array_equal(a, b), "two identical launches differ: the K reduction is not deterministic"
     check_bf16_output(a, ref, SLACK_DEFAULT)
     check_bf16_output(c, ref, SLACK_DEFAULT)
+    # the slices added up by the last CTA to arrive or by the kernel behind: same order, same bits (split pinned)
+    pin = ops.FLAG_NO_AUTOTUNE | (4 << 24)
+    d = run(kernels, X, Wq, S, G, pin | ops.FLAG_NO_SPLIT_SUM_KERNEL)
+    for _ in range(2):
+        e = run(kernels, X, Wq, S, G, pin | ops.FLAG_SPLIT_SUM_KERNEL)
+        assert np.array_equal(d, e)
+    check_bf16_output(d, ref, SLACK_DEFAULT)
     assert kernels.device_status() == 0
 
 
