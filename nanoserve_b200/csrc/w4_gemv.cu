@@ -1558,6 +1558,9 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
                    const GemvTp* tp) {
   Workspace ws = ws_in;
   if (ws.partial && ws.partial_bytes > 2 * kTrialBytes) ws.partial_bytes -= kTrialBytes;  // trial outputs live there
+  // a tensor-parallel producer sums its slices in the kernel (its CTAs signal the peers after their stores): plans and
+  // trial launches must assume that too
+  if (tp != nullptr && tp->world > 0) flags |= kFlagNoSplitSumKernel;
   const bool tunable = !(flags & (kShapeFlagMask | kFlagNarrowCta | kFlagNoAutotune)) && autotune_enabled() &&
                        ws.partial && ws_in.partial_bytes > 2 * kTrialBytes && (size_t)M * N * 2 <= kTrialBytes;
   if (!tunable) return gemv_launch_planned(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
