@@ -2,6 +2,7 @@
 //
 // Plain pointers and sizes only; no PyTorch types.  Per-device state (SM count, scratch memory, status
 // word) is created lazily under a mutex, once per device, with that device current.
+#include <atomic>
 #include <cstdio>
 #include <mutex>
 
@@ -17,7 +18,7 @@ constexpr int kCounters = 1 << 16;             // one per 32-row group: N up to 
 constexpr size_t kXStageBytes = 4ull << 20;    // X of a GEMV launch in its staged form: M * K up to 1.8 M values
 
 struct DeviceState {
-  bool ready = false;
+  std::atomic<bool> ready{false};  // release-stored once the fields below are final, acquire-loaded outside the mutex
   int sm_count = 0;
   b2::Workspace ws;
 };
@@ -31,9 +32,9 @@ DeviceState* device_state(int* rc) {
   if (e != cudaSuccess) { *rc = (int)e; return nullptr; }
   if (dev < 0 || dev >= kMaxDevices) { *rc = b2::kErrTooLarge; return nullptr; }
   DeviceState& st = g_dev[dev];
-  if (st.ready) { *rc = 0; return &st; }
+  if (st.ready.load(std::memory_order_acquire)) { *rc = 0; return &st; }
   std::lock_guard<std::mutex> lock(g_mu);
-  if (st.ready) { *rc = 0; return &st; }
+  if (st.ready.load(std::memory_order_relaxed)) { *rc = 0; return &st; }
   e = cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) { *rc = (int)e; return nullptr; }
   void *partial = nullptr, *small = nullptr;
@@ -51,9 +52,17 @@ DeviceState* device_state(int* rc) {
   st.ws.status = static_cast<int*>(small);          // word 0
   st.ws.counters = static_cast<int*>(small) + 64;   // 256-byte offset
   st.ws.n_counters = kCounters;
-  st.ready = true;
+  st.ready.store(true, std::memory_order_release);
   *rc = 0;
   return &st;
+}
+
+// The state of the current device if it exists already; never creates it (the status calls must not allocate).
+DeviceState* device_state_if_ready(int* dev_out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  *dev_out = dev;
+  return g_dev[dev].ready.load(std::memory_order_acquire) ? &g_dev[dev] : nullptr;
 }
 
 int linear_dispatch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
@@ -185,25 +194,27 @@ int b2_init(void) {
 }
 
 int b2_device_status(void) {
-  int rc = 0;
-  DeviceState* st = device_state(&rc);
-  if (!st) return rc;
+  int dev = -1;
+  DeviceState* st = device_state_if_ready(&dev);
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return (int)e;
-  int word = 0;
-  e = cudaMemcpy(&word, st->ws.status, sizeof(int), cudaMemcpyDeviceToHost);
-  if (e != cudaSuccess) return (int)e;
-  return word == 0 ? 0 : b2::kErrDevice;
+  int word = 0, word2 = 0;
+  if (st) {
+    e = cudaMemcpy(&word, st->ws.status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return (int)e;
+  }
+  b2::noalloc_status_word(dev, &word2);  // the fixed array of b2_w4_gemv_noalloc, if that entry point has run
+  return (word | word2) == 0 ? 0 : b2::kErrDevice;
 }
 
 int b2_clear_status(void) {
-  int rc = 0;
-  DeviceState* st = device_state(&rc);
-  if (!st) return rc;
+  int dev = -1;
+  DeviceState* st = device_state_if_ready(&dev);
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return (int)e;
   // a time-out may have left arrival counters half counted: clear them with the status word
-  e = cudaMemset(st->ws.status, 0, (kCounters + 64) * sizeof(int));
+  if (st) e = cudaMemset(st->ws.status, 0, (kCounters + 64) * sizeof(int));
+  b2::noalloc_clear(dev);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   return (int)e;
 }

@@ -17,6 +17,7 @@
 //   * The first call on a device looks up the array's device address (once per device, with that device
 //     current).  It allocates nothing, but it is set-up work: make that first call before any stream
 //     capture.
+#include <atomic>
 #include <mutex>
 
 #include "../../include/nanoserve_b200.h"
@@ -29,7 +30,7 @@ constexpr int kCounters = 4096;               // row groups of 32: N up to 13107
 constexpr size_t kCountersOffset = kPartialBytes;
 constexpr size_t kStatusOffset = kCountersOffset + kCounters * sizeof(int);
 constexpr size_t kScratchBytes = kStatusOffset + 256;
-constexpr long long kMaxOutputs = 1 << 20;    // M * N: two slices of partials always fit
+constexpr long long kMaxOutputs = 1 << 20;    // M * N: two K slices of fp32 partial sums fit in the 8 MiB
 constexpr int kMaxDevices = 64;
 
 // In host code this name is only a handle for the runtime (cudaGetSymbolAddress); it is not a device
@@ -37,7 +38,7 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 
 struct DeviceSlot {
-  bool ready = false;
+  std::atomic<bool> ready{false};  // release-stored after base and sm_count, acquire-loaded outside the mutex
   unsigned char* base = nullptr;  // device address of g_scratch on this device
   int sm_count = 0;
 };
@@ -45,6 +46,23 @@ DeviceSlot g_slot[kMaxDevices];
 std::mutex g_mu;
 
 }  // namespace
+
+namespace b2 {
+
+// The status word of the fixed scratch array of device `dev`, for b2_device_status / b2_clear_status: they must not
+// allocate either, so they read this word directly instead of creating the library's malloc'ed per-device state.
+// Returns false when b2_w4_gemv_noalloc has not run on the device (nothing to report).  The caller has synchronised.
+bool noalloc_status_word(int dev, int* word) {
+  if (dev < 0 || dev >= kMaxDevices || !g_slot[dev].ready.load(std::memory_order_acquire)) return false;
+  return cudaMemcpy(word, g_slot[dev].base + kStatusOffset, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess;
+}
+// Clears that word and the arrival counters (a time-out may have left them half counted).
+bool noalloc_clear(int dev) {
+  if (dev < 0 || dev >= kMaxDevices || !g_slot[dev].ready.load(std::memory_order_acquire)) return false;
+  return cudaMemset(g_slot[dev].base + kCountersOffset, 0, kCounters * sizeof(int) + 256) == cudaSuccess;
+}
+
+}  // namespace b2
 
 extern "C" int b2_w4_gemv_noalloc(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
                                   void* stream) {
@@ -57,16 +75,19 @@ extern "C" int b2_w4_gemv_noalloc(const void* X, const void* Wq, const void* S, 
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kMaxDevices) return b2::kErrTooLarge;
   DeviceSlot& slot = g_slot[dev];
-  if (!slot.ready) {
+  if (!slot.ready.load(std::memory_order_acquire)) {
     std::lock_guard<std::mutex> lock(g_mu);
-    if (!slot.ready) {
+    if (!slot.ready.load(std::memory_order_relaxed)) {
       void* ptr = nullptr;
       e = cudaGetSymbolAddress(&ptr, g_scratch);  // device `dev` is current: this is its copy of the array
       if (e != cudaSuccess) return (int)e;
       e = cudaDeviceGetAttribute(&slot.sm_count, cudaDevAttrMultiProcessorCount, dev);
       if (e != cudaSuccess) return (int)e;
       slot.base = static_cast<unsigned char*>(ptr);
-      slot.ready = true;
+      // the status word starts at zero with the image; clear it anyway, on the caller's stream, before first use
+      e = cudaMemsetAsync(slot.base + kStatusOffset, 0, sizeof(int), static_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) return (int)e;
+      slot.ready.store(true, std::memory_order_release);
     }
   }
 

@@ -54,6 +54,8 @@ enum : int {
   kFlagSplitSumKernel = 32768,    // GEMV, split K: the slices' partial sums are added up by a small kernel behind the GEMV
                                   // instead of by the last CTA of a row group to arrive (not for tensor-parallel producers)
   kFlagNoSplitSumKernel = 65536,  // GEMV: never do that
+  kFlagRingKernel = 131072,  // GEMV: run the shared-memory ring kernel (w4_gemv.cu) even where the register-streaming
+                             // kernel (w4_gemv_stream.cu) applies; bits 20-23: force that kernel's warps per row block
   kFlagNoPdl = 8,          // GEMV: do NOT launch with programmatic stream serialization (by default the kernel may
                            // begin -- weight prefetch only -- while the previous kernel of the stream still runs)
 };
@@ -107,6 +109,22 @@ int tp_wait_launch(const void* wait_sig, const void* epoch, unsigned wait_per_ep
 int rope_kv_store_launch(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
                          void* cache_v, int Hq, int Hk, int D, int max_len, const void* wait_sig, const void* epoch,
                          unsigned wait_per_epoch, int* status, cudaStream_t stream);
+
+// The register-streaming GEMV (w4_gemv_stream.cu): G % 128 == 0, K % 128 == 0, Wq 16-byte aligned, no kFlagFloatX.
+// gemv_stream_launch returns kStreamNotApplicable when no plan fits (the staged X does not fit in shared memory and
+// K may not be split): the caller falls back to the ring kernel.  Arguments are validated by the caller.
+constexpr int kStreamNotApplicable = 0x40000000;
+bool gemv_stream_applies(const void* Wq, int M, int N, int K, int G, int flags);
+int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
+                       const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream,
+                       const GemvTp* tp);
+size_t gemv_stream_grid(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);
+size_t gemv_stream_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);
+
+// Status word of b2_w4_gemv_noalloc's fixed scratch array (w4_gemv_noalloc.cu); false when that entry point has not
+// run on the device.
+bool noalloc_status_word(int dev, int* word);
+bool noalloc_clear(int dev);
 
 // Scratch bytes gemv_launch would use for this shape (0 when it runs without split-K).
 size_t gemv_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);

@@ -19,8 +19,9 @@ from tests.util import bits_to_torch, check_bf16_output, torch_to_bits, u32_to_t
 pytestmark = pytest.mark.gpu
 
 
-def _call(lib, name, x, wq, s, M, N, K, G):
-    y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+def _call(lib, name, x, wq, s, M, N, K, G, y=None):
+    if y is None:
+        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
     rc = getattr(lib, name)(x.data_ptr(), wq.data_ptr(), s.data_ptr(), y.data_ptr(), M, N, K, G,
                             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0, (name, rc)
@@ -34,9 +35,18 @@ def test_matches_existing_entry_point_twice_in_a_row(kernels, M, N, K):
     X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=77)
     x, wq, s = bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S)
     want = _call(lib, "ns_w4_linear", x, wq, s, M, N, K, G)
-    first = _call(lib, "b2_w4_gemv_noalloc", x, wq, s, M, N, K, G)
-    second = _call(lib, "b2_w4_gemv_noalloc", x, wq, s, M, N, K, G)
+    # outputs allocated up front and one untimed call made (kernel images load on first use), so that the free
+    # device memory can be compared across the two calls proper: the entry point itself must not allocate
+    out1, out2 = torch.empty_like(want), torch.empty_like(want)
+    _call(lib, "b2_w4_gemv_noalloc", x, wq, s, M, N, K, G, y=out1)
     torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    first = _call(lib, "b2_w4_gemv_noalloc", x, wq, s, M, N, K, G, y=out1)
+    second = _call(lib, "b2_w4_gemv_noalloc", x, wq, s, M, N, K, G, y=out2)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, "device memory was allocated or freed during the calls"
+    assert lib.b2_device_status() == 0  # reads the fixed array's own status word, without allocating either
+    assert torch.cuda.mem_get_info()[0] == free_before
     a = want.float()
     for got in (first, second):
         b = got.float()
