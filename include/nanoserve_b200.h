@@ -169,6 +169,24 @@ int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v,
                         void* workspace, int Hq, int Hk, int D, int max_len, void* stream);
 int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* pos, void* out_tokens, void* step,
                    void* x_next, void* workspace, void* stream);
+/*
+ * The bf16 vocabulary projection of a decode step with the greedy argmax in its epilogue.  No counterpart in the
+ * reference library: the reference runs F.linear on the bf16 lm_head and argmax over the logits on the host side of
+ * the step (python/nanoserve/qwen.py:164,174-177).
+ *   b2_lm_head: logits[M, V] (bf16; may be NULL when only the argmax is wanted) = X[M, K] . W[V, K]^T, fp32
+ *     accumulation, 1 <= M <= 8, K % 32 == 0.  prologue / R / Wn / eps / Xout as in b2_w4_linear_fused (0 or 1: the
+ *     model's final add + RMSNorm folded in).  If part_max / part_idx are not NULL, entry b of them receives the
+ *     largest bf16 logit of token 0 among rows [128 b, 128 b + 128) and its row index + idx_offset (lowest index on
+ *     ties); b2_lm_head_blocks(V) entries each.  A rank that holds a slice of the vocabulary passes its first row
+ *     as idx_offset.
+ *   b2_greedy_pick: b2_greedy_next starting from such (value, index) pairs instead of the logits.
+ */
+int b2_lm_head_blocks(int V);
+int b2_lm_head(const void* X, const void* W, void* logits, int M, int V, int K, int prologue, const void* R,
+               const void* Wn, float eps, void* Xout, void* part_max, void* part_idx, int idx_offset, void* stream);
+int b2_greedy_pick(const void* part_max, const void* part_idx, int nparts, int V, const void* embed, int H, void* pos,
+                   void* out_tokens, void* step, void* x_next, void* stream);
+
 /* Bytes of caller-owned device scratch (`workspace`) the two calls above need (split partials; Hq / Hk <= 8). */
 size_t b2_decode_workspace_bytes(int Hq, int D);
 

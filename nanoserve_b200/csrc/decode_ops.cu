@@ -356,4 +356,18 @@ int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* po
   return (int)cudaGetLastError();
 }
 
+// Second half of b2_greedy_next for callers whose logits kernel already reduced blocks of the vocabulary
+// (b2_lm_head): picks the largest of `nparts` (value, index) pairs, lowest index on ties, then does what
+// b2_greedy_next does with the token.
+int b2_greedy_pick(const void* part_max, const void* part_idx, int nparts, int V, const void* embed, int H, void* pos,
+                   void* out_tokens, void* step, void* x_next, void* stream) {
+  if (V < 1 || H < 1 || nparts < 1) return b2::kErrBadShape;
+  if (!part_max || !part_idx || !embed || !pos || !out_tokens || !step || !x_next) return b2::kErrBadPointer;
+  greedy_finish_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(part_max), static_cast<const int*>(part_idx), nparts, V,
+      static_cast<const bf16*>(embed), H, static_cast<int*>(pos), static_cast<long long*>(out_tokens),
+      static_cast<int*>(step), static_cast<bf16*>(x_next));
+  return (int)cudaGetLastError();
+}
+
 }  // extern "C"

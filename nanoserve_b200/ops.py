@@ -50,6 +50,9 @@ SIGNATURES = {
     "b2_decode_attention": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
     "b2_greedy_next": ([_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp], _i32),
     "b2_decode_workspace_bytes": ([_i32, _i32], ctypes.c_size_t),
+    "b2_lm_head_blocks": ([_i32], _i32),
+    "b2_lm_head": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _f32, _vp, _vp, _vp, _i32, _vp], _i32),
+    "b2_greedy_pick": ([_vp, _vp, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp], _i32),
     "b2_w4_linear_tp": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _f32, _vp, _vp, _i32, _vp], _i32),
     "b2_w4_gemv_grid": ([_i32, _i32, _i32, _i32, _i32], ctypes.c_size_t),
     "b2_rope_kv_store_tp": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_uint, _vp], _i32),
@@ -213,6 +216,22 @@ class Kernels:
         rc = self.lib.b2_w4_linear_tp(x.data_ptr(), Wq.data_ptr(), S.data_ptr(), M, N, K, group, prologue, p(r), p(wn),
                                       eps, p(x_out), ctypes.byref(desc), flags, self._stream())
         self._check(rc, "b2_w4_linear_tp")
+
+    def lm_head(self, x, W, logits=None, part_max=None, part_idx=None, idx_offset=0, r=None, wn=None, eps=0.0):
+        """bf16 vocabulary projection (x [M, K] . W [V, K]^T) with the per-128-row argmax of token 0 in its epilogue
+        and, when `wn` is given, the final add + RMSNorm in its prologue.  Returns the logits tensor (or None)."""
+        self._cuda(x, W, logits, part_max, part_idx, r, wn)
+        M, K = x.shape
+        V = W.shape[0]
+        assert x.is_contiguous() and W.is_contiguous()
+        p = lambda t: None if t is None else t.data_ptr()
+        rc = self.lib.b2_lm_head(x.data_ptr(), W.data_ptr(), p(logits), M, V, K, 1 if wn is not None else 0, p(r),
+                                 p(wn), eps, None, p(part_max), p(part_idx), idx_offset, self._stream())
+        self._check(rc, "b2_lm_head")
+        return logits
+
+    def lm_head_blocks(self, V) -> int:
+        return int(self.lib.b2_lm_head_blocks(V))
 
     def tp_wait(self, wait_sig: int, epoch: int, wait_per_epoch: int):
         self._check(self.lib.b2_tp_wait(wait_sig, epoch, wait_per_epoch, self._stream()), "b2_tp_wait")

@@ -12,7 +12,10 @@ Differences from the reference, all on the host side of the boundary:
   * Tensor parallel: every matrix is sharded by output rows over the ranks, outputs are all-gathered at the four
     layer boundaries; attention, norms and RoPE run replicated on the gathered activations.  In the decode step the
     gather is fused into the GEMVs (``b2_w4_linear_tp``: peer stores into every rank's gathered row + arrival
-    counters, the consumer waits on the counter); the prompt and the lm_head use NCCL.
+    counters, the consumer waits on the counter); the prompt uses NCCL.
+  * The bf16 lm_head runs through the library's own GEMV (``b2_lm_head``) with the final norm in its prologue and
+    the argmax per 128 rows in its epilogue; ranks hold slices of the vocabulary and exchange only their
+    (largest logit, index) pairs.
 Batch size 1, as in the reference (qwen.py:12).
 """
 import ctypes
@@ -102,6 +105,12 @@ class Qwen2Runner:
         self.stream = torch.cuda.Stream(device=device)
         self.scratch = torch.empty(int(kernels.lib.b2_decode_workspace_bytes(cfg.n_heads, D)), dtype=torch.uint8,
                                    device=device)
+        # vocabulary projection: this rank's logits and one (largest logit, index) pair per 128 rows of its shard
+        self.v_local = cfg.vocab // world
+        self.nblk = kernels.lm_head_blocks(self.v_local)
+        self.logits = torch.zeros(1, self.v_local, dtype=torch.bfloat16, device=device)
+        self.part_max = torch.zeros(world, self.nblk, dtype=torch.float32, device=device)
+        self.part_idx = torch.zeros(world, self.nblk, dtype=torch.int32, device=device)
         kernels.init()
         self.peer = None
         if world > 1 and fused_gather:
@@ -205,13 +214,29 @@ class Qwen2Runner:
             act = self._gather(k.swiglu(gu[:, :il].contiguous(), gu[:, il:].contiguous()))
             nxt = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
             h = k.rmsnorm(x, self._gather(self.linear(act, L["d"])), nxt, cfg.rms_eps)
-        logits = self._gather(F.linear(h[-1:], self.lm_head))
-        self.pos.fill_(T - 1)  # greedy_next advances it to T, the position of the first generated token
+        self.pos.fill_(T - 1)  # the pick advances it to T, the position of the first generated token
         self.step.zero_()
         if self.peer is not None:
             self.peer.reset()  # counters and epoch restart together, on every rank
-        self._greedy_next(logits)
+        self._lm_head_and_pick(h[-1:].contiguous(), None, None)
         return self.tokens[0]
+
+    def _lm_head_and_pick(self, x, r, wn):
+        """Vocabulary projection of this rank's rows (final add + RMSNorm in its prologue, argmax per 128 rows in its
+        epilogue), then the pick over all ranks' (value, index) pairs: two all-gathers of a few hundred bytes
+        instead of one of the 152064 logits.  Returns this rank's logits."""
+        cfg, k, w = self.cfg, self.k, self.world
+        mine_v, mine_i = self.part_max[self.rank], self.part_idx[self.rank]
+        k.lm_head(x, self.lm_head, logits=self.logits, part_max=mine_v, part_idx=mine_i,
+                  idx_offset=self.rank * self.v_local, r=r, wn=wn, eps=cfg.rms_eps)
+        if w > 1:
+            dist.all_gather_into_tensor(self.part_max, mine_v, group=self.group)
+            dist.all_gather_into_tensor(self.part_idx, mine_i, group=self.group)
+        rc = k.lib.b2_greedy_pick(self.part_max.data_ptr(), self.part_idx.data_ptr(), w * self.nblk, cfg.vocab,
+                                  self.embed.data_ptr(), cfg.hidden, self.pos.data_ptr(), self.tokens.data_ptr(),
+                                  self.step.data_ptr(), self.x.data_ptr(), self._st())
+        k._check(rc, "b2_greedy_pick")
+        return self.logits
 
     def _greedy_next(self, logits):
         rc = self.k.lib.b2_greedy_next(logits.data_ptr(), self.cfg.vocab, self.embed.data_ptr(), self.cfg.hidden,
@@ -260,11 +285,9 @@ class Qwen2Runner:
                 d = self._gather(self.linear(self._gather(k.swiglu(gu[:, :il], gu[:, il:])), L["d"]))
             r = d
             wn = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
-        h = k.rmsnorm(x, r, wn, cfg.rms_eps)  # the stream is not needed after this: the next step starts from
-        # the embedding b2_greedy_next writes into self.x, whichever buffer the last layer ended on
-        logits = self._gather(F.linear(h, self.lm_head))
-        self._greedy_next(logits)
-        return logits
+        # final add + RMSNorm folded into the vocabulary projection, argmax partials in its epilogue.  The residual
+        # stream is not needed after this: the next step starts from the embedding the pick writes into self.x.
+        return self._lm_head_and_pick(x, r, wn)
 
     @torch.no_grad()
     def _decode_step_fused_gather(self):
@@ -301,9 +324,7 @@ class Qwen2Runner:
             x, x_alt = x_alt, x
             k.w4_linear_tp(gu_buf, L["d"][0], L["d"][1], dsc["d"], G, prologue=2)
         k.tp_wait(peer.counter(4 * cfg.n_layers - 1), ep, self.tp_wait_d)
-        h = k.rmsnorm(x, d_buf, self.final_norm, eps)
-        logits = self._gather(F.linear(h, self.lm_head))
-        self._greedy_next(logits)
+        logits = self._lm_head_and_pick(x, d_buf, self.final_norm)
         peer.epoch.add_(1)
         return logits
 
