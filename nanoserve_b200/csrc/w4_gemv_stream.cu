@@ -34,6 +34,7 @@
 //     into every rank's gathered row, one arrival signal per launch) and input wait.
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 
 #include "w4_gemv_shared.cuh"
 
@@ -43,9 +44,12 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kHeader = 2048;       // abort flag, RMSNorm partial sums [16][16] at 256, factors [16] at 1280
-constexpr int kNormSs = 256;
-constexpr int kNormInv = 1280;
+constexpr int kHeader = 3072;       // abort flag; mbarriers [warp][slot] at 64; RMSNorm partial sums [16][16] at 1024,
+constexpr int kBarOffset = 64;      // factors [16] at 2048; the weight ring follows (1024-byte aligned)
+constexpr int kMaxDepth = 8;
+constexpr int kZeroOffset = 640;    // 64 bytes of zeros: what lanes without a real B column or info record read
+constexpr int kNormSs = 1024;
+constexpr int kNormInv = 2048;
 constexpr int kSmemTwoPerSm = 112 * 1024;
 constexpr int kSmemMax = 227 * 1024;
 
@@ -53,21 +57,15 @@ struct StreamParams {
   const uint32_t* Wq;
   int wrow;          // 32-bit words per row of Wq (K / 8)
   int ks;            // warps that share one 16-row block along K (1, 2, 4 or 8)
-  int nch;           // 128-chunks in K
-  int cps;           // chunks per cross-CTA slice (blockIdx.y)
+  int nsc;           // 256-wide super-chunks in K
+  int scps;          // super-chunks per cross-CTA slice (blockIdx.y)
   int gs_pitch;      // scale columns per row held in shared memory
   int sc_contig;     // the CTA's scales are one contiguous 16-byte aligned region of S
   int off_info, off_sc, off_x, off_red;
   int pstride;       // bytes between planes of the staged X
+  int depth;         // ring slots per warp
 };
 
-__device__ __forceinline__ uint4 ldg_stream(const uint32_t* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
 __device__ __forceinline__ uint32_t lds_u16s(uint32_t addr) {
   unsigned short v;
   asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
@@ -186,42 +184,213 @@ __device__ __forceinline__ void stage_x_planes(const GemvParams& p, uint32_t xs_
   }
 }
 
-// NT: tiles of eight B columns (M x P columns in all).  P: planes per token.  RING: chunks a lane keeps in flight.
-template <int NT, int P, int RING>
+// Everything a lane carries through the main loop: running shared-memory addresses (incremented, never recomputed),
+// the ring position, and the constants the unpack needs in registers.
+template <int NT>
+struct LoopState {
+  uint32_t xaddr[NT], xstep[NT], iaddr[NT], istep[NT];
+  int sel_a[NT];
+  uint32_t sc_row;
+  int sc_rstep, goff[2];
+  uint32_t a_u0, a_u1, k_nib_lo, k_nib_hi;
+  uint32_t ring0, bar0, slot, bar, ph;
+  int d, depth;
+  volatile int* abort_flag;
+  // feed: this lane's share of a slot's copies (16 bytes of row r4 + 4 j, j = 0 .. 4 RB - 1)
+  const unsigned char* src;       // row r4 of the warp's tile, this lane's 16-byte column, NEXT super-chunk to feed
+  uint32_t row4;                  // bytes between rows r4 + 4 j and r4 + 4 (j + 1)
+  uint32_t valid;                 // bit j: row r4 + 4 j exists (all ones except in the last tile of a ragged N)
+  uint32_t dst_even, dst_odd;     // swizzled offset in the slot for even / odd j (without j * 512)
+};
+
+// Copies this lane's 16-byte pieces of the next super-chunk into the slot at `slot` and lets the slot's barrier count
+// the lane in when they have landed.  A warp instruction covers four rows x 128 bytes: whole lines.  Rows beyond N
+// are zero-filled (their source address is clamped to row r4).  The layout in the slot is that of a 128-byte-swizzled
+// tile: 16-byte unit u of row r at u ^ (r & 7).
+template <int RB, int NT>
+__device__ __forceinline__ void feed_slot(LoopState<NT>& st, uint32_t slot, uint32_t bar) {
+  const unsigned char* s = st.src;
+  if (st.valid == (1u << (4 * RB)) - 1u) {
+#pragma unroll
+    for (int j = 0; j < 4 * RB; ++j) {
+      asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(slot + ((j & 1) ? st.dst_odd : st.dst_even) +
+                                                                            j * 512),
+                   "l"(s)
+                   : "memory");
+      s += st.row4;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4 * RB; ++j) {
+      const bool ok = (st.valid >> j) & 1u;
+      asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(slot + ((j & 1) ? st.dst_odd
+                                                                                                 : st.dst_even) + j * 512),
+                   "l"(ok ? s + (size_t)j * st.row4 : s), "r"(ok ? 16u : 0u)
+                   : "memory");
+    }
+  }
+  cp_async_mbar_arrive_noinc(bar);
+  st.src += 128;
+}
+
+// The A-side words of this lane for the slot st.slot: rows g and g + 8 of every 16-row block, 32 bytes each.
+template <int RB, int NT>
+__device__ __forceinline__ void load_fragments(const LoopState<NT>& st, uint32_t (&f)[2 * RB][8]) {
+#pragma unroll
+  for (int i = 0; i < 2 * RB; ++i) {
+    const uint4 v0 = lds128(st.slot + i * 1024 + st.a_u0), v1 = lds128(st.slot + i * 1024 + st.a_u1);
+    f[i][0] = v0.x; f[i][1] = v0.y; f[i][2] = v0.z; f[i][3] = v0.w;
+    f[i][4] = v1.x; f[i][5] = v1.y; f[i][6] = v1.z; f[i][7] = v1.w;
+  }
+}
+
+// One super-chunk of the warp: wait for its slot, pull the fragments out, products and scaling, then hand the slot the
+// super-chunk `depth` ahead.  GD1: one quantization group per 128-chunk (G == 128), the scale offsets just advance.
+template <int NT, int P, int RB, bool GD1>
+__device__ __forceinline__ void gemv_step(LoopState<NT>& st, float (&fin)[RB][NT][4], int sc, bool refill, int gdiv,
+                                          int gs0) {
+  constexpr int kSlotBytes = RB * 16 * 128;
+  // scales of this lane's rows (bf16 -> fp32 is a shift); they do not depend on the weights' arrival
+  float s_lo[RB][2], s_hi[RB][2];
+#pragma unroll
+  for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (NT == 1 && h != 0) continue;  // one tile: all of a lane's accumulators belong to one chunk, goff[0] tracks it
+      s_lo[rb][h] = __uint_as_float(lds_u16s(st.sc_row + (2 * rb) * st.sc_rstep + st.goff[h]) << 16);
+      s_hi[rb][h] = __uint_as_float(lds_u16s(st.sc_row + (2 * rb + 1) * st.sc_rstep + st.goff[h]) << 16);
+    }
+  uint32_t cur[2 * RB][8];
+  mbar_wait(st.bar, st.ph, st.abort_flag);
+  load_fragments<RB>(st, cur);
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    uint4 x[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = lds128(st.xaddr[nt] + j * 16);
+    const uint4 inf = lds128(st.iaddr[nt]);
+    st.xaddr[nt] += st.xstep[nt];
+    st.iaddr[nt] += st.istep[nt];
+    const float up0 = __uint_as_float(inf.z), up1 = __uint_as_float(inf.w);
+#pragma unroll
+    for (int rb = 0; rb < RB; ++rb) {
+      // unpack on the fly: (w & 0x0F0F0F0F) / (w & 0xF0F0F0F0) are the A fragments of the even- / odd-nibble mma
+      int acc_e[4], acc_o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t a0 = cur[2 * rb][2 * j], a1 = cur[2 * rb + 1][2 * j];
+        const uint32_t a2 = cur[2 * rb][2 * j + 1], a3 = cur[2 * rb + 1][2 * j + 1];
+        if (j == 0) {
+          imma_u8s8(acc_e, a0 & st.k_nib_lo, a1 & st.k_nib_lo, a2 & st.k_nib_lo, a3 & st.k_nib_lo, x[j].x, x[j].y, 0, 0,
+                    0, 0);
+          imma_u8s8(acc_o, a0 & st.k_nib_hi, a1 & st.k_nib_hi, a2 & st.k_nib_hi, a3 & st.k_nib_hi, x[j].z, x[j].w,
+                    (int)inf.x, (int)inf.y, (int)inf.x, (int)inf.y);
+        } else {
+          imma_u8s8(acc_e, a0 & st.k_nib_lo, a1 & st.k_nib_lo, a2 & st.k_nib_lo, a3 & st.k_nib_lo, x[j].x, x[j].y,
+                    acc_e[0], acc_e[1], acc_e[2], acc_e[3]);
+          imma_u8s8(acc_o, a0 & st.k_nib_hi, a1 & st.k_nib_hi, a2 & st.k_nib_hi, a3 & st.k_nib_hi, x[j].z, x[j].w,
+                    acc_o[0], acc_o[1], acc_o[2], acc_o[3]);
+        }
+      }
+      const int sel = NT == 1 ? 0 : st.sel_a[nt];
+      const float sl = sel ? s_lo[rb][1] : s_lo[rb][0], sh = sel ? s_hi[rb][1] : s_hi[rb][0];
+      fin[rb][nt][0] = fmaf(sl * up0, (float)(acc_e[0] * 16 + acc_o[0]), fin[rb][nt][0]);
+      fin[rb][nt][1] = fmaf(sl * up1, (float)(acc_e[1] * 16 + acc_o[1]), fin[rb][nt][1]);
+      fin[rb][nt][2] = fmaf(sh * up0, (float)(acc_e[2] * 16 + acc_o[2]), fin[rb][nt][2]);
+      fin[rb][nt][3] = fmaf(sh * up1, (float)(acc_e[3] * 16 + acc_o[3]), fin[rb][nt][3]);
+    }
+  }
+  // every product above has consumed `cur`, so every lane's loads from the slot have completed: the slot takes the
+  // super-chunk `depth` ahead
+  __syncwarp();
+  if (refill) feed_slot<RB>(st, st.slot, st.bar);
+  st.slot += kSlotBytes;
+  st.bar += 8;
+  if (++st.d == st.depth) {
+    st.d = 0;
+    st.slot = st.ring0;
+    st.bar = st.bar0;
+    st.ph ^= 1;
+  }
+  // scale offsets of the next super-chunk (one tile: goff[0] follows the lane's own chunk)
+  if constexpr (GD1) {
+    st.goff[0] += 4;
+    st.goff[1] += 4;
+  } else {
+    st.goff[0] = ((2 * (sc + 1) + (NT == 1 ? st.sel_a[0] : 0)) / gdiv - gs0) * 2;
+    st.goff[1] = ((2 * (sc + 1) + 1) / gdiv - gs0) * 2;
+  }
+}
+
+// NT: tiles of eight B columns.  P: planes per token.  RB: 16-row blocks per warp.  GD1: G == 128.
+//
+// Every warp owns a private ring of q.depth shared-memory slots (RB * 16 rows x 128 bytes each: one 256-wide piece of K,
+// a "super-chunk") and is its own producer: its lanes copy their 16-byte pieces with cp.async (four rows x 128 bytes per
+// warp instruction: whole lines) onto the slot's mbarrier, and refill the slot as soon as the warp has pulled its
+// fragments out of it.  No warp ever waits for another warp.  Measured on the way, same bytes, no arithmetic: loads
+// straight into registers keep only four to six instructions per warp in flight whatever the code issues (8 warps:
+// 3.0 TB/s, 32 warps: 6.1); per-warp tiled TMA boxes of 2 KB stay near 5 TB/s (the copy engine, not DRAM, sets the
+// pace: prefetching the matrix into L2 first changed nothing); cp.async rings reach 6.4 TB/s with 64 KB in flight
+// per SM.
+//
+// Lane (g, t) reads the 32 bytes [32t, 32t + 32) of row g (and g + 8, ...) of a slot: k in [64t, 64t + 64) of the
+// super-chunk.  The k-slots of one mma then span two quantization groups (lanes 0-1 hold chunk 2j, lanes 2-3 chunk
+// 2j + 1), which an accumulator must not mix: the B operand therefore has TWO columns per (token, plane), one whose
+// digits are non-zero only in the k-slots of the even chunk and one for the odd chunk -- 2 M P columns, eight per
+// mma.  For one token with four planes that is exactly one mma tile, and every accumulator of every lane is a real
+// partial sum.
+template <int NT, int P, int RB, bool GD1>
 __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvParams p, const StreamParams q) {
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ __align__(1024) unsigned char smem[];
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int MP = p.M * P;
+  constexpr int kSlots = NT * 4;        // accumulator column pairs per warp and row block
+  constexpr int kRows = RB * 16;        // rows per warp
+  constexpr int kSlotBytes = kRows * 128;
 
-  // ---- geometry: the CTA owns kWarps / ks row blocks of 16 rows; a warp one K slice of one of them
-  const int rbpc = kWarps / q.ks;
-  const int rbl = warp / q.ks, sl_in = warp - rbl * q.ks;
-  const int row0 = blockIdx.x * rbpc * 16;                 // first row of the CTA
-  const int rows_cta = min(rbpc * 16, p.N - row0);
-  const int cb = blockIdx.y * q.cps, ce = min(q.nch, cb + q.cps);  // the CTA's chunks of K
-  const int ncc = ce - cb;
-  const int c0 = cb + (ncc * sl_in) / q.ks, c1 = cb + (ncc * (sl_in + 1)) / q.ks;  // the warp's chunks
-  const bool active = row0 + rbl * 16 < p.N;
-  if (tid == 0) *abort_flag = 0;
-
-  pdl_launch_dependents();  // the next kernel of the stream may become resident and start its own prefetch
-
-  // ---- weight prefetch: constant data, needs nothing from the previous kernel
-  const int row_lo = min(row0 + rbl * 16 + g, p.N - 1), row_hi = min(row0 + rbl * 16 + g + 8, p.N - 1);
-  const uint32_t* wlo = q.Wq + (size_t)row_lo * q.wrow + t * 4;
-  const uint32_t* whi = q.Wq + (size_t)row_hi * q.wrow + t * 4;
-  uint4 wb[RING][2];
-#pragma unroll
-  for (int d = 0; d < RING; ++d) {
-    wb[d][0] = make_uint4(0u, 0u, 0u, 0u);
-    wb[d][1] = make_uint4(0u, 0u, 0u, 0u);
-    if (active && c0 + d < c1) {
-      wb[d][0] = ldg_stream(wlo + (c0 + d) * 16);
-      wb[d][1] = ldg_stream(whi + (c0 + d) * 16);
-    }
+  // ---- geometry: the CTA owns kWarps / ks row tiles of kRows rows; a warp one K slice of one of them
+  const int tpc = kWarps / q.ks;
+  const int tl = warp / q.ks, sl_in = warp - tl * q.ks;
+  const int row0 = blockIdx.x * tpc * kRows;               // first row of the CTA
+  const int rows_cta = min(tpc * kRows, p.N - row0);
+  const int wrow0 = row0 + tl * kRows;                     // first row of the warp
+  const int scb = blockIdx.y * q.scps, sce = min(q.nsc, scb + q.scps);  // the CTA's super-chunks of K
+  const int nscc = sce - scb;
+  const int s0 = scb + (nscc * sl_in) / q.ks, s1 = scb + (nscc * (sl_in + 1)) / q.ks;  // the warp's
+  const bool active = wrow0 < p.N && s0 < s1;
+  const uint32_t bar0 = smem_u32(smem + kBarOffset) + warp * (8 * kMaxDepth);
+  const uint32_t ring0 = smem_u32(smem + kHeader) + warp * q.depth * kSlotBytes;
+  if (tid < 4) sts128(smem_u32(smem + kZeroOffset) + tid * 16, make_uint4(0u, 0u, 0u, 0u));
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < kWarps * kMaxDepth; ++i) mbar_init(smem_u32(smem + kBarOffset) + 8 * i, 32);
+    fence_mbar_init();
   }
+  __syncthreads();
+  pdl_launch_dependents();  // the next kernel of the stream may become resident and start its own weight stream
+
+  // ---- weight stream: constant data, needs nothing from the previous kernel.  Rows beyond N are zero-filled.
+  LoopState<NT> st;
+  {
+    const int r4 = lane >> 3, c16 = lane & 7;
+    const int last = p.N - 1 - wrow0;  // last valid row of the warp's tile, relative (negative: none)
+    st.row4 = (uint32_t)q.wrow * 16u;
+    st.src = reinterpret_cast<const unsigned char*>(q.Wq) + ((size_t)(active ? wrow0 : 0) + min(r4, max(last, 0))) * q.wrow * 4 +
+             (size_t)s0 * 128 + c16 * 16;
+    st.valid = 0;
+#pragma unroll
+    for (int j = 0; j < 4 * RB; ++j)
+      if (r4 + 4 * j <= last) st.valid |= 1u << j;
+    st.dst_even = r4 * 128 + ((uint32_t)(c16 ^ r4) << 4);
+    st.dst_odd = r4 * 128 + ((uint32_t)(c16 ^ (r4 + 4)) << 4);
+    st.depth = q.depth;
+  }
+  if (active)
+    for (int d = 0; d < q.depth && s0 + d < s1; ++d) feed_slot<RB>(st, ring0 + d * kSlotBytes, bar0 + 8 * d);
+
   // ---- scales of the CTA's rows and chunks -> shared memory [rows_cta][gs_pitch] bf16
+  const int cb = 2 * scb, ncc = 2 * nscc;  // in 128-chunks
   const int gs0 = cb / p.gdiv;
   const uint32_t sc_base = smem_u32(smem + q.off_sc);
   {
@@ -258,209 +427,219 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
     if (p.pro == kProAddRmsNorm) rmsnorm_factors<kThreads>(p, reinterpret_cast<float*>(smem + kNormSs), inv, tid);
     stage_x_planes<P>(p, xs_base, q.pstride, info_base, inv, cb, ncc, tid);
   }
+  // The scales were copied with cp.async.wait_all semantics per thread; the weight copies of the ring are tracked by
+  // their mbarriers, but wait_all waits for them as well, so only the scale copies' own group is waited for here.
   cp_async_wait_all();
   __syncthreads();
 
   // ---- main loop
-  float fin[NT][4];
+  float fin[RB][NT][4];
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
+  for (int rb = 0; rb < RB; ++rb)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) fin[nt][i] = 0.f;
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) fin[rb][nt][i] = 0.f;
 
-  if (active && c0 < c1) {
-    // B fragments: lane (g, t) holds column nt * 8 + g, items 2t and 2t + 1 of the chunk
-    uint32_t xaddr[NT], iaddr[NT];
-    bool bval[NT], aval[NT];
+  if (active) {
+    // Column c = h M P + (m P + p): h = which chunk of the super-chunk.  B fragments: lane (g, t) holds column
+    // nt * 8 + g, and only the lanes whose k-slots lie in that column's chunk (t >> 1 == h) hold digits; accumulators:
+    // columns nt * 8 + 2t, + 1.  Lanes without a real column read a block of zeros (stride zero): no predicates in the loop.
+    const uint32_t zero_base = smem_u32(smem + kZeroOffset);
+    const int istep = MP * 16;  // bytes of info per super-chunk (two chunks of M P / 2 column pairs)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int colb = nt * 8 + g, cola = nt * 8 + 2 * t;
-      bval[nt] = colb < MP;
-      aval[nt] = cola < MP;
-      xaddr[nt] = xs_base + (bval[nt] ? colb : 0) * q.pstride + t * 32;
-      iaddr[nt] = info_base + ((aval[nt] ? cola : 0) >> 1) * 16;
+      const int hb = colb / MP, cb_ = colb - hb * MP;
+      const int ha = cola / MP, ca_ = cola - ha * MP;
+      const bool bval = colb < 2 * MP && hb == (t >> 1);
+      const bool aval = cola < 2 * MP;
+      st.sel_a[nt] = aval ? ha : 0;
+      st.xaddr[nt] = bval ? xs_base + cb_ * q.pstride + t * 64 + (s0 - scb) * 256 : zero_base;
+      st.xstep[nt] = bval ? 256 : 0;
+      st.iaddr[nt] = aval ? info_base + ((ha * MP + ca_) >> 1) * 16 + (s0 - scb) * istep : zero_base;
+      st.istep[nt] = aval ? istep : 0;
     }
-    const int istep = (MP >> 1) * 16;  // bytes of info per chunk
-    // this lane's scales: rows g and g + 8 of the warp's block
-    const uint32_t sc_lo = sc_base + ((rbl * 16 + g) * q.gs_pitch) * 2;
-    const uint32_t sc_hi = sc_base + ((min(rbl * 16 + g + 8, rows_cta - 1)) * q.gs_pitch) * 2;
-    uint32_t k_nib_lo = 0x0F0F0F0Fu, k_nib_hi = 0xF0F0F0F0u;
-    asm volatile("" : "+r"(k_nib_lo), "+r"(k_nib_hi));
-    const int gdiv = p.gdiv;
+    // this lane's scales: rows g + 8 i of the warp's tile (rows beyond N read whatever follows: their sums are dropped)
+    st.sc_row = sc_base + ((tl * kRows + g) * q.gs_pitch) * 2;
+    st.sc_rstep = 8 * q.gs_pitch * 2;
+    st.goff[0] = (((2 * s0 + (NT == 1 ? st.sel_a[0] : 0)) / p.gdiv) - gs0) * 2;  // one tile: the lane's own chunk
+    st.goff[1] = (((2 * s0 + 1) / p.gdiv) - gs0) * 2;
+    // fragment source: row g (+ 8 i) of the slot, 16-byte units 2t and 2t + 1, swizzled by the row
+    st.a_u0 = g * 128 + ((uint32_t)((2 * t) ^ g) << 4);
+    st.a_u1 = g * 128 + ((uint32_t)((2 * t + 1) ^ g) << 4);
+    st.k_nib_lo = 0x0F0F0F0Fu;
+    st.k_nib_hi = 0xF0F0F0F0u;
+    asm volatile("" : "+r"(st.k_nib_lo), "+r"(st.k_nib_hi));
+    st.ring0 = ring0;
+    st.bar0 = bar0;
+    st.slot = ring0;
+    st.bar = bar0;
+    st.d = 0;
+    st.ph = 0;
+    st.abort_flag = abort_flag;
+    const int s_refill_end = s1 - q.depth;  // super-chunks before this one refill their slot
+    for (int sc = s0; sc < s1; ++sc) gemv_step<NT, P, RB, GD1>(st, fin, sc, sc < s_refill_end, p.gdiv, gs0);
+  }
 
-    for (int cc = c0; cc < c1; cc += RING) {
+  if (NT == 1 && q.ks == 1 && p.nslices == 1 && p.tp.world == 0) {
+    // ---- one tile, no K slices: the lanes of a quad hold the chunks and planes of the same rows; two shuffles, and
+    // the outputs go straight from registers to Y
 #pragma unroll
-      for (int d = 0; d < RING; ++d) {
-        const int c = cc + d;
-        if (c < c1) {
-          // unpack: A fragments of the two even-nibble and the two odd-nibble products
-          const uint32_t lo[4] = {wb[d][0].x, wb[d][0].y, wb[d][0].z, wb[d][0].w};
-          const uint32_t hi[4] = {wb[d][1].x, wb[d][1].y, wb[d][1].z, wb[d][1].w};
-          uint32_t ae[2][4], ao[2][4];
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            ae[j][0] = lo[2 * j] & k_nib_lo;
-            ae[j][1] = hi[2 * j] & k_nib_lo;
-            ae[j][2] = lo[2 * j + 1] & k_nib_lo;
-            ae[j][3] = hi[2 * j + 1] & k_nib_lo;
-            ao[j][0] = lo[2 * j] & k_nib_hi;
-            ao[j][1] = hi[2 * j] & k_nib_hi;
-            ao[j][2] = lo[2 * j + 1] & k_nib_hi;
-            ao[j][3] = hi[2 * j + 1] & k_nib_hi;
-          }
-          // the registers are free again: fetch the chunk RING ahead
-          if (c + RING < c1) {
-            wb[d][0] = ldg_stream(wlo + (c + RING) * 16);
-            wb[d][1] = ldg_stream(whi + (c + RING) * 16);
-          }
-          const int crel = c - cb;
-          const int gi = (gdiv == 1 ? c : c / gdiv) - gs0;
-          const float s_lo = __uint_as_float(lds_u16s(sc_lo + gi * 2) << 16);
-          const float s_hi = __uint_as_float(lds_u16s(sc_hi + gi * 2) << 16);
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            uint4 x0 = make_uint4(0u, 0u, 0u, 0u), x1 = make_uint4(0u, 0u, 0u, 0u);
-            if (bval[nt]) {
-              x0 = lds128(xaddr[nt] + crel * 128);
-              x1 = lds128(xaddr[nt] + crel * 128 + 16);
-            }
-            uint4 inf = make_uint4(0u, 0u, 0u, 0u);
-            if (aval[nt]) inf = lds128(iaddr[nt] + crel * istep);
-            int acc_e[4], acc_o[4];
-            imma_u8s8(acc_e, ae[0][0], ae[0][1], ae[0][2], ae[0][3], x0.x, x0.y, 0, 0, 0, 0);
-            imma_u8s8(acc_o, ao[0][0], ao[0][1], ao[0][2], ao[0][3], x0.z, x0.w, (int)inf.x, (int)inf.y, (int)inf.x,
-                      (int)inf.y);
-            imma_u8s8(acc_e, ae[1][0], ae[1][1], ae[1][2], ae[1][3], x1.x, x1.y, acc_e[0], acc_e[1], acc_e[2],
-                      acc_e[3]);
-            imma_u8s8(acc_o, ao[1][0], ao[1][1], ao[1][2], ao[1][3], x1.z, x1.w, acc_o[0], acc_o[1], acc_o[2],
-                      acc_o[3]);
-            const float up0 = __uint_as_float(inf.z), up1 = __uint_as_float(inf.w);
-            fin[nt][0] = fmaf(s_lo * up0, (float)(acc_e[0] * 16 + acc_o[0]), fin[nt][0]);
-            fin[nt][1] = fmaf(s_lo * up1, (float)(acc_e[1] * 16 + acc_o[1]), fin[nt][1]);
-            fin[nt][2] = fmaf(s_hi * up0, (float)(acc_e[2] * 16 + acc_o[2]), fin[nt][2]);
-            fin[nt][3] = fmaf(s_hi * up1, (float)(acc_e[3] * 16 + acc_o[3]), fin[nt][3]);
-          }
-        }
+    for (int rb = 0; rb < RB; ++rb) {
+      float v_lo = fin[rb][0][0] + fin[rb][0][1], v_hi = fin[rb][0][2] + fin[rb][0][3];
+      v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 2);
+      v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 2);
+      if (P == 4) {
+        v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
+        v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+      }
+      const int m = P == 4 ? 0 : t;  // two planes: lanes t = 0, 1 of a quad hold tokens 0, 1
+      const bool writer = P == 4 ? t == 0 : (t < 2 && t < p.M);
+      const int n = wrow0 + rb * 16 + g;
+      if (writer && active) {
+        if (n < p.N) p.Y[(size_t)m * p.N + n] = __float2bfloat16(v_lo);
+        if (n + 8 < p.N) p.Y[(size_t)m * p.N + n + 8] = __float2bfloat16(v_hi);
       }
     }
-  }
-
-  // ---- the warp's sums per (token, row): digits of one token are added here, K slices after the barrier
-  float* red = reinterpret_cast<float*>(smem + q.off_red);  // [warp][token][16 rows]
+  } else {
+    // ---- every accumulator column pair of the warp goes to shared memory; the sums over the two chunks of a
+    // super-chunk, the planes of a token and the K slices of a row tile are taken after the barrier, in fixed order
+    float* red = reinterpret_cast<float*>(smem + q.off_red);  // [warp][column pair][kRows]
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    const int cola = nt * 8 + 2 * t;
-    float v_lo = fin[nt][0] + fin[nt][1], v_hi = fin[nt][2] + fin[nt][3];
-    if constexpr (P == 4) {
-      v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
-      v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
-    }
-    const bool writer = cola < MP && (P == 2 || (t & 1) == 0);
-    if (writer) {
-      const int m = cola / P;
-      red[(warp * p.M + m) * 16 + g] = v_lo;
-      red[(warp * p.M + m) * 16 + g + 8] = v_hi;
-    }
-  }
-  __syncthreads();
-  const int slice = blockIdx.y;
-  for (int idx = tid; idx < p.M * rows_cta; idx += kThreads) {
-    const int m = idx / rows_cta, r = idx - m * rows_cta;
-    const float* src = red + (((r >> 4) * q.ks) * p.M + m) * 16 + (r & 15);
-    float sum = 0.f;
-    for (int s = 0; s < q.ks; ++s) sum += src[s * p.M * 16];
-    const int n = row0 + r;
-    if (p.nslices > 1)
-      __stcg(p.partial + ((size_t)slice * p.M + m) * p.N + n, sum);
-    else if (p.tp.world)
-      tp_store(p.tp, m, n, __float2bfloat16(sum));
-    else
-      p.Y[(size_t)m * p.N + n] = __float2bfloat16(sum);
-  }
-  if (p.tp.world) {
+    for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int slot = nt * 4 + t;
+        red[(warp * kSlots + slot) * kRows + rb * 16 + g] = fin[rb][nt][0] + fin[rb][nt][1];
+        red[(warp * kSlots + slot) * kRows + rb * 16 + g + 8] = fin[rb][nt][2] + fin[rb][nt][3];
+      }
     __syncthreads();
-    if (warp == 0) tp_signal(p.tp, lane);
+    const int slice = blockIdx.y;
+    const int half_mp = MP >> 1;
+    for (int idx = tid; idx < p.M * rows_cta; idx += kThreads) {
+      const int m = idx / rows_cta, r = idx - m * rows_cta;
+      const int tile = r / kRows, rr = r - tile * kRows;
+      float sum = 0.f;
+      for (int s = 0; s < q.ks; ++s) {
+        const float* src = red + ((tile * q.ks + s) * kSlots) * kRows + rr;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int j = 0; j < P / 2; ++j) sum += src[(h * half_mp + ((m * P) >> 1) + j) * kRows];
+      }
+      const int n = row0 + r;
+      if (p.nslices > 1)
+        __stcg(p.partial + ((size_t)slice * p.M + m) * p.N + n, sum);
+      else if (p.tp.world)
+        tp_store(p.tp, m, n, __float2bfloat16(sum));
+      else
+        p.Y[(size_t)m * p.N + n] = __float2bfloat16(sum);
+    }
+    if (p.tp.world) {
+      __syncthreads();
+      if (warp == 0) tp_signal(p.tp, lane);
+    }
   }
-  if (*abort_flag && tid == 0) atomicCAS(p.status, kStatusOk, kStatusGemvTimeout);
+  if (*abort_flag) {
+    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusGemvTimeout);
+    // give copies that may still be in flight time to land before the shared memory is released
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
 }
 
 struct StreamPlan {
-  int P, NT, ks, nslices, cps, grid_x;
+  int P, NT, RB, ks, nslices, scps, grid_x;
   size_t smem;
   StreamParams q;
 };
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Shared memory of a CTA that owns `rbpc` row blocks and `cps` chunks of K.
-size_t stream_smem(int M, int P, int rbpc, int cps, int gs_pitch, StreamParams* q) {
-  const int MP = M * P;
-  size_t off = kHeader;
+// Shared memory of a CTA whose warps own RB * 16 rows each, `scps` super-chunks of K and `depth` ring slots.
+size_t stream_smem(int M, int P, int NT, int RB, int tpc, int scps, int gs_pitch, int depth, StreamParams* q) {
+  const int MP = M * P, rows = RB * 16;
+  size_t off = kHeader + (size_t)kWarps * depth * rows * 128;
   q->off_info = (int)off;
-  off += (size_t)cps * (MP / 2) * 16;
+  off += (size_t)scps * MP * 16;
   q->off_sc = (int)off;
-  off = align_up(off + (size_t)rbpc * 16 * gs_pitch * 2 + 16, 128);
+  off = align_up(off + (size_t)tpc * rows * gs_pitch * 2 + 16, 128);
   q->off_x = (int)off;
-  q->pstride = cps * 128 + 16;
+  q->pstride = scps * 256 + 16;
   off = align_up(off + (size_t)MP * q->pstride, 128);
   q->off_red = (int)off;
-  off += (size_t)kWarps * M * 16 * 4;
+  off += (size_t)kWarps * NT * 4 * rows * 4;
+  q->depth = depth;
   return off;
 }
 
 bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int sm_count, size_t partial_cap,
                       StreamPlan* out) {
   StreamPlan pl{};
-  pl.P = M <= 2 ? 4 : 2;
-  pl.NT = (M * pl.P + 7) / 8;
-  const int nch = K / 128, gdiv = G / 128, KG = K / G;
-  const int n_rb = (N + 15) / 16;
-  // warps per row block: as few as keep every SM busy with one CTA (each warp then has a long run of chunks to
-  // stream), more for matrices with few rows.  Bits 20-23 of the flags force a value (diagnostics).
+  // four planes (32-bit block fixed point) for one token: its 2 x 4 columns fill exactly one mma tile; two above
+  pl.P = M <= 1 ? 4 : 2;
+  pl.NT = (2 * M * pl.P + 7) / 8;
+  // 32 rows per warp where 16 would make more than 1.25 CTAs per SM (fewer, longer CTAs stream better than an
+  // uneven second wave); bits 18-19 of the flags force 16 (1) or 32 (2) rows (diagnostics)
+  pl.RB = (long)((N + 15) / 16 + kWarps - 1) / kWarps * 4 > (long)sm_count * 5 ? 2 : 1;
+  if (((flags >> 18) & 3) == 1) pl.RB = 1;
+  if (((flags >> 18) & 3) == 2) pl.RB = 2;
+  if (pl.NT > 1) pl.RB = 1;
+  const int rows = pl.RB * 16;
+  const int nsc = K / 256, gdiv = G / 128, KG = K / G;
+  const int n_tiles = (N + rows - 1) / rows;
+  // warps per row tile: as few as keep every SM busy with one CTA (each warp then has a long run of K to stream),
+  // more for matrices with few rows.  Bits 20-23 of the flags force a value (diagnostics).
   int ks = 1;
-  while (ks < 8 && (long)n_rb * ks < (long)sm_count * kWarps * 3 / 4 && nch / (ks * 2) >= 2) ks *= 2;
+  while (ks < 8 && (long)n_tiles * ks < (long)sm_count * kWarps * 3 / 4 && nsc / (ks * 2) >= 2) ks *= 2;
   const int forced_ks = (flags >> 20) & 0xF;
   if (forced_ks == 1 || forced_ks == 2 || forced_ks == 4 || forced_ks == 8) ks = forced_ks;
   pl.ks = ks;
-  const int rbpc = kWarps / ks;
-  pl.grid_x = (n_rb + rbpc - 1) / rbpc;
+  const int tpc = kWarps / ks;
+  pl.grid_x = (n_tiles + tpc - 1) / tpc;
   // K slices across CTAs: only when the staged X of one CTA does not fit otherwise
   const int forced_ns = (flags >> 24) & 0x3F;
+  const int forced_depth = (flags >> 4) & 0xF;  // bits 4-7: ring slots per warp (diagnostics)
   bool found = false;
   for (int pass = 0; pass < 2 && !found; ++pass) {
     const size_t cap = pass == 0 ? kSmemTwoPerSm : kSmemMax;
-    for (int ns = 1; ns <= std::min(nch, 16); ++ns) {
+    for (int ns = 1; ns <= std::min(nsc, 16) && !found; ++ns) {
       if (forced_ns && ns != forced_ns) continue;
       if (pass == 0 && ns > 1 && !forced_ns) break;  // first choice: no split, two CTAs per SM
-      const int cps = (nch + ns - 1) / ns;
-      if ((nch + cps - 1) / cps != ns) continue;
+      const int scps = (nsc + ns - 1) / ns;
+      if ((nsc + scps - 1) / scps != ns) continue;
       if (ns > 1 && ((flags & kFlagForceNoSplitK) || (size_t)ns * M * N * sizeof(float) > partial_cap)) continue;
-      const int gs_pitch = ns == 1 ? KG : (cps + gdiv - 1) / gdiv + 1;
-      StreamParams q{};
-      const size_t smem = stream_smem(M, pl.P, rbpc, cps, gs_pitch, &q);
-      if (smem > cap) continue;
-      pl.nslices = ns;
-      pl.cps = cps;
-      pl.smem = smem;
-      pl.q = q;
-      pl.q.gs_pitch = gs_pitch;
-      found = true;
-      break;
+      const int gs_pitch = ns == 1 ? KG : (2 * scps + gdiv - 1) / gdiv + 1;
+      // as many ring slots as fit (a warp never needs more than its own super-chunks), at least two
+      const int longest = (scps + ks - 1) / ks;
+      for (int depth = std::min(kMaxDepth, std::max(2, longest)); depth >= 2; --depth) {
+        if (forced_depth >= 2 && forced_depth <= kMaxDepth && depth != forced_depth && depth > 2) continue;
+        StreamParams q{};
+        const size_t smem = stream_smem(M, pl.P, pl.NT, pl.RB, tpc, scps, gs_pitch, depth, &q);
+        if (smem > cap) continue;
+        pl.nslices = ns;
+        pl.scps = scps;
+        pl.smem = smem;
+        pl.q = q;
+        pl.q.gs_pitch = gs_pitch;
+        found = true;
+        break;
+      }
     }
   }
   if (!found) return false;
   pl.q.ks = ks;
-  pl.q.nch = nch;
-  pl.q.cps = pl.cps;
+  pl.q.nsc = nsc;
+  pl.q.scps = pl.scps;
   pl.q.wrow = K / 8;
   pl.q.sc_contig = pl.nslices == 1 && (reinterpret_cast<uintptr_t>(S) & 15) == 0;
   *out = pl;
   return true;
 }
 
-template <int NT, int P, int RING>
-int launch_stream(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStream_t stream) {
-  auto kernel = w4_gemv_stream_kernel<NT, P, RING>;
+template <int NT, int P, int RB, bool GD1>
+int launch_stream_g(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStream_t stream) {
+  auto kernel = w4_gemv_stream_kernel<NT, P, RB, GD1>;
   // Raising the dynamic shared-memory limit and the carve-out is remembered per device: done once.
   static bool attr_done[64] = {};
   int dev = 0;
@@ -486,10 +665,18 @@ int launch_stream(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStrea
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
+template <int NT, int P, int RB>
+int launch_stream(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStream_t stream) {
+  return p.gdiv == 1 ? launch_stream_g<NT, P, RB, true>(p, pl, pdl, stream)
+                     : launch_stream_g<NT, P, RB, false>(p, pl, pdl, stream);
+}
+
 }  // namespace
 
 bool gemv_stream_applies(const void* Wq, int M, int N, int K, int G, int flags) {
-  return !(flags & (kFlagRingKernel | kFlagFloatX)) && M >= 1 && M <= 16 && N >= 1 && G % 128 == 0 && K % 128 == 0 &&
+  // (more than two tokens: the ring kernel is the faster one for now; bit 12-free diagnostics flag forces this kernel)
+  const int max_m = (flags & kFlagStreamKernel) ? 16 : 2;
+  return !(flags & (kFlagRingKernel | kFlagFloatX)) && M >= 1 && M <= max_m && N >= 1 && G % 128 == 0 && K % 256 == 0 &&
          K % G == 0 && (reinterpret_cast<uintptr_t>(Wq) & 15) == 0;
 }
 
@@ -524,7 +711,7 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
   p.gdiv = G / 128;
   p.nchunks = K / 128;
   p.nslices = pl.nslices;
-  p.cps = pl.cps;
+  p.cps = 2 * pl.scps;
   p.partial = ws.partial;
   p.counters = ws.counters;
   p.status = ws.status;
@@ -545,13 +732,17 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
   const bool pdl = (flags & kFlagNoPdl) == 0;
   int rc;
   if (pl.P == 4) {
-    rc = launch_stream<1, 4, 8>(p, pl, pdl, stream);
+    rc = pl.RB == 2 ? launch_stream<1, 4, 2>(p, pl, pdl, stream) : launch_stream<1, 4, 1>(p, pl, pdl, stream);
   } else {
     switch (pl.NT) {
-      case 1: rc = launch_stream<1, 2, 8>(p, pl, pdl, stream); break;
-      case 2: rc = launch_stream<2, 2, 6>(p, pl, pdl, stream); break;
-      case 3: rc = launch_stream<3, 2, 4>(p, pl, pdl, stream); break;
-      default: rc = launch_stream<4, 2, 4>(p, pl, pdl, stream); break;
+      case 1: rc = pl.RB == 2 ? launch_stream<1, 2, 2>(p, pl, pdl, stream) : launch_stream<1, 2, 1>(p, pl, pdl, stream); break;
+      case 2: rc = launch_stream<2, 2, 1>(p, pl, pdl, stream); break;
+      case 3: rc = launch_stream<3, 2, 1>(p, pl, pdl, stream); break;
+      case 4: rc = launch_stream<4, 2, 1>(p, pl, pdl, stream); break;
+      case 5: rc = launch_stream<5, 2, 1>(p, pl, pdl, stream); break;
+      case 6: rc = launch_stream<6, 2, 1>(p, pl, pdl, stream); break;
+      case 7: rc = launch_stream<7, 2, 1>(p, pl, pdl, stream); break;
+      default: rc = launch_stream<8, 2, 1>(p, pl, pdl, stream); break;
     }
   }
   if (rc != 0 || !p.sum_kernel) return rc;

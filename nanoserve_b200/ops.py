@@ -27,6 +27,8 @@ FLAG_PRE_STAGE_X = 8192
 FLAG_NO_PRE_STAGE_X = 16384
 FLAG_SPLIT_SUM_KERNEL = 32768
 FLAG_NO_SPLIT_SUM_KERNEL = 65536
+FLAG_RING_KERNEL = 131072    # decode GEMV: the shared-memory ring kernel even where the streaming kernel applies
+FLAG_STREAM_KERNEL = 524288  # decode GEMV: the streaming kernel for every M <= 16 it can serve (default: M <= 2)
 
 # Every symbol include/nanoserve_b200.h declares, with its ctypes signature.
 _vp, _i32, _f32, _i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong

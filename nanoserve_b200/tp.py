@@ -146,6 +146,56 @@ class ShardedLayer:
                 per_epoch += self.world  # every launch of every rank signals once
             self.waits.append((peer.counter(b), per_epoch))
 
+    # ------------------------------------------------------------------ four launches per pass
+    # q | k | v and gate | up as one row-concatenated matrix each (rows of Wq / S are independent, so this is the same
+    # arithmetic in fewer launches; the decode runner stores its weights this way).  Tensor parallel: every rank
+    # concatenates ITS rows of the pieces, and the fused gather puts each piece at its own column of the gathered row.
+    FUSED = (("qkv", ("q", "k", "v")), ("o", ("o",)), ("gu", ("gate", "up")), ("down", ("down",)))
+
+    def fuse(self):
+        """Builds the row-concatenated matrices (a copy: 7 matrices -> 4) and, with peer buffers attached, the
+        descriptors of the four tensor-parallel launches.  Each launch also waits, before it reads its input, for
+        the previous launch's gathered row -- the consumer-side wait of a decode step -- so a pass needs no wait
+        kernels except one behind the last launch."""
+        from .ops import make_tp_desc
+        self.fused = {}
+        for fname, names in self.FUSED:
+            self.fused[fname] = (torch.cat([self.shards[n][0] for n in names]).contiguous(),
+                                 torch.cat([self.shards[n][1] for n in names]).contiguous())
+        if self.peer is None:
+            return
+        peer, P, r = self.peer, self.world, self.rank
+        self.fdescs, prev = {}, None
+        for b, (fname, names) in enumerate(self.FUSED):
+            widths = [self.shapes[n][0] for n in names]
+            pieces, col = [], 0
+            for w in widths:
+                pieces.append((w // P, col + r * (w // P)))
+                col += w
+            wait = dict(wait_sig=peer.counter(prev), epoch=peer.epoch.data_ptr(), wait_per_epoch=P) if prev is not None else {}
+            self.fdescs[fname] = make_tp_desc(y_peers=peer.peers(fname), sig_peers=peer.counter_peers(b), ld=col,
+                                              pieces=pieces, **wait)
+            prev = b
+
+    def decode_pass_fused4(self, x: torch.Tensor, act: torch.Tensor) -> List[torch.Tensor]:
+        """One pass as four launches: q|k|v, o, gate|up take ``x``; down takes ``act``.  Returns the four full-width
+        outputs [M, nq + 2 nkv], [M, hidden], [M, 2 I], [M, hidden]."""
+        k = self.kernels
+        outs = []
+        if self.peer is None:
+            for fname, _ in self.FUSED:
+                Wq, S = self.fused[fname]
+                outs.append(k.w4_linear(act if fname == "down" else x, Wq, S, self.G, flags=self.flags))
+            return outs
+        peer = self.peer
+        for fname, _ in self.FUSED:
+            Wq, S = self.fused[fname]
+            k.w4_linear_tp(act if fname == "down" else x, Wq, S, self.fdescs[fname], self.G, flags=self.flags)
+            outs.append(peer.local(fname, self.M))
+        k.tp_wait(peer.counter(len(self.FUSED) - 1), peer.epoch.data_ptr(), self.world)
+        peer.epoch.add_(1)
+        return outs
+
     def resident_bytes(self) -> int:
         return sum(w.numel() * 4 + s.numel() * 2 for w, s in self.shards.values())
 
