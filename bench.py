@@ -6,14 +6,18 @@
 
 Workload (N = 1): the decode GEMV sweep of the benchmark configuration "batched decode GEMV over every
 linear of a Qwen2.5-7B-shaped layer" at M = 1 -- one STEP is one pass over the seven int4 group-128 linears
-of a layer (q, k, v, o, gate, up, down): seven launches of the library's GEMV through its C ABI.  Weights
-rotate through eight distinct layer copies (961 MB) so every step streams from HBM, not from the 126 MB L2.
+of a layer (q, k, v, o, gate, up, down) through the library's GEMV and its C ABI, as FOUR launches: q|k|v and
+gate|up are row-concatenated matrices (rows of Wq / S are independent, so this is the same arithmetic in fewer
+launches; `--seven-launches` runs them separately).  Weights rotate through eight distinct layer copies (961 MB)
+so every step streams from HBM, not from the 126 MB L2.
 Metric: algorithmic bytes moved per second (packed weights + scales + X + bf16 Y, the reference's byte model,
 bench/bench_w4a16.cu:239).
 
 With N > 1 ranks (one per GPU) every matrix is sharded by output rows over the ranks (tensor parallel) and
-the outputs are all-gathered with NCCL at the four layer boundaries (after q/k/v, o, gate/up, down); the value
-is the whole-layer bytes over the slowest rank's time, so scaling is "strong".
+the outputs are all-gathered at the four layer boundaries (after q/k/v, o, gate/up, down) -- inside the GEMVs
+(peer stores + arrival counters) or, with --tp-collective, by NCCL; the value is the whole-layer bytes over the
+slowest rank's time, so scaling is "strong".  Rank 0 also holds one layer unsharded and checks the gathered
+outputs of the sharded pass against it (`tp_check`).
 
 One JSON line is printed by rank 0.  `value` is measured with inputs resident in HBM; `e2e` is the same
 pass through the public Python/C-ABI call path with the step's activations copied from pinned host memory and
@@ -39,6 +43,9 @@ sys.path.insert(0, ROOT)
 from nanoserve_b200 import synth  # noqa: E402
 
 METRIC = "W4A16 GEMV HBM GB/s at M=1 (Qwen2.5-7B-shaped layer, int4 g128)"
+METRIC_70B = "W4A16 GEMV HBM GB/s at M=1 (70B-class layer: hidden 8192, intermediate 28672, int4 g128)"
+DTYPE = ("int4 weights x bf16 activations; X as block fixed point per (token, 128-chunk) -- 32-bit for one token, 15-bit + "
+         "sign above -- on 8-bit integer mma, s32 accumulation per chunk, fp32 across chunks, bf16 output")
 UNIT = "GB/s"
 G = 128
 M_DECODE = 1
@@ -304,7 +311,197 @@ def run_prefill_tp(k, dev, stream, rank, world, M=4096, N=28672, K=8192, reps=6)
     return out
 
 
+# ---------------------------------------------------------------------------- reference GPU kernels, copy ceiling
+def ref_gpu_numbers(dev, stream):
+    """The reference's own kernels (its C-ABI library built unchanged for sm_100a by oracle/Makefile, when present) on
+    the same B200: the M = 1 GEMV of the dominant shape and the M = 2048 GEMM, CUDA events around a replayed graph
+    over rotating weight copies.  Outside every timed region of this library's arm."""
+    import torch
+    path = os.path.join(ROOT, "oracle", "_ref", "libnanoserve_ref.so")  # the reference's library, not the oracle
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/libnanoserve_ref.so not built"}
+    lib = ctypes.CDLL(path)
+    vp, i32 = ctypes.c_void_p, ctypes.c_int
+    lib.ns_w4_linear.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.ns_w4_linear.restype = i32
+    gen = torch.Generator(device=dev).manual_seed(17)
+    out = {}
+    for key, M, N, K, copies, reps in (("gemv_m1_18944x3584", 1, 18944, 3584, 16, 10),
+                                       ("gemm_m2048_18944x3584", 2048, 18944, 3584, 4, 3)):
+        ws = []
+        for _ in range(copies):
+            Wq = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, device=dev, generator=gen)
+            S = (0.005 + (torch.randn(N, K // G, device=dev, generator=gen) * 0.01).abs()).to(torch.bfloat16)
+            ws.append((Wq, S))
+        x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+
+        def call(w):
+            rc = lib.ns_w4_linear(x.data_ptr(), w[0].data_ptr(), w[1].data_ptr(), y.data_ptr(), M, N, K, G,
+                                  ctypes.c_void_p(stream.cuda_stream))
+            if rc != 0:
+                raise RuntimeError(f"reference ns_w4_linear returned {rc}")
+        try:
+            with torch.cuda.stream(stream):
+                for w in ws[:2]:
+                    call(w)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    for w in ws:
+                        call(w)
+                g.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(reps):
+                    g.replay()
+                e1.record(stream)
+                torch.cuda.synchronize()
+            out[key + "_us"] = round(e0.elapsed_time(e1) * 1e3 / (reps * copies), 2)
+        except Exception as e:  # noqa: BLE001 - a failure of the comparison leg must not lose the line
+            out[key + "_us"] = f"{type(e).__name__}: {e}"
+        del ws
+        torch.cuda.empty_cache()
+    return out
+
+
+def copy_ceiling_gbs(dev, stream):
+    """The reference's notion of the bandwidth ceiling (kernels/fused/vec.cuh:43-47, used at
+    bench/bench_w4a16.cu:122-136): a device-to-device copy of 512 MiB with 16-byte accesses, read + write bytes over
+    the time.  Restated with the device copy of the tensor library (the same access pattern)."""
+    import torch
+    n = (512 << 20) // 2
+    a = torch.ones(n, dtype=torch.bfloat16, device=dev)
+    b = torch.empty_like(a)
+    best = 1e9
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            b.copy_(a)
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            b.copy_(a)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) * 1e-3)
+    return 2.0 * n * 2 / best / 1e9
+
+
 # ---------------------------------------------------------------------------- GPU arm
+class LayerBench:
+    """Resident layer copies (sharded over the ranks), one CUDA graph per copy, replayed in rotation."""
+
+    def __init__(self, k, shapes, n_copies, M, rank, world, dev, flags, fused_gather, seven, seed0=1000):
+        import torch
+        from nanoserve_b200.tp import PeerBuffers, ShardedLayer
+        self.k, self.shapes, self.M, self.world, self.rank, self.dev = k, shapes, M, world, rank, dev
+        self.seven, self.n_copies = seven, n_copies
+        self.layers = [ShardedLayer.synthetic(k, shapes, ORDER, G, seed=seed0 + c, rank=rank, world=world, device=dev,
+                                              flags=flags) for c in range(n_copies)]
+        self.peer = None
+        if fused_gather:
+            if seven:
+                rows = {name: M * shapes[name][0] for name in ORDER}
+                ncnt = len(ShardedLayer.BOUNDARIES)
+            else:
+                rows = {f: M * sum(shapes[n][0] for n in names) for f, names in ShardedLayer.FUSED}
+                ncnt = len(ShardedLayer.FUSED)
+            self.peer = PeerBuffers(rows, ncnt, dev)
+        for l in self.layers:
+            if self.peer is not None:
+                if seven:
+                    l.attach_peer_buffers(self.peer, M)
+                else:
+                    l.peer, l.M = self.peer, M
+            if not seven:
+                l.fuse()
+        hidden, inter = shapes["q"][1], shapes["down"][1]
+        self.x_h = torch.from_numpy(synth.synth_x(M, hidden, 1).view(np.int16)).view(torch.bfloat16).pin_memory()
+        self.a_h = torch.from_numpy(synth.synth_x(M, inter, 2).view(np.int16)).view(torch.bfloat16).pin_memory()
+        self.x_d, self.a_d = self.x_h.to(dev), self.a_h.to(dev)
+        self.stream = torch.cuda.Stream(device=dev)
+        self.graphs = []
+
+    def one_pass(self, l, x, a):
+        return l.decode_pass(x, a) if self.seven else l.decode_pass_fused4(x, a)
+
+    def capture(self):
+        import torch
+        with torch.cuda.stream(self.stream):
+            for l in self.layers:
+                self.one_pass(l, self.x_d, self.a_d)  # warm every kernel variant before capture
+            torch.cuda.synchronize()
+            for l in self.layers:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.stream):
+                    self.one_pass(l, self.x_d, self.a_d)
+                self.graphs.append(g)
+
+    def barrier(self):
+        import torch
+        import torch.distributed as dist
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_replays(self, n):
+        import torch
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        with torch.cuda.stream(self.stream):
+            ev0.record(self.stream)
+            for i in range(n):
+                self.graphs[i % self.n_copies].replay()
+            ev1.record(self.stream)
+        self.barrier()
+        return ev0.elapsed_time(ev1) * 1e-3
+
+    def resident_bytes(self):
+        return sum(l.resident_bytes() for l in self.layers)
+
+    def launches_per_step(self):
+        from nanoserve_b200.tp import ShardedLayer
+        if self.seven:
+            return len(ORDER) + (len(ShardedLayer.BOUNDARIES) if self.peer is not None else 0)
+        return len(ShardedLayer.FUSED) + (1 if self.peer is not None else 0)
+
+
+def tp_check(lb, k, dev):
+    """Tensor parallel == single GPU.  The reference has no multi-GPU code, so the checker for the sharded path is
+    this library's own unsharded result: rank 0 uploads layer copy 0 whole, runs the plain ns_w4_linear on it and
+    compares with the gathered outputs of the sharded pass (every rank holds them).  Bound: one bf16 rounding of the
+    value plus 1e-5 of the largest output (the sharded and the whole matrix may split K differently)."""
+    import torch
+    import torch.distributed as dist
+    from nanoserve_b200.tp import ShardedLayer, _to_torch_bits
+    with torch.cuda.stream(lb.stream):
+        outs = [o.clone() for o in lb.one_pass(lb.layers[0], lb.x_d, lb.a_d)]
+    lb.barrier()
+    res = {"max_rel": 0.0, "ok": True, "matrices": 0}
+    if lb.rank == 0:
+        groups = [(n,) for n in ORDER] if lb.seven else [names for _, names in ShardedLayer.FUSED]
+        for names, got in zip(groups, outs):
+            full = []
+            for n in names:
+                N, K = lb.shapes[n]
+                Wq, S = synth.synth_weight(N, K, G, 1000)
+                y = k.w4_linear(lb.a_d if n == "down" else lb.x_d, _to_torch_bits(Wq, torch.int32, dev),
+                                _to_torch_bits(S, torch.bfloat16, dev), G)
+                full.append(y)
+            want = torch.cat(full, dim=1).float()
+            g = got.float()
+            scale = want.abs().max()
+            excess = ((g - want).abs() - torch.maximum(g.abs(), want.abs()) * 2.0**-7).clamp(min=0) / scale
+            res["max_rel"] = max(res["max_rel"], float(excess.max()))
+            res["matrices"] += len(names)
+        res["ok"] = res["max_rel"] <= 1e-5
+    torch.cuda.synchronize()
+    if lb.world > 1:
+        dist.barrier()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -316,28 +513,26 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the Qwen2.5-7B-shaped greedy-decode tokens/s leg")
     ap.add_argument("--flags", type=int, default=0, help="library flags for every launch (see include/nanoserve_b200.h)")
     ap.add_argument("--layer", default="7b", choices=["7b", "70b"],
-                    help="shapes of the layer pass: the Qwen2.5-7B-shaped layer of the headline metric, or the 70B-class "
-                         "layer (hidden 8192, intermediate 28672) of the multi-GPU configuration")
+                    help="shapes of the headline layer pass: the Qwen2.5-7B-shaped layer of the headline metric, or the "
+                         "70B-class layer (hidden 8192, intermediate 28672) of the multi-GPU configuration")
     ap.add_argument("--tp-collective", action="store_true",
                     help="N > 1: all-gather the outputs with NCCL at the layer boundaries instead of fusing the gather "
-                         "into the GEMVs (peer stores + arrival counters)")
+                         "into the GEMVs (peer stores + arrival counters); implies --seven-launches")
+    ap.add_argument("--seven-launches", action="store_true",
+                    help="run q, k, v and gate, up as separate launches (seven per pass) instead of row-concatenated")
     ap.add_argument("--no-sweep", action="store_true",
                     help="skip the single-GPU sweep over the other benchmark configurations (decode GEMV at M = 1..16 over "
-                         "every 7B-shaped and 70B-class linear, prefill GEMM at M = 512..8192) and, with --layer 70b, the "
-                         "70B-class prefill GEMM sharded over the ranks")
+                         "every 7B-shaped and 70B-class linear, prefill GEMM at M = 512..8192), the 70B-class layer pass and "
+                         "the 70B-class prefill GEMM sharded over the ranks")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
         return
-    global LAYER, N_COPIES
-    if args.layer == "70b":
-        LAYER, N_COPIES = synth.CLASS_70B_LAYER, 4
 
     import torch
     import torch.distributed as dist
     from nanoserve_b200 import build as b2build
     from nanoserve_b200.ops import Kernels
-    from nanoserve_b200.tp import PeerBuffers, ShardedLayer
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
@@ -361,73 +556,46 @@ def main():
     k.init()
     M = args.m
     warm = max(3, args.warmup)
-
-    # ---- resident weights: N_COPIES layer copies, sharded by output rows over the ranks
-    layers = [ShardedLayer.synthetic(k, LAYER, ORDER, G, seed=1000 + c, rank=rank, world=world, device=dev,
-                                     flags=args.flags)
-              for c in range(N_COPIES)]
+    seven = args.seven_launches or args.tp_collective
     fused_gather = world > 1 and not args.tp_collective
-    if fused_gather:
-        peer = PeerBuffers({name: M * LAYER[name][0] for name in ORDER}, len(ShardedLayer.BOUNDARIES), dev)
-        for l in layers:
-            l.attach_peer_buffers(peer, M)
-    hidden, inter = LAYER["q"][1], LAYER["down"][1]
-    x_h = torch.from_numpy(synth.synth_x(M, hidden, 1).view(np.int16)).view(torch.bfloat16).pin_memory()
-    a_h = torch.from_numpy(synth.synth_x(M, inter, 2).view(np.int16)).view(torch.bfloat16).pin_memory()
-    x_d, a_d = x_h.to(dev), a_h.to(dev)
-    resident = sum(l.resident_bytes() for l in layers)
+    shapes = synth.QWEN25_7B_LAYER if args.layer == "7b" else synth.CLASS_70B_LAYER
+    n_copies = N_COPIES if args.layer == "7b" else 4
+    nbytes = sum(synth.gemv_bytes(M, n, kk, G) for n, kk in (shapes[x] for x in ORDER))
 
-    # ---- device-resident timing: one CUDA graph per layer copy (7 launches + the gathers), replayed in rotation
-    stream = torch.cuda.Stream(device=dev)
-    graphs = []
-    with torch.cuda.stream(stream):
-        for l in layers:
-            l.decode_pass(x_d, a_d)  # warm every kernel variant before capture
-        torch.cuda.synchronize()
-        for l in layers:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                l.decode_pass(x_d, a_d)
-            graphs.append(g)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed_replays(n):
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        with torch.cuda.stream(stream):
-            ev0.record(stream)
-            for i in range(n):
-                graphs[i % N_COPIES].replay()
-            ev1.record(stream)
-        barrier()
-        return ev0.elapsed_time(ev1) * 1e-3
-
-    timed_replays(warm)
+    # ---- device-resident timing: one CUDA graph per layer copy, replayed in rotation
+    lb = LayerBench(k, shapes, n_copies, M, rank, world, dev, args.flags, fused_gather, seven)
+    lb.capture()
+    resident = lb.resident_bytes()
+    lb.timed_replays(warm)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    t_dev = timed_replays(args.steps)
-    # keep the GPUs under the same load a little longer so the 100 ms clock sampler sees it; every rank runs
-    # the same number of extra replays (the count comes from rank 0), because the replays contain collectives
+    t_first = lb.timed_replays(args.steps)
+    # the K steps are timed again until at least 50 ms have been timed in all (a 56 us step would otherwise be measured
+    # over a millisecond); every rank runs the same number of blocks (the count comes from rank 0: the replays hold
+    # collectives or peer waits), and the per-step time is the mean over all of them
+    blocks = [max(1, min(400, int(np.ceil(0.05 / max(t_first, 1e-6)))))]
+    if world > 1:
+        dist.broadcast_object_list(blocks, src=0)
+    t_blocks = [lb.timed_replays(args.steps) for _ in range(blocks[0])]
+    t_dev = float(np.mean(t_blocks))
+    # keep the GPUs under the same load a little longer so the 100 ms clock sampler sees it
     n_extra = [max(1, int(0.6 / max(t_dev / args.steps, 1e-6) / 200))]
     if world > 1:
         dist.broadcast_object_list(n_extra, src=0)
     for _ in range(min(n_extra[0], 200)):
-        timed_replays(200)
+        lb.timed_replays(200)
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end: public API, host buffers, copies inside the timed region
     outs_h = None
+    stream = lb.stream
 
     def e2e_step(l):
         nonlocal outs_h
-        xd = x_h.to(dev, non_blocking=True)
-        ad = a_h.to(dev, non_blocking=True)
-        outs = l.decode_pass(xd, ad)
+        xd = lb.x_h.to(dev, non_blocking=True)
+        ad = lb.a_h.to(dev, non_blocking=True)
+        outs = lb.one_pass(l, xd, ad)
         if outs_h is None:
             outs_h = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
         for oh, o in zip(outs_h, outs):
@@ -436,34 +604,34 @@ def main():
 
     with torch.cuda.stream(stream):
         for i in range(warm):
-            e2e_step(layers[i % N_COPIES])
-        barrier()
+            e2e_step(lb.layers[i % n_copies])
+        lb.barrier()
         t0 = time.perf_counter()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record(stream)
         for i in range(args.steps):
-            e2e_step(layers[i % N_COPIES])
-        ev1.record(stream)
-        barrier()
-        t_e2e = max(ev0.elapsed_time(ev1) * 1e-3, 0.0)
+            e2e_step(lb.layers[i % n_copies])
+        lb.barrier()
         t_e2e_wall = time.perf_counter() - t0
-    h2d = x_h.numel() * 2 + a_h.numel() * 2
+    h2d = lb.x_h.numel() * 2 + lb.a_h.numel() * 2
     d2h = sum(o.numel() * 2 for o in outs_h)
+
+    # ---- tensor parallel == single GPU, on the real GPUs
+    check = tp_check(lb, k, dev) if world > 1 else None
 
     # ---- the dominant kernel alone: the 18944 x 3584 GEMV over 16 distinct matrices (gate and up of 8 copies)
     roof = None
+    peaks, which = measured_peaks()
     if world == 1 and args.layer == "7b":
-        big = [(l.full["gate"]) for l in layers] + [(l.full["up"]) for l in layers]
+        big = [l.shards["gate"] for l in lb.layers] + [l.shards["up"] for l in lb.layers]
         y_big = torch.empty(M, 18944, dtype=torch.bfloat16, device=dev)
         with torch.cuda.stream(stream):
             gk = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gk, stream=stream):
                 for (Wq, S) in big:
-                    k.w4_linear(x_d, Wq, S, G, flags=args.flags, out=y_big)
+                    k.w4_linear(lb.x_d, Wq, S, G, flags=args.flags, out=y_big)
             for _ in range(3):
                 gk.replay()
             torch.cuda.synchronize()
-            reps = max(5, min(50, args.steps))
+            reps = 200  # 16 launches x 200 replays x ~8 us: 25 ms timed
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record(stream)
             for _ in range(reps):
@@ -471,36 +639,74 @@ def main():
             ev1.record(stream)
             torch.cuda.synchronize()
             t_k = ev0.elapsed_time(ev1) * 1e-3 / (reps * len(big))
-        peaks, which = measured_peaks()
         kb = synth.gemv_bytes(M, 18944, 3584, G)
         ach = kb / t_k / 1e9
-        roof = {"bound": "hbm", "kernel": "w4_gemv_kernel (N=18944, K=3584, M=%d)" % M, "achieved": ach,
+        ceiling = copy_ceiling_gbs(dev, stream)
+        roof = {"bound": "hbm", "kernel": "w4_gemv_stream_kernel (N=18944, K=3584, M=%d)" % M, "achieved": ach,
                 "peak": peaks["hbm_gbs"], "peak_source": which + " copy bandwidth (MEASURED_PEAKS.json)"
                 if which == "measured" else "fallback 6650 GB/s",
                 "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "us_per_launch": t_k * 1e6,
-                "bytes_per_launch": kb, "traffic": None}
+                "bytes_per_launch": kb, "traffic": None,
+                "frac_of_copy_ceiling": ach / ceiling, "copy_ceiling_gbs": ceiling,
+                "copy_ceiling_def": "512 MiB device copy, 16-byte accesses, read + write bytes (reference: kernels/fused/"
+                                    "vec.cuh:43-47, bench/bench_w4a16.cu:122-136), measured in this run",
+                "frac_of_nominal_8tbs": ach / 8000.0}
         traffic_file = os.path.join(ROOT, "profiles", "gemv_traffic.json")
         if os.path.exists(traffic_file):
             with open(traffic_file) as f:
                 roof["traffic"] = json.load(f).get("dram_bytes_per_launch_m%d" % M)
+        del big, y_big
+
+    # ---- the reference's own GPU kernels on the same box (the kernels to beat), outside the timed regions
+    ref_gpu = ref_gpu_numbers(dev, stream) if world == 1 and not args.no_sweep else None
+    if ref_gpu is not None and roof is not None and isinstance(ref_gpu.get("gemv_m1_18944x3584_us"), float):
+        ref_gpu["gemv_speedup"] = round(ref_gpu["gemv_m1_18944x3584_us"] / roof["us_per_launch"], 2)
+
+    # ---- free the headline layer copies before the wider legs
+    del lb.graphs[:], lb.layers[:]
+    torch.cuda.empty_cache()
 
     # ---- the other benchmark configurations on one GPU: every decode shape at M = 1..16, the prefill GEMMs
     sweep = None
     if world == 1 and not args.no_sweep and args.layer == "7b":
-        del big, y_big
         sweep = run_sweep(k, dev, stream, args.flags)
+        if ref_gpu is not None and isinstance(ref_gpu.get("gemm_m2048_18944x3584_us"), float):
+            ours = [e for e in sweep["gemm"] if e["N"] == 18944 and e["M"] == 2048]
+            if ours:
+                ref_gpu["gemm_speedup"] = round(ref_gpu["gemm_m2048_18944x3584_us"] / ours[0]["us"], 2)
 
-    # ---- 70B-class prefill GEMM, output features sharded over the ranks, outputs all-gathered
+    # ---- configuration 5: the 70B-class layer pass (same code, other shapes) and its sharded prefill GEMM, at every N
+    layer70 = None
     prefill = None
-    if args.layer == "70b" and not args.no_sweep:
-        prefill = run_prefill_tp(k, dev, stream, rank, world)
+    if not args.no_sweep:
+        if args.layer == "7b":
+            try:
+                lb70 = LayerBench(k, synth.CLASS_70B_LAYER, 4, M, rank, world, dev, args.flags, fused_gather, seven, seed0=2000)
+                lb70.capture()
+                lb70.timed_replays(warm)
+                t70 = float(np.mean([lb70.timed_replays(40) for _ in range(3)])) / 40
+                tt = torch.tensor([t70], dtype=torch.float64, device=dev)
+                if world > 1:
+                    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                t70 = float(tt.item())
+                nb70 = sum(synth.gemv_bytes(M, n, kk, G) for n, kk in (synth.CLASS_70B_LAYER[x] for x in ORDER))
+                layer70 = {"us_per_pass": round(t70 * 1e6, 2), "gbs": round(nb70 / t70 / 1e9, 1), "bytes_per_pass": nb70,
+                           "frac_of_hbm_peak_x_gpus": round(nb70 / t70 / 1e9 / (peaks["hbm_gbs"] * world), 3),
+                           "launches_per_pass": lb70.launches_per_step()}
+                if world > 1:
+                    layer70["tp_check"] = tp_check(lb70, k, dev)
+                del lb70.graphs[:], lb70.layers[:]
+                del lb70
+                torch.cuda.empty_cache()
+            except Exception as e:  # noqa: BLE001 - the headline must not be lost to a failure of the wider leg
+                layer70 = {"error": f"{type(e).__name__}: {e}"}
+        if world > 1 or args.layer == "70b":
+            prefill = run_prefill_tp(k, dev, stream, rank, world)
 
     # ---- second half of the headline metric: W4 greedy decode tokens/s of a Qwen2.5-7B-shaped model (512-token prompt,
-    # 256 new tokens, batch 1, tensor parallel over the ranks); free the GEMV benchmark's weights first
+    # 256 new tokens, batch 1, tensor parallel over the ranks)
     decode = None
     if not args.no_decode and args.layer == "7b":
-        del graphs, layers
-        torch.cuda.empty_cache()
         try:
             from nanoserve_b200.qwen import decode_rate
             d = decode_rate(k, dev, rank=rank, world=world, fused_gather=not args.tp_collective)
@@ -509,50 +715,57 @@ def main():
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
             d["ms_per_token"] = float(t.item())
             d["tok_s"] = 1e3 / d["ms_per_token"]
-            peaks, which = measured_peaks()
             d["hbm_frac_of_" + which] = d["weight_bytes_per_token_per_rank"] / (d["ms_per_token"] * 1e-3) / 1e9 / peaks["hbm_gbs"]
             decode = d
         except Exception as e:  # the GEMV line must not be lost to a failure of the wider leg
             decode = {"error": f"{type(e).__name__}: {e}"}
 
     # ---- max over ranks
-    times = torch.tensor([t_dev, t_e2e, t_e2e_wall], dtype=torch.float64, device=dev)
+    times = torch.tensor([t_dev, t_e2e_wall], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    t_dev, t_e2e, t_e2e_wall = times.tolist()
+    t_dev, t_e2e_wall = times.tolist()
     status = k.device_status()
     if status != 0:
         raise SystemExit(f"device status {status}: a kernel reported a time-out; numbers are invalid")
 
     if rank == 0:
-        nbytes = layer_bytes(M)
-        launches_per_step = len(ORDER)
+        metric = METRIC if args.layer == "7b" else METRIC_70B
+        layer_name = "Qwen2.5-7B-shaped" if args.layer == "7b" else "70B-class (hidden 8192, intermediate 28672)"
         line = {
-            "metric": METRIC if M == 1 else METRIC.replace("M=1", f"M={M}"), "value": nbytes * args.steps / t_dev / 1e9,
+            "metric": metric if M == 1 else metric.replace("M=1", f"M={M}"), "value": nbytes * args.steps / t_dev / 1e9,
             "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": t_dev / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "int4 weights x bf16 activations, fp32 accumulate", "data": "synthetic",
+            "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
             "config": {
-                "workload": "decode GEMV pass over the 7 linears of a " +
-                            ("Qwen2.5-7B-shaped" if args.layer == "7b" else "70B-class (hidden 8192, intermediate 28672)") +
-                            f" layer, M={M}, int4 g128",
-                "parallelism": (f"tp{world}, all-gather " + ("fused into the GEMVs (peer stores + arrival counters)"
+                "workload": f"decode GEMV pass over the 7 linears of a {layer_name} layer, M={M}, int4 g128",
+                "launches": ("7 GEMV launches per pass" if seven else
+                             "4 GEMV launches per pass: q|k|v and gate|up as row-concatenated matrices (same arithmetic)"),
+                "parallelism": (f"tp{world}, all-gather " + ("fused into the GEMVs (peer stores + arrival counters; each "
+                                                             "launch waits for the previous gathered row in-kernel)"
                                                              if fused_gather else "by NCCL at the 4 layer boundaries"))
                 if world > 1 else "single GPU",
-                "l2": f"weights rotate through {N_COPIES} layer copies ({resident * world / 1e6:.0f} MB) > 126 MB L2",
+                "l2": f"weights rotate through {n_copies} layer copies ({resident * world / 1e6:.0f} MB) > 126 MB L2",
                 "bytes_per_step": nbytes, "launch": "one CUDA graph per layer copy, replayed in rotation",
+                "timed": f"{blocks[0]} blocks of {args.steps} steps ({t_dev * blocks[0] * 1e3:.1f} ms in all), mean per step",
                 "seeds": "X 1/2, layer copy c: 1000+c", "flags": args.flags,
             },
             "e2e": {"value": nbytes * args.steps / t_e2e_wall / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e_wall / args.steps * 1e3,
-                    "path": "Kernels.w4_linear per linear (ctypes -> C ABI), pinned host X in, all outputs out"},
-            "gpu_launches": (launches_per_step + (len(ShardedLayer.BOUNDARIES) if fused_gather else 0)) * args.steps,
+                    "path": "Kernels.w4_linear per launch (ctypes -> C ABI), pinned host X in, all outputs out"},
+            "gpu_launches": lb.launches_per_step() * args.steps * (blocks[0] + 1),
             "clocks": clocks,
         }
         if roof is not None:
             line["roofline"] = roof
+        if check is not None:
+            line["tp_check"] = check
+        if ref_gpu is not None:
+            line["ref_gpu"] = ref_gpu
         if sweep is not None:
             line["sweep"] = sweep
+        if layer70 is not None:
+            line["layer_70b"] = layer70
         if decode is not None:
             line["decode"] = decode
         if prefill is not None:
@@ -566,8 +779,8 @@ def main():
                                               f"runs its check), {dt:.2f} s per pass"}
         print(json.dumps(line), flush=True)
     if world > 1:
-        # Captured graphs hold NCCL work; tearing the communicator down under them can block.  Everything is
-        # measured and printed: synchronise, meet once more, and leave without running the destructors.
+        # Captured graphs hold peer waits or NCCL work; tearing the communicator down under them can block.  Everything
+        # is measured and printed: synchronise, meet once more, and leave without running the destructors.
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()

@@ -116,52 +116,86 @@ __global__ void rope_kv_store_kernel(bf16* qkv, const bf16* __restrict__ bias,
 }
 
 // Decode attention in two launches.  Pass 1, grid (Hk, kSplits): a CTA takes one KV head and one slice of the
-// cached positions; warp w serves query head w of the group (Hq / Hk <= 8 heads share a KV head, so K and V rows
-// are read once per CTA, not once per query head); lanes split the head dimension; online softmax per warp.
-// It writes un-normalised partials (max, sum, acc[D]) per (query head, split).  Pass 2, grid Hq: merges the
-// splits.  With 4 KV heads x 32 splits the first pass fills 128 SMs however long the cache is.
+// cached positions; it first copies the slice's K and V rows into shared memory with 16-byte loads that are all in
+// flight together (one L2 round trip for the whole slice; a loop of dependent-looking 8-byte loads per position
+// cost a round trip per position: 16 us per layer at 600 positions), then warp w serves query head w of the group
+// (Hq / Hk <= 8 heads share a KV head); lanes split the head dimension; online softmax per warp.  It writes
+// un-normalised partials (max, sum, acc[D]) per (query head, split).  Pass 2, grid Hq: merges the splits, all of
+// its loads issued before the first use.  With 4 KV heads x 32 splits the first pass fills 128 SMs however long
+// the cache is.
 constexpr int kSplits = 32;
+constexpr int kTileRows = 32;  // positions staged in shared memory at a time
 
 template <int D>
 __global__ void __launch_bounds__(256) decode_attention_partial_kernel(
     const bf16* q, const bf16* cache_k, const bf16* cache_v, const int* pos_ptr, float* part, int Hq, int Hk,
     int max_len, float scale) {
-  constexpr int E = D / 32;  // elements per lane
+  constexpr int E = D / 32;        // elements per lane
+  constexpr int kRowU4 = D / 8;    // 16-byte units per row
+  __shared__ __align__(16) bf16 s_k[kTileRows * D];
+  __shared__ __align__(16) bf16 s_v[kTileRows * D];
   const int kh = blockIdx.x, sp = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rep = Hq / Hk;
   pdl_begin();
-  if (warp >= rep) return;
-  const int h = kh * rep + warp;
+  const int h = kh * rep + min(warp, rep - 1);
   const int n = min(__ldcg(pos_ptr) + 1, max_len);
   const int per = (n + kSplits - 1) / kSplits;
   const int j0 = sp * per, j1 = min(n, j0 + per);
-  const bf16* kbase = cache_k + (size_t)kh * max_len * D;
-  const bf16* vbase = cache_v + (size_t)kh * max_len * D;
+  const uint4* kbase = reinterpret_cast<const uint4*>(cache_k + (size_t)kh * max_len * D);
+  const uint4* vbase = reinterpret_cast<const uint4*>(cache_v + (size_t)kh * max_len * D);
   float qf[E];
-#pragma unroll
-  for (int e = 0; e < E; ++e) qf[e] = 0.f;
   ld_row<E>(q + (size_t)h * D + lane * E, qf);
 #pragma unroll
   for (int e = 0; e < E; ++e) qf[e] *= scale;
   float m = -FLT_MAX, l = 0.f, acc[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) acc[e] = 0.f;
-  for (int j = j0; j < j1; ++j) {
-    const bf16* kr = kbase + (size_t)j * D + lane * E;
-    float s = 0.f, kf[E], vf[E];
-    ld_row<E>(kr, kf);
-    ld_row<E>(vbase + (size_t)j * D + lane * E, vf);
+  for (int t0 = j0; t0 < j1; t0 += kTileRows) {
+    const int rows = min(kTileRows, j1 - t0);
+    const int units = rows * kRowU4;
+    if (t0 > j0) __syncthreads();  // everybody is done with the previous tile
+    // all loads first, then all stores: one round trip for the tile
+    constexpr int kPerThread = (kTileRows * kRowU4 + 255) / 256;
+    uint4 kv[kPerThread], vv[kPerThread];
 #pragma unroll
-    for (int e = 0; e < E; ++e) s += qf[e] * kf[e];
+    for (int i = 0; i < kPerThread; ++i) {
+      const int u = threadIdx.x + i * 256;
+      if (u < units) {
+        kv[i] = __ldcg(kbase + (size_t)t0 * kRowU4 + u);
+        vv[i] = __ldcg(vbase + (size_t)t0 * kRowU4 + u);
+      }
+    }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    const float mn = fmaxf(m, s);
-    const float corr = __expf(m - mn), pj = __expf(s - mn);
-    l = l * corr + pj;
+    for (int i = 0; i < kPerThread; ++i) {
+      const int u = threadIdx.x + i * 256;
+      if (u < units) {
+        reinterpret_cast<uint4*>(s_k)[u] = kv[i];
+        reinterpret_cast<uint4*>(s_v)[u] = vv[i];
+      }
+    }
+    __syncthreads();
+    if (warp < rep) {
+      for (int r = 0; r < rows; ++r) {
+        float s = 0.f, kf[E], vf[E];
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[e] = acc[e] * corr + pj * vf[e];
-    m = mn;
+        for (int e = 0; e < E; ++e) {
+          kf[e] = __bfloat162float(s_k[r * D + lane * E + e]);
+          vf[e] = __bfloat162float(s_v[r * D + lane * E + e]);
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) s += qf[e] * kf[e];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float mn = fmaxf(m, s);
+        const float corr = __expf(m - mn), pj = __expf(s - mn);
+        l = l * corr + pj;
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] = acc[e] * corr + pj * vf[e];
+        m = mn;
+      }
+    }
   }
+  if (warp >= rep) return;
   float* out = part + ((size_t)h * kSplits + sp) * (D + 2);
   if (lane == 0) {
     out[0] = m;
@@ -176,16 +210,23 @@ __global__ void decode_attention_merge_kernel(const float* part, bf16* out) {
   const int h = blockIdx.x, d = threadIdx.x;  // block: D threads
   pdl_begin();
   const float* p = part + (size_t)h * kSplits * (D + 2);
-  float mm = -FLT_MAX;
-#pragma unroll 4
-  for (int s = 0; s < kSplits; ++s) mm = fmaxf(mm, __ldcg(p + s * (D + 2)));
-  float num = 0.f, den = 0.f;
-#pragma unroll 4
+  // every load of the merge is issued before the first use: one L2 round trip, not one per split
+  float ms[kSplits], ls[kSplits], as[kSplits];
+#pragma unroll
   for (int s = 0; s < kSplits; ++s) {
-    const float ms = __ldcg(p + s * (D + 2));
-    const float f = ms == -FLT_MAX ? 0.f : __expf(ms - mm);
-    num += f * __ldcg(p + s * (D + 2) + 2 + d);
-    den += f * __ldcg(p + s * (D + 2) + 1);
+    ms[s] = __ldcg(p + s * (D + 2));
+    ls[s] = __ldcg(p + s * (D + 2) + 1);
+    as[s] = __ldcg(p + s * (D + 2) + 2 + d);
+  }
+  float mm = -FLT_MAX;
+#pragma unroll
+  for (int s = 0; s < kSplits; ++s) mm = fmaxf(mm, ms[s]);
+  float num = 0.f, den = 0.f;
+#pragma unroll
+  for (int s = 0; s < kSplits; ++s) {
+    const float f = ms[s] == -FLT_MAX ? 0.f : __expf(ms[s] - mm);
+    num += f * as[s];
+    den += f * ls[s];
   }
   out[(size_t)h * D + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
 }

@@ -76,6 +76,7 @@ class Qwen2Runner:
             return shard(Wq), shard(S)
 
         self.layers = []
+        norm_gain = 0.001
         for _ in range(cfg.n_layers):
             q, k, v = w4(self.nq, H), w4(self.nkv, H), w4(self.nkv, H)
             o = w4(H, self.nq)
@@ -86,12 +87,19 @@ class Qwen2Runner:
                 "qkv": (torch.cat([q[0], k[0], v[0]]), torch.cat([q[1], k[1], v[1]])),
                 "o": o, "gu": (torch.cat([g[0], u[0]]), torch.cat([g[1], u[1]])), "d": d,
                 "bias": bias,  # full-width: applied after the gather (Qwen2 has q/k/v biases, qwen.py:76,147-148)
-                "ln_in": (1 + 0.02 * torch.randn(H, device=device, generator=gen)).to(torch.bfloat16),
-                "ln_post": (1 + 0.02 * torch.randn(H, device=device, generator=gen)).to(torch.bfloat16),
+                "ln_in": (norm_gain * (1 + 0.02 * torch.randn(H, device=device, generator=gen))).to(torch.bfloat16),
+                "ln_post": (norm_gain * (1 + 0.02 * torch.randn(H, device=device, generator=gen))).to(torch.bfloat16),
             })
         self.final_norm = (1 + 0.02 * torch.randn(H, device=device, generator=gen)).to(torch.bfloat16)
-        self.embed = (torch.randn(cfg.vocab, H, device=device, generator=gen) * 0.02).to(torch.bfloat16)
-        self.lm_head = shard((torch.randn(cfg.vocab, H, device=device, generator=gen) * 0.02).to(torch.bfloat16))
+        # Random nibbles make every linear amplify its input (about 2.8x at K = 3584), and a stack of them drives the
+        # residual stream to one direction whatever the token: greedy decoding of such a model repeats a single id.
+        # To keep the generated sequence input-dependent -- so that a wrong kernel shows up as different tokens -- the
+        # norm gains are small (the layers perturb the stream instead of replacing it), the embeddings have unit
+        # scale, and the lm_head is the embedding table under a fixed permutation of the vocabulary: the next token is,
+        # up to the layers' perturbation, the permutation's image of the current one.
+        self.embed = torch.randn(cfg.vocab, H, device=device, generator=gen).to(torch.bfloat16)
+        perm = torch.randperm(cfg.vocab, device=device, generator=gen)
+        self.lm_head = shard((self.embed[perm].float() * 0.02).to(torch.bfloat16))
         self.inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2, dtype=torch.int64, device=device).float() / D))
         self.cache_k = torch.zeros(cfg.n_layers, cfg.n_kv_heads, max_len, D, dtype=torch.bfloat16, device=device)
         self.cache_v = torch.zeros_like(self.cache_k)
@@ -383,10 +391,34 @@ def decode_rate(kernels: Kernels, device, rank: int = 0, world: int = 1, cfg: Op
     torch.cuda.synchronize()
     t_prefill, t_decode = e0.elapsed_time(e1) * 1e-3, e1.elapsed_time(e2) * 1e-3
     tokens = r.tokens[:n_new].tolist()
-    return {"tok_s": (n_new - 1) / t_decode, "ms_per_token": t_decode / (n_new - 1) * 1e3,
+    import hashlib
+    sha = hashlib.sha1(",".join(map(str, tokens)).encode()).hexdigest()[:16]
+    # tensor parallel == single GPU: rank 0 builds the same model unsharded and compares the logits of the first
+    # generated token (its own slice of the vocabulary) and the whole generated sequence
+    tp_check = None
+    if world > 1:
+        with torch.cuda.stream(r.stream):
+            r.prefill(prompt)
+        torch.cuda.synchronize()
+        mine = r.logits.float().clone()
+        if rank == 0:
+            r1 = Qwen2Runner(cfg, kernels, device, rank=0, world=1, seed=seed, max_len=prompt_len + n_new + 8)
+            toks1 = r1.generate(prompt, n_new)
+            with torch.cuda.stream(r1.stream):
+                r1.prefill(prompt)
+            torch.cuda.synchronize()
+            want = r1.logits.float()[:, :mine.shape[1]]
+            scale = want.abs().max()
+            tp_check = {"logits_max_rel": float(((mine - want).abs() / scale).max()), "tokens_equal": toks1 == tokens,
+                        "first_difference": next((i for i, (a, b) in enumerate(zip(toks1, tokens)) if a != b), None)}
+            tp_check["ok"] = tp_check["logits_max_rel"] <= 2e-2 and tp_check["tokens_equal"]
+            del r1
+            torch.cuda.empty_cache()
+        dist.barrier()
+    return {"tp_check": tp_check, "tokens_sha1": sha, "distinct_tokens": len(set(tokens)), "tok_s": (n_new - 1) / t_decode, "ms_per_token": t_decode / (n_new - 1) * 1e3,
             "prefill_tok_s": prompt_len / t_prefill, "prompt_len": prompt_len, "n_new": n_new,
             "weight_bytes_per_token_per_rank": r.weight_bytes_per_token(), "first_tokens": tokens[:8],
-            "launches_per_token": "7 per layer + final norm + lm_head + 2 for argmax, one CUDA graph; " +
+            "launches_per_token": "7 per layer + lm_head (final norm and block argmax folded in) + the pick, one CUDA graph; " +
                                   ("all-gathers fused into the GEMVs" if r.peer is not None else
                                    "NCCL all-gathers at the layer boundaries" if world > 1 else "one GPU")}
 
