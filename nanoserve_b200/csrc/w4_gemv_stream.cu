@@ -94,7 +94,9 @@ __device__ __forceinline__ void stage_x_planes(const GemvParams& p, uint32_t xs_
                                                const float* inv, int cb, int nch, int tid) {
   constexpr int B = 8 * P;
   constexpr uint32_t kBias = P == 4 ? 0x00808080u : 0x00000080u;
-  constexpr int UN = 2;  // items in flight per thread: a load from L2 takes a microsecond under the weight stream
+  // items in flight per thread: a load from L2 takes a microsecond under the weight stream.  (Five -- all of a
+  // thread's loads at K = 18944 -- was measured too: the 23 registers more cost more than the round trips saved.)
+  constexpr int UN = 2;
   const int items_tok = nch * 8;
   const int items = p.M * items_tok;
   const int items_pad = (items + 31) & ~31;
@@ -322,6 +324,79 @@ __device__ __forceinline__ void gemv_step(LoopState<NT>& st, float (&fin)[RB][NT
   }
 }
 
+// The same step for more than one token ("one-group" layout): the fragments come out of shared memory, so a lane is
+// free to take 16 bytes of the even chunk and 16 bytes of the odd chunk of its row instead of 32 consecutive bytes;
+// every mma then stays inside one quantization group, the B operand needs ONE column per (token, plane), and a
+// super-chunk costs 2 x 4 mma per column tile instead of 8 per tile of twice as many columns.  mma row g reads slot
+// row rho(g) = (g >> 1) | ((g & 1) << 2) so that the eight lanes of a shared-memory phase land in opposite halves
+// of the swizzled 128-byte rows.  Columns: m P + p; B fragments: lane (g, t) holds column nt * 8 + g, items 2t and
+// 2t + 1 of the chunk; accumulators: columns nt * 8 + 2t, + 1.
+template <int NT, int P, bool GD1>
+__device__ __forceinline__ void gemv_step_one(LoopState<NT>& st, float (&fin)[1][NT][4], int sc, bool refill, int gdiv,
+                                              int gs0) {
+  constexpr int kSlotBytes = 16 * 128;
+  float s_lo[2], s_hi[2];
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    s_lo[c] = __uint_as_float(lds_u16s(st.sc_row + st.goff[c]) << 16);
+    s_hi[c] = __uint_as_float(lds_u16s(st.sc_row + st.sc_rstep + st.goff[c]) << 16);
+  }
+  mbar_wait(st.bar, st.ph, st.abort_flag);
+  uint4 wl[2], wh[2];
+  wl[0] = lds128(st.slot + st.a_u0);
+  wh[0] = lds128(st.slot + 1024 + st.a_u0);
+  wl[1] = lds128(st.slot + st.a_u1);
+  wh[1] = lds128(st.slot + 1024 + st.a_u1);
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const uint32_t lo[4] = {wl[c].x, wl[c].y, wl[c].z, wl[c].w};
+    const uint32_t hi[4] = {wh[c].x, wh[c].y, wh[c].z, wh[c].w};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      // (steps are zero for lanes that read the block of zeros: their chunk offset is zero too)
+      const uint32_t xa = st.xaddr[nt] + c * (st.xstep[nt] >> 1);
+      const uint4 x0 = lds128(xa), x1 = lds128(xa + 16);
+      const uint4 inf = lds128(st.iaddr[nt] + c * (st.istep[nt] >> 1));
+      int acc_e[4], acc_o[4];
+      imma_u8s8(acc_e, lo[0] & st.k_nib_lo, hi[0] & st.k_nib_lo, lo[1] & st.k_nib_lo, hi[1] & st.k_nib_lo, x0.x, x0.y, 0,
+                0, 0, 0);
+      imma_u8s8(acc_o, lo[0] & st.k_nib_hi, hi[0] & st.k_nib_hi, lo[1] & st.k_nib_hi, hi[1] & st.k_nib_hi, x0.z, x0.w,
+                (int)inf.x, (int)inf.y, (int)inf.x, (int)inf.y);
+      imma_u8s8(acc_e, lo[2] & st.k_nib_lo, hi[2] & st.k_nib_lo, lo[3] & st.k_nib_lo, hi[3] & st.k_nib_lo, x1.x, x1.y,
+                acc_e[0], acc_e[1], acc_e[2], acc_e[3]);
+      imma_u8s8(acc_o, lo[2] & st.k_nib_hi, hi[2] & st.k_nib_hi, lo[3] & st.k_nib_hi, hi[3] & st.k_nib_hi, x1.z, x1.w,
+                acc_o[0], acc_o[1], acc_o[2], acc_o[3]);
+      const float up0 = __uint_as_float(inf.z), up1 = __uint_as_float(inf.w);
+      fin[0][nt][0] = fmaf(s_lo[c] * up0, (float)(acc_e[0] * 16 + acc_o[0]), fin[0][nt][0]);
+      fin[0][nt][1] = fmaf(s_lo[c] * up1, (float)(acc_e[1] * 16 + acc_o[1]), fin[0][nt][1]);
+      fin[0][nt][2] = fmaf(s_hi[c] * up0, (float)(acc_e[2] * 16 + acc_o[2]), fin[0][nt][2]);
+      fin[0][nt][3] = fmaf(s_hi[c] * up1, (float)(acc_e[3] * 16 + acc_o[3]), fin[0][nt][3]);
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    st.xaddr[nt] += st.xstep[nt];
+    st.iaddr[nt] += st.istep[nt];
+  }
+  __syncwarp();
+  if (refill) feed_slot<1>(st, st.slot, st.bar);
+  st.slot += kSlotBytes;
+  st.bar += 8;
+  if (++st.d == st.depth) {
+    st.d = 0;
+    st.slot = st.ring0;
+    st.bar = st.bar0;
+    st.ph ^= 1;
+  }
+  if constexpr (GD1) {
+    st.goff[0] += 4;
+    st.goff[1] += 4;
+  } else {
+    st.goff[0] = ((2 * (sc + 1)) / gdiv - gs0) * 2;
+    st.goff[1] = ((2 * (sc + 1) + 1) / gdiv - gs0) * 2;
+  }
+}
+
 // NT: tiles of eight B columns.  P: planes per token.  RB: 16-row blocks per warp.  GD1: G == 128.
 //
 // Every warp owns a private ring of q.depth shared-memory slots (RB * 16 rows x 128 bytes each: one 256-wide piece of K,
@@ -339,7 +414,7 @@ __device__ __forceinline__ void gemv_step(LoopState<NT>& st, float (&fin)[RB][NT
 // digits are non-zero only in the k-slots of the even chunk and one for the odd chunk -- 2 M P columns, eight per
 // mma.  For one token with four planes that is exactly one mma tile, and every accumulator of every lane is a real
 // partial sum.
-template <int NT, int P, int RB, bool GD1>
+template <int NT, int P, int RB, bool GD1, bool ONE>
 __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvParams p, const StreamParams q) {
   extern __shared__ __align__(1024) unsigned char smem[];
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
@@ -441,33 +516,12 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
 #pragma unroll
       for (int i = 0; i < 4; ++i) fin[rb][nt][i] = 0.f;
 
+  // mma row g of this lane <-> row `grow` of a 16-row block (two-chunk layout: g; one-group layout: rho(g))
+  const int grow = ONE ? ((g >> 1) | ((g & 1) << 2)) : g;
   if (active) {
-    // Column c = h M P + (m P + p): h = which chunk of the super-chunk.  B fragments: lane (g, t) holds column
-    // nt * 8 + g, and only the lanes whose k-slots lie in that column's chunk (t >> 1 == h) hold digits; accumulators:
-    // columns nt * 8 + 2t, + 1.  Lanes without a real column read a block of zeros (stride zero): no predicates in the loop.
     const uint32_t zero_base = smem_u32(smem + kZeroOffset);
-    const int istep = MP * 16;  // bytes of info per super-chunk (two chunks of M P / 2 column pairs)
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int colb = nt * 8 + g, cola = nt * 8 + 2 * t;
-      const int hb = colb / MP, cb_ = colb - hb * MP;
-      const int ha = cola / MP, ca_ = cola - ha * MP;
-      const bool bval = colb < 2 * MP && hb == (t >> 1);
-      const bool aval = cola < 2 * MP;
-      st.sel_a[nt] = aval ? ha : 0;
-      st.xaddr[nt] = bval ? xs_base + cb_ * q.pstride + t * 64 + (s0 - scb) * 256 : zero_base;
-      st.xstep[nt] = bval ? 256 : 0;
-      st.iaddr[nt] = aval ? info_base + ((ha * MP + ca_) >> 1) * 16 + (s0 - scb) * istep : zero_base;
-      st.istep[nt] = aval ? istep : 0;
-    }
-    // this lane's scales: rows g + 8 i of the warp's tile (rows beyond N read whatever follows: their sums are dropped)
-    st.sc_row = sc_base + ((tl * kRows + g) * q.gs_pitch) * 2;
+    st.sc_row = sc_base + ((tl * kRows + grow) * q.gs_pitch) * 2;
     st.sc_rstep = 8 * q.gs_pitch * 2;
-    st.goff[0] = (((2 * s0 + (NT == 1 ? st.sel_a[0] : 0)) / p.gdiv) - gs0) * 2;  // one tile: the lane's own chunk
-    st.goff[1] = (((2 * s0 + 1) / p.gdiv) - gs0) * 2;
-    // fragment source: row g (+ 8 i) of the slot, 16-byte units 2t and 2t + 1, swizzled by the row
-    st.a_u0 = g * 128 + ((uint32_t)((2 * t) ^ g) << 4);
-    st.a_u1 = g * 128 + ((uint32_t)((2 * t + 1) ^ g) << 4);
     st.k_nib_lo = 0x0F0F0F0Fu;
     st.k_nib_hi = 0xF0F0F0F0u;
     asm volatile("" : "+r"(st.k_nib_lo), "+r"(st.k_nib_hi));
@@ -479,40 +533,97 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
     st.ph = 0;
     st.abort_flag = abort_flag;
     const int s_refill_end = s1 - q.depth;  // super-chunks before this one refill their slot
-    for (int sc = s0; sc < s1; ++sc) gemv_step<NT, P, RB, GD1>(st, fin, sc, sc < s_refill_end, p.gdiv, gs0);
+    if constexpr (ONE) {
+      // Column c = m P + p.  Lanes without a real column read a block of zeros (stride zero): no predicates in the loop.
+      const int chunk_info = (MP >> 1) * 16;  // bytes of info per chunk
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int colb = nt * 8 + g, cola = nt * 8 + 2 * t;
+        const bool bval = colb < MP, aval = cola < MP;
+        st.sel_a[nt] = 0;
+        st.xaddr[nt] = bval ? xs_base + colb * q.pstride + t * 32 + (s0 - scb) * 256 : zero_base;
+        st.xstep[nt] = bval ? 256 : 0;
+        st.iaddr[nt] = aval ? info_base + (cola >> 1) * 16 + (s0 - scb) * 2 * chunk_info : zero_base;
+        st.istep[nt] = aval ? 2 * chunk_info : 0;
+      }
+      st.goff[0] = (((2 * s0) / p.gdiv) - gs0) * 2;
+      st.goff[1] = (((2 * s0 + 1) / p.gdiv) - gs0) * 2;
+      // fragment source: slot row rho(g), 16-byte unit t of the even chunk / 4 + t of the odd chunk, swizzled by the row
+      st.a_u0 = grow * 128 + ((uint32_t)(t ^ grow) << 4);
+      st.a_u1 = grow * 128 + ((uint32_t)((4 + t) ^ grow) << 4);
+      for (int sc = s0; sc < s1; ++sc)
+        gemv_step_one<NT, P, GD1>(st, fin, sc, sc < s_refill_end, p.gdiv, gs0);
+    } else {
+      // Column c = h M P + (m P + p): h = which chunk of the super-chunk.  B fragments: lane (g, t) holds column
+      // nt * 8 + g, and only the lanes whose k-slots lie in that column's chunk (t >> 1 == h) hold digits;
+      // accumulators: columns nt * 8 + 2t, + 1.  Lanes without a real column read a block of zeros (stride zero).
+      const int istep = MP * 16;  // bytes of info per super-chunk (two chunks of M P / 2 column pairs)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int colb = nt * 8 + g, cola = nt * 8 + 2 * t;
+        const int hb = colb / MP, cb_ = colb - hb * MP;
+        const int ha = cola / MP, ca_ = cola - ha * MP;
+        const bool bval = colb < 2 * MP && hb == (t >> 1);
+        const bool aval = cola < 2 * MP;
+        st.sel_a[nt] = aval ? ha : 0;
+        st.xaddr[nt] = bval ? xs_base + cb_ * q.pstride + t * 64 + (s0 - scb) * 256 : zero_base;
+        st.xstep[nt] = bval ? 256 : 0;
+        st.iaddr[nt] = aval ? info_base + ((ha * MP + ca_) >> 1) * 16 + (s0 - scb) * istep : zero_base;
+        st.istep[nt] = aval ? istep : 0;
+      }
+      st.goff[0] = (((2 * s0 + (NT == 1 ? st.sel_a[0] : 0)) / p.gdiv) - gs0) * 2;  // one tile: the lane's own chunk
+      st.goff[1] = (((2 * s0 + 1) / p.gdiv) - gs0) * 2;
+      // fragment source: row g (+ 8 i) of the slot, 16-byte units 2t and 2t + 1, swizzled by the row
+      st.a_u0 = g * 128 + ((uint32_t)((2 * t) ^ g) << 4);
+      st.a_u1 = g * 128 + ((uint32_t)((2 * t + 1) ^ g) << 4);
+      for (int sc = s0; sc < s1; ++sc) gemv_step<NT, P, RB, GD1>(st, fin, sc, sc < s_refill_end, p.gdiv, gs0);
+    }
   }
 
   if (NT == 1 && q.ks == 1 && p.nslices == 1 && p.tp.world == 0) {
-    // ---- one tile, no K slices: the lanes of a quad hold the chunks and planes of the same rows; two shuffles, and
-    // the outputs go straight from registers to Y
+    // ---- one tile, no K slices: the lanes of a quad hold the chunks and planes of the same rows; a shuffle or two,
+    // and the outputs go straight from registers to Y
 #pragma unroll
     for (int rb = 0; rb < RB; ++rb) {
       float v_lo = fin[rb][0][0] + fin[rb][0][1], v_hi = fin[rb][0][2] + fin[rb][0][3];
-      v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 2);
-      v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 2);
-      if (P == 4) {
-        v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
-        v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+      int m;
+      bool writer;
+      if constexpr (ONE) {
+        // columns 2t, 2t + 1 = planes of token (2t) / P
+        if (P == 4) {
+          v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
+          v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+        }
+        m = P == 4 ? (t >> 1) : t;
+        writer = (P == 4 ? (t & 1) == 0 : true) && m < p.M;
+      } else {
+        v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 2);
+        v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 2);
+        if (P == 4) {
+          v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
+          v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+        }
+        m = P == 4 ? 0 : t;  // two planes: lanes t = 0, 1 of a quad hold tokens 0, 1
+        writer = P == 4 ? t == 0 : (t < 2 && t < p.M);
       }
-      const int m = P == 4 ? 0 : t;  // two planes: lanes t = 0, 1 of a quad hold tokens 0, 1
-      const bool writer = P == 4 ? t == 0 : (t < 2 && t < p.M);
-      const int n = wrow0 + rb * 16 + g;
+      const int n = wrow0 + rb * 16 + grow;
       if (writer && active) {
         if (n < p.N) p.Y[(size_t)m * p.N + n] = __float2bfloat16(v_lo);
         if (n + 8 < p.N) p.Y[(size_t)m * p.N + n + 8] = __float2bfloat16(v_hi);
       }
     }
   } else {
-    // ---- every accumulator column pair of the warp goes to shared memory; the sums over the two chunks of a
-    // super-chunk, the planes of a token and the K slices of a row tile are taken after the barrier, in fixed order
+    // ---- every accumulator column pair of the warp goes to shared memory; the sums over the chunks of a super-chunk
+    // (two-chunk layout), the planes of a token and the K slices of a row tile are taken after the barrier, in fixed
+    // order
     float* red = reinterpret_cast<float*>(smem + q.off_red);  // [warp][column pair][kRows]
 #pragma unroll
     for (int rb = 0; rb < RB; ++rb)
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         const int slot = nt * 4 + t;
-        red[(warp * kSlots + slot) * kRows + rb * 16 + g] = fin[rb][nt][0] + fin[rb][nt][1];
-        red[(warp * kSlots + slot) * kRows + rb * 16 + g + 8] = fin[rb][nt][2] + fin[rb][nt][3];
+        red[(warp * kSlots + slot) * kRows + rb * 16 + grow] = fin[rb][nt][0] + fin[rb][nt][1];
+        red[(warp * kSlots + slot) * kRows + rb * 16 + grow + 8] = fin[rb][nt][2] + fin[rb][nt][3];
       }
     __syncthreads();
     const int slice = blockIdx.y;
@@ -524,7 +635,7 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
       for (int s = 0; s < q.ks; ++s) {
         const float* src = red + ((tile * q.ks + s) * kSlots) * kRows + rr;
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < (ONE ? 1 : 2); ++h)
 #pragma unroll
           for (int j = 0; j < P / 2; ++j) sum += src[(h * half_mp + ((m * P) >> 1) + j) * kRows];
       }
@@ -549,6 +660,7 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
 }
 
 struct StreamPlan {
+  bool one;
   int P, NT, RB, ks, nslices, scps, grid_x;
   size_t smem;
   StreamParams q;
@@ -576,15 +688,17 @@ size_t stream_smem(int M, int P, int NT, int RB, int tpc, int scps, int gs_pitch
 bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int sm_count, size_t partial_cap,
                       StreamPlan* out) {
   StreamPlan pl{};
-  // four planes (32-bit block fixed point) for one token: its 2 x 4 columns fill exactly one mma tile; two above
-  pl.P = M <= 1 ? 4 : 2;
-  pl.NT = (2 * M * pl.P + 7) / 8;
+  // One token: the two-chunk layout, four planes (32-bit block fixed point): its 2 x 4 columns fill exactly one mma
+  // tile.  More tokens: the one-group layout, M P columns; four planes while they fit one tile (M <= 2), two above.
+  pl.one = M > 1;
+  pl.P = M <= 2 ? 4 : 2;
+  pl.NT = pl.one ? (M * pl.P + 7) / 8 : 1;
   // 32 rows per warp where 16 would make more than 1.25 CTAs per SM (fewer, longer CTAs stream better than an
   // uneven second wave); bits 18-19 of the flags force 16 (1) or 32 (2) rows (diagnostics)
   pl.RB = (long)((N + 15) / 16 + kWarps - 1) / kWarps * 4 > (long)sm_count * 5 ? 2 : 1;
   if (((flags >> 18) & 3) == 1) pl.RB = 1;
   if (((flags >> 18) & 3) == 2) pl.RB = 2;
-  if (pl.NT > 1) pl.RB = 1;
+  if (pl.one) pl.RB = 1;
   const int rows = pl.RB * 16;
   const int nsc = K / 256, gdiv = G / 128, KG = K / G;
   const int n_tiles = (N + rows - 1) / rows;
@@ -637,9 +751,9 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   return true;
 }
 
-template <int NT, int P, int RB, bool GD1>
+template <int NT, int P, int RB, bool GD1, bool ONE>
 int launch_stream_g(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStream_t stream) {
-  auto kernel = w4_gemv_stream_kernel<NT, P, RB, GD1>;
+  auto kernel = w4_gemv_stream_kernel<NT, P, RB, GD1, ONE>;
   // Raising the dynamic shared-memory limit and the carve-out is remembered per device: done once.
   static bool attr_done[64] = {};
   int dev = 0;
@@ -665,19 +779,28 @@ int launch_stream_g(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStr
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
-template <int NT, int P, int RB>
+template <int NT, int P, int RB, bool ONE>
 int launch_stream(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStream_t stream) {
-  return p.gdiv == 1 ? launch_stream_g<NT, P, RB, true>(p, pl, pdl, stream)
-                     : launch_stream_g<NT, P, RB, false>(p, pl, pdl, stream);
+  return p.gdiv == 1 ? launch_stream_g<NT, P, RB, true, ONE>(p, pl, pdl, stream)
+                     : launch_stream_g<NT, P, RB, false, ONE>(p, pl, pdl, stream);
 }
 
 }  // namespace
 
 bool gemv_stream_applies(const void* Wq, int M, int N, int K, int G, int flags) {
-  // (more than two tokens: the ring kernel is the faster one for now; bit 12-free diagnostics flag forces this kernel)
-  const int max_m = (flags & kFlagStreamKernel) ? 16 : 2;
-  return !(flags & (kFlagRingKernel | kFlagFloatX)) && M >= 1 && M <= max_m && N >= 1 && G % 128 == 0 && K % 256 == 0 &&
-         K % G == 0 && (reinterpret_cast<uintptr_t>(Wq) & 15) == 0;
+  if ((flags & (kFlagRingKernel | kFlagFloatX)) || M < 1 || M > 16 || N < 1 || G % 128 || K % 256 || K % G ||
+      (reinterpret_cast<uintptr_t>(Wq) & 15))
+    return false;
+  if (flags & kFlagStreamKernel) return true;
+  // Which kernel is faster, from measurements on the 7B-shaped and 70B-class linears (chained launches, weights from
+  // DRAM): one token always streams; two tokens unless the matrix is of the 70B class; three to eight tokens only on
+  // tall matrices with a short K (gate/up), where the staging of M x K activations per CTA stays small.
+  const long weights = (long)N * K;
+  if (M == 1) return true;
+  if (M == 2) return weights <= 160l << 20;
+  if (M <= 4) return K <= 4096 && N >= 8192;
+  if (M <= 8) return K <= 4096 && N >= 32768;
+  return false;
 }
 
 size_t gemv_stream_grid(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap) {
@@ -731,18 +854,16 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
   pl.q.Wq = static_cast<const uint32_t*>(Wq);
   const bool pdl = (flags & kFlagNoPdl) == 0;
   int rc;
-  if (pl.P == 4) {
-    rc = pl.RB == 2 ? launch_stream<1, 4, 2>(p, pl, pdl, stream) : launch_stream<1, 4, 1>(p, pl, pdl, stream);
+  if (!pl.one) {
+    rc = pl.RB == 2 ? launch_stream<1, 4, 2, false>(p, pl, pdl, stream) : launch_stream<1, 4, 1, false>(p, pl, pdl, stream);
+  } else if (pl.P == 4) {
+    rc = launch_stream<1, 4, 1, true>(p, pl, pdl, stream);
   } else {
     switch (pl.NT) {
-      case 1: rc = pl.RB == 2 ? launch_stream<1, 2, 2>(p, pl, pdl, stream) : launch_stream<1, 2, 1>(p, pl, pdl, stream); break;
-      case 2: rc = launch_stream<2, 2, 1>(p, pl, pdl, stream); break;
-      case 3: rc = launch_stream<3, 2, 1>(p, pl, pdl, stream); break;
-      case 4: rc = launch_stream<4, 2, 1>(p, pl, pdl, stream); break;
-      case 5: rc = launch_stream<5, 2, 1>(p, pl, pdl, stream); break;
-      case 6: rc = launch_stream<6, 2, 1>(p, pl, pdl, stream); break;
-      case 7: rc = launch_stream<7, 2, 1>(p, pl, pdl, stream); break;
-      default: rc = launch_stream<8, 2, 1>(p, pl, pdl, stream); break;
+      case 1: rc = launch_stream<1, 2, 1, true>(p, pl, pdl, stream); break;
+      case 2: rc = launch_stream<2, 2, 1, true>(p, pl, pdl, stream); break;
+      case 3: rc = launch_stream<3, 2, 1, true>(p, pl, pdl, stream); break;
+      default: rc = launch_stream<4, 2, 1, true>(p, pl, pdl, stream); break;
     }
   }
   if (rc != 0 || !p.sum_kernel) return rc;

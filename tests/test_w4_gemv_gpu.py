@@ -264,7 +264,9 @@ def test_random_shapes_property(kernels):
         K = G * j
         X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=seed)
         ref = oracle.w4_linear_f32(X, Wq, S, G)
-        check_bf16_output(run(kernels, X, Wq, S, G, which), ref, slack_for(G, which))
+        # G < 128: every weight is rounded to bf16 first (as on the reference's tensor-core path); with few rows the
+        # largest output is a small yardstick, so the reference's own gate (1e-2, bench/bench_w4a16.cu:120) applies
+        check_bf16_output(run(kernels, X, Wq, S, G, which), ref, 1e-2 if G % 128 else slack_for(G, which))
 
     prop()
     assert kernels.device_status() == 0
