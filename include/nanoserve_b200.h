@@ -65,33 +65,34 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
 
 /* ---- additions (no counterpart in the reference library) --------------------------------------- */
 
-/* Flags for b2_w4_linear. */
-#define B2_FLAG_FOLD_ZERO_POINT 1 /* GEMV with B2_FLAG_FLOAT_X: apply the -8 as one fp32 correction per 128-wide chunk */
+/*
+ * Flags for b2_w4_linear.  Two kernels serve the decode GEMV (M <= 16).  The streaming kernel (G % 128 == 0,
+ * K % 256 == 0, Wq 16-byte aligned) runs one token always, two tokens unless the matrix is of the 70B class, three to
+ * eight tokens on tall matrices with K <= 4096; it carries X as block fixed point per (token, 128-wide chunk of K) --
+ * 32 bits for M <= 2 (exact to fp32 summation order), 15 bits + sign above -- on an 8-bit integer mma.  The ring kernel
+ * runs everything else, with X as 16-bit block fixed point (every element off by at most 2^-16 of its chunk's largest
+ * magnitude) or as the flags below say.  Neither kernel measures anything or synchronises: every call is asynchronous.
+ */
+#define B2_FLAG_FOLD_ZERO_POINT 1 /* ring kernel with B2_FLAG_FLOAT_X: apply the -8 as one fp32 correction per 128-wide chunk */
 #define B2_FLAG_NO_SPLIT_K 2      /* GEMV: never split K across CTAs (uses no scratch memory) */
-#define B2_FLAG_NARROW_CTA 4      /* GEMV: 8 consumer warps per CTA instead of 16 */
-#define B2_FLAG_FLOAT_X 256       /* GEMV, G % 128 == 0: keep X in floating point (fp16 operands of a floating-point mma).
-                                     By default X is carried as 16-bit block fixed point per (token, 128-wide chunk of K)
-                                     -- every element is off by at most 2^-16 of its chunk's largest magnitude -- and the
-                                     nibbles feed an 8-bit integer mma without conversion */
-#define B2_FLAG_WIDE_X 512        /* GEMV, G % 128 == 0: 24-bit instead of 16-bit block fixed point for X */
-#define B2_FLAG_NO_AUTOTUNE 4096  /* GEMV (M <= 8): the first launch of a shape on a device, when its stream is not being
-                                     captured, times the five CTA shapes (8 / 14 / 16 consumer warps, one or two K chunks
-                                     per warp and stage) on the caller's operands -- under a millisecond, one stream
-                                     synchronisation -- and later launches use the fastest.  With this flag (or
-                                     B2_GEMV_AUTOTUNE=0 in the environment) the built-in cost model decides.  Warm a shape
-                                     up once before capturing it in a CUDA graph */
-#define B2_FLAG_PRE_STAGE_X 8192  /* GEMV, integer path: convert X to its fixed-point form once, in a small kernel launched in
-                                     front of the GEMV, and let every CTA copy its slice (default from M = 8 on, from M = 4 where
-                                     K >= 8192, and one of
-                                     the things the first-launch measurement tries from M = 2 on); ignored where it does
-                                     not apply (RMSNorm prologue, tensor-parallel consumer, B2_FLAG_FLOAT_X, M * K beyond
-                                     the staging area) */
-#define B2_FLAG_NO_PRE_STAGE_X 16384 /* GEMV: every CTA converts the slice of X it needs itself, at every M */
+#define B2_FLAG_NARROW_CTA 4      /* ring kernel: 8 consumer warps per CTA instead of 16 */
+#define B2_FLAG_FLOAT_X 256       /* GEMV, G % 128 == 0: keep X in floating point (fp16 operands of a floating-point mma, ring
+                                     kernel) instead of block fixed point */
+#define B2_FLAG_WIDE_X 512        /* ring kernel, G % 128 == 0: 24-bit instead of 16-bit block fixed point for X */
+#define B2_FLAG_NO_AUTOTUNE 4096  /* ring kernel: never time CTA shapes.  (Timing is off unless B2_GEMV_AUTOTUNE=1 is set in the
+                                     environment: it synchronises the stream on the first call of a shape, which a drop-in
+                                     for an asynchronous call must not do.  The built-in cost model decides otherwise.) */
+#define B2_FLAG_PRE_STAGE_X 8192  /* ring kernel, integer path: convert X to its fixed-point form once, in a small kernel launched
+                                     in front of the GEMV, and let every CTA copy its slice (default from M = 8 on, from M = 4
+                                     where K >= 8192); ignored where it does not apply (RMSNorm prologue, tensor-parallel
+                                     consumer, B2_FLAG_FLOAT_X, M * K beyond the staging area) */
+#define B2_FLAG_NO_PRE_STAGE_X 16384 /* ring kernel: every CTA converts the slice of X it needs itself, at every M */
 #define B2_FLAG_SPLIT_SUM_KERNEL 32768   /* GEMV with K split across CTAs: a small kernel behind the GEMV adds up the slices'
-                                           partial sums (the default where no measurement has decided; never for
-                                           tensor-parallel producers) */
-#define B2_FLAG_NO_SPLIT_SUM_KERNEL 65536 /* GEMV: the last CTA of a row group to arrive adds them up (a hand-shake of three
-                                           L2 round trips per tile, but no second kernel) */
+                                           partial sums (the default; never for tensor-parallel producers) */
+#define B2_FLAG_NO_SPLIT_SUM_KERNEL 65536 /* ring kernel: the last CTA of a row group to arrive adds them up (a hand-shake of
+                                           three L2 round trips per tile, but no second kernel) */
+#define B2_FLAG_RING_KERNEL 131072 /* GEMV: the ring kernel even where the streaming kernel would run */
+#define B2_FLAG_STREAM_KERNEL 524288 /* GEMV: the streaming kernel for every M <= 16 it can serve */
 #define B2_FLAG_NO_PDL 8          /* GEMV: plain launch.  By default the GEMV is launched with programmatic stream
                                      serialization: it may begin (weight prefetch only) while the previous kernel of
                                      the stream is still running, and touches X, Y and scratch only after that kernel
@@ -147,7 +148,9 @@ size_t b2_w4_gemv_scratch_bytes(int M, int N, int K, int G, int flags);
  * array inside the library's device image (8 MiB + 16.25 KiB per GPU that loads the library, held until
  * exit).  Limits: M * N <= 1048576 and N <= 131072, otherwise B2_ERR_TOO_LARGE.  All calls on a device
  * share the array: calls whose kernels overlap in time race, so keep them on one stream.  The first call
- * on a device looks up the array's address; make that call before any stream capture.
+ * on a device looks up the array's address, and the first call of a shape loads its kernel image; make those
+ * calls before any stream capture.  A device-side time-out of such a call is recorded in a status word inside the
+ * array; b2_device_status reports it (and b2_clear_status clears it) without allocating anything either.
  */
 int b2_w4_gemv_noalloc(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
                        void* stream);

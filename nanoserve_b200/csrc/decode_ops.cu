@@ -334,6 +334,11 @@ int rope_kv_store_launch(void* qkv, const void* bias, const void* inv_freq, cons
   if (Hq < 1 || Hk < 1 || D < 2 || D % 2 || D / 2 > 1024 || max_len < 1) return kErrBadShape;
   if (!qkv || !inv_freq || !pos || !cache_k || !cache_v) return kErrBadPointer;
   if (wait_sig != nullptr && !epoch) return kErrBadPointer;
+  // the kernel moves bf16 pairs: 4-byte alignment of the activations, the bias and the caches
+  if ((reinterpret_cast<uintptr_t>(qkv) & 3) || (reinterpret_cast<uintptr_t>(bias) & 3) ||
+      (reinterpret_cast<uintptr_t>(cache_k) & 3) || (reinterpret_cast<uintptr_t>(cache_v) & 3) ||
+      (reinterpret_cast<uintptr_t>(inv_freq) & 3) || (reinterpret_cast<uintptr_t>(pos) & 3))
+    return kErrBadPointer;
   const cudaError_t e = launch_pdl(rope_kv_store_kernel, dim3(Hq + 2 * Hk), dim3(D / 2), stream,
                                    static_cast<bf16*>(qkv), static_cast<const bf16*>(bias),
                                    static_cast<const float*>(inv_freq), static_cast<const int*>(pos),
@@ -363,6 +368,11 @@ int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v,
   if (Hq < 1 || Hk < 1 || Hq % Hk || Hq / Hk > 8 || max_len < 1) return b2::kErrBadShape;
   if (D != 128 && D != 64) return b2::kErrNotImplemented;
   if (!q || !cache_k || !cache_v || !pos || !out || !workspace) return b2::kErrBadPointer;
+  // 8-byte loads of q, 16-byte loads of the cache rows, float partials in the workspace
+  if ((reinterpret_cast<uintptr_t>(q) & 7) || (reinterpret_cast<uintptr_t>(cache_k) & 15) ||
+      (reinterpret_cast<uintptr_t>(cache_v) & 15) || (reinterpret_cast<uintptr_t>(out) & 1) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 3) || (reinterpret_cast<uintptr_t>(pos) & 3))
+    return b2::kErrBadPointer;
   const float scale = 1.f / sqrtf((float)D);
   const auto st = static_cast<cudaStream_t>(stream);
   float* part = static_cast<float*>(workspace);

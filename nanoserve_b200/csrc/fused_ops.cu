@@ -119,6 +119,10 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const __nv_bfloat16* __rest
   }
 }
 
+// The kernels above load and store 16 bytes at a time: a pointer that is not 16-byte aligned (a view into the middle
+// of a row) would fault on the device, so it is refused on the host instead.
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 unsigned blocks_for(size_t n, int block) {
   const size_t b = (n + block - 1) / block;
   return (unsigned)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
@@ -129,6 +133,7 @@ unsigned blocks_for(size_t n, int block) {
 int rmsnorm_launch(void* x, const void* r, const void* w, void* y, int T, int H, float eps, cudaStream_t s) {
   if (T < 1 || H < 8 || H % 8) return kErrBadShape;
   if (!x || !w || !y) return kErrBadPointer;
+  if (!aligned16(x) || !aligned16(r) || !aligned16(w) || !aligned16(y)) return kErrBadPointer;
   const int threads = H >= 4096 ? 512 : 256;
   rmsnorm_kernel<<<T, threads, 0, s>>>(static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(r),
                                        static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), H,
@@ -140,6 +145,7 @@ int rope_launch(void* q, void* k, const void* inv_freq, int T, int Hq, int Hk, i
                 long long q_stride, long long k_stride, cudaStream_t s) {
   if (T < 1 || D < 16 || D % 16 || Hq < 0 || Hk < 0 || q_stride % 8 || k_stride % 8) return kErrBadShape;
   if (!q || !k || !inv_freq) return kErrBadPointer;
+  if (!aligned16(q) || !aligned16(k) || (reinterpret_cast<uintptr_t>(inv_freq) & 3)) return kErrBadPointer;
   const size_t total = (size_t)T * (Hq + Hk) * (D / 16);
   rope_kernel<<<blocks_for(total, 256), 256, 0, s>>>(static_cast<__nv_bfloat16*>(q),
                                                      static_cast<__nv_bfloat16*>(k),
@@ -151,6 +157,7 @@ int rope_launch(void* q, void* k, const void* inv_freq, int T, int Hq, int Hk, i
 int swiglu_launch(const void* gate, const void* up, void* out, int T, int I, cudaStream_t s) {
   if (T < 1 || I < 1 || ((long long)T * I) % 8) return kErrBadShape;  // reference: -1 (nanoserve_ops.cu:39)
   if (!gate || !up || !out) return kErrBadPointer;
+  if (!aligned16(gate) || !aligned16(up) || !aligned16(out)) return kErrBadPointer;
   const size_t n8 = (size_t)T * I / 8;
   swiglu_kernel<<<blocks_for(n8, 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(gate),
                                                     static_cast<const __nv_bfloat16*>(up),

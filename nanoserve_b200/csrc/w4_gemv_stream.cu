@@ -628,24 +628,37 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
     __syncthreads();
     const int slice = blockIdx.y;
     const int half_mp = MP >> 1;
-    for (int idx = tid; idx < p.M * rows_cta; idx += kThreads) {
-      const int m = idx / rows_cta, r = idx - m * rows_cta;
-      const int tile = r / kRows, rr = r - tile * kRows;
-      float sum = 0.f;
-      for (int s = 0; s < q.ks; ++s) {
-        const float* src = red + ((tile * q.ks + s) * kSlots) * kRows + rr;
+    // a thread sums four consecutive rows of one token: 16-byte partial-sum stores, 8-byte output stores (also into
+    // the peers' gathered rows, where two-byte stores over NVLink are dear)
+    const int quads = (rows_cta + 3) >> 2;
+    for (int idx = tid; idx < p.M * quads; idx += kThreads) {
+      const int m = idx / quads, r0 = (idx - m * quads) * 4;
+      float f[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int h = 0; h < (ONE ? 1 : 2); ++h)
+      for (int i = 0; i < 4; ++i) {
+        const int r = min(r0 + i, rows_cta - 1);
+        const int tile = r / kRows, rr = r - tile * kRows;
+        for (int s = 0; s < q.ks; ++s) {
+          const float* src = red + ((tile * q.ks + s) * kSlots) * kRows + rr;
 #pragma unroll
-          for (int j = 0; j < P / 2; ++j) sum += src[(h * half_mp + ((m * P) >> 1) + j) * kRows];
+          for (int h = 0; h < (ONE ? 1 : 2); ++h)
+#pragma unroll
+            for (int j = 0; j < P / 2; ++j) f[i] += src[(h * half_mp + ((m * P) >> 1) + j) * kRows];
+        }
       }
-      const int n = row0 + r;
-      if (p.nslices > 1)
-        __stcg(p.partial + ((size_t)slice * p.M + m) * p.N + n, sum);
-      else if (p.tp.world)
-        tp_store(p.tp, m, n, __float2bfloat16(sum));
-      else
-        p.Y[(size_t)m * p.N + n] = __float2bfloat16(sum);
+      const int n0 = row0 + r0;
+      if (p.nslices > 1) {
+        float* d = p.partial + ((size_t)slice * p.M + m) * p.N + n0;
+        if ((p.N & 3) == 0 && n0 + 3 < p.N) {
+          __stcg(reinterpret_cast<float4*>(d), make_float4(f[0], f[1], f[2], f[3]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (n0 + i < p.N) __stcg(d + i, f[i]);
+        }
+      } else {
+        store_out4(p, m, n0, make_float4(f[0], f[1], f[2], f[3]));
+      }
     }
     if (p.tp.world) {
       __syncthreads();

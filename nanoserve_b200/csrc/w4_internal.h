@@ -75,11 +75,12 @@ struct GemvPrologue {
 // Tensor parallelism over the output rows, with the all-gather fused into the GEMV (all fields zero: off).
 // Producer side (world > 0): every output value is stored into the gathered row [M, ld] of EVERY rank through
 // peer-mapped pointers -- local column n goes to column seg_dst[i] + (n - start of piece i), the local shard being up
-// to three row-concatenated pieces ending at seg_end[0], seg_end[1], N -- and each CTA, after its last store, adds one
-// to an arrival counter on every rank (release, system scope).
+// to three row-concatenated pieces ending at seg_end[0], seg_end[1], N -- and the launch, after its last store, adds
+// one to an arrival counter on every rank (release, system scope).
 // Consumer side (wait_sig != null): before it reads X the kernel waits (bounded; a time-out sets the device status)
-// until its own rank's counter has reached (*epoch + 1) * wait_per_epoch, where wait_per_epoch is the number of CTAs
-// that count in per use (ranks x grid of the producing launch) and *epoch counts completed uses (the decode step).
+// until its own rank's counter has reached (*epoch + 1) * wait_per_epoch, where wait_per_epoch is the number of
+// signals per use of the counter -- ONE per producing launch and rank, sent by the launch's last CTA after every CTA
+// has counted itself in on a device-scope counter -- and *epoch counts completed uses (the decode step).
 // Counters only ever grow.
 constexpr int kMaxTpRanks = 8;
 struct GemvTp {

@@ -62,7 +62,11 @@ int quantize_launch(const void* W, void* Wq, void* S, int N, int K, int G, cudaS
   // 16-byte loads of W need 16-byte aligned rows and groups: K % 8 == 0 follows from G % 32 == 0
   if (reinterpret_cast<uintptr_t>(W) & 15) return kErrBadPointer;
   const size_t groups = (size_t)N * (K / G);
-  const size_t blocks = std::min<size_t>((groups + 7) / 8, 148 * 32);
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+    return kErrDevice;
+  const size_t blocks = std::min<size_t>((groups + 7) / 8, (size_t)sms * 32);  // grid-stride: 32 CTAs per SM at most
   w4_quantize_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(W),
                                                           static_cast<uint32_t*>(Wq),
                                                           static_cast<__nv_bfloat16*>(S), N, K, G);

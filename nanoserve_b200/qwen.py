@@ -352,10 +352,13 @@ class Qwen2Runner:
     def generate(self, prompt_ids: torch.Tensor, n_new: int, use_graph: bool = True) -> List[int]:
         """Greedy decoding.  Returns the generated ids (list), as the reference's generate does (qwen.py:166-178)."""
         assert prompt_ids.shape[0] + n_new <= self.max_len
-        if use_graph and self.graph is None:
-            self.prefill(prompt_ids)
-            self.capture()
+        # Everything runs on the runner's own stream: split-K launches of one device share scratch memory and arrival
+        # counters, so a prefill on the caller's stream must never overlap the warm-up steps of capture().
         with torch.cuda.stream(self.stream):
+            if use_graph and self.graph is None:
+                self.prefill(prompt_ids)
+                torch.cuda.synchronize()
+                self.capture()
             self.prefill(prompt_ids)
             for _ in range(n_new - 1):
                 if use_graph:
@@ -363,7 +366,15 @@ class Qwen2Runner:
                 else:
                     self.decode_step()
         torch.cuda.synchronize()
+        self.check_status()
         return self.tokens[:n_new].tolist()
+
+    def check_status(self):
+        """Raises if a kernel gave up on a bounded wait (a ring slot, a tensor-parallel arrival counter): the tokens
+        generated since the last check are then meaningless."""
+        rc = self.k.device_status()
+        if rc != 0:
+            raise RuntimeError(f"device status {rc}: a kernel reported a time-out during decoding")
 
 
 def decode_rate(kernels: Kernels, device, rank: int = 0, world: int = 1, cfg: Optional[Qwen2Config] = None,
@@ -389,6 +400,7 @@ def decode_rate(kernels: Kernels, device, rank: int = 0, world: int = 1, cfg: Op
             r.graph.replay()
         e2.record(r.stream)
     torch.cuda.synchronize()
+    r.check_status()
     t_prefill, t_decode = e0.elapsed_time(e1) * 1e-3, e1.elapsed_time(e2) * 1e-3
     tokens = r.tokens[:n_new].tolist()
     import hashlib

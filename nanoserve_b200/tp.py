@@ -177,16 +177,19 @@ class ShardedLayer:
                                               pieces=pieces, **wait)
             prev = b
 
-    def decode_pass_fused4(self, x: torch.Tensor, act: torch.Tensor) -> List[torch.Tensor]:
+    def decode_pass_fused4(self, x: torch.Tensor, act: torch.Tensor,
+                           outs: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
         """One pass as four launches: q|k|v, o, gate|up take ``x``; down takes ``act``.  Returns the four full-width
-        outputs [M, nq + 2 nkv], [M, hidden], [M, 2 I], [M, hidden]."""
+        outputs [M, nq + 2 nkv], [M, hidden], [M, 2 I], [M, hidden] (written into ``outs`` when given, single GPU)."""
         k = self.kernels
-        outs = []
         if self.peer is None:
-            for fname, _ in self.FUSED:
+            res = []
+            for i, (fname, _) in enumerate(self.FUSED):
                 Wq, S = self.fused[fname]
-                outs.append(k.w4_linear(act if fname == "down" else x, Wq, S, self.G, flags=self.flags))
-            return outs
+                res.append(k.w4_linear(act if fname == "down" else x, Wq, S, self.G, flags=self.flags,
+                                       out=None if outs is None else outs[i]))
+            return res
+        outs = []
         peer = self.peer
         for fname, _ in self.FUSED:
             Wq, S = self.fused[fname]

@@ -19,11 +19,15 @@ REF_LIB_PATH = os.path.join(_HERE, "_ref", "libnanoserve_ref.so")
 _lib = None
 
 
-def build(with_ref: bool = False) -> None:
-    """Compile the C oracle (and, if asked and the reference checkout exists, the reference .so)."""
+def build(with_ref: bool = False, ref_root: str = "") -> None:
+    """Compile the C oracle and, if asked, the reference's own library from the checkout at `ref_root` (or at
+    NANOSERVE_REFERENCE_ROOT in the environment)."""
     subprocess.check_call(["make", "-s", "-C", _HERE])
     if with_ref:
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref"])
+        root = ref_root or os.environ.get("NANOSERVE_REFERENCE_ROOT", "")
+        if not root:
+            raise RuntimeError("the reference checkout's location is not given (NANOSERVE_REFERENCE_ROOT)")
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF_ROOT={root}"])
 
 
 def lib():

@@ -27,7 +27,9 @@ from tests.util import bits_to_torch, torch_to_bits, torch_to_u32, u32_to_torch 
 
 
 def main():
-    out_dir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <output directory>")
+    out_dir = sys.argv[1]
     os.makedirs(out_dir, exist_ok=True)
     ref = ctypes.CDLL(oracle.REF_LIB_PATH)
     vp, i32 = ctypes.c_void_p, ctypes.c_int
