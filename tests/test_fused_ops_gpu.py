@@ -52,6 +52,68 @@ def test_rope_and_swiglu(kernels):
         kernels.swiglu(a[:1, :4].contiguous(), b[:1, :4].contiguous())  # T*I % 8 (csrc/nanoserve_ops.cu:39)
 
 
+def _reference_kernels():
+    """The reference's own library (its C-ABI source built unchanged for sm_100a by oracle/Makefile) behind this
+    repository's binding class: the live checker for the three element-wise operators."""
+    import os
+    import oracle
+    from nanoserve_b200.ops import Kernels
+    if not os.path.exists(oracle.REF_LIB_PATH):
+        pytest.skip("reference library not built (oracle/_ref/libnanoserve_ref.so)")
+    return Kernels(oracle.REF_LIB_PATH)
+
+
+@pytest.mark.parametrize("T,H", [(1, 3584), (7, 512), (3, 8192)])
+def test_rmsnorm_rope_swiglu_against_the_reference_kernels(kernels, T, H):
+    """Same inputs through the reference's ns_rmsnorm / ns_rope / ns_swiglu (kernels/fused/*.cuh behind
+    csrc/nanoserve_ops.cu:21-45) and through this library's.  Both compute in fp32 and round once to bf16; the
+    summation order of the norm's sum of squares differs, so the bound is one bf16 ulp of the value plus 1e-3 absolute;
+    the residual stream (bf16(x + r), an exact operation) must be bit-identical."""
+    ref = _reference_kernels()
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    r = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).to(torch.bfloat16)
+
+    def near(a, b):
+        a, b = a.float(), b.float()
+        return bool(torch.all((a - b).abs() <= torch.maximum(a.abs(), b.abs()) * 2.0**-7 + 1e-3))
+
+    for res in (None, r):
+        xa, xb = x.clone(), x.clone()
+        ya, yb = kernels.rmsnorm(xa, res, w, 1e-6), ref.rmsnorm(xb, res, w, 1e-6)
+        assert near(ya, yb) and torch.equal(xa, xb)
+    D, Hq, Hk = 128, H // 128, max(1, H // 512)
+    if H % 128 == 0:
+        q = torch.randn(T, Hq * D, device="cuda", generator=g).to(torch.bfloat16)
+        k = torch.randn(T, Hk * D, device="cuda", generator=g).to(torch.bfloat16)
+        inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+        qa, ka, qb, kb = q.clone(), k.clone(), q.clone(), k.clone()
+        kernels.rope(qa, ka, inv, Hq, Hk, D, 37)
+        ref.rope(qb, kb, inv, Hq, Hk, D, 37)
+        assert near(qa, qb) and near(ka, kb)
+    a = (3 * torch.randn(T, H, device="cuda", generator=g)).to(torch.bfloat16)
+    b = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    assert near(kernels.swiglu(a, b), ref.swiglu(a, b))
+    torch.cuda.synchronize()
+
+
+def test_misaligned_pointers_are_refused_not_faulted(kernels):
+    """The element-wise kernels move 16 bytes at a time: a view that starts in the middle of a row is refused with -4
+    on the host (nothing is launched) instead of faulting on the device."""
+    lib = kernels.lib
+    t = torch.zeros(4096, dtype=torch.bfloat16, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = t.data_ptr()
+    assert lib.ns_rmsnorm(p + 2, None, p, p, 1, 64, 1e-6, st) == -4
+    assert lib.ns_rmsnorm(p, p + 4, p, p, 1, 64, 1e-6, st) == -4
+    assert lib.ns_swiglu(p, p + 8, p, 1, 64, st) == -4
+    assert lib.ns_rope(p + 2, p, p, 1, 1, 1, 64, 0, 64, 64, st) == -4
+    assert lib.b2_decode_attention(p + 2, p, p, p, p, p, 4, 2, 128, 16, st) == -4
+    torch.cuda.synchronize()
+    assert kernels.device_status() == 0
+
+
 def test_flash_fwd_is_reported_as_not_implemented(kernels):
     q = torch.zeros(64, 128, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError, match="ns_flash_fwd failed with code -3"):
