@@ -93,6 +93,9 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
                                            three L2 round trips per tile, but no second kernel) */
 #define B2_FLAG_RING_KERNEL 131072 /* GEMV: the ring kernel even where the streaming kernel would run */
 #define B2_FLAG_STREAM_KERNEL 524288 /* GEMV: the streaming kernel for every M <= 16 it can serve */
+#define B2_FLAG_GEMM_WHOLE_TILES 1073741824 /* prefill GEMM (M > 16): every CTA takes whole output tiles; by default the CTAs
+                                           take equal shares of the (tile, K block) pairs and tiles that several CTAs cover
+                                           are finished from fp32 part-tiles in the scratch */
 #define B2_FLAG_NO_PDL 8          /* GEMV: plain launch.  By default the GEMV is launched with programmatic stream
                                      serialization: it may begin (weight prefetch only) while the previous kernel of
                                      the stream is still running, and touches X, Y and scratch only after that kernel
@@ -100,10 +103,10 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
 
 /*
  * Sets up the calling thread's current device: queries the SM count and allocates the per-device scratch
- * (split-K partial sums, arrival counters, the staged X of a launch, a status word; 68 MiB + 256 KiB).  ns_w4_linear does this on
+ * (split-K partial sums, arrival counters, the staged X of a launch, a status word; 100 MiB + 256 KiB).  ns_w4_linear does this on
  * its first call on a device; call b2_init first when that first call would fall inside a CUDA-graph
- * capture.  Launches on different streams of one device share the scratch: split-K launches that overlap
- * in time race (shapes that fill the GPU without split-K never touch it).
+ * capture.  Launches on different streams of one device share the scratch: launches that use it (split-K GEMVs, GEMMs whose
+ * tile count is not a multiple of the SM count) race when they overlap in time.
  */
 int b2_init(void);
 

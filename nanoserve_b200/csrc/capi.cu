@@ -13,7 +13,7 @@
 namespace {
 
 constexpr int kMaxDevices = 64;
-constexpr size_t kPartialBytes = 64ull << 20;  // split-K partial sums
+constexpr size_t kPartialBytes = 96ull << 20;  // split-K partial sums (GEMM: two 256 KB part-tiles per SM)
 constexpr int kCounters = 1 << 16;             // one per 32-row group: N up to 2 M rows
 constexpr size_t kXStageBytes = 4ull << 20;    // X of a GEMV launch in its staged form: M * K up to 1.8 M values
 

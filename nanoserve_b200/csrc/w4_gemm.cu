@@ -5,7 +5,13 @@
 // multiples of 128 only.  Same numerics: each weight is dequantised to RN_bf16((q - 8) * s)
 // (w4a16.cuh:196-197), the contraction accumulates in fp32, one rounding to bf16 at the store.
 //
-// Design (tensor-bound; one CTA per SM, one output tile per CTA):
+// Design (tensor-bound; one CTA per SM, one work item per CTA):
+//   work     the output tiles in row-major order with the token tile fastest.  As many whole waves of tiles as
+//            there are (tile count rounded down to a multiple of the SM count) are one item each; the tiles of the
+//            last, partial wave may be split along K into several items each, which run as SMs come free, so the
+//            tail of a launch is a fraction of a tile's time instead of a whole one (3584 x 18944 at M = 8192 has
+//            448 tiles on 148 SMs: 3.03 waves).  The last item of a split tile to arrive adds the fp32 part-tiles
+//            in split order (deterministic, nobody waits for anybody).
 //   tile     MI x 128 tokens by 256 output features, K walked in blocks of 64
 //   warp 0   TMA producer: per K block, the X tile(s) (128 rows x 128 B, 128-byte swizzle) and the packed
 //            weight tile (256 rows x 32 B) land in a ring stage; completion counted on an mbarrier
@@ -51,8 +57,11 @@ struct GemmParams {
   __nv_bfloat16* Y;
   int M, N, K, G, KG;
   int nkb;  // K blocks of 64
-  int ksplit;       // CTAs sharing one output tile along K (grid.z)
-  float* partial;   // [ksplit][tile][MI*256 columns][128 rows] fp32, split-K only
+  int tiles_x;      // token tiles (fastest in the tile order)
+  int n_whole;      // the first n_whole tiles are one work item each
+  int n_tail;       // the remaining tiles are tail_ks items each: item n_whole + z * n_tail + t = split z of tile t
+  int tail_ks;
+  float* partial;   // [tail_ks][n_tail][MI*256 columns][128 rows] fp32, split tiles only
   int* counters;    // one arrival counter per output tile, zero between launches
   int* status;
 };
@@ -90,11 +99,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   // token tiles vary fastest over the CTAs that run together: they then read many different X tiles and few
   // weight tiles at a time, which spreads the L2 traffic (74 CTAs pulling the same X tile at once made a few L2
   // slices the bottleneck)
-  const int m0 = blockIdx.x * (128 * MI);
-  const int n0 = blockIdx.y * kBN;
-  // this CTA's share of the K blocks (split-K: grid.z CTAs per output tile)
-  const int kb_per = (p.nkb + p.ksplit - 1) / p.ksplit;
-  const int kb0 = blockIdx.z * kb_per;
+  // (the hardware starts CTAs in index order, so the split tiles of the tail run last)
+  const int item = blockIdx.x;
+  const bool split = item >= p.n_whole;
+  const int tail_t = split ? (item - p.n_whole) % p.n_tail : 0;   // tile of the tail
+  const int tail_z = split ? (item - p.n_whole) / p.n_tail : 0;   // which K range of it
+  const int tile = split ? p.n_whole + tail_t : item;
+  const int ksplit = split ? p.tail_ks : 1;
+  const int m0 = (tile % p.tiles_x) * (128 * MI);
+  const int n0 = (tile / p.tiles_x) * kBN;
+  // this CTA's share of the K blocks
+  const int kb_per = (p.nkb + ksplit - 1) / ksplit;
+  const int kb0 = tail_z * kb_per;
   const int nkb = max(0, min(p.nkb, kb0 + kb_per) - kb0);
 
   if (tid == 0) {
@@ -242,8 +258,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int col_end = col_begin + (MI == 2 ? kBN / 2 : kBN / 4);
       const int m = m0 + mi * 128 + quad * 32 + lane;
       const bool vec_ok = (p.N % 8) == 0;
-      const bool split = p.ksplit > 1;
-      const int ntiles = gridDim.x * gridDim.y, tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+      const bool parts = ksplit > 1;
+      const int ntiles = p.n_tail, tile_id = tail_t;
       for (int c0 = col_begin; c0 < col_end; c0 += 32) {
         uint32_t v[32];
         if (nkb > 0) {
@@ -253,10 +269,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
           for (int e = 0; e < 32; ++e) v[e] = 0u;  // a split with no K blocks contributes zeros
         }
-        if (split) {
+        if (parts) {
           // fp32 partial of this (split, tile), stored column-major inside the tile (row fastest): for a given
           // column the 32 lanes of a warp write 32 consecutive floats
-          float* pt = p.partial + ((size_t)blockIdx.z * ntiles + tile_id) * (size_t)(MI * 128 * kBN) +
+          float* pt = p.partial + ((size_t)tail_z * ntiles + tile_id) * (size_t)(MI * 128 * kBN) +
                       (size_t)(mi * kBN + c0) * 128 + quad * 32 + lane;
 #pragma unroll
           for (int e = 0; e < 32; ++e) __stcg(pt + e * 128, __uint_as_float(v[e]));
@@ -284,16 +300,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       }
-      if (split) {
+      if (parts) {
         // the last of the ksplit CTAs of this tile to arrive sums the partials in split order (deterministic;
         // nobody waits for anybody) and stores bf16
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"r"(kDequantThreads) : "memory");
         int* flag = reinterpret_cast<int*>(gen_base + geo::kBarOffset + 28 * 8);
         if (tid == 64) {
-          int* ctr = p.counters + blockIdx.y * gridDim.x + blockIdx.x;
+          int* ctr = p.counters + tile_id;
           const int old = atomicAdd(ctr, 1);
-          const int last = old == p.ksplit - 1;
+          const int last = old == ksplit - 1;
           if (last) *ctr = 0;
           *flag = last;
         }
@@ -304,7 +320,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             float sum[32];
 #pragma unroll
             for (int e = 0; e < 32; ++e) sum[e] = 0.f;
-            for (int z = 0; z < p.ksplit; ++z) {
+            for (int z = 0; z < ksplit; ++z) {
               const float* pt = p.partial + ((size_t)z * ntiles + tile_id) * (size_t)(MI * 128 * kBN) +
                                 (size_t)(mi * kBN + c0) * 128 + quad * 32 + lane;
 #pragma unroll
@@ -356,7 +372,7 @@ int launch_gemm(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& 
   cudaError_t e =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmGeo<MI>::kSmemBytes);
   if (e != cudaSuccess) return (int)e;
-  const dim3 grid((p.M + 128 * MI - 1) / (128 * MI), (p.N + kBN - 1) / kBN, p.ksplit);
+  const dim3 grid(p.n_whole + p.n_tail * p.tail_ks);
   kernel<<<grid, kGemmThreads, GemmGeo<MI>::kSmemBytes, stream>>>(tx, tw, p);
   return (int)cudaGetLastError();
 }
@@ -365,7 +381,6 @@ int launch_gemm(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& 
 
 int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
                 const Workspace& ws, int flags, int sm_count, cudaStream_t stream) {
-  (void)flags;
   static_assert(GemmGeo<2>::kSmemBytes <= kGemmSmemLimit && GemmGeo<1>::kSmemBytes <= kGemmSmemLimit, "smem");
   if (M < 1) return kErrUnsupportedM;
   if (N < 1 || K < 32 || G < 32 || K % 32 || G % 32 || K % G) return kErrBadShape;
@@ -390,28 +405,36 @@ int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, in
   p.KG = K / G;
   p.nkb = (K + kBK - 1) / kBK;
   p.status = ws.status;
-  // Split K when the output tiles alone leave SMs idle (e.g. the 3584 x 18944 projection at M = 512 has 28
-  // tiles): pick the split whose makespan in K blocks is smallest, charging a split its fp32 round trip.
+  // Whole waves of tiles run one tile per CTA.  The tiles of the last, partial wave are split along K when that
+  // shortens it: pick the split whose makespan in K blocks is smallest, charging a split its fp32 round trip
+  // (e.g. the 3584 x 18944 projection: 28 tiles at M = 512 run as 5 splits each; at M = 8192 the 4 tiles that
+  // 3 waves of 148 leave over run as 8 splits each instead of a fourth wave).
   {
     const int mi = M <= 128 ? 1 : 2;
-    const long tiles = (long)((M + 128 * mi - 1) / (128 * mi)) * ((N + kBN - 1) / kBN);
+    p.tiles_x = (M + 128 * mi - 1) / (128 * mi);
+    const long tiles = (long)p.tiles_x * ((N + kBN - 1) / kBN);
+    if (tiles > 0x3fffffff) return kErrBadShape;
     const int sms = std::max(1, sm_count);
+    const long n_tail = tiles % sms ? tiles % sms : std::min<long>(tiles, sms);
     long best_cost = -1;
     int best = 1;
     for (int ks = 1; ks <= 8; ++ks) {
-      if (ks > 1 && (!ws.partial || !ws.counters || (size_t)ks * tiles * (size_t)(mi * 128 * kBN) * sizeof(float) > ws.partial_bytes ||
-                     tiles > ws.n_counters || p.nkb / ks < 8))
+      if (ks > 1 && ((flags & kFlagGemmWholeTiles) || !ws.partial || !ws.counters ||
+                     (size_t)ks * n_tail * (size_t)(mi * 128 * kBN) * sizeof(float) > ws.partial_bytes ||
+                     n_tail > ws.n_counters || p.nkb / ks < 8))
         break;
-      const long waves = (tiles * ks + sms - 1) / sms;
+      const long waves = (n_tail * ks + sms - 1) / sms;
       const long cost = waves * ((p.nkb + ks - 1) / ks + (ks > 1 ? 6 + 2 * ks : 4));
       // a split must win by a margin: its fp32 partials cost memory traffic the model only roughly accounts for
-      // (measured: 3584 x 18944 at M = 512 goes from 267 to 747 TFLOP/s with 5 splits, M = 8192 gains 8 % with 2)
+      // (measured: 3584 x 18944 at M = 512 goes from 267 to 747 TFLOP/s with 5 splits)
       if (best_cost < 0 || cost * 100 < best_cost * (best == 1 ? 95 : 100)) {
         best_cost = cost;
         best = ks;
       }
     }
-    p.ksplit = best;
+    p.n_tail = (int)n_tail;
+    p.n_whole = (int)(tiles - n_tail);
+    p.tail_ks = best;
     p.partial = ws.partial;
     p.counters = ws.counters;
   }

@@ -28,6 +28,7 @@ FLAG_NO_PRE_STAGE_X = 16384
 FLAG_SPLIT_SUM_KERNEL = 32768
 FLAG_NO_SPLIT_SUM_KERNEL = 65536
 FLAG_RING_KERNEL = 131072    # decode GEMV: the shared-memory ring kernel even where the streaming kernel applies
+FLAG_GEMM_WHOLE_TILES = 1 << 30  # prefill GEMM: every CTA takes whole output tiles (no fp32 part-tiles)
 FLAG_STREAM_KERNEL = 524288  # decode GEMV: the streaming kernel for every M <= 16 it can serve (default: M <= 2)
 
 # Every symbol include/nanoserve_b200.h declares, with its ctypes signature.

@@ -109,6 +109,30 @@ def test_split_k_shapes(kernels, M, N, K):
     assert kernels.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1024, 3584, 1024), (700, 1300, 1536), (3000, 3584, 3584), (100, 5000, 4096)])
+def test_split_tail_wave(kernels, M, N, K):
+    """Tile counts that are not a multiple of the SM count: the tiles of the last, partial wave are split along K and
+    finished from fp32 part-tiles, the whole waves before them are not.  The result must not depend on which CTA
+    came last (two launches equal), must match the oracle, and must agree with the whole-tile schedule to fp32
+    noise."""
+    from nanoserve_b200.ops import FLAG_GEMM_WHOLE_TILES
+    G = 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=21)
+    a = run(kernels, X, Wq, S, G)
+    b = run(kernels, X, Wq, S, G)
+    assert np.array_equal(a, b)
+    w = torch_to_bits(kernels.w4_linear(bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S), G,
+                                        flags=FLAG_GEMM_WHOLE_TILES))
+    rows = np.unique(np.concatenate([[0, 127, 128, 255, 256, M - 1], np.random.default_rng(3).integers(0, M, 10)]))
+    rows = rows[rows < M]
+    ref = rounded_weight_reference(X[rows], Wq, S, G)
+    check_bf16_output(a[rows], ref, 3e-5)
+    check_bf16_output(w[rows], ref, 3e-5)
+    fa, fw = oracle.bf16_bits_to_f32(a), oracle.bf16_bits_to_f32(w)
+    assert np.all(np.abs(fa - fw) <= np.abs(fw) * 2.0**-7 + 1e-4 * np.abs(fw).max())
+    assert kernels.device_status() == 0
+
+
 def test_x_doubling_is_exact(kernels):
     M, N, K, G = 256, 512, 1024, 128
     X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=4)
