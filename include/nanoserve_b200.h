@@ -166,6 +166,16 @@ int b2_w4_gemv_noalloc(const void* X, const void* Wq, const void* S, void* Y, in
  *     the q and k heads at position *pos, k and v written to cache_k / cache_v [Hk, max_len, D] at that position.
  *   b2_decode_attention: out [Hq*D] = softmax(q K^T / sqrt(D)) V over cache positions 0..*pos (D = 64 or 128);
  *     two launches (32 key slices per KV head, then a merge).
+ *   b2_decode_attention_fused: both of the above with the RoPE / KV-store launch folded into the attention pass.
+ *     qkv is read, not modified: every CTA rotates the query heads it serves in registers; the CTA whose key slice
+ *     holds position *pos builds the new k and v rows, stores them to the caches and uses them from shared memory.
+ *     flags 0: the merge of the key slices is a second launch (two launches in all; the faster form: 9.0 -> about
+ *     7 us per layer at 600 positions).  flags 1: ONE launch; the last CTA of a KV head to finish merges the slices
+ *     (an arrival counter per KV head; nobody waits), which puts a fence, an atomic and the merge's two L2 round
+ *     trips behind the slowest CTA.  Results are bit-identical to the two calls above either way.
+ *     workspace: b2_decode_attention_fused_workspace_bytes(Hq, Hk, D) bytes, ZEROED once by the caller (the counters
+ *     at its end return to zero after every launch).  wait_sig / epoch / wait_per_epoch: NULL / NULL / 0, or the
+ *     arrival counter of the tensor-parallel GEMV that produced qkv (see b2_w4_linear_tp): the kernel waits on it.
  *   b2_greedy_next: token = argmax(logits[0..V)) (lowest index on ties); out_tokens[*step] = token; *step += 1;
  *     *pos += 1; x_next[0..H) = embed[token].  pos, step: int32 on the device; out_tokens: int64 on the device.
  */
@@ -173,6 +183,11 @@ int b2_rope_kv_store(void* qkv, const void* bias, const void* inv_freq, const vo
                      int Hq, int Hk, int D, int max_len, void* stream);
 int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v, const void* pos, void* out,
                         void* workspace, int Hq, int Hk, int D, int max_len, void* stream);
+size_t b2_decode_attention_fused_workspace_bytes(int Hq, int Hk, int D);
+int b2_decode_attention_fused(const void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
+                              void* cache_v, void* out, void* workspace, int Hq, int Hk, int D, int max_len,
+                              const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int flags,
+                              void* stream);
 int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* pos, void* out_tokens, void* step,
                    void* x_next, void* workspace, void* stream);
 /*
@@ -180,7 +195,7 @@ int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* po
  * reference library: the reference runs F.linear on the bf16 lm_head and argmax over the logits on the host side of
  * the step (python/nanoserve/qwen.py:164,174-177).
  *   b2_lm_head: logits[M, V] (bf16; may be NULL when only the argmax is wanted) = X[M, K] . W[V, K]^T, fp32
- *     accumulation, 1 <= M <= 8, K % 32 == 0.  prologue / R / Wn / eps / Xout as in b2_w4_linear_fused (0 or 1: the
+ *     accumulation, 1 <= M <= 8, K % 64 == 0.  prologue / R / Wn / eps / Xout as in b2_w4_linear_fused (0 or 1: the
  *     model's final add + RMSNorm folded in).  If part_max / part_idx are not NULL, entry b of them receives the
  *     largest bf16 logit of token 0 among rows [128 b, 128 b + 128) and its row index + idx_offset (lowest index on
  *     ties); b2_lm_head_blocks(V) entries each.  A rank that holds a slice of the vocabulary passes its first row

@@ -65,6 +65,17 @@ DeviceState* device_state_if_ready(int* dev_out) {
   return g_dev[dev].ready.load(std::memory_order_acquire) ? &g_dev[dev] : nullptr;
 }
 
+}  // namespace
+
+namespace b2 {
+int* device_status_word(int* rc) {
+  DeviceState* st = device_state(rc);
+  return st ? st->ws.status : nullptr;
+}
+}  // namespace b2
+
+namespace {
+
 int linear_dispatch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
                     int flags, void* stream) {
   if (M < 1) return b2::kErrUnsupportedM;
@@ -97,7 +108,8 @@ int b2_w4_linear_fused(const void* X, const void* Wq, const void* S, void* Y, in
   DeviceState* st = device_state(&rc);
   if (!st) return rc;
   b2::GemvPrologue pro;
-  pro.kind = prologue;
+  pro.kind = prologue & 0xFF;
+  pro.epilogue = (prologue >> 8) & 0xFF;
   pro.R = R;
   pro.Wn = Wn;
   pro.Xout = Xout;
@@ -115,7 +127,8 @@ int b2_w4_linear_tp(const void* X, const void* Wq, const void* S, int M, int N, 
   DeviceState* st = device_state(&rc);
   if (!st) return rc;
   b2::GemvPrologue pro;
-  pro.kind = prologue;
+  pro.kind = prologue & 0xFF;
+  pro.epilogue = (prologue >> 8) & 0xFF;
   pro.R = R;
   pro.Wn = Wn;
   pro.Xout = Xout;
@@ -162,6 +175,22 @@ int b2_rope_kv_store_tp(void* qkv, const void* bias, const void* inv_freq, const
   if (!st) return rc;
   return b2::rope_kv_store_launch(qkv, bias, inv_freq, pos, cache_k, cache_v, Hq, Hk, D, max_len, wait_sig, epoch,
                                   wait_per_epoch, st->ws.status, static_cast<cudaStream_t>(stream));
+}
+
+int b2_decode_attention_fused(const void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
+                              void* cache_v, void* out, void* workspace, int Hq, int Hk, int D, int max_len,
+                              const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int flags,
+                              void* stream) {
+  int* status = nullptr;
+  if (wait_sig != nullptr) {  // only a wait can time out
+    int rc = 0;
+    DeviceState* st = device_state(&rc);
+    if (!st) return rc;
+    status = st->ws.status;
+  }
+  return b2::decode_attention_fused_launch(qkv, bias, inv_freq, pos, cache_k, cache_v, out, workspace, Hq, Hk, D,
+                                           max_len, wait_sig, epoch, wait_per_epoch, flags, status,
+                                           static_cast<cudaStream_t>(stream));
 }
 
 int ns_w4_quantize(const void* W, void* Wq, void* S, int N, int K, int G, void* stream) {

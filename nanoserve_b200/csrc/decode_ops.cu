@@ -231,6 +231,213 @@ __global__ void decode_attention_merge_kernel(const float* part, bf16* out) {
   out[(size_t)h * D + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
 }
 
+// The attention of one decode step in ONE launch: bias add + RoPE on q and k of the new token, the new k/v row
+// appended to the cache, the partial pass over the cache, and the merge.  Same grid and tile loop as the two-launch
+// form above.  Every warp prepares its own query head in registers (bias, rotation, rounding to bf16 as
+// b2_rope_kv_store stores it).  The CTA whose slice holds the new position computes the new k and v rows, stores them
+// to the cache and serves them to its own tile loop from shared memory.  The last CTA of a KV head to have written
+// its partials (an arrival counter per KV head; nobody waits) merges the splits of that head's query heads.
+// Launches per layer of a decode step: 5 instead of 7.
+template <int D>
+__global__ void __launch_bounds__(256) decode_attention_fused_kernel(
+    const bf16* qkv, const bf16* __restrict__ bias, const float* __restrict__ inv_freq, const int* pos_ptr,
+    bf16* cache_k, bf16* cache_v, float* part, int* counters, bf16* out, int Hq, int Hk, int max_len, float scale,
+    const unsigned* wait_sig, const int* epoch, unsigned wait_per_epoch, int* status) {
+  constexpr int E = D / 32;        // elements per lane
+  constexpr int kRowU4 = D / 8;    // 16-byte units per row
+  constexpr int half = D / 2;
+  __shared__ __align__(16) bf16 s_k[kTileRows * D];
+  __shared__ __align__(16) bf16 s_v[kTileRows * D];
+  __shared__ __align__(16) bf16 s_newk[D];
+  __shared__ __align__(16) bf16 s_newv[D];
+  __shared__ float s_f[8 * kSplits];   // merge: weight of every (query head of the group, split)
+  __shared__ float s_den[8];
+  __shared__ int s_last;
+  const int kh = blockIdx.x, sp = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rep = Hq / Hk;
+  pdl_begin();
+  if (wait_sig != nullptr) {
+    if (tid == 0) {
+      const unsigned target = ((unsigned)*reinterpret_cast<const volatile int*>(epoch) + 1u) * wait_per_epoch;
+      const long long t0 = clock64();
+      for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wait_sig) : "memory");
+        if ((int)(v - target) >= 0) break;
+        if (clock64() - t0 > 1000000000LL) {  // about half a second: report and go on with what is there
+          if (status != nullptr) atomicCAS(status, 0, b2::kStatusGemvTimeout);
+          break;
+        }
+        __nanosleep(40);
+      }
+    }
+    __syncthreads();
+  }
+  const int pos = __ldcg(pos_ptr);
+  const int n = min(pos + 1, max_len);
+  const int per = (n + kSplits - 1) / kSplits;
+  const int j0 = sp * per, j1 = min(n, j0 + per);
+  const bool owner = pos < max_len && pos >= j0 && pos < j1;  // this CTA's slice holds the new position
+
+  // the first tile's cache rows are requested before anything else: the q and new-row work below runs under them
+  const uint4* kbase = reinterpret_cast<const uint4*>(cache_k + (size_t)kh * max_len * D);
+  const uint4* vbase = reinterpret_cast<const uint4*>(cache_v + (size_t)kh * max_len * D);
+  constexpr int kPerThread = (kTileRows * kRowU4 + 255) / 256;
+  uint4 kv[kPerThread], vv[kPerThread];
+  auto request = [&](int t0) {
+    const int units = min(kTileRows, j1 - t0) * kRowU4;
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int u = tid + i * 256;
+      if (u < units && t0 + u / kRowU4 != pos) {  // the row this launch appends is not in the cache yet
+        kv[i] = __ldcg(kbase + (size_t)t0 * kRowU4 + u);
+        vv[i] = __ldcg(vbase + (size_t)t0 * kRowU4 + u);
+      }
+    }
+  };
+  if (j0 < j1) request(j0);
+
+  // ---- the new k and v rows (owner only): thread i < D/2 rotates the pair (i, i + D/2) of k, the next D/2 threads
+  // add the bias to a pair of v
+  if (owner && tid < D) {
+    const bool is_v = tid >= half;
+    const int i = is_v ? tid - half : tid;
+    const int hh = Hq + (is_v ? Hk : 0) + kh;
+    const bf16* x = qkv + (size_t)hh * D;
+    float a = ld_bf16(x + i), b = ld_bf16(x + i + half);
+    if (bias != nullptr) {
+      a = __bfloat162float(__float2bfloat16(a + __bfloat162float(bias[(size_t)hh * D + i])));
+      b = __bfloat162float(__float2bfloat16(b + __bfloat162float(bias[(size_t)hh * D + i + half])));
+    }
+    if (!is_v) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+      a = ra;
+      b = rb;
+    }
+    const bf16 oa = __float2bfloat16(a), ob = __float2bfloat16(b);
+    bf16* sm = is_v ? s_newv : s_newk;
+    sm[i] = oa;
+    sm[i + half] = ob;
+    bf16* dst = (is_v ? cache_v : cache_k) + ((size_t)kh * max_len + pos) * D;
+    dst[i] = oa;
+    dst[i + half] = ob;
+  }
+
+  // ---- this warp's query head: bias, rotation, bf16 rounding, softmax scale
+  const int h = kh * rep + min(warp, rep - 1);
+  float qf[E];
+  {
+    ld_row<E>(qkv + (size_t)h * D + lane * E, qf);
+    if (bias != nullptr) {
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        qf[e] = __bfloat162float(__float2bfloat16(qf[e] + __bfloat162float(bias[(size_t)h * D + lane * E + e])));
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const float other = __shfl_xor_sync(0xffffffffu, qf[e], 16);  // the element D/2 away
+      float sn, cs;
+      sincosf((float)pos * inv_freq[(lane * E + e) % half], &sn, &cs);
+      const float r = lane < 16 ? qf[e] * cs - other * sn : qf[e] * cs + other * sn;
+      qf[e] = __bfloat162float(__float2bfloat16(r)) * scale;
+    }
+  }
+
+  float m = -FLT_MAX, l = 0.f, acc[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) acc[e] = 0.f;
+  for (int t0 = j0; t0 < j1; t0 += kTileRows) {
+    const int rows = min(kTileRows, j1 - t0);
+    const int units = rows * kRowU4;
+    if (t0 > j0) request(t0);
+    __syncthreads();  // everybody is done with the previous tile; the new rows are in shared memory
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int u = tid + i * 256;
+      if (u < units) {
+        const bool fresh = t0 + u / kRowU4 == pos;
+        reinterpret_cast<uint4*>(s_k)[u] = fresh ? reinterpret_cast<const uint4*>(s_newk)[u % kRowU4] : kv[i];
+        reinterpret_cast<uint4*>(s_v)[u] = fresh ? reinterpret_cast<const uint4*>(s_newv)[u % kRowU4] : vv[i];
+      }
+    }
+    __syncthreads();
+    if (warp < rep) {
+      for (int r = 0; r < rows; ++r) {
+        float s = 0.f, kf[E], vf[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          kf[e] = __bfloat162float(s_k[r * D + lane * E + e]);
+          vf[e] = __bfloat162float(s_v[r * D + lane * E + e]);
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) s += qf[e] * kf[e];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float mn = fmaxf(m, s);
+        const float corr = __expf(m - mn), pj = __expf(s - mn);
+        l = l * corr + pj;
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] = acc[e] * corr + pj * vf[e];
+        m = mn;
+      }
+    }
+  }
+  if (warp < rep) {
+    float* o = part + ((size_t)h * kSplits + sp) * (D + 2);
+    if (lane == 0) {
+      __stcg(o, m);
+      __stcg(o + 1, l);
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) __stcg(o + 2 + lane * E + e, acc[e]);
+  }
+
+  if (counters == nullptr) return;  // a merge launch follows
+  // ---- the last CTA of this KV head to arrive merges the splits
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(counters + kh, 1);
+    const int last = old == kSplits - 1;
+    if (last) counters[kh] = 0;  // ready for the next launch (launches that share the counters are stream-ordered)
+    s_last = last;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // weight of every (query head, split): exp(m - max m), and the denominator of every head
+  if (warp < rep) {
+    const int hq = kh * rep + warp;
+    const float* pp = part + ((size_t)hq * kSplits + lane) * (D + 2);  // kSplits == 32: one split per lane
+    const float ms = __ldcg(pp), ls = __ldcg(pp + 1);
+    float mm = ms;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    const float f = ms == -FLT_MAX ? 0.f : __expf(ms - mm);
+    float den = f * ls;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+    s_f[warp * kSplits + lane] = f;
+    if (lane == 0) s_den[warp] = den;
+  }
+  __syncthreads();
+  for (int item = tid; item < rep * D; item += 256) {
+    const int w = item / D, d = item - w * D;
+    const int hq = kh * rep + w;
+    const float* pp = part + (size_t)hq * kSplits * (D + 2) + 2 + d;
+    float as[kSplits];
+#pragma unroll
+    for (int sidx = 0; sidx < kSplits; ++sidx) as[sidx] = __ldcg(pp + sidx * (D + 2));
+    float num = 0.f;
+#pragma unroll
+    for (int sidx = 0; sidx < kSplits; ++sidx) num += s_f[w * kSplits + sidx] * as[sidx];
+    const float den = s_den[w];
+    out[(size_t)hq * D + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+  }
+}
+
 // Greedy choice in two launches.  Pass 1, kArgBlocks CTAs: each scans a slice of the logits and writes its best
 // (value, index).  Pass 2, one CTA: picks the best of those (lowest index on ties, as torch.argmax returns the
 // first occurrence), records the token, advances step and position, and copies the token's embedding row.
@@ -349,6 +556,45 @@ int rope_kv_store_launch(void* qkv, const void* bias, const void* inv_freq, cons
 }
 }  // namespace b2
 
+namespace b2 {
+int decode_attention_fused_launch(const void* qkv, const void* bias, const void* inv_freq, const void* pos,
+                                  void* cache_k, void* cache_v, void* out, void* workspace, int Hq, int Hk, int D,
+                                  int max_len, const void* wait_sig, const void* epoch, unsigned wait_per_epoch,
+                                  int flags, int* status, cudaStream_t stream) {
+  static_assert(kSplits == 32, "the merge takes one split per lane");
+  if (Hq < 1 || Hk < 1 || Hq % Hk || Hq / Hk > 8 || max_len < 1) return b2::kErrBadShape;
+  if (D != 128 && D != 64) return b2::kErrNotImplemented;
+  if (!qkv || !inv_freq || !cache_k || !cache_v || !pos || !out || !workspace) return b2::kErrBadPointer;
+  if (wait_sig != nullptr && !epoch) return b2::kErrBadPointer;
+  // 8-byte loads of q, 16-byte loads and stores of cache rows, float partials and counters in the workspace
+  if ((reinterpret_cast<uintptr_t>(qkv) & 7) || (reinterpret_cast<uintptr_t>(bias) & 3) ||
+      (reinterpret_cast<uintptr_t>(cache_k) & 15) || (reinterpret_cast<uintptr_t>(cache_v) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 1) || (reinterpret_cast<uintptr_t>(workspace) & 3) ||
+      (reinterpret_cast<uintptr_t>(pos) & 3) || (reinterpret_cast<uintptr_t>(inv_freq) & 3))
+    return b2::kErrBadPointer;
+  const float scale = 1.f / sqrtf((float)D);
+  float* part = static_cast<float*>(workspace);
+  const bool one_launch = (flags & 1) != 0;
+  int* counters = one_launch ? reinterpret_cast<int*>(part + (size_t)Hq * kSplits * (D + 2)) : nullptr;
+  const dim3 grid(Hk, kSplits);
+  auto go = [&](auto kernel) {
+    return launch_pdl(kernel, grid, dim3(256), stream, static_cast<const bf16*>(qkv),
+                      static_cast<const bf16*>(bias), static_cast<const float*>(inv_freq),
+                      static_cast<const int*>(pos), static_cast<bf16*>(cache_k), static_cast<bf16*>(cache_v), part,
+                      counters, static_cast<bf16*>(out), Hq, Hk, max_len, scale,
+                      static_cast<const unsigned*>(wait_sig), static_cast<const int*>(epoch), wait_per_epoch, status);
+  };
+  cudaError_t e = D == 128 ? go(decode_attention_fused_kernel<128>) : go(decode_attention_fused_kernel<64>);
+  if (e == cudaSuccess && !one_launch) {
+    e = D == 128 ? launch_pdl(decode_attention_merge_kernel<128>, dim3(Hq), dim3(128), stream,
+                              static_cast<const float*>(part), static_cast<bf16*>(out))
+                 : launch_pdl(decode_attention_merge_kernel<64>, dim3(Hq), dim3(64), stream,
+                              static_cast<const float*>(part), static_cast<bf16*>(out));
+  }
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+}  // namespace b2
+
 extern "C" {
 
 int b2_rope_kv_store(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k, void* cache_v,
@@ -391,6 +637,10 @@ int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v,
                static_cast<bf16*>(out));
   }
   return (int)cudaGetLastError();
+}
+
+size_t b2_decode_attention_fused_workspace_bytes(int Hq, int Hk, int D) {
+  return (size_t)Hq * kSplits * (D + 2) * sizeof(float) + (size_t)Hk * sizeof(int);
 }
 
 int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* pos, void* out_tokens, void* step,

@@ -1,16 +1,22 @@
 // bf16 vocabulary projection of the decode step with the greedy argmax in its epilogue:
-//   logits[M, V] (bf16) = X[M, K] (bf16) . W[V, K]^T (bf16), fp32 accumulation, 1 <= M <= 8;
+//   logits[M, V] (bf16) = X[M, K] (bf16) . W[V, K]^T (bf16), fp32 accumulation, 1 <= M <= 8, K % 64 == 0;
 //   per 128-row block the largest logit of token 0 and its index (lowest index on ties).
 //
 // The reference keeps the lm_head in bf16 and runs it through F.linear, then argmax on the host side of the step
 // (python/nanoserve/qwen.py:164,174-177).  At batch 1 this is a 1.09 GB stream for the 152064 x 3584 Qwen2.5-7B
 // head -- a quarter of the bytes of a W4 decode step -- so it gets the same treatment as the quantized GEMV:
-// weights go from global memory straight into registers in mma fragment layout (lane (g, t) loads 16 bytes of rows
-// g and g + 8 per 32-wide chunk of K, eight chunks in flight), mma.sync.m16n8k16 bf16 with the tokens in the
-// columns, no shared-memory staging of W, CTAs of half an SM launched with programmatic stream serialization so
-// that the weight stream starts while the previous kernel drains.  The 16 bytes a lane loads are eight
-// consecutive k; the contraction index of an mma is a dummy, so the B fragment is simply the same 16 bytes of X.
-// The final residual add + RMSNorm of the model can be folded into the staging of X (same prologue as the GEMV).
+// every warp owns 16 rows of W and a private ring of shared-memory slots (16 rows x 128 bytes: 64 values of K) that
+// its own lanes fill with 16-byte cp.async copies, four rows x 128 bytes per warp instruction (whole lines), each
+// slot completing on its own mbarrier; nobody waits for another warp.  (Loads straight into registers, 16 bytes of
+// rows g and g + 8 per lane, moved half lines and kept few loads in flight: 3.0 TB/s on this matrix.)  The
+// fragments of mma.sync.m16n8k16 (bf16, tokens in the columns) come out of the slot with 16-byte shared loads: the
+// 16 bytes a lane reads are eight consecutive k; the contraction index of an mma is a dummy, so the B fragment is
+// simply the same 16 bytes of X.  16-byte unit u of slot row r sits at u ^ ((r & 1) << 2), which keeps the eight
+// lanes of a shared-memory phase (rows g, g + 1; units t) on different banks.  Two CTAs per SM, launched with
+// programmatic stream serialization: the weight stream starts while the previous kernel drains, and a CTA's X
+// staging hides behind the other CTA's stream.  The final residual add + RMSNorm of the model can be folded into
+// the staging of X (same prologue as the GEMV).
+#include <algorithm>
 #include <cfloat>
 
 #include "../../include/nanoserve_b200.h"
@@ -21,45 +27,61 @@ namespace b2 {
 namespace {
 
 constexpr int kThreads = 256;
+constexpr int kWarps = 8;
 constexpr int kRowsPerCta = 128;
-constexpr int kRing = 8;
-
-__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
+constexpr int kSlotBytes = 16 * 128;
+constexpr int kMaxDepth = 6;
+constexpr int kBarOffset = 1152;   // [kWarps][8] mbarriers
+constexpr int kAbortOffset = 1664;
+constexpr int kXOffset = 1792;     // X as bf16 [M][K], then the rings (128-byte aligned)
+constexpr int kSmemTwoPerSm = 112 * 1024;
 
 __global__ void __launch_bounds__(kThreads, 2)
     lm_head_kernel(const GemvParams p, const __nv_bfloat16* __restrict__ W, float* __restrict__ part_v,
-                   int* __restrict__ part_i, int idx_offset) {
+                   int* __restrict__ part_i, int idx_offset, int depth) {
   extern __shared__ __align__(128) unsigned char smem[];
   float* ss = reinterpret_cast<float*>(smem);              // [16][16] RMSNorm partial sums
   float* inv = reinterpret_cast<float*>(smem + 1024);      // [16]
   float* s_v = reinterpret_cast<float*>(smem + 1088);      // [8] per-warp maxima
   int* s_i = reinterpret_cast<int*>(smem + 1120);          // [8]
-  const uint32_t xs = smem_u32(smem + 1280);               // X as bf16 [M][K]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kAbortOffset);
+  const uint32_t xs = smem_u32(smem + kXOffset);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int V = p.N, K = p.K;
   const int row0 = blockIdx.x * kRowsPerCta + warp * 16;
   const bool active = row0 < V;
-  const int nch = K / 32;
+  const int nslots = K / 64;
+  const uint32_t ring0 = xs + (((uint32_t)p.M * K * 2 + 127u) & ~127u) + warp * depth * kSlotBytes;
+  const uint32_t bar0 = smem_u32(smem + kBarOffset) + warp * 64;
 
   pdl_launch_dependents();
-  const int row_lo = min(row0 + g, V - 1), row_hi = min(row0 + g + 8, V - 1);
-  const unsigned char* wlo = reinterpret_cast<const unsigned char*>(W + (size_t)row_lo * K) + t * 16;
-  const unsigned char* whi = reinterpret_cast<const unsigned char*>(W + (size_t)row_hi * K) + t * 16;
-  uint4 wb[kRing][2];
+  if (tid == 0) *abort_flag = 0;
+  if (lane < depth) mbar_init(bar0 + 8 * lane, 32);
+  fence_mbar_init();
+  __syncwarp();
+
+  // this lane's share of a slot: rows 4 j + (lane >> 3), j = 0..3, 16-byte unit lane & 7
+  const int frow = lane >> 3, funit = lane & 7;
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(W) + funit * 16;
+  const size_t row_bytes = (size_t)K * 2;
+  const uint32_t fdst = frow * 128 + ((funit ^ ((frow & 1) << 2)) << 4);
+  const bool whole = row0 + 16 <= V;
+  auto feed = [&](int ks, int d) {
+    const uint32_t slot = ring0 + d * kSlotBytes + fdst;
 #pragma unroll
-  for (int d = 0; d < kRing; ++d) {
-    wb[d][0] = make_uint4(0u, 0u, 0u, 0u);
-    wb[d][1] = make_uint4(0u, 0u, 0u, 0u);
-    if (active && d < nch) {
-      wb[d][0] = ldg_stream16(wlo + d * 64);
-      wb[d][1] = ldg_stream16(whi + d * 64);
+    for (int j = 0; j < 4; ++j) {
+      const int row = row0 + 4 * j + frow;
+      const bool ok = whole || row < V;
+      const unsigned char* sp = src + (size_t)(ok ? row : row0) * row_bytes + (size_t)ks * 128;
+      asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(slot + j * 512), "l"(sp),
+                   "r"(ok ? 16u : 0u)
+                   : "memory");
     }
+    cp_async_mbar_arrive_noinc(bar0 + 8 * d);
+  };
+  if (active) {
+    for (int d = 0; d < depth; ++d)
+      if (d < nslots) feed(d, d);
   }
 
   pdl_wait_prior_grid();
@@ -75,21 +97,29 @@ __global__ void __launch_bounds__(kThreads, 2)
   if (active) {
     const bool bval = g < p.M;
     const uint32_t xaddr = xs + ((bval ? g : 0) * K + t * 8) * 2;
-    for (int cc = 0; cc < nch; cc += kRing) {
-#pragma unroll
-      for (int d = 0; d < kRing; ++d) {
-        const int c = cc + d;
-        if (c < nch) {
-          const uint4 lo = wb[d][0], hi = wb[d][1];
-          if (c + kRing < nch) {
-            wb[d][0] = ldg_stream16(wlo + (c + kRing) * 64);
-            wb[d][1] = ldg_stream16(whi + (c + kRing) * 64);
-          }
-          uint4 x = make_uint4(0u, 0u, 0u, 0u);
-          if (bval) x = lds128(xaddr + c * 64);
-          mma_16816_bf16(acc, lo.x, hi.x, lo.y, hi.y, x.x, x.y);
-          mma_16816_bf16(acc, lo.z, hi.z, lo.w, hi.w, x.z, x.w);
-        }
+    const uint32_t pg = (uint32_t)(g & 1) << 2;
+    const uint32_t a_u0 = g * 128 + (((uint32_t)t ^ pg) << 4), a_u1 = g * 128 + (((uint32_t)(t + 4) ^ pg) << 4);
+    int d = 0;
+    uint32_t ph = 0;
+    for (int ks = 0; ks < nslots; ++ks) {
+      const uint32_t slot = ring0 + d * kSlotBytes;
+      mbar_wait(bar0 + 8 * d, ph, abort_flag);
+      const uint4 lo0 = lds128(slot + a_u0), hi0 = lds128(slot + 1024 + a_u0);
+      const uint4 lo1 = lds128(slot + a_u1), hi1 = lds128(slot + 1024 + a_u1);
+      __syncwarp();
+      if (ks + depth < nslots) feed(ks + depth, d);
+      uint4 x0 = make_uint4(0u, 0u, 0u, 0u), x1 = x0;
+      if (bval) {
+        x0 = lds128(xaddr + ks * 128);
+        x1 = lds128(xaddr + ks * 128 + 64);
+      }
+      mma_16816_bf16(acc, lo0.x, hi0.x, lo0.y, hi0.y, x0.x, x0.y);
+      mma_16816_bf16(acc, lo0.z, hi0.z, lo0.w, hi0.w, x0.z, x0.w);
+      mma_16816_bf16(acc, lo1.x, hi1.x, lo1.y, hi1.y, x1.x, x1.y);
+      mma_16816_bf16(acc, lo1.z, hi1.z, lo1.w, hi1.w, x1.z, x1.w);
+      if (++d == depth) {
+        d = 0;
+        ph ^= 1;
       }
     }
   }
@@ -133,25 +163,31 @@ __global__ void __launch_bounds__(kThreads, 2)
       s_v[warp] = best;
       s_i[warp] = bi;
     }
+  }
+  __syncthreads();
+  if (part_v != nullptr && tid == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (s_v[w] > best || (s_v[w] == best && s_i[w] < bi)) {
+        best = s_v[w];
+        bi = s_i[w];
+      }
+    part_v[blockIdx.x] = best;
+    part_i[blockIdx.x] = bi == 0x7fffffff ? bi : bi + idx_offset;
+  }
+  if (*abort_flag) {
+    // a copy never completed: record it, and let what is in flight land before the shared memory is released
+    if (tid == 0 && p.status != nullptr) atomicCAS(p.status, kStatusOk, kStatusGemvTimeout);
+    cp_async_wait_all();
     __syncthreads();
-    if (tid == 0) {
-      for (int w = 1; w < 8; ++w)
-        if (s_v[w] > best || (s_v[w] == best && s_i[w] < bi)) {
-          best = s_v[w];
-          bi = s_i[w];
-        }
-      part_v[blockIdx.x] = best;
-      part_i[blockIdx.x] = bi == 0x7fffffff ? bi : bi + idx_offset;
-    }
   }
 }
 
 }  // namespace
 
 int lm_head_launch(const void* X, const void* W, void* logits, int M, int V, int K, const GemvPrologue& pro,
-                   float* part_v, int* part_i, int idx_offset, cudaStream_t stream) {
+                   float* part_v, int* part_i, int idx_offset, int* status, cudaStream_t stream) {
   if (M < 1 || M > 8) return kErrUnsupportedM;
-  if (V < 1 || K < 32 || K % 32) return kErrBadShape;
+  if (V < 1 || K < 64 || K % 64) return kErrBadShape;
   if (!X || !W) return kErrBadPointer;
   if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
       (reinterpret_cast<uintptr_t>(logits) & 1))
@@ -162,8 +198,11 @@ int lm_head_launch(const void* X, const void* W, void* logits, int M, int V, int
       (!pro.Wn || (reinterpret_cast<uintptr_t>(pro.Wn) & 15) || (reinterpret_cast<uintptr_t>(pro.R) & 15) ||
        (reinterpret_cast<uintptr_t>(pro.Xout) & 15)))
     return kErrBadPointer;
-  const size_t smem = 1280 + (size_t)M * K * 2;
-  if (smem > 100 * 1024) return kErrTooLarge;
+  // as many slots per warp as fit beside X with two CTAs on an SM
+  const size_t fixed = kXOffset + (((size_t)M * K * 2 + 127) & ~(size_t)127);
+  if (fixed + (size_t)kWarps * 2 * kSlotBytes > (size_t)kSmemTwoPerSm) return kErrTooLarge;
+  const int depth = (int)std::min<size_t>(kMaxDepth, (kSmemTwoPerSm - fixed) / ((size_t)kWarps * kSlotBytes));
+  const size_t smem = fixed + (size_t)kWarps * depth * kSlotBytes;
   GemvParams p{};
   p.X = static_cast<const __nv_bfloat16*>(X);
   p.Y = static_cast<__nv_bfloat16*>(logits);
@@ -173,11 +212,12 @@ int lm_head_launch(const void* X, const void* W, void* logits, int M, int V, int
   p.Wn = static_cast<const __nv_bfloat16*>(pro.Wn);
   p.Xout = static_cast<__nv_bfloat16*>(pro.Xout);
   p.eps = pro.eps;
+  p.status = status;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTwoPerSm);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return (int)e;
@@ -194,7 +234,7 @@ int lm_head_launch(const void* X, const void* W, void* logits, int M, int V, int
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, lm_head_kernel, p, static_cast<const __nv_bfloat16*>(W), part_v,
-                                           part_i, idx_offset);
+                                           part_i, idx_offset, depth);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -212,8 +252,11 @@ int b2_lm_head(const void* X, const void* W, void* logits, int M, int V, int K, 
   pro.Wn = Wn;
   pro.Xout = Xout;
   pro.eps = eps;
+  int rc = 0;
+  int* status = b2::device_status_word(&rc);  // a copy that never completes is reported there (b2_device_status)
+  if (!status) return rc;
   return b2::lm_head_launch(X, W, logits, M, V, K, pro, static_cast<float*>(part_max), static_cast<int*>(part_idx),
-                            idx_offset, static_cast<cudaStream_t>(stream));
+                            idx_offset, status, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1451,6 +1451,7 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
     const int rc = gemv_stream_launch(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
     if (rc != kStreamNotApplicable) return rc;
   }
+  if (pro.epilogue != kEpiNone) return kErrNotImplemented;  // epilogues exist in the streaming kernel only
   const bool have_scratch = ws.partial && ws.counters;
   GemvPlan pl;
   if (reinterpret_cast<uintptr_t>(S) & 3) flags |= 0x800;  // scale copies need a 4-byte aligned base: one chunk per warp

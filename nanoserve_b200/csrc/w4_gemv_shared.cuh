@@ -12,6 +12,8 @@ namespace b2 {
 
 // What the kernel does to its input before the product (the operators that precede a linear in a decoder layer)
 enum : int { kProNone = 0, kProAddRmsNorm = 1, kProSwiglu = 2 };
+// Epilogues (bits above the prologue kind in the `prologue` argument of the fused entry points).
+enum : int { kEpiNone = 0, kEpiSwigluPairs = 1, kEpiShift = 8 };
 
 struct GemvParams {
   const __nv_bfloat16* X;

@@ -64,6 +64,7 @@ struct StreamParams {
   int off_info, off_sc, off_x, off_red;
   int pstride;       // bytes between planes of the staged X
   int depth;         // ring slots per warp
+  int epi;           // kEpi*
 };
 
 __device__ __forceinline__ uint32_t lds_u16s(uint32_t addr) {
@@ -583,33 +584,53 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
   if (NT == 1 && q.ks == 1 && p.nslices == 1 && p.tp.world == 0) {
     // ---- one tile, no K slices: the lanes of a quad hold the chunks and planes of the same rows; a shuffle or two,
     // and the outputs go straight from registers to Y
+    float v_lo[RB], v_hi[RB];
+    int m = 0;
+    bool writer = false;
 #pragma unroll
     for (int rb = 0; rb < RB; ++rb) {
-      float v_lo = fin[rb][0][0] + fin[rb][0][1], v_hi = fin[rb][0][2] + fin[rb][0][3];
-      int m;
-      bool writer;
+      v_lo[rb] = fin[rb][0][0] + fin[rb][0][1];
+      v_hi[rb] = fin[rb][0][2] + fin[rb][0][3];
       if constexpr (ONE) {
         // columns 2t, 2t + 1 = planes of token (2t) / P
         if (P == 4) {
-          v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
-          v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+          v_lo[rb] += __shfl_xor_sync(0xffffffffu, v_lo[rb], 1);
+          v_hi[rb] += __shfl_xor_sync(0xffffffffu, v_hi[rb], 1);
         }
         m = P == 4 ? (t >> 1) : t;
         writer = (P == 4 ? (t & 1) == 0 : true) && m < p.M;
       } else {
-        v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 2);
-        v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 2);
+        v_lo[rb] += __shfl_xor_sync(0xffffffffu, v_lo[rb], 2);
+        v_hi[rb] += __shfl_xor_sync(0xffffffffu, v_hi[rb], 2);
         if (P == 4) {
-          v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
-          v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+          v_lo[rb] += __shfl_xor_sync(0xffffffffu, v_lo[rb], 1);
+          v_hi[rb] += __shfl_xor_sync(0xffffffffu, v_hi[rb], 1);
         }
         m = P == 4 ? 0 : t;  // two planes: lanes t = 0, 1 of a quad hold tokens 0, 1
         writer = P == 4 ? t == 0 : (t < 2 && t < p.M);
       }
-      const int n = wrow0 + rb * 16 + grow;
+    }
+    if (RB == 2 && q.epi == kEpiSwigluPairs) {
+      // rows come as 16 gate rows followed by their 16 up rows: the warp's first block is gate, its second up, and a
+      // lane holds both halves of its rows.  Each half is rounded to bf16 first (what a plain launch would have
+      // stored), then silu(gate) * up in fp32 as ns_swiglu computes it, one rounding at the store.
+      auto act = [](float gv, float uv) {
+        const float a = __bfloat162float(__float2bfloat16(gv)), b = __bfloat162float(__float2bfloat16(uv));
+        return __float2bfloat16(a / (1.f + __expf(-a)) * b);
+      };
+      const int n = (wrow0 >> 1) + grow, n_act = p.N >> 1;
       if (writer && active) {
-        if (n < p.N) p.Y[(size_t)m * p.N + n] = __float2bfloat16(v_lo);
-        if (n + 8 < p.N) p.Y[(size_t)m * p.N + n + 8] = __float2bfloat16(v_hi);
+        if (n < n_act) p.Y[(size_t)m * n_act + n] = act(v_lo[0], v_lo[RB - 1]);
+        if (n + 8 < n_act) p.Y[(size_t)m * n_act + n + 8] = act(v_hi[0], v_hi[RB - 1]);
+      }
+    } else {
+#pragma unroll
+      for (int rb = 0; rb < RB; ++rb) {
+        const int n = wrow0 + rb * 16 + grow;
+        if (writer && active) {
+          if (n < p.N) p.Y[(size_t)m * p.N + n] = __float2bfloat16(v_lo[rb]);
+          if (n + 8 < p.N) p.Y[(size_t)m * p.N + n + 8] = __float2bfloat16(v_hi[rb]);
+        }
       }
     }
   } else {
@@ -699,7 +720,7 @@ size_t stream_smem(int M, int P, int NT, int RB, int tpc, int scps, int gs_pitch
 }
 
 bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int sm_count, size_t partial_cap,
-                      StreamPlan* out) {
+                      StreamPlan* out, int epilogue = kEpiNone) {
   StreamPlan pl{};
   // One token: the two-chunk layout, four planes (32-bit block fixed point): its 2 x 4 columns fill exactly one mma
   // tile.  More tokens: the one-group layout, M P columns; four planes while they fit one tile (M <= 2), two above.
@@ -707,11 +728,12 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   pl.P = M <= 2 ? 4 : 2;
   pl.NT = pl.one ? (M * pl.P + 7) / 8 : 1;
   // 32 rows per warp where 16 would make more than 1.25 CTAs per SM (fewer, longer CTAs stream better than an
-  // uneven second wave); bits 18-19 of the flags force 16 (1) or 32 (2) rows (diagnostics)
+  // uneven second wave); bits 10-11 of the flags force 16 (1) or 32 (2) rows (diagnostics)
   pl.RB = (long)((N + 15) / 16 + kWarps - 1) / kWarps * 4 > (long)sm_count * 5 ? 2 : 1;
-  if (((flags >> 18) & 3) == 1) pl.RB = 1;
-  if (((flags >> 18) & 3) == 2) pl.RB = 2;
+  if (((flags >> 10) & 3) == 1) pl.RB = 1;
+  if (((flags >> 10) & 3) == 2) pl.RB = 2;
   if (pl.one) pl.RB = 1;
+  if (epilogue == kEpiSwigluPairs) pl.RB = 2;  // a warp then owns a gate block and its up block
   const int rows = pl.RB * 16;
   const int nsc = K / 256, gdiv = G / 128, KG = K / G;
   const int n_tiles = (N + rows - 1) / rows;
@@ -721,6 +743,7 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   while (ks < 8 && (long)n_tiles * ks < (long)sm_count * kWarps * 3 / 4 && nsc / (ks * 2) >= 2) ks *= 2;
   const int forced_ks = (flags >> 20) & 0xF;
   if (forced_ks == 1 || forced_ks == 2 || forced_ks == 4 || forced_ks == 8) ks = forced_ks;
+  if (epilogue == kEpiSwigluPairs) ks = 1;  // the register epilogue: a warp holds whole dot products
   pl.ks = ks;
   const int tpc = kWarps / ks;
   pl.grid_x = (n_tiles + tpc - 1) / tpc;
@@ -760,6 +783,7 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   pl.q.scps = pl.scps;
   pl.q.wrow = K / 8;
   pl.q.sc_contig = pl.nslices == 1 && (reinterpret_cast<uintptr_t>(S) & 15) == 0;
+  pl.q.epi = epilogue;
   *out = pl;
   return true;
 }
@@ -835,9 +859,19 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
   StreamPlan pl;
   const bool have_scratch = ws.partial != nullptr;
   // a tensor-parallel producer signals its peers after its stores: no sum kernel behind it, so no split across CTAs
-  const bool no_split = !have_scratch || (tp != nullptr && tp->world > 0);
-  if (!make_stream_plan(M, N, K, G, S, no_split ? (flags | kFlagForceNoSplitK) : flags, sm_count, ws.partial_bytes, &pl))
-    return kStreamNotApplicable;
+  bool no_split = !have_scratch || (tp != nullptr && tp->world > 0);
+  if (pro.epilogue == kEpiSwigluPairs) {
+    // served by the register epilogue of the one-token kernel only: a caller that gets this code runs the plain
+    // launch followed by the SwiGLU prologue of the next one
+    if (M != 1 || (N & 31) || (tp != nullptr && tp->world > 0)) return kErrNotImplemented;
+    no_split = true;
+  } else if (pro.epilogue != kEpiNone) {
+    return kErrBadShape;
+  }
+  if (!make_stream_plan(M, N, K, G, S, no_split ? (flags | kFlagForceNoSplitK) : flags, sm_count, ws.partial_bytes, &pl,
+                        pro.epilogue))
+    return pro.epilogue != kEpiNone ? kErrNotImplemented : kStreamNotApplicable;
+  if (pro.epilogue != kEpiNone && (pl.nslices != 1 || pl.one || pl.RB != 2 || pl.ks != 1)) return kErrNotImplemented;
   GemvParams p{};
   p.X = static_cast<const __nv_bfloat16*>(X);
   p.S = static_cast<const __nv_bfloat16*>(S);

@@ -67,6 +67,7 @@ enum : int {
 // Xout (may be null); 2: X is a [M, 2K] gate|up row, input = silu(gate) * up.
 struct GemvPrologue {
   int kind = 0;
+  int epilogue = 0;  // kEpi*
   const void* R = nullptr;
   const void* Wn = nullptr;
   void* Xout = nullptr;
@@ -108,6 +109,12 @@ int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, in
                 const Workspace& ws, int flags, int sm_count, cudaStream_t stream);
 int quantize_launch(const void* W, void* Wq, void* S, int N, int K, int G, cudaStream_t stream);
 
+int decode_attention_fused_launch(const void* qkv, const void* bias, const void* inv_freq, const void* pos,
+                                  void* cache_k, void* cache_v, void* out, void* workspace, int Hq, int Hk, int D,
+                                  int max_len, const void* wait_sig, const void* epoch, unsigned wait_per_epoch,
+                                  int flags, int* status, cudaStream_t stream);
+// The status word of the current device's scratch (created on first use); rc receives 0 or an error code.
+int* device_status_word(int* rc);
 int tp_wait_launch(const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int* status, cudaStream_t stream);
 int rope_kv_store_launch(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
                          void* cache_v, int Hq, int Hk, int D, int max_len, const void* wait_sig, const void* epoch,

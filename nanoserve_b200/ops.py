@@ -28,6 +28,7 @@ FLAG_NO_PRE_STAGE_X = 16384
 FLAG_SPLIT_SUM_KERNEL = 32768
 FLAG_NO_SPLIT_SUM_KERNEL = 65536
 FLAG_RING_KERNEL = 131072    # decode GEMV: the shared-memory ring kernel even where the streaming kernel applies
+EPI_SWIGLU_PAIRS = 1  # epilogue of b2_w4_linear_fused: silu(gate) * up over row blocks of 16 gate + 16 up rows
 FLAG_GEMM_WHOLE_TILES = 1 << 30  # prefill GEMM: every CTA takes whole output tiles (no fp32 part-tiles)
 FLAG_STREAM_KERNEL = 524288  # decode GEMV: the streaming kernel for every M <= 16 it can serve (default: M <= 2)
 
@@ -58,6 +59,8 @@ SIGNATURES = {
     "b2_greedy_pick": ([_vp, _vp, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp], _i32),
     "b2_w4_linear_tp": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _f32, _vp, _vp, _i32, _vp], _i32),
     "b2_w4_gemv_grid": ([_i32, _i32, _i32, _i32, _i32], ctypes.c_size_t),
+    "b2_decode_attention_fused": ([_vp] * 8 + [_i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_uint, _i32, _vp], _i32),
+    "b2_decode_attention_fused_workspace_bytes": ([_i32, _i32, _i32], ctypes.c_size_t),
     "b2_rope_kv_store_tp": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_uint, _vp], _i32),
     "b2_tp_wait": ([_vp, _vp, ctypes.c_uint, _vp], _i32),
     "b2_version": ([], ctypes.c_char_p),
@@ -193,17 +196,20 @@ class Kernels:
         return y
 
     # ---- additions
-    def w4_linear_fused(self, x, Wq, S, group=128, prologue=0, r=None, wn=None, eps=0.0, x_out=None, flags=0):
-        """Decode GEMV with the preceding operator folded in: prologue 1 = add + RMSNorm (x + r normalised with
-        weights wn; the sum goes to x_out), prologue 2 = SwiGLU (x is [M, 2K] gate | up)."""
+    def w4_linear_fused(self, x, Wq, S, group=128, prologue=0, r=None, wn=None, eps=0.0, x_out=None, flags=0,
+                        epilogue=0):
+        """Decode GEMV with the neighbouring operators folded in: prologue 1 = add + RMSNorm (x + r normalised with
+        weights wn; the sum goes to x_out), prologue 2 = SwiGLU (x is [M, 2K] gate | up); epilogue EPI_SWIGLU_PAIRS =
+        the rows of Wq are 16 gate rows, their 16 up rows, the next 16 gate rows ... and the output is
+        silu(gate) * up, [M, N / 2] (one token; raises with code -3 where the kernel cannot serve it)."""
         self._cuda(x, Wq, S, r, wn, x_out)
         M = x.shape[0]
         N, K = Wq.shape[0], Wq.shape[1] * 8
         assert x.is_contiguous() and x.shape[1] == (2 * K if prologue == 2 else K)
-        y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        y = torch.empty((M, N // 2 if epilogue == EPI_SWIGLU_PAIRS else N), dtype=torch.bfloat16, device=x.device)
         p = lambda t: None if t is None else t.data_ptr()
         rc = self.lib.b2_w4_linear_fused(x.data_ptr(), Wq.data_ptr(), S.data_ptr(), y.data_ptr(), M, N, K, group,
-                                         prologue, p(r), p(wn), eps, p(x_out), flags, self._stream())
+                                         prologue | (epilogue << 8), p(r), p(wn), eps, p(x_out), flags, self._stream())
         self._check(rc, "b2_w4_linear_fused")
         return y
 

@@ -6,8 +6,8 @@ are no checkpoints offline, so weights are seeded random nibbles and scales with
 Differences from the reference, all on the host side of the boundary:
   * q/k/v and gate/up are stored as one row-concatenated matrix each (one GEMV instead of three / two): rows of
     ``Wq``/``S`` are independent, so this is the same arithmetic in fewer launches.
-  * One decode step is captured in a CUDA graph; the position lives in device memory (``b2_rope_kv_store``,
-    ``b2_decode_attention``, ``b2_greedy_next``), so the same graph is replayed for every token.  The reference runs
+  * One decode step is captured in a CUDA graph; the position lives in device memory (``b2_decode_attention_fused``,
+    ``b2_lm_head``, ``b2_greedy_pick``), so the same graph is replayed for every token.  The reference runs
     ~400 eager launches per token (README.md:227-228).
   * Tensor parallel: every matrix is sharded by output rows over the ranks, outputs are all-gathered at the four
     layer boundaries; attention, norms and RoPE run replicated on the gathered activations.  In the decode step the
@@ -19,6 +19,7 @@ Differences from the reference, all on the host side of the boundary:
 Batch size 1, as in the reference (qwen.py:12).
 """
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -26,7 +27,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from .ops import Kernels, make_tp_desc
+from .ops import EPI_SWIGLU_PAIRS, Kernels, make_tp_desc
 
 
 @dataclass
@@ -83,9 +84,18 @@ class Qwen2Runner:
             g, u = w4(self.I, H), w4(self.I, H)
             d = w4(H, self.I)
             bias = (torch.randn(self.nq + 2 * self.nkv, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+            if world == 1:
+                # 16 gate rows, their 16 up rows, the next 16 gate rows ...: the decode GEMV then holds a gate value
+                # and its up value in the same lane and applies SwiGLU in its epilogue (same rows, same arithmetic)
+                def pairs(a, b):
+                    return torch.stack([a.view(self.I // 16, 16, -1), b.view(self.I // 16, 16, -1)], 1).reshape(
+                        2 * self.I, -1).contiguous()
+                gu = (pairs(g[0], u[0]), pairs(g[1], u[1]))
+            else:
+                gu = (torch.cat([g[0], u[0]]), torch.cat([g[1], u[1]]))
             self.layers.append({
                 "qkv": (torch.cat([q[0], k[0], v[0]]), torch.cat([q[1], k[1], v[1]])),
-                "o": o, "gu": (torch.cat([g[0], u[0]]), torch.cat([g[1], u[1]])), "d": d,
+                "o": o, "gu": gu, "d": d,
                 "bias": bias,  # full-width: applied after the gather (Qwen2 has q/k/v biases, qwen.py:76,147-148)
                 "ln_in": (norm_gain * (1 + 0.02 * torch.randn(H, device=device, generator=gen))).to(torch.bfloat16),
                 "ln_post": (norm_gain * (1 + 0.02 * torch.randn(H, device=device, generator=gen))).to(torch.bfloat16),
@@ -113,6 +123,10 @@ class Qwen2Runner:
         self.stream = torch.cuda.Stream(device=device)
         self.scratch = torch.empty(int(kernels.lib.b2_decode_workspace_bytes(cfg.n_heads, D)), dtype=torch.uint8,
                                    device=device)
+        self.attn_flags = int(os.environ.get("B2_QWEN_ATTN_FLAGS", "0"))  # 1: merge inside the attention launch
+        # partials and arrival counters (zero between launches) of the fused attention kernel
+        self.attn_ws = torch.zeros(int(kernels.lib.b2_decode_attention_fused_workspace_bytes(
+            cfg.n_heads, cfg.n_kv_heads, D)), dtype=torch.uint8, device=device)
         # vocabulary projection: this rank's logits and one (largest logit, index) pair per 128 rows of its shard
         self.v_local = cfg.vocab // world
         self.nblk = kernels.lm_head_blocks(self.v_local)
@@ -219,7 +233,11 @@ class Qwen2Runner:
             h = k.rmsnorm(x, self._gather(self.linear(a, L["o"])), L["ln_post"], cfg.rms_eps)
             gu = self.linear(h, L["gu"])
             il = self.I // self.world
-            act = self._gather(k.swiglu(gu[:, :il].contiguous(), gu[:, il:].contiguous()))
+            if self.world == 1:  # blocks of 16 gate rows and 16 up rows alternate (see __init__)
+                gu = gu.view(T, il // 16, 2, 16)
+                act = k.swiglu(gu[:, :, 0].reshape(T, il), gu[:, :, 1].reshape(T, il))
+            else:
+                act = self._gather(k.swiglu(gu[:, :il].contiguous(), gu[:, il:].contiguous()))
             nxt = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
             h = k.rmsnorm(x, self._gather(self.linear(act, L["d"])), nxt, cfg.rms_eps)
         self.pos.fill_(T - 1)  # the pick advances it to T, the position of the first generated token
@@ -259,8 +277,9 @@ class Qwen2Runner:
 
     @torch.no_grad()
     def decode_step(self):
-        """One token.  Seven launches per layer on one GPU: qkv GEMV (residual add + RMSNorm folded in), RoPE + KV
-        store, attention (two passes), o GEMV, gate|up GEMV (add + norm folded in), down GEMV (SwiGLU folded in).
+        """One token.  Six launches per layer on one GPU: qkv GEMV (residual add + RMSNorm folded in), attention
+        (bias, RoPE, KV store and the pass over the cache in one kernel, then the merge), o GEMV, gate|up GEMV (add + norm
+        in its prologue, SwiGLU in its epilogue), down GEMV.
         The residual stream alternates between two buffers because a fused GEMV may not overwrite the X other CTAs
         are still reading; every step starts again from `self.x`, where b2_greedy_next puts the next embedding."""
         if self.peer is not None:
@@ -274,21 +293,22 @@ class Qwen2Runner:
             if r is not None:
                 x, x_alt = x_alt, x
             qkv = self._gather_parts(y, [self.nq, self.nkv, self.nkv]).contiguous()
-            rc = lib.b2_rope_kv_store(qkv.data_ptr(), L["bias"].data_ptr(), self.inv_freq.data_ptr(),
-                                      self.pos.data_ptr(), self.cache_k[li].data_ptr(), self.cache_v[li].data_ptr(),
-                                      cfg.n_heads, cfg.n_kv_heads, D, self.max_len, self._st())
-            k._check(rc, "b2_rope_kv_store")
             a = torch.empty(1, self.nq, dtype=torch.bfloat16, device=self.dev)
-            rc = lib.b2_decode_attention(qkv.data_ptr(), self.cache_k[li].data_ptr(), self.cache_v[li].data_ptr(),
-                                         self.pos.data_ptr(), a.data_ptr(), self.scratch.data_ptr(), cfg.n_heads,
-                                         cfg.n_kv_heads, D, self.max_len, self._st())
-            k._check(rc, "b2_decode_attention")
+            rc = lib.b2_decode_attention_fused(qkv.data_ptr(), L["bias"].data_ptr(), self.inv_freq.data_ptr(),
+                                               self.pos.data_ptr(), self.cache_k[li].data_ptr(),
+                                               self.cache_v[li].data_ptr(), a.data_ptr(), self.attn_ws.data_ptr(),
+                                               cfg.n_heads, cfg.n_kv_heads, D, self.max_len, None, None, 0, self.attn_flags,
+                                               self._st())
+            k._check(rc, "b2_decode_attention_fused")
             o = self._gather(self.linear(a, L["o"]))
-            gu = self._fused(x, L["gu"], 1, r=o, wn=L["ln_post"], x_out=x_alt)
-            x, x_alt = x_alt, x
-            if self.world == 1:
-                d = self._fused(gu, L["d"], 2)
+            if self.world == 1:  # SwiGLU in the epilogue of gate|up: the down projection reads the activation as is
+                act = self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o, wn=L["ln_post"],
+                                             eps=cfg.rms_eps, x_out=x_alt, epilogue=EPI_SWIGLU_PAIRS)
+                x, x_alt = x_alt, x
+                d = self.linear(act, L["d"])
             else:  # the activation is gathered between SwiGLU and the down projection
+                gu = self._fused(x, L["gu"], 1, r=o, wn=L["ln_post"], x_out=x_alt)
+                x, x_alt = x_alt, x
                 il = self.I // self.world
                 d = self._gather(self.linear(self._gather(k.swiglu(gu[:, :il], gu[:, il:])), L["d"]))
             r = d
@@ -299,9 +319,9 @@ class Qwen2Runner:
 
     @torch.no_grad()
     def _decode_step_fused_gather(self):
-        """The decode step on more than one GPU with the all-gathers inside the GEMVs: the same seven launches per
+        """The decode step on more than one GPU with the all-gathers inside the GEMVs: the same five launches per
         layer as on one GPU, no collective.  Every GEMV stores its rows into the gathered row of every rank and counts
-        itself in; the kernel that consumes the row (the next GEMV, or the RoPE kernel) waits on the counter."""
+        itself in; the kernel that consumes the row (the next GEMV, or the attention kernel) waits on the counter."""
         cfg, k, lib, peer = self.cfg, self.k, self.k.lib, self.peer
         D, G, eps = cfg.head_dim, cfg.group, cfg.rms_eps
         ep = peer.epoch.data_ptr()
@@ -316,16 +336,13 @@ class Qwen2Runner:
                 k.w4_linear_tp(x, L["qkv"][0], L["qkv"][1], dsc["qkv"], G, prologue=1, r=d_buf, wn=L["ln_in"], eps=eps,
                                x_out=x_alt)
                 x, x_alt = x_alt, x
-            rc = lib.b2_rope_kv_store_tp(qkv_buf.data_ptr(), L["bias"].data_ptr(), self.inv_freq.data_ptr(),
-                                         self.pos.data_ptr(), self.cache_k[li].data_ptr(),
-                                         self.cache_v[li].data_ptr(), cfg.n_heads, cfg.n_kv_heads, D, self.max_len,
-                                         peer.counter(4 * li), ep, self.tp_wait_qkv, self._st())
-            k._check(rc, "b2_rope_kv_store_tp")
             a = torch.empty(1, self.nq, dtype=torch.bfloat16, device=self.dev)
-            rc = lib.b2_decode_attention(qkv_buf.data_ptr(), self.cache_k[li].data_ptr(), self.cache_v[li].data_ptr(),
-                                         self.pos.data_ptr(), a.data_ptr(), self.scratch.data_ptr(), cfg.n_heads,
-                                         cfg.n_kv_heads, D, self.max_len, self._st())
-            k._check(rc, "b2_decode_attention")
+            rc = lib.b2_decode_attention_fused(qkv_buf.data_ptr(), L["bias"].data_ptr(), self.inv_freq.data_ptr(),
+                                               self.pos.data_ptr(), self.cache_k[li].data_ptr(),
+                                               self.cache_v[li].data_ptr(), a.data_ptr(), self.attn_ws.data_ptr(),
+                                               cfg.n_heads, cfg.n_kv_heads, D, self.max_len, peer.counter(4 * li), ep,
+                                               self.tp_wait_qkv, self.attn_flags, self._st())
+            k._check(rc, "b2_decode_attention_fused")
             k.w4_linear_tp(a, L["o"][0], L["o"][1], dsc["o"], G)
             k.w4_linear_tp(x, L["gu"][0], L["gu"][1], dsc["gu"], G, prologue=1, r=o_buf, wn=L["ln_post"], eps=eps,
                            x_out=x_alt)
@@ -430,7 +447,7 @@ def decode_rate(kernels: Kernels, device, rank: int = 0, world: int = 1, cfg: Op
     return {"tp_check": tp_check, "tokens_sha1": sha, "distinct_tokens": len(set(tokens)), "tok_s": (n_new - 1) / t_decode, "ms_per_token": t_decode / (n_new - 1) * 1e3,
             "prefill_tok_s": prompt_len / t_prefill, "prompt_len": prompt_len, "n_new": n_new,
             "weight_bytes_per_token_per_rank": r.weight_bytes_per_token(), "first_tokens": tokens[:8],
-            "launches_per_token": "7 per layer + lm_head (final norm and block argmax folded in) + the pick, one CUDA graph; " +
+            "launches_per_token": "6 per layer + lm_head (final norm and block argmax folded in) + the pick, one CUDA graph; " +
                                   ("all-gathers fused into the GEMVs" if r.peer is not None else
                                    "NCCL all-gathers at the layer boundaries" if world > 1 else "one GPU")}
 

@@ -151,6 +151,47 @@ def test_decode_attention_and_rope_kv_store(kernels):
     assert close(out.view(Hq, D), ref_o[0, :, 0])
 
 
+@pytest.mark.parametrize("Hq,Hk,D,L,pos", [(8, 2, 128, 64, 37), (28, 4, 128, 1024, 0), (28, 4, 128, 1024, 599),
+                                            (28, 4, 128, 1024, 1023), (16, 2, 64, 300, 131), (4, 4, 128, 96, 95),
+                                            (8, 1, 128, 40, 40)])
+def test_fused_attention_equals_the_two_calls(kernels, Hq, Hk, D, L, pos):
+    """b2_decode_attention_fused against b2_rope_kv_store + b2_decode_attention on the same inputs: the attention
+    output and the appended cache rows must be bit-identical, qkv must be left as it was, and the arrival counters
+    must be back at zero (the launch is repeated).  pos == L: the cache is full, nothing is appended."""
+    lib = kernels.lib
+    g = torch.Generator(device="cuda").manual_seed(100 + pos)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ck = torch.randn(Hk, L, D, device="cuda", generator=g).to(torch.bfloat16)
+    cv = torch.randn(Hk, L, D, device="cuda", generator=g).to(torch.bfloat16)
+    qkv = torch.randn((Hq + 2 * Hk) * D, device="cuda", generator=g).to(torch.bfloat16)
+    bias = (0.1 * torch.randn((Hq + 2 * Hk) * D, device="cuda", generator=g)).to(torch.bfloat16)
+    inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    p = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    # the two-call form on copies
+    qkv2, ck2, cv2 = qkv.clone(), ck.clone(), cv.clone()
+    out2 = torch.empty(Hq * D, dtype=torch.bfloat16, device="cuda")
+    ws2 = torch.empty(int(lib.b2_decode_workspace_bytes(Hq, D)), dtype=torch.uint8, device="cuda")
+    assert lib.b2_rope_kv_store(qkv2.data_ptr(), bias.data_ptr(), inv.data_ptr(), p.data_ptr(), ck2.data_ptr(),
+                                cv2.data_ptr(), Hq, Hk, D, L, st) == 0
+    assert lib.b2_decode_attention(qkv2.data_ptr(), ck2.data_ptr(), cv2.data_ptr(), p.data_ptr(), out2.data_ptr(),
+                                   ws2.data_ptr(), Hq, Hk, D, L, st) == 0
+    # the fused form, twice
+    ws = torch.zeros(int(lib.b2_decode_attention_fused_workspace_bytes(Hq, Hk, D)), dtype=torch.uint8, device="cuda")
+    keep = qkv.clone()
+    for flags in (1, 1, 0):
+        ck1, cv1 = ck.clone(), cv.clone()
+        out = torch.full((Hq * D,), 7.0, dtype=torch.bfloat16, device="cuda")
+        assert lib.b2_decode_attention_fused(qkv.data_ptr(), bias.data_ptr(), inv.data_ptr(), p.data_ptr(),
+                                             ck1.data_ptr(), cv1.data_ptr(), out.data_ptr(), ws.data_ptr(), Hq, Hk, D,
+                                             L, None, None, 0, flags, st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out, out2)
+        assert torch.equal(ck1, ck2) and torch.equal(cv1, cv2)
+        assert torch.equal(qkv, keep)
+        assert int(ws[-4 * Hk:].view(torch.int32).abs().sum()) == 0
+    assert kernels.device_status() == 0
+
+
 def test_greedy_next(kernels):
     lib = kernels.lib
     V, H = 152064, 64

@@ -16,7 +16,7 @@ def _ref_logits(x, W):
     return x.float() @ W.float().T
 
 
-@pytest.mark.parametrize("M,V,K", [(1, 1000, 256), (1, 4096, 3584), (3, 777, 512), (8, 130, 128), (1, 128, 32)])
+@pytest.mark.parametrize("M,V,K", [(1, 1000, 256), (1, 4096, 3584), (3, 777, 512), (8, 130, 128), (1, 128, 64), (2, 152064 // 8, 3584)])
 def test_logits_and_block_argmax(kernels, M, V, K):
     dev = torch.device("cuda")
     gen = torch.Generator(device=dev).manual_seed(M * 1000 + V)
@@ -39,6 +39,15 @@ def test_logits_and_block_argmax(kernels, M, V, K):
         assert pv[b].item() == blk.max().item()
         first = int((blk == blk.max()).nonzero()[0])  # lowest index on ties
         assert pi[b].item() == 5000 + b * 128 + first
+
+
+def test_ragged_k_is_refused(kernels):
+    """A ring slot is 64 values of K: other K are refused on the host, nothing is launched."""
+    x = torch.ones(1, 96, dtype=torch.bfloat16, device="cuda")
+    W = torch.ones(128, 96, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="code -1"):
+        kernels.lm_head(x, W, logits=torch.empty(1, 128, dtype=torch.bfloat16, device="cuda"))
+    assert kernels.device_status() == 0
 
 
 def test_argmax_only_and_ties(kernels):

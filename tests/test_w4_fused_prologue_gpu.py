@@ -79,3 +79,44 @@ def test_prologue_error_codes(kernels):
         kernels.w4_linear_fused(x, wq, s, 128, prologue=1)
     with pytest.raises(RuntimeError, match="code -1"):
         kernels.w4_linear_fused(x, wq, s, 128, prologue=7)
+
+
+def _pairs(a, b):
+    """16 rows of a, the same 16 rows of b, the next 16 of a ..."""
+    n = a.shape[0]
+    return torch.stack([a.view(n // 16, 16, -1), b.view(n // 16, 16, -1)], 1).reshape(2 * n, -1).contiguous()
+
+
+@pytest.mark.parametrize("I,K,norm", [(18944, 3584, True), (18944, 3584, False), (2048, 1024, False), (160, 512, True)])
+def test_swiglu_pairs_epilogue(kernels, I, K, norm):
+    """gate|up with SwiGLU in its epilogue (rows in blocks of 16 gate + 16 up) against the plain launch on the
+    row-concatenated matrix followed by ns_swiglu: the same rows, the same arithmetic, so bit-identical."""
+    G = 128
+    _, Wq, S = oracle.synth_inputs(1, 2 * I, K, G, seed=47)
+    wq, s = u32_to_torch(Wq), bits_to_torch(S)
+    g = torch.Generator(device="cuda").manual_seed(I + K)
+    x = torch.randn(1, K, device="cuda", generator=g).to(torch.bfloat16)
+    r = torch.randn(1, K, device="cuda", generator=g).to(torch.bfloat16) if norm else None
+    wn = (1 + 0.1 * torch.randn(K, device="cuda", generator=g)).to(torch.bfloat16) if norm else None
+    pro = 1 if norm else 0
+    # one warp per row block along K in the plain launch too (bits 20-23 of the flags), so that both sum in one order
+    gu = kernels.w4_linear_fused(x, wq, s, G, prologue=pro, r=r, wn=wn, eps=1e-6, flags=1 << 20)
+    ref = kernels.swiglu(gu[:, :I].contiguous(), gu[:, I:].contiguous())
+    wq2, s2 = _pairs(wq[:I], wq[I:]), _pairs(s[:I], s[I:])
+    act = kernels.w4_linear_fused(x, wq2, s2, G, prologue=pro, r=r, wn=wn, eps=1e-6, epilogue=ops.EPI_SWIGLU_PAIRS)
+    torch.cuda.synchronize()
+    assert act.shape == (1, I)
+    assert torch.equal(act, ref)
+    assert kernels.device_status() == 0
+
+
+def test_swiglu_pairs_epilogue_is_refused_where_it_cannot_run(kernels):
+    """More than one token, a row count that is not whole blocks, or a group size the streaming kernel does not take:
+    code -3, nothing launched; the caller runs the plain launch and the SwiGLU prologue of the next one instead."""
+    G = 128
+    for M, N, K, grp in [(2, 256, 512, G), (1, 240, 512, G), (1, 256, 512, 64)]:
+        _, Wq, S = oracle.synth_inputs(1, N, K, grp, seed=5)
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        with pytest.raises(RuntimeError, match="code -3"):
+            kernels.w4_linear_fused(x, u32_to_torch(Wq), bits_to_torch(S), grp, epilogue=ops.EPI_SWIGLU_PAIRS)
+    assert kernels.device_status() == 0
