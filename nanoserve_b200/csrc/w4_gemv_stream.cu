@@ -65,7 +65,32 @@ struct StreamParams {
   int pstride;       // bytes between planes of the staged X
   int depth;         // ring slots per warp
   int epi;           // kEpi*
+  int cluster;       // CTAs per cluster (1: no cluster launch); they share the conversion of X
 };
+
+// ---- thread-block clusters: the CTAs of a cluster split the conversion of X and write every piece into the shared
+// memory of all of them (plain distributed-shared-memory stores), then meet at the cluster barrier
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 16 bytes into this CTA's shared memory and into the same place of every other CTA of the cluster
+template <bool CL>
+__device__ __forceinline__ void share128(uint32_t addr, const uint4& v, uint32_t crank, uint32_t csize) {
+  sts128(addr, v);
+  if constexpr (!CL) return;
+  for (uint32_t r = 0; r < csize; ++r) {
+    if (r == crank) continue;
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(addr), "r"(r));
+    asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(ra), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+  }
+}
 
 __device__ __forceinline__ uint32_t lds_u16s(uint32_t addr) {
   unsigned short v;
@@ -90,9 +115,10 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1,
 // info[chunk][column pair] = { zc, zc', up, up' }: zc = -128 * (digit sum of the chunk) -- the zero-point 8 times
 // the 16 the nibble products carry -- and up = 2^(e - 127 - (8P - 3)) * 256^p / 16 as a float.  A chunk that holds
 // an inf or a nan gets nan factors, so the outputs become nan.
-template <int P>
+template <int P, bool CL>
 __device__ __forceinline__ void stage_x_planes(const GemvParams& p, uint32_t xs_base, int pstride, uint32_t info_base,
-                                               const float* inv, int cb, int nch, int tid) {
+                                               const float* inv, int cb, int nch, int tid, uint32_t crank,
+                                               uint32_t csize) {
   constexpr int B = 8 * P;
   constexpr uint32_t kBias = P == 4 ? 0x00808080u : 0x00000080u;
   // items in flight per thread: a load from L2 takes a microsecond under the weight stream.  (Five -- all of a
@@ -103,7 +129,8 @@ __device__ __forceinline__ void stage_x_planes(const GemvParams& p, uint32_t xs_
   const int items_pad = (items + 31) & ~31;
   const int half_mp = (p.M * P) >> 1;
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-  for (int it0 = tid; it0 < items_pad; it0 += kThreads * UN) {
+  // the CTAs of a cluster take rounds of kThreads * UN items in turn
+  for (int it0 = tid + (int)crank * kThreads * UN; it0 < items_pad; it0 += kThreads * UN * (int)csize) {
     uint4 va[UN], vb[UN];
 #pragma unroll
     for (int q = 0; q < UN; ++q) {
@@ -171,7 +198,9 @@ __device__ __forceinline__ void stage_x_planes(const GemvParams& p, uint32_t xs_
         c += __shfl_xor_sync(0xffffffffu, c, 2);
         c += __shfl_xor_sync(0xffffffffu, c, 1);
         zc[l] = -128 * c;
-        if (valid) sts128(xs_base + (m * P + l) * pstride + r * 16, make_uint4(pl[l][0], pl[l][1], pl[l][2], pl[l][3]));
+        if (valid)
+          share128<CL>(xs_base + (m * P + l) * pstride + r * 16, make_uint4(pl[l][0], pl[l][1], pl[l][2], pl[l][3]), crank,
+                   csize);
       }
       if (valid && (r & 7) == 0) {
         const int ch = r >> 3;
@@ -179,8 +208,8 @@ __device__ __forceinline__ void stage_x_planes(const GemvParams& p, uint32_t xs_
         for (int j = 0; j < P / 2; ++j) {
           const uint32_t up0 = bad ? 0x7FC00000u : (uint32_t)((int)eb - B - 1 + 16 * j) << 23;
           const uint32_t up1 = bad ? 0x7FC00000u : (uint32_t)((int)eb - B + 7 + 16 * j) << 23;
-          sts128(info_base + (ch * half_mp + ((m * P) >> 1) + j) * 16,
-                 make_uint4((uint32_t)zc[2 * j], (uint32_t)zc[2 * j + 1], up0, up1));
+          share128<CL>(info_base + (ch * half_mp + ((m * P) >> 1) + j) * 16,
+                   make_uint4((uint32_t)zc[2 * j], (uint32_t)zc[2 * j + 1], up0, up1), crank, csize);
         }
       }
     }
@@ -415,7 +444,9 @@ __device__ __forceinline__ void gemv_step_one(LoopState<NT>& st, float (&fin)[1]
 // digits are non-zero only in the k-slots of the even chunk and one for the odd chunk -- 2 M P columns, eight per
 // mma.  For one token with four planes that is exactly one mma tile, and every accumulator of every lane is a real
 // partial sum.
-template <int NT, int P, int RB, bool GD1, bool ONE>
+// CL: launched in clusters of q.cluster CTAs that share the conversion of X.  The plain variant holds no cluster
+// instruction at all: with them in the code, a launch WITHOUT the cluster attribute was 0.7 us slower than before.
+template <int NT, int P, int RB, bool GD1, bool ONE, bool CL>
 __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvParams p, const StreamParams q) {
   extern __shared__ __align__(1024) unsigned char smem[];
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
@@ -429,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
   const int tpc = kWarps / q.ks;
   const int tl = warp / q.ks, sl_in = warp - tl * q.ks;
   const int row0 = blockIdx.x * tpc * kRows;               // first row of the CTA
-  const int rows_cta = min(tpc * kRows, p.N - row0);
+  const int rows_cta = max(0, min(tpc * kRows, p.N - row0));  // 0: a CTA that only pads the grid to whole clusters
   const int wrow0 = row0 + tl * kRows;                     // first row of the warp
   const int scb = blockIdx.y * q.scps, sce = min(q.nsc, scb + q.scps);  // the CTA's super-chunks of K
   const int nscc = sce - scb;
@@ -501,12 +532,17 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
   {
     float* inv = reinterpret_cast<float*>(smem + kNormInv);
     if (p.pro == kProAddRmsNorm) rmsnorm_factors<kThreads>(p, reinterpret_cast<float*>(smem + kNormSs), inv, tid);
-    stage_x_planes<P>(p, xs_base, q.pstride, info_base, inv, cb, ncc, tid);
+    uint32_t crank = 0;
+    if constexpr (CL) crank = cluster_ctarank();
+    stage_x_planes<P, CL>(p, xs_base, q.pstride, info_base, inv, cb, ncc, tid, crank, CL ? (uint32_t)q.cluster : 1u);
   }
   // The scales were copied with cp.async.wait_all semantics per thread; the weight copies of the ring are tracked by
   // their mbarriers, but wait_all waits for them as well, so only the scale copies' own group is waited for here.
   cp_async_wait_all();
-  __syncthreads();
+  if constexpr (CL)
+    cluster_sync_all();  // every CTA's share of X has landed in every CTA; nobody writes remote memory after this
+  else
+    __syncthreads();
 
   // ---- main loop
   float fin[RB][NT][4];
@@ -784,13 +820,33 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   pl.q.wrow = K / 8;
   pl.q.sc_contig = pl.nslices == 1 && (reinterpret_cast<uintptr_t>(S) & 15) == 0;
   pl.q.epi = epilogue;
+  // CTAs per cluster.  The conversion of X (M * K / 16 items; every CTA needs all of them) can go round by round of
+  // 512 items over the CTAs of a cluster, which write every piece into the shared memory of all of them.  Measured,
+  // it does not pay: a cluster launch costs more than the rounds it saves (3584 x 18944 at one token, three rounds:
+  // 13.3 us plain, 14.2 us in clusters of four; 18944 x 3584 at eight tokens, four rounds: level with the ring
+  // kernel at best), a grid that fills every SM loses 4 us with clusters of four and 7 us with eight (the CTAs of a
+  // cluster must sit in one GPC, so some SMs get two CTAs while others idle), and the mere presence of cluster
+  // instructions in a kernel made its plain launches 0.7 us slower (hence the separate instantiation).  So it is
+  // off unless B2_GEMV_CLUSTER=2|4|8 asks for it (diagnostics, and the test that keeps the path correct).
+  {
+    static const int forced = [] {
+      const char* e = std::getenv("B2_GEMV_CLUSTER");
+      const int v = e ? std::atoi(e) : 0;
+      return (v == 1 || v == 2 || v == 4 || v == 8) ? v : 0;
+    }();
+    int c = 1;
+    if (forced) c = forced;
+    while (c > 1 && pl.grid_x < c) c /= 2;
+    pl.q.cluster = c;
+    pl.grid_x = (pl.grid_x + c - 1) / c * c;
+  }
   *out = pl;
   return true;
 }
 
-template <int NT, int P, int RB, bool GD1, bool ONE>
+template <int NT, int P, int RB, bool GD1, bool ONE, bool CL>
 int launch_stream_g(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStream_t stream) {
-  auto kernel = w4_gemv_stream_kernel<NT, P, RB, GD1, ONE>;
+  auto kernel = w4_gemv_stream_kernel<NT, P, RB, GD1, ONE, CL>;
   // Raising the dynamic shared-memory limit and the carve-out is remembered per device: done once.
   static bool attr_done[64] = {};
   int dev = 0;
@@ -807,19 +863,33 @@ int launch_stream_g(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStr
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (pl.q.cluster > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = pl.q.cluster;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = na;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p, pl.q);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 template <int NT, int P, int RB, bool ONE>
 int launch_stream(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStream_t stream) {
-  return p.gdiv == 1 ? launch_stream_g<NT, P, RB, true, ONE>(p, pl, pdl, stream)
-                     : launch_stream_g<NT, P, RB, false, ONE>(p, pl, pdl, stream);
+  if (pl.q.cluster > 1)
+    return p.gdiv == 1 ? launch_stream_g<NT, P, RB, true, ONE, true>(p, pl, pdl, stream)
+                       : launch_stream_g<NT, P, RB, false, ONE, true>(p, pl, pdl, stream);
+  return p.gdiv == 1 ? launch_stream_g<NT, P, RB, true, ONE, false>(p, pl, pdl, stream)
+                     : launch_stream_g<NT, P, RB, false, ONE, false>(p, pl, pdl, stream);
 }
 
 }  // namespace
@@ -830,11 +900,13 @@ bool gemv_stream_applies(const void* Wq, int M, int N, int K, int G, int flags) 
     return false;
   if (flags & kFlagStreamKernel) return true;
   // Which kernel is faster, from measurements on the 7B-shaped and 70B-class linears (chained launches, weights from
-  // DRAM): one token always streams; two tokens unless the matrix is of the 70B class; three to eight tokens only on
+  // DRAM): one token always streams; two tokens on the large 7B-shaped matrices (gate/up, down) but not on the small
+  // ones (q, k, v, o: the ring kernel is 0.7 us shorter there) nor on the 70B class; three to eight tokens only on
   // tall matrices with a short K (gate/up), where the staging of M x K activations per CTA stays small.
   const long weights = (long)N * K;
   if (M == 1) return true;
-  if (M == 2) return weights <= 160l << 20;
+  if (weights > 160l << 20) return false;
+  if (M == 2) return N >= 8192 || K >= 8192;
   if (M <= 4) return K <= 4096 && N >= 8192;
   if (M <= 8) return K <= 4096 && N >= 32768;
   return false;

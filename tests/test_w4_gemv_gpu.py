@@ -325,3 +325,40 @@ def test_against_reference_kernels(kernels, N, K, M):
     tol = torch.maximum(a.abs(), b.abs()) * 2.0**-7 + 1e-5 * b.abs().max()
     assert torch.all((a - b).abs() <= tol)
     assert (a != b).float().mean().item() < 0.02
+
+
+def test_cluster_shared_staging_in_a_child_process():
+    """B2_GEMV_CLUSTER is read once per process, so the cluster variant of the streaming kernel (CTAs of a cluster
+    convert X in turns and write into each other's shared memory) is exercised in a child: same outputs as the
+    plain variant, bit for bit, on a shape with several conversion rounds and on a ragged one."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import sys, torch
+sys.path.insert(0, %r)
+from nanoserve_b200.ops import Kernels, FLAG_STREAM_KERNEL
+k = Kernels(); k.init()
+g = torch.Generator(device="cuda").manual_seed(7)
+out = []
+for M, N, K in [(1, 3584, 18944), (8, 4000, 3584), (3, 72, 1024)]:
+    Wq = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, device="cuda", generator=g)
+    S = (0.005 + (torch.randn(N, K // 128, device="cuda", generator=g) * 0.01).abs()).to(torch.bfloat16)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    y = k.w4_linear(x, Wq, S, 128, flags=FLAG_STREAM_KERNEL)
+    torch.cuda.synchronize()
+    out.append(y.view(torch.int16).cpu())
+assert k.device_status() == 0
+torch.save(out, sys.argv[1])
+''' % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    import tempfile
+    res = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        for c in ("1", "4", "2"):
+            path = os.path.join(tmp, f"y{c}.pt")
+            env = dict(os.environ, B2_GEMV_CLUSTER=c)
+            subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=600)
+            res[c] = torch.load(path)
+    for c in ("4", "2"):
+        for a, b in zip(res["1"], res[c]):
+            assert torch.equal(a, b)
