@@ -174,8 +174,8 @@ int b2_w4_gemv_noalloc(const void* X, const void* Wq, const void* S, void* Y, in
  *     (an arrival counter per KV head; nobody waits), which puts a fence, an atomic and the merge's two L2 round
  *     trips behind the slowest CTA.  Results are bit-identical to the two calls above either way.
  *     workspace: b2_decode_attention_fused_workspace_bytes(Hq, Hk, D) bytes, ZEROED once by the caller (the counters
- *     at its end return to zero after every launch).  wait_sig / epoch / wait_per_epoch: NULL / NULL / 0, or the
- *     arrival counter of the tensor-parallel GEMV that produced qkv (see b2_w4_linear_tp): the kernel waits on it.
+ *     at its end return to zero after every launch).  tp: NULL, or the consumer side (wait_sig, epoch,
+ *     wait_per_epoch, announce_peer) of the tensor-parallel GEMV that produced qkv (see b2_tp_desc).
  *   b2_greedy_next: token = argmax(logits[0..V)) (lowest index on ties); out_tokens[*step] = token; *step += 1;
  *     *pos += 1; x_next[0..H) = embed[token].  pos, step: int32 on the device; out_tokens: int64 on the device.
  */
@@ -183,11 +183,11 @@ int b2_rope_kv_store(void* qkv, const void* bias, const void* inv_freq, const vo
                      int Hq, int Hk, int D, int max_len, void* stream);
 int b2_decode_attention(const void* q, const void* cache_k, const void* cache_v, const void* pos, void* out,
                         void* workspace, int Hq, int Hk, int D, int max_len, void* stream);
+typedef struct b2_tp_desc b2_tp_desc; /* defined below, with the tensor-parallel entry points */
 size_t b2_decode_attention_fused_workspace_bytes(int Hq, int Hk, int D);
 int b2_decode_attention_fused(const void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
                               void* cache_v, void* out, void* workspace, int Hq, int Hk, int D, int max_len,
-                              const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int flags,
-                              void* stream);
+                              const b2_tp_desc* tp, int flags, void* stream);
 int b2_greedy_next(const void* logits, int V, const void* embed, int H, void* pos, void* out_tokens, void* step,
                    void* x_next, void* workspace, void* stream);
 /*
@@ -239,10 +239,22 @@ typedef struct b2_tp_desc {
   const void* wait_sig;
   const void* epoch;
   unsigned wait_per_epoch;
+  /* Deferred signal (the cheaper protocol: a producer that signals for itself pays a fence per CTA and a release per
+   * launch, about 4.5 us, before it may end).  A producer with defer_signal set stores its outputs and ends; sig_peer
+   * is not used.  The NEXT kernel of the same stream -- the consumer of some other gathered row, as a rule -- has
+   * seen that producer complete when it starts reading, and then adds one to announce_peer[0..announce_world): the
+   * arrival counters, one per rank, that the producer would have signalled.  wait_per_epoch of such a counter is the
+   * number of ranks (x producing launches per use). */
+  int defer_signal;
+  int announce_world;
+  void* announce_peer[8];
 } b2_tp_desc;
 int b2_w4_linear_tp(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, int prologue,
                     const void* R, const void* Wn, float eps, void* Xout, const b2_tp_desc* tp, int flags,
                     void* stream);
+/* The consumer side of a descriptor as a small kernel of its own (announce, wait, and with advance_epoch != 0 add one
+ * to *epoch afterwards): behind the last producer of a step, or in front of a consumer that is not a GEMV. */
+int b2_tp_wait_desc(const b2_tp_desc* tp, int advance_epoch, void* stream);
 /* CTAs the decode GEMV launches for this shape on the current device (0: not served by the GEMV). */
 size_t b2_w4_gemv_grid(int M, int N, int K, int G, int flags);
 int b2_rope_kv_store_tp(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,

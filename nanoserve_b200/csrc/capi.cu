@@ -87,6 +87,37 @@ int linear_dispatch(const void* X, const void* Wq, const void* S, void* Y, int M
   return b2::gemm_launch(X, Wq, S, Y, M, N, K, G, st->ws, flags, st->sm_count, s);
 }
 
+// The public descriptor as the kernels take it.
+int to_gemv_tp(const b2_tp_desc* tp, b2::GemvTp* out) {
+  b2::GemvTp t;
+  if (tp->world < 0 || tp->world > b2::kMaxTpRanks || tp->announce_world < 0 || tp->announce_world > b2::kMaxTpRanks)
+    return b2::kErrBadShape;
+  t.world = tp->world;
+  for (int r = 0; r < tp->world; ++r) {
+    t.y_peer[r] = tp->y_peer[r];
+    t.sig_peer[r] = static_cast<unsigned*>(tp->sig_peer[r]);
+  }
+  t.ld = tp->ld;
+  t.seg_end[0] = tp->seg_end[0];
+  t.seg_end[1] = tp->seg_end[1];
+  for (int i = 0; i < 3; ++i) t.seg_dst[i] = tp->seg_dst[i];
+  t.wait_sig = static_cast<const unsigned*>(tp->wait_sig);
+  t.epoch = static_cast<const int*>(tp->epoch);
+  t.wait_per_epoch = tp->wait_per_epoch;
+  t.defer = tp->defer_signal;
+  t.announce_world = tp->announce_world;
+  for (int r = 0; r < tp->announce_world; ++r) {
+    if (!tp->announce_peer[r] || (reinterpret_cast<uintptr_t>(tp->announce_peer[r]) & 3)) return b2::kErrBadPointer;
+    t.announce_peer[r] = static_cast<unsigned*>(tp->announce_peer[r]);
+  }
+  if (t.defer && t.world > 0) {  // the signal pointers are not used
+    for (int r = 0; r < t.world; ++r)
+      if (!t.sig_peer[r]) t.sig_peer[r] = reinterpret_cast<unsigned*>(t.y_peer[r]);
+  }
+  *out = t;
+  return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -134,20 +165,8 @@ int b2_w4_linear_tp(const void* X, const void* Wq, const void* S, int M, int N, 
   pro.Xout = Xout;
   pro.eps = eps;
   b2::GemvTp t;
-  if (tp->world < 0 || tp->world > b2::kMaxTpRanks) return b2::kErrBadShape;
+  if (const int bad = to_gemv_tp(tp, &t)) return bad;
   if (tp->world == 0 && !tp->wait_sig) return b2::kErrBadShape;  // nothing tensor-parallel about this call
-  t.world = tp->world;
-  for (int r = 0; r < tp->world; ++r) {
-    t.y_peer[r] = tp->y_peer[r];
-    t.sig_peer[r] = static_cast<unsigned*>(tp->sig_peer[r]);
-  }
-  t.ld = tp->ld;
-  t.seg_end[0] = tp->seg_end[0];
-  t.seg_end[1] = tp->seg_end[1];
-  for (int i = 0; i < 3; ++i) t.seg_dst[i] = tp->seg_dst[i];
-  t.wait_sig = static_cast<const unsigned*>(tp->wait_sig);
-  t.epoch = static_cast<const int*>(tp->epoch);
-  t.wait_per_epoch = tp->wait_per_epoch;
   void* y = tp->world > 0 ? tp->y_peer[0] : tp->y_local;
   return b2::gemv_launch_ex(X, Wq, S, y, M, N, K, G, pro, st->ws, flags, st->sm_count,
                             static_cast<cudaStream_t>(stream), &t);
@@ -167,6 +186,17 @@ int b2_tp_wait(const void* wait_sig, const void* epoch, unsigned wait_per_epoch,
   return b2::tp_wait_launch(wait_sig, epoch, wait_per_epoch, st->ws.status, static_cast<cudaStream_t>(stream));
 }
 
+int b2_tp_wait_desc(const b2_tp_desc* tp, int advance_epoch, void* stream) {
+  if (!tp) return b2::kErrBadPointer;
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return rc;
+  b2::GemvTp t;
+  if (const int bad = to_gemv_tp(tp, &t)) return bad;
+  return b2::tp_wait_launch(tp->wait_sig, tp->epoch, tp->wait_per_epoch, st->ws.status,
+                            static_cast<cudaStream_t>(stream), &t, advance_epoch);
+}
+
 int b2_rope_kv_store_tp(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
                         void* cache_v, int Hq, int Hk, int D, int max_len, const void* wait_sig, const void* epoch,
                         unsigned wait_per_epoch, void* stream) {
@@ -179,17 +209,18 @@ int b2_rope_kv_store_tp(void* qkv, const void* bias, const void* inv_freq, const
 
 int b2_decode_attention_fused(const void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
                               void* cache_v, void* out, void* workspace, int Hq, int Hk, int D, int max_len,
-                              const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int flags,
-                              void* stream) {
+                              const b2_tp_desc* tp, int flags, void* stream) {
   int* status = nullptr;
-  if (wait_sig != nullptr) {  // only a wait can time out
+  b2::GemvTp t;
+  if (tp != nullptr) {  // only a wait can time out
     int rc = 0;
     DeviceState* st = device_state(&rc);
     if (!st) return rc;
     status = st->ws.status;
+    if (const int bad = to_gemv_tp(tp, &t)) return bad;
   }
   return b2::decode_attention_fused_launch(qkv, bias, inv_freq, pos, cache_k, cache_v, out, workspace, Hq, Hk, D,
-                                           max_len, wait_sig, epoch, wait_per_epoch, flags, status,
+                                           max_len, tp != nullptr ? &t : nullptr, flags, status,
                                            static_cast<cudaStream_t>(stream));
 }
 

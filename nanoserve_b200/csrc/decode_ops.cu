@@ -242,7 +242,7 @@ template <int D>
 __global__ void __launch_bounds__(256) decode_attention_fused_kernel(
     const bf16* qkv, const bf16* __restrict__ bias, const float* __restrict__ inv_freq, const int* pos_ptr,
     bf16* cache_k, bf16* cache_v, float* part, int* counters, bf16* out, int Hq, int Hk, int max_len, float scale,
-    const unsigned* wait_sig, const int* epoch, unsigned wait_per_epoch, int* status) {
+    const unsigned* wait_sig, const int* epoch, unsigned wait_per_epoch, int* status, const b2::GemvTp ann) {
   constexpr int E = D / 32;        // elements per lane
   constexpr int kRowU4 = D / 8;    // 16-byte units per row
   constexpr int half = D / 2;
@@ -256,6 +256,9 @@ __global__ void __launch_bounds__(256) decode_attention_fused_kernel(
   const int kh = blockIdx.x, sp = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rep = Hq / Hk;
   pdl_begin();
+  // deferred signal of the tensor-parallel GEMV in front of this kernel (it has completed: see pdl_begin)
+  if (ann.announce_world && blockIdx.x == 0 && blockIdx.y == 0 && tid < ann.announce_world)
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ann.announce_peer[tid]) : "memory");
   if (wait_sig != nullptr) {
     if (tid == 0) {
       const unsigned target = ((unsigned)*reinterpret_cast<const volatile int*>(epoch) + 1u) * wait_per_epoch;
@@ -513,7 +516,12 @@ __global__ void __launch_bounds__(256) greedy_finish_kernel(const float* __restr
 
 // One thread waits (bounded) for an arrival counter of a fused all-gather: kernels that follow on the stream may then
 // read the gathered rows without a wait of their own.
-__global__ void tp_wait_kernel(const unsigned* wait_sig, const int* epoch, unsigned wait_per_epoch, int* status) {
+__global__ void tp_wait_kernel(const unsigned* wait_sig, int* epoch, unsigned wait_per_epoch, int* status,
+                               const b2::GemvTp ann, int advance_epoch) {
+  // deferred signal of the kernel in front of this one (complete: plain stream order), one thread per rank
+  if (threadIdx.x < ann.announce_world)
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ann.announce_peer[threadIdx.x]) : "memory");
+  if (threadIdx.x != 0) return;
   const unsigned target = ((unsigned)*reinterpret_cast<const volatile int*>(epoch) + 1u) * wait_per_epoch;
   const long long t0 = clock64();
   for (;;) {
@@ -526,13 +534,18 @@ __global__ void tp_wait_kernel(const unsigned* wait_sig, const int* epoch, unsig
     }
     __nanosleep(40);
   }
+  if (advance_epoch) *epoch += 1;  // the use of the counters that this wait closes is over
 }
 
 namespace b2 {
-int tp_wait_launch(const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int* status, cudaStream_t stream) {
+int tp_wait_launch(const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int* status, cudaStream_t stream,
+                   const GemvTp* announce, int advance_epoch) {
   if (!wait_sig || !epoch) return kErrBadPointer;
-  tp_wait_kernel<<<1, 1, 0, stream>>>(static_cast<const unsigned*>(wait_sig), static_cast<const int*>(epoch),
-                                      wait_per_epoch, status);
+  GemvTp ann;
+  if (announce != nullptr) ann = *announce;
+  tp_wait_kernel<<<1, 32, 0, stream>>>(static_cast<const unsigned*>(wait_sig),
+                                       static_cast<int*>(const_cast<void*>(epoch)), wait_per_epoch, status, ann,
+                                       advance_epoch);
   return (int)cudaGetLastError();
 }
 int rope_kv_store_launch(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
@@ -559,12 +572,16 @@ int rope_kv_store_launch(void* qkv, const void* bias, const void* inv_freq, cons
 namespace b2 {
 int decode_attention_fused_launch(const void* qkv, const void* bias, const void* inv_freq, const void* pos,
                                   void* cache_k, void* cache_v, void* out, void* workspace, int Hq, int Hk, int D,
-                                  int max_len, const void* wait_sig, const void* epoch, unsigned wait_per_epoch,
-                                  int flags, int* status, cudaStream_t stream) {
+                                  int max_len, const GemvTp* tp, int flags, int* status, cudaStream_t stream) {
   static_assert(kSplits == 32, "the merge takes one split per lane");
   if (Hq < 1 || Hk < 1 || Hq % Hk || Hq / Hk > 8 || max_len < 1) return b2::kErrBadShape;
   if (D != 128 && D != 64) return b2::kErrNotImplemented;
   if (!qkv || !inv_freq || !cache_k || !cache_v || !pos || !out || !workspace) return b2::kErrBadPointer;
+  GemvTp ann;
+  if (tp != nullptr) ann = *tp;
+  const void* wait_sig = ann.wait_sig;
+  const void* epoch = ann.epoch;
+  const unsigned wait_per_epoch = ann.wait_per_epoch;
   if (wait_sig != nullptr && !epoch) return b2::kErrBadPointer;
   // 8-byte loads of q, 16-byte loads and stores of cache rows, float partials and counters in the workspace
   if ((reinterpret_cast<uintptr_t>(qkv) & 7) || (reinterpret_cast<uintptr_t>(bias) & 3) ||
@@ -582,7 +599,8 @@ int decode_attention_fused_launch(const void* qkv, const void* bias, const void*
                       static_cast<const bf16*>(bias), static_cast<const float*>(inv_freq),
                       static_cast<const int*>(pos), static_cast<bf16*>(cache_k), static_cast<bf16*>(cache_v), part,
                       counters, static_cast<bf16*>(out), Hq, Hk, max_len, scale,
-                      static_cast<const unsigned*>(wait_sig), static_cast<const int*>(epoch), wait_per_epoch, status);
+                      static_cast<const unsigned*>(wait_sig), static_cast<const int*>(epoch), wait_per_epoch, status,
+                      ann);
   };
   cudaError_t e = D == 128 ? go(decode_attention_fused_kernel<128>) : go(decode_attention_fused_kernel<64>);
   if (e == cudaSuccess && !one_launch) {

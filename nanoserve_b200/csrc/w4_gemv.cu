@@ -613,7 +613,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
         }
       }
     }
-    if (p.tp.world) tp_signal(p.tp, lane);  // every CTA counts itself in once, after its last store
+    if (p.tp.world && !p.tp.defer) tp_signal(p.tp, lane);  // every CTA counts itself in once, after its last store
   } else {
     // ------------------------------------------------------------ consumer warps
     const int g = lane >> 2, t = lane & 3;
@@ -642,6 +642,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, (MT == 1 && NCW <= 12) ? 2 : 1
     // running: the weight stream (constant data) is already flowing; X, produced upstream, is touched only
     // after the previous grid has completed and flushed.
     pdl_wait_prior_grid();
+    if (p.tp.announce_world && blockIdx.x == 0 && ctid < 32) tp_announce(p.tp, ctid);
     if (p.tp.wait_sig != nullptr) {
       // the input is the gathered output of the producing kernels of every rank: wait until all their CTAs have
       // counted themselves in (their stores are visible by then)
@@ -1513,7 +1514,7 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
   p.eps = pro.eps;
   if (tp != nullptr) {
     p.tp = *tp;
-    if (tp->world > 0) {
+    if (tp->world > 0 && !tp->defer) {
       if (!ws.counters || ws.n_counters < 2) return kErrWorkspace;
       p.tp.local_count = ws.counters + ws.n_counters - 1;  // the last counter is never used by split-K (see make_plan)
     }

@@ -262,6 +262,13 @@ __device__ __forceinline__ void tp_signal(const GemvTp& tp, int lane) {
     asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(tp.sig_peer[lane]) : "memory");
   }
 }
+// Deferred signal, consumer side: called by one warp of one CTA after the kernel has seen the previous kernel of its
+// stream complete (programmatic wait or plain stream order).  That kernel's stores into the peers' memory happen
+// before this release in causality order, so a peer that acquires the counter sees them.
+__device__ __forceinline__ void tp_announce(const GemvTp& tp, int lane) {
+  if (lane < tp.announce_world)
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(tp.announce_peer[lane]) : "memory");
+}
 // Waits (bounded) until every producing launch of every rank has counted itself in on this rank's counter for the
 // current epoch.  One thread polls; the caller synchronises the rest.  Returns false on time-out.
 __device__ __forceinline__ bool tp_wait(const GemvTp& tp, volatile int* abort_flag) {

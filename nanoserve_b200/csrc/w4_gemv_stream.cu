@@ -523,6 +523,7 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
 
   // ---- everything below depends on the previous kernel of the stream
   pdl_wait_prior_grid();
+  if (p.tp.announce_world && blockIdx.x == 0 && blockIdx.y == 0 && warp == 0) tp_announce(p.tp, lane);
   if (p.tp.wait_sig != nullptr) {
     if (tid == 0) tp_wait(p.tp, abort_flag);
     __syncthreads();
@@ -717,7 +718,7 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
         store_out4(p, m, n0, make_float4(f[0], f[1], f[2], f[3]));
       }
     }
-    if (p.tp.world) {
+    if (p.tp.world && !p.tp.defer) {
       __syncthreads();
       if (warp == 0) tp_signal(p.tp, lane);
     }
@@ -964,7 +965,7 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
   p.eps = pro.eps;
   if (tp != nullptr) {
     p.tp = *tp;
-    if (tp->world > 0) {
+    if (tp->world > 0 && !tp->defer) {
       if (!ws.counters || ws.n_counters < 2) return kErrWorkspace;
       p.tp.local_count = ws.counters + ws.n_counters - 1;
     }

@@ -96,6 +96,12 @@ struct GemvTp {
   const int* epoch = nullptr;
   unsigned wait_per_epoch = 0;
   int* local_count = nullptr;
+  // Deferred signal: a producer with `defer` set stores its outputs and does nothing else; the NEXT kernel of the
+  // same stream, once it has seen that producer complete, adds one to announce_peer[0..announce_world) before it
+  // waits for its own input.
+  int defer = 0;
+  unsigned* announce_peer[kMaxTpRanks] = {};
+  int announce_world = 0;
 };
 
 int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
@@ -111,11 +117,11 @@ int quantize_launch(const void* W, void* Wq, void* S, int N, int K, int G, cudaS
 
 int decode_attention_fused_launch(const void* qkv, const void* bias, const void* inv_freq, const void* pos,
                                   void* cache_k, void* cache_v, void* out, void* workspace, int Hq, int Hk, int D,
-                                  int max_len, const void* wait_sig, const void* epoch, unsigned wait_per_epoch,
-                                  int flags, int* status, cudaStream_t stream);
+                                  int max_len, const GemvTp* tp, int flags, int* status, cudaStream_t stream);
 // The status word of the current device's scratch (created on first use); rc receives 0 or an error code.
 int* device_status_word(int* rc);
-int tp_wait_launch(const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int* status, cudaStream_t stream);
+int tp_wait_launch(const void* wait_sig, const void* epoch, unsigned wait_per_epoch, int* status, cudaStream_t stream,
+                   const GemvTp* announce = nullptr, int advance_epoch = 0);
 int rope_kv_store_launch(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
                          void* cache_v, int Hq, int Hk, int D, int max_len, const void* wait_sig, const void* epoch,
                          unsigned wait_per_epoch, int* status, cudaStream_t stream);

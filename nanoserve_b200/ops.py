@@ -59,7 +59,8 @@ SIGNATURES = {
     "b2_greedy_pick": ([_vp, _vp, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp], _i32),
     "b2_w4_linear_tp": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _f32, _vp, _vp, _i32, _vp], _i32),
     "b2_w4_gemv_grid": ([_i32, _i32, _i32, _i32, _i32], ctypes.c_size_t),
-    "b2_decode_attention_fused": ([_vp] * 8 + [_i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_uint, _i32, _vp], _i32),
+    "b2_decode_attention_fused": ([_vp] * 8 + [_i32, _i32, _i32, _i32, _vp, _i32, _vp], _i32),
+    "b2_tp_wait_desc": ([_vp, _i32, _vp], _i32),
     "b2_decode_attention_fused_workspace_bytes": ([_i32, _i32, _i32], ctypes.c_size_t),
     "b2_rope_kv_store_tp": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_uint, _vp], _i32),
     "b2_tp_wait": ([_vp, _vp, ctypes.c_uint, _vp], _i32),
@@ -71,16 +72,25 @@ class TpDesc(ctypes.Structure):
     """struct b2_tp_desc of include/nanoserve_b200.h."""
     _fields_ = [("world", _i32), ("y_peer", _vp * 8), ("sig_peer", _vp * 8), ("ld", _i64), ("seg_end", _i32 * 2),
                 ("seg_dst", _i32 * 3), ("y_local", _vp), ("wait_sig", _vp), ("epoch", _vp),
-                ("wait_per_epoch", ctypes.c_uint)]
+                ("wait_per_epoch", ctypes.c_uint), ("defer_signal", _i32), ("announce_world", _i32),
+                ("announce_peer", _vp * 8)]
 
 
 def make_tp_desc(y_peers=(), sig_peers=(), ld=0, pieces=None, y_local=None, wait_sig=None, epoch=None,
-                 wait_per_epoch=0) -> TpDesc:
-    """pieces: [(local_width, gathered_column), ...] of the row-concatenated local shard (at most three)."""
+                 wait_per_epoch=0, defer=False, announce_peers=()) -> TpDesc:
+    """pieces: [(local_width, gathered_column), ...] of the row-concatenated local shard (at most three).
+    defer: the producer only stores; announce_peers: the counters (one per rank) this call adds one to once the kernel
+    in front of it on the stream has completed (see struct b2_tp_desc)."""
     d = TpDesc()
     d.world = len(y_peers)
-    for r, (y, sg) in enumerate(zip(y_peers, sig_peers)):
-        d.y_peer[r], d.sig_peer[r] = y, sg
+    for r, y in enumerate(y_peers):
+        d.y_peer[r] = y
+    for r, sg in enumerate(sig_peers):
+        d.sig_peer[r] = sg
+    d.defer_signal = 1 if defer else 0
+    d.announce_world = len(announce_peers)
+    for r, a in enumerate(announce_peers):
+        d.announce_peer[r] = a
     d.ld = ld
     ends, dst, acc = [0x7FFFFFFF, 0x7FFFFFFF], [0, 0, 0], 0
     for i, (w, col) in enumerate(pieces or []):
@@ -244,6 +254,11 @@ class Kernels:
 
     def tp_wait(self, wait_sig: int, epoch: int, wait_per_epoch: int):
         self._check(self.lib.b2_tp_wait(wait_sig, epoch, wait_per_epoch, self._stream()), "b2_tp_wait")
+
+    def tp_wait_desc(self, desc: "TpDesc", advance_epoch: bool = False):
+        """The consumer side of a descriptor as a kernel of its own: announce, wait, optionally *epoch += 1."""
+        self._check(self.lib.b2_tp_wait_desc(ctypes.byref(desc), 1 if advance_epoch else 0, self._stream()),
+                    "b2_tp_wait_desc")
 
     def gemv_grid(self, M, N, K, group=128, flags=0) -> int:
         return int(self.lib.b2_w4_gemv_grid(M, N, K, group, flags))

@@ -142,31 +142,34 @@ class Qwen2Runner:
         """Symmetric buffers for the four gathered rows of a layer (shared by all layers: a rank cannot pass a wait
         before every rank has delivered, so it is never more than one boundary ahead of the slowest rank and a buffer
         is consumed everywhere before anyone overwrites it), four arrival counters per layer, and the descriptors of
-        every tensor-parallel launch."""
+        every tensor-parallel launch.  Signals are deferred: a GEMV only stores into the peers' rows; the kernel behind
+        it on the stream announces it (one release per rank) before waiting for its own input."""
         from .tp import PeerBuffers
         cfg, k, P, r = self.cfg, self.k, self.world, self.rank
         H, I, nq, nkv, G = cfg.hidden, self.I, self.nq, self.nkv, cfg.group
         self.peer = peer = PeerBuffers({"qkv": nq + 2 * nkv, "o": H, "gu": 2 * I, "d": H}, 4 * cfg.n_layers,
                                        self.dev, self.group)
         ep = peer.epoch.data_ptr()
-        g_qkv = g_o = g_gu = g_d = P  # signals per use of a counter: one per producing launch and rank
-        self.tp_wait_d = g_d
-        self.tp_wait_qkv = g_qkv
         self.tp_desc = []
+
+        def after(c):
+            """Consumer side of boundary c: announce this rank's producer of c (the kernel in front on the stream),
+            then wait until every rank has announced its own."""
+            return dict(wait_sig=peer.counter(c), epoch=ep, wait_per_epoch=P, announce_peers=peer.counter_peers(c))
+
         for li in range(cfg.n_layers):
             c = 4 * li
-            wait_prev = dict(wait_sig=peer.counter(c - 1), epoch=ep, wait_per_epoch=g_d) if li > 0 else {}
             self.tp_desc.append({
-                "qkv": make_tp_desc(peer.peers("qkv"), peer.counter_peers(c), ld=nq + 2 * nkv,
+                "qkv": make_tp_desc(peer.peers("qkv"), ld=nq + 2 * nkv, defer=True,
                                     pieces=[(nq // P, r * nq // P), (nkv // P, nq + r * nkv // P),
-                                            (nkv // P, nq + nkv + r * nkv // P)], **wait_prev),
-                "o": make_tp_desc(peer.peers("o"), peer.counter_peers(c + 1), ld=H, pieces=[(H // P, r * H // P)]),
-                "gu": make_tp_desc(peer.peers("gu"), peer.counter_peers(c + 2), ld=2 * I,
-                                   pieces=[(I // P, r * I // P), (I // P, I + r * I // P)],
-                                   wait_sig=peer.counter(c + 1), epoch=ep, wait_per_epoch=g_o),
-                "d": make_tp_desc(peer.peers("d"), peer.counter_peers(c + 3), ld=H, pieces=[(H // P, r * H // P)],
-                                  wait_sig=peer.counter(c + 2), epoch=ep, wait_per_epoch=g_gu),
+                                            (nkv // P, nq + nkv + r * nkv // P)], **(after(c - 1) if li > 0 else {})),
+                "attn": make_tp_desc(**after(c)),
+                "o": make_tp_desc(peer.peers("o"), ld=H, pieces=[(H // P, r * H // P)], defer=True),
+                "gu": make_tp_desc(peer.peers("gu"), ld=2 * I, defer=True,
+                                   pieces=[(I // P, r * I // P), (I // P, I + r * I // P)], **after(c + 1)),
+                "d": make_tp_desc(peer.peers("d"), ld=H, pieces=[(H // P, r * H // P)], defer=True, **after(c + 2)),
             })
+        self.tp_tail = make_tp_desc(**after(4 * cfg.n_layers - 1))
 
     # ------------------------------------------------------------------ helpers
     def weight_bytes_per_token(self) -> int:
@@ -297,7 +300,7 @@ class Qwen2Runner:
             rc = lib.b2_decode_attention_fused(qkv.data_ptr(), L["bias"].data_ptr(), self.inv_freq.data_ptr(),
                                                self.pos.data_ptr(), self.cache_k[li].data_ptr(),
                                                self.cache_v[li].data_ptr(), a.data_ptr(), self.attn_ws.data_ptr(),
-                                               cfg.n_heads, cfg.n_kv_heads, D, self.max_len, None, None, 0, self.attn_flags,
+                                               cfg.n_heads, cfg.n_kv_heads, D, self.max_len, None, self.attn_flags,
                                                self._st())
             k._check(rc, "b2_decode_attention_fused")
             o = self._gather(self.linear(a, L["o"]))
@@ -340,18 +343,16 @@ class Qwen2Runner:
             rc = lib.b2_decode_attention_fused(qkv_buf.data_ptr(), L["bias"].data_ptr(), self.inv_freq.data_ptr(),
                                                self.pos.data_ptr(), self.cache_k[li].data_ptr(),
                                                self.cache_v[li].data_ptr(), a.data_ptr(), self.attn_ws.data_ptr(),
-                                               cfg.n_heads, cfg.n_kv_heads, D, self.max_len, peer.counter(4 * li), ep,
-                                               self.tp_wait_qkv, self.attn_flags, self._st())
+                                               cfg.n_heads, cfg.n_kv_heads, D, self.max_len,
+                                               ctypes.byref(dsc["attn"]), self.attn_flags, self._st())
             k._check(rc, "b2_decode_attention_fused")
             k.w4_linear_tp(a, L["o"][0], L["o"][1], dsc["o"], G)
             k.w4_linear_tp(x, L["gu"][0], L["gu"][1], dsc["gu"], G, prologue=1, r=o_buf, wn=L["ln_post"], eps=eps,
                            x_out=x_alt)
             x, x_alt = x_alt, x
             k.w4_linear_tp(gu_buf, L["d"][0], L["d"][1], dsc["d"], G, prologue=2)
-        k.tp_wait(peer.counter(4 * cfg.n_layers - 1), ep, self.tp_wait_d)
-        logits = self._lm_head_and_pick(x, d_buf, self.final_norm)
-        peer.epoch.add_(1)
-        return logits
+        k.tp_wait_desc(self.tp_tail, advance_epoch=True)  # the last down projection; closes the step's epoch
+        return self._lm_head_and_pick(x, d_buf, self.final_norm)
 
     def capture(self):
         """Warms up and captures one decode step.  The warm-up steps advance the device state; callers that

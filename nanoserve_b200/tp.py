@@ -156,7 +156,7 @@ class ShardedLayer:
         """Builds the row-concatenated matrices (a copy: 7 matrices -> 4) and, with peer buffers attached, the
         descriptors of the four tensor-parallel launches.  Each launch also waits, before it reads its input, for
         the previous launch's gathered row -- the consumer-side wait of a decode step -- so a pass needs no wait
-        kernels except one behind the last launch."""
+        kernels except one behind the last launch (which also advances the epoch)."""
         from .ops import make_tp_desc
         self.fused = {}
         for fname, names in self.FUSED:
@@ -172,10 +172,15 @@ class ShardedLayer:
             for w in widths:
                 pieces.append((w // P, col + r * (w // P)))
                 col += w
-            wait = dict(wait_sig=peer.counter(prev), epoch=peer.epoch.data_ptr(), wait_per_epoch=P) if prev is not None else {}
-            self.fdescs[fname] = make_tp_desc(y_peers=peer.peers(fname), sig_peers=peer.counter_peers(b), ld=col,
-                                              pieces=pieces, **wait)
+            # deferred signal: a launch only stores; the next launch, which has seen it complete, announces it to
+            # every rank and waits until every rank has announced its own
+            wait = dict(wait_sig=peer.counter(prev), epoch=peer.epoch.data_ptr(), wait_per_epoch=P,
+                        announce_peers=peer.counter_peers(prev)) if prev is not None else {}
+            self.fdescs[fname] = make_tp_desc(y_peers=peer.peers(fname), ld=col, pieces=pieces, defer=True, **wait)
             prev = b
+        # behind the last launch: announce it, wait for everybody's, close the epoch
+        self.tail_desc = make_tp_desc(wait_sig=peer.counter(prev), epoch=peer.epoch.data_ptr(), wait_per_epoch=P,
+                                      announce_peers=peer.counter_peers(prev))
 
     def decode_pass_fused4(self, x: torch.Tensor, act: torch.Tensor,
                            outs: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
@@ -195,8 +200,7 @@ class ShardedLayer:
             Wq, S = self.fused[fname]
             k.w4_linear_tp(act if fname == "down" else x, Wq, S, self.fdescs[fname], self.G, flags=self.flags)
             outs.append(peer.local(fname, self.M))
-        k.tp_wait(peer.counter(len(self.FUSED) - 1), peer.epoch.data_ptr(), self.world)
-        peer.epoch.add_(1)
+        k.tp_wait_desc(self.tail_desc, advance_epoch=True)
         return outs
 
     def resident_bytes(self) -> int:

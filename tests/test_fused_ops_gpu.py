@@ -183,7 +183,7 @@ def test_fused_attention_equals_the_two_calls(kernels, Hq, Hk, D, L, pos):
         out = torch.full((Hq * D,), 7.0, dtype=torch.bfloat16, device="cuda")
         assert lib.b2_decode_attention_fused(qkv.data_ptr(), bias.data_ptr(), inv.data_ptr(), p.data_ptr(),
                                              ck1.data_ptr(), cv1.data_ptr(), out.data_ptr(), ws.data_ptr(), Hq, Hk, D,
-                                             L, None, None, 0, flags, st) == 0
+                                             L, None, flags, st) == 0
         torch.cuda.synchronize()
         assert torch.equal(out, out2)
         assert torch.equal(ck1, ck2) and torch.equal(cv1, cv2)

@@ -92,6 +92,39 @@ def test_consumer_waits_on_the_counter_and_reads_the_gathered_row(kernels):
     assert kernels.device_status() == 0
 
 
+def test_deferred_signal_chain(kernels):
+    """The cheaper protocol, one rank standing in for the group: the producer only stores (defer), the consumer behind
+    it on the stream announces it on the arrival counter and waits on that counter; a wait kernel behind the consumer
+    does the same for the consumer's own output and closes the epoch.  Three epochs in a row, no host-side reset."""
+    G, M, K1, I = 128, 1, 512, 768
+    _, Wa, Sa = oracle.synth_inputs(1, 2 * I, K1, G, seed=71)  # gate | up
+    _, Wb, Sb = oracle.synth_inputs(1, 384, I, G, seed=72)     # down
+    wa, sa, wb, sb = u32_to_torch(Wa), bits_to_torch(Sa), u32_to_torch(Wb), bits_to_torch(Sb)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(M, K1, device="cuda", generator=g).to(torch.bfloat16)
+    want = kernels.w4_linear_fused(kernels.w4_linear(x, wa, sa, G), wb, sb, G, prologue=2)
+    buf = torch.zeros(M, 2 * I, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(M, 384, dtype=torch.bfloat16, device="cuda")
+    sig = torch.zeros(2, dtype=torch.int32, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ep = epoch.data_ptr()
+    prod = ops.make_tp_desc(y_peers=[buf.data_ptr()], ld=2 * I, pieces=[(2 * I, 0)], defer=True)
+    cons = ops.make_tp_desc(y_peers=[out.data_ptr()], ld=384, pieces=[(384, 0)], defer=True, wait_sig=sig.data_ptr(),
+                            epoch=ep, wait_per_epoch=1, announce_peers=[sig.data_ptr()])
+    tail = ops.make_tp_desc(wait_sig=sig.data_ptr() + 4, epoch=ep, wait_per_epoch=1,
+                            announce_peers=[sig.data_ptr() + 4])
+    for step in range(3):
+        buf.zero_()
+        out.zero_()
+        kernels.w4_linear_tp(x, wa, sa, prod, G)
+        kernels.w4_linear_tp(buf, wb, sb, cons, G, prologue=2)
+        kernels.tp_wait_desc(tail, advance_epoch=True)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), step
+        assert sig.tolist() == [step + 1, step + 1] and int(epoch) == step + 1
+    assert kernels.device_status() == 0
+
+
 def test_bounded_wait_reports_a_time_out(kernels):
     """A counter nobody bumps: the consumer gives up after its bounded wait and the device status says so; the
     context stays usable."""
