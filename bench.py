@@ -539,6 +539,11 @@ def main():
         run_reference_arm(args)
         return
 
+    # stdout carries the one JSON line and nothing else: whatever a library prints there (NCCL announces its version
+    # when the communicator is created) goes to stderr
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
     from nanoserve_b200 import build as b2build
@@ -638,7 +643,30 @@ def main():
         for i in range(args.steps):
             e2e_step(lb.layers[i % n_copies])
         lb.barrier()
-        t_e2e_wall = time.perf_counter() - t0
+        t_e2e_eager = time.perf_counter() - t0
+    # the same step as a serving loop would issue it: ShardedLayer.host_step, one CUDA graph per step with the two
+    # copies inside (one graph launch + one stream synchronisation per step)
+    t_e2e_wall, e2e_path = t_e2e_eager, "Kernels.w4_linear per launch (ctypes -> C ABI), pinned host X in, all outputs out"
+    if not seven:
+        host_steps = [l.host_step(M, stream) for l in lb.layers]
+        for hs in host_steps:
+            hs.x_host.copy_(lb.x_h)
+            hs.act_host.copy_(lb.a_h)
+        with torch.cuda.stream(stream):
+            for i in range(warm):
+                host_steps[i % n_copies]()
+            lb.barrier()
+            t0 = time.perf_counter()
+            for i in range(args.steps):
+                host_steps[i % n_copies]()
+            lb.barrier()
+            t_e2e_wall = time.perf_counter() - t0
+        e2e_path = ("ShardedLayer.host_step: one CUDA graph per step (pinned host X in, 4 GEMV launches through the C "
+                    "ABI, all outputs out to pinned host memory), graph launch + stream synchronise per step")
+        if world == 1:
+            last = (args.steps - 1) % n_copies  # the layer copy both paths ran last
+            assert torch.equal(host_steps[last].out_host, out_h), "host_step and the per-launch path disagree"
+        del host_steps
     h2d = in_h.numel() * 2
     d2h = out_h.numel() * 2 if out_h is not None else sum(o.numel() * 2 for o in outs_h)
     leg_status["e2e"] = k.device_status()
@@ -753,10 +781,10 @@ def main():
             decode = {"error": f"{type(e).__name__}: {e}"}
 
     # ---- max over ranks
-    times = torch.tensor([t_dev, t_e2e_wall], dtype=torch.float64, device=dev)
+    times = torch.tensor([t_dev, t_e2e_wall, t_e2e_eager], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    t_dev, t_e2e_wall = times.tolist()
+    t_dev, t_e2e_wall, t_e2e_eager = times.tolist()
     status = k.device_status()
     if status != 0:
         raise SystemExit(f"rank {rank}: device status {status}: a kernel reported a time-out; numbers are invalid "
@@ -784,8 +812,10 @@ def main():
                 "seeds": "X 1/2, layer copy c: 1000+c", "flags": args.flags,
             },
             "e2e": {"value": nbytes * args.steps / t_e2e_wall / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e_wall / args.steps * 1e3,
-                    "path": "Kernels.w4_linear per launch (ctypes -> C ABI), pinned host X in, all outputs out"},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e_wall / args.steps * 1e3, "path": e2e_path,
+                    "per_launch_api": {"value": nbytes * args.steps / t_e2e_eager / 1e9,
+                                       "ms_per_step": t_e2e_eager / args.steps * 1e3,
+                                       "path": "Kernels.w4_linear per launch (ctypes -> C ABI), same copies, no graph"}},
             "gpu_launches": lb.launches_per_step() * args.steps * (blocks[0] + 1),
             "clocks": clocks,
         }
@@ -810,7 +840,7 @@ def main():
             line["cpu_baseline"] = {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": used, "kind": "port",
                                     "sample": f"{n} full layer passes at M=1 on one host thread (as the reference "
                                               f"runs its check), {dt:.2f} s per pass"}
-        print(json.dumps(line), flush=True)
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         # Captured graphs hold peer waits or NCCL work; tearing the communicator down under them can block.  Everything
         # is measured and printed: synchronise, meet once more, and leave without running the destructors.

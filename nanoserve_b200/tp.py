@@ -203,6 +203,10 @@ class ShardedLayer:
         k.tp_wait_desc(self.tail_desc, advance_epoch=True)
         return outs
 
+    def host_step(self, M: int, stream: "torch.cuda.Stream") -> "HostStep":
+        """The pass as a serving loop calls it -- inputs and outputs in pinned host memory: see HostStep."""
+        return HostStep(self, M, stream)
+
     def resident_bytes(self) -> int:
         return sum(w.numel() * 4 + s.numel() * 2 for w, s in self.shards.values())
 
@@ -238,3 +242,57 @@ class ShardedLayer:
             k.tp_wait(sig, peer.epoch.data_ptr(), per_epoch)
         peer.epoch.add_(1)
         return outs
+
+
+class HostStep:
+    """One decode pass of a fused ShardedLayer from host memory to host memory as ONE CUDA graph: the copy of the
+    step's inputs from a pinned buffer (`x_host [M, hidden]`, `act_host [M, intermediate]`: views of one allocation,
+    one copy), the four GEMV launches (and, tensor parallel, the wait behind them), the copy of all outputs into one
+    pinned buffer (`out_host`, the four outputs back to back).  Calling the object replays the graph and waits for it:
+    one graph launch and one stream synchronisation per step, whatever the number of kernels inside.  Fill the input
+    views before the call; read `outs` (views of `out_host`) after it."""
+
+    def __init__(self, layer: ShardedLayer, M: int, stream):
+        dev = layer.fused["qkv"][0].device
+        hidden, inter = layer.shapes["q"][1], layer.shapes["down"][1]
+        widths = [sum(layer.shapes[n][0] for n in names) for _, names in layer.FUSED]
+        self.layer, self.M, self.stream = layer, M, stream
+        self.in_host = torch.empty(M * (hidden + inter), dtype=torch.bfloat16).pin_memory()
+        self.x_host = self.in_host[:M * hidden].view(M, hidden)
+        self.act_host = self.in_host[M * hidden:].view(M, inter)
+        self.out_host = torch.empty(M * sum(widths), dtype=torch.bfloat16).pin_memory()
+        self.in_dev = torch.empty_like(self.in_host, device=dev)
+        self.out_dev = torch.empty(M * sum(widths), dtype=torch.bfloat16, device=dev)
+        self.outs, views, off = [], [], 0
+        for w in widths:
+            self.outs.append(self.out_host[off:off + M * w].view(M, w))
+            views.append(self.out_dev[off:off + M * w].view(M, w))
+            off += M * w
+        self.h2d_bytes, self.d2h_bytes = self.in_host.numel() * 2, self.out_host.numel() * 2
+        x_d, a_d = self.in_dev[:M * hidden].view(M, hidden), self.in_dev[M * hidden:].view(M, inter)
+
+        def body():
+            self.in_dev.copy_(self.in_host, non_blocking=True)
+            if layer.peer is None:
+                layer.decode_pass_fused4(x_d, a_d, outs=views)
+            else:  # the gathered rows live in the symmetric buffers: bring them together for the one copy back
+                for v, o in zip(views, layer.decode_pass_fused4(x_d, a_d)):
+                    v.copy_(o)
+            self.out_host.copy_(self.out_dev, non_blocking=True)
+
+        with torch.cuda.stream(stream):
+            body()  # every kernel variant loaded before the capture
+            stream.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=stream):
+                body()
+
+    def __call__(self):
+        # (a caller that already runs on `stream` saves the context switch: some microseconds of a step of eighty)
+        if torch.cuda.current_stream(self.in_dev.device) == self.stream:
+            self.graph.replay()
+        else:
+            with torch.cuda.stream(self.stream):
+                self.graph.replay()
+        self.stream.synchronize()
+        return self.outs

@@ -157,3 +157,29 @@ def test_tp_error_codes(kernels):
     with pytest.raises(RuntimeError, match="code -1"):  # gathered row narrower than the shard
         kernels.w4_linear_tp(x, wq, s, ops.make_tp_desc(y_peers=[buf.data_ptr()], sig_peers=[buf.data_ptr()], ld=32,
                                                           pieces=[(64, 0)]), 128)
+
+
+def test_host_step_equals_the_device_pass(kernels):
+    """ShardedLayer.host_step (one CUDA graph: copy in, four launches, copy out) against the same pass on device
+    tensors; the inputs are changed between two calls to show that the graph reads the pinned buffer each time."""
+    from nanoserve_b200 import synth
+    from nanoserve_b200.tp import ShardedLayer
+    shapes = {"q": (256, 256), "k": (64, 256), "v": (64, 256), "o": (256, 256), "gate": (512, 256), "up": (512, 256),
+              "down": (256, 512)}
+    order = ["q", "k", "v", "o", "gate", "up", "down"]
+    layer = ShardedLayer.synthetic(kernels, shapes, order, 128, seed=3, rank=0, world=1, device=torch.device("cuda"))
+    layer.fuse()
+    st = torch.cuda.Stream()
+    hs = layer.host_step(1, st)
+    g = torch.Generator().manual_seed(1)
+    for _ in range(2):
+        x = torch.randn(1, 256, generator=g).to(torch.bfloat16)
+        a = torch.randn(1, 512, generator=g).to(torch.bfloat16)
+        hs.x_host.copy_(x)
+        hs.act_host.copy_(a)
+        outs = hs()
+        want = layer.decode_pass_fused4(x.cuda(), a.cuda())
+        torch.cuda.synchronize()
+        for o, w in zip(outs, want):
+            assert torch.equal(o, w.cpu())
+    assert kernels.device_status() == 0
