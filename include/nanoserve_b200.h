@@ -93,6 +93,8 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
                                            three L2 round trips per tile, but no second kernel) */
 #define B2_FLAG_RING_KERNEL 131072 /* GEMV: the ring kernel even where the streaming kernel would run */
 #define B2_FLAG_STREAM_KERNEL 524288 /* GEMV: the streaming kernel for every M <= 16 it can serve */
+#define B2_FLAG_GEMM_NO_PAIRS 536870912 /* prefill GEMM: no clusters of two CTAs (by default two CTAs on neighbouring token
+                                           tiles unpack half of the weight tile each, for both) */
 #define B2_FLAG_GEMM_WHOLE_TILES 1073741824 /* prefill GEMM (M > 16): every CTA takes whole output tiles; by default the CTAs
                                            take equal shares of the (tile, K block) pairs and tiles that several CTAs cover
                                            are finished from fp32 part-tiles in the scratch */

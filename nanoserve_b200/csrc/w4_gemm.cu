@@ -57,7 +57,7 @@ struct GemmParams {
   __nv_bfloat16* Y;
   int M, N, K, G, KG;
   int nkb;  // K blocks of 64
-  int tiles_x;      // token tiles (fastest in the tile order)
+  int tiles_x;      // token tiles (fastest in the tile order; padded to an even number for CTA pairs)
   int n_whole;      // the first n_whole tiles are one work item each
   int n_tail;       // the remaining tiles are tail_ks items each: item n_whole + z * n_tail + t = split z of tile t
   int tail_ks;
@@ -66,22 +66,90 @@ struct GemmParams {
   int* status;
 };
 
-template <int MI>
+// ---- CTA pairs (clusters of two) on one tcgen05.mma.cta_group::2: the two CTAs work on neighbouring token tiles of
+// the same weight tile.  Each loads and unpacks HALF of the weight tile (128 rows) into its own shared memory; the
+// MMA, issued by the CTA of rank 0 for both, has M = 256 (128 token rows from each CTA's X tile, accumulators in each
+// CTA's own TMEM) and reads the two halves of the N = 256 weight operand from the two CTAs.  Per CTA and K block the
+// shared memory then serves 32 KB of weight-operand reads instead of 64, takes 16 KB of dequantised stores instead
+// of 32, and every weight is unpacked once per 2 * 128 * MI tokens.  (Measured on the way: with one CTA per tile the
+// operand reads of the MMAs alone take three quarters of the shared-memory bandwidth; a pair that only SHARED the
+// unpacking -- each CTA copying its half into the peer's tile -- was slower than single CTAs, 0.57 against 0.68 of the
+// dense peak, since it adds shared-memory traffic instead of removing it.)
+__device__ __forceinline__ uint32_t cluster_ctarank_u32() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// tcgen05 in its two-CTA form.  Allocation, release of the permit and deallocation are executed by the same warp of
+// BOTH CTAs; the MMA and its commits by one thread of the rank-0 CTA for both.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives once on the mbarrier (any CTA of the cluster) when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster)
+               : "memory");
+}
+// Tiled load whose completion is counted on a barrier of the rank-0 CTA (the form that permits that).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* tmap, int x, int y, uint32_t bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+      "[%2];" ::"r"(dst_smem),
+      "l"(tmap), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+// Arrival on a barrier of the other CTA.  Default semantics, as for a barrier of the own CTA: the data the arrival
+// vouches for is shared memory of THIS CTA, read by the tensor core through the async proxy (fence.proxy.async before
+// the arrival); nothing of it is read by another CTA's threads.  (With .release.cluster the arriving warps spent two
+// issue slots in three stalled on the memory barrier it implies.)
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t rbar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(rbar) : "memory");
+}
+// PAIR: the CTA holds HALF of the weight tile (128 rows): packed and dequantised tiles are half as large, which buys
+// a fourth ring stage and a fourth dequantised buffer.
+template <int MI, bool PAIR = false>
 struct GemmGeo {
-  static constexpr int kStageBytes = MI * kATileBytes + kWpTileBytes;
-  static constexpr int kStages = MI == 2 ? 3 : 5;
+  static constexpr int kWRows = PAIR ? kBN / 2 : kBN;             // weight rows this CTA loads and unpacks
+  static constexpr int kStageBytes = MI * kATileBytes + kWRows * 32;
+  static constexpr int kStages = PAIR ? 4 : (MI == 2 ? 3 : 5);
   static constexpr int kRingBytes = kStages * kStageBytes;
   static constexpr int kBdOffset = kRingBytes;
-  static constexpr int kBarOffset = kBdOffset + kBdBuffers * kBdTileBytes;
-  static constexpr int kSmemBytes = kBarOffset + 256 + 1024;  // barriers + slack for 1024-byte alignment
+  static constexpr int kBdBytes = kWRows * 128;                    // one dequantised buffer
+  static constexpr int kBdCount = PAIR ? 4 : kBdBuffers;
+  static constexpr int kBarOffset = kBdOffset + kBdCount * kBdBytes;
+  static constexpr int kSmemBytes = kBarOffset + 512 + 1024;  // barriers + slack for 1024-byte alignment
   static constexpr int kTmemCols = MI * kBN;                  // 256 or 512: powers of two
 };
 
-template <int MI>
+template <int MI, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     w4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const GemmParams p) {
-  using geo = GemmGeo<MI>;
+  using geo = GemmGeo<MI, PAIR>;
   extern __shared__ unsigned char smem_raw[];
   // 128-byte-swizzled tiles need a 1024-byte aligned base
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -92,10 +160,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const uint32_t bar_bd_full = bar_base + 16 * 8;            // [kBdBuffers]
   const uint32_t bar_bd_empty = bar_base + 20 * 8;           // [kBdBuffers]
   const uint32_t bar_acc = bar_base + 24 * 8;                // [1]
+  const uint32_t bar_full_w = bar_base + 32 * 8;             // [kStages], pairs only: this CTA's packed half
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + geo::kBarOffset + 26 * 8);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + geo::kBarOffset + 27 * 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // CTA pair: this CTA loads and unpacks rows [wr0, wr0 + kWRows) of the weight tile; the peer the other half
+  uint32_t crank = 0;
+  if constexpr (PAIR) crank = cluster_ctarank_u32();
+  constexpr int kWRows = geo::kWRows;
+  constexpr uint32_t kStageTx = MI * kATileBytes + kWRows * 32;  // bytes the copies of one stage deliver (one CTA)
+  const int wr0 = PAIR ? (int)crank * kWRows : 0;
+  const bool leader = crank == 0;
+  // the same offsets in the shared memory of the peer and of the rank-0 CTA
+  uint32_t peer_base = 0, lead_base = base;
+  if constexpr (PAIR) {
+    peer_base = mapa_u32(base, crank ^ 1u);
+    lead_base = mapa_u32(base, 0u);
+  }
   // token tiles vary fastest over the CTAs that run together: they then read many different X tiles and few
   // weight tiles at a time, which spreads the L2 traffic (74 CTAs pulling the same X tile at once made a few L2
   // slices the bottleneck)
@@ -116,11 +198,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (tid == 0) {
     *abort_flag = 0;
     for (int s = 0; s < geo::kStages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, 1);   // pairs: the X tiles of BOTH CTAs, counted on the rank-0 CTA's barrier
+      mbar_init(bar_full_w + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, kDequantThreads + 1);
     }
-    for (int b = 0; b < kBdBuffers; ++b) {
-      mbar_init(bar_bd_full + 8 * b, kDequantThreads);
+    for (int b = 0; b < geo::kBdCount; ++b) {
+      // this CTA's dequant threads and, on the rank-0 CTA of a pair, one arrival per dequant warp of the peer
+      mbar_init(bar_bd_full + 8 * b, PAIR ? kDequantThreads + kDequantThreads / 32 : kDequantThreads);
       mbar_init(bar_bd_empty + 8 * b, 1);
     }
     mbar_init(bar_acc, 1);
@@ -129,11 +213,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     tma_prefetch_desc(&tmap_w);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), geo::kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), geo::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), geo::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anybody arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const bool poisoned = *reinterpret_cast<volatile int*>(p.status) != 0;
@@ -148,51 +238,89 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const int kb = kb0 + i;
           mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag);
           const uint32_t stage = base + s * geo::kStageBytes;
-          mbar_arrive_expect_tx(bar_full + 8 * s, geo::kStageBytes);
+          if constexpr (PAIR) {
+            // X tiles of both CTAs complete on the rank-0 CTA's barrier (its producer expects the bytes of both);
+            // the packed half on this CTA's own
+            if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * MI * kATileBytes);
 #pragma unroll
-          for (int mi = 0; mi < MI; ++mi)
-            tma_load_2d(stage + mi * kATileBytes, &tmap_x, kb * kBK, m0 + mi * 128, bar_full + 8 * s);
-          tma_load_2d(stage + MI * kATileBytes, &tmap_w, kb * (kBK / 8), n0, bar_full + 8 * s);
+            for (int mi = 0; mi < MI; ++mi)
+              tma_load_2d_pair(stage + mi * kATileBytes, &tmap_x, kb * kBK, m0 + mi * 128,
+                               lead_base + (bar_full - base) + 8 * s);
+            mbar_arrive_expect_tx(bar_full_w + 8 * s, kWRows * 32);
+            tma_load_2d(stage + MI * kATileBytes, &tmap_w, kb * (kBK / 8), n0 + wr0, bar_full_w + 8 * s);
+          } else {
+            mbar_arrive_expect_tx(bar_full + 8 * s, kStageTx);
+#pragma unroll
+            for (int mi = 0; mi < MI; ++mi)
+              tma_load_2d(stage + mi * kATileBytes, &tmap_x, kb * kBK, m0 + mi * 128, bar_full + 8 * s);
+            tma_load_2d(stage + MI * kATileBytes, &tmap_w, kb * (kBK / 8), n0 + wr0, bar_full + 8 * s);
+          }
           if (++s == geo::kStages) { s = 0; ph ^= 1; }
         }
       }
       __syncwarp();
     } else if (warp == 1) {
-      // ------------------------------------------------------------ MMA issuer
-      if (lane == 0) {
-        constexpr uint32_t idesc = umma_idesc_bf16(128, kBN);
+      // ------------------------------------------------------------ MMA issuer (pairs: the rank-0 CTA's, for both)
+      if (lane == 0 && (!PAIR || leader)) {
+        constexpr uint32_t idesc = umma_idesc_bf16(PAIR ? 256 : 128, kBN);
         int s = 0, b = 0;
         uint32_t ph = 0, bph = 0;
         for (int kb = 0; kb < nkb; ++kb) {
-          mbar_wait(bar_full + 8 * s, ph, abort_flag);
-          mbar_wait(bar_bd_full + 8 * b, bph, abort_flag);
+          if constexpr (PAIR) {
+            // X tiles of both CTAs (counted here), dequantised halves of both CTAs (the peer's warps arrive here)
+            mbar_wait(bar_full + 8 * s, ph, abort_flag);
+            mbar_wait(bar_bd_full + 8 * b, bph, abort_flag);
+          } else {
+            mbar_wait(bar_full + 8 * s, ph, abort_flag);
+            mbar_wait(bar_bd_full + 8 * b, bph, abort_flag);
+          }
           tc_fence_after_sync();
           const uint32_t a_addr = base + s * geo::kStageBytes;
-          const uint32_t b_addr = base + geo::kBdOffset + b * kBdTileBytes;
+          const uint32_t b_addr = base + geo::kBdOffset + b * geo::kBdBytes;
 #pragma unroll
           for (int kk = 0; kk < kBK / 16; ++kk) {
             const uint64_t db = umma_desc_k128(b_addr + kk * 32);
 #pragma unroll
             for (int mi = 0; mi < MI; ++mi) {
               const uint64_t da = umma_desc_k128(a_addr + mi * kATileBytes + kk * 32);
-              umma_f16_ss(tmem_base + mi * kBN, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              if constexpr (PAIR)
+                umma_f16_ss_pair(tmem_base + mi * kBN, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              else
+                umma_f16_ss(tmem_base + mi * kBN, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             }
           }
-          umma_commit(bar_empty + 8 * s);      // the X tile and the packed tile of this stage are consumed
-          umma_commit(bar_bd_empty + 8 * b);   // the dequantised tile may be overwritten
+          if constexpr (PAIR) {
+            // the stage and the dequantised buffer are free in BOTH CTAs
+            umma_commit_pair(bar_empty + 8 * s);
+            umma_commit_pair(peer_base + (bar_empty - base) + 8 * s);
+            umma_commit_pair(bar_bd_empty + 8 * b);
+            umma_commit_pair(peer_base + (bar_bd_empty - base) + 8 * b);
+          } else {
+            umma_commit(bar_empty + 8 * s);      // the X tile and the packed tile of this stage are consumed
+            umma_commit(bar_bd_empty + 8 * b);   // the dequantised tile may be overwritten
+          }
           if (++s == geo::kStages) { s = 0; ph ^= 1; }
-          if (++b == kBdBuffers) { b = 0; bph ^= 1; }
+          if (++b == geo::kBdCount) { b = 0; bph ^= 1; }
         }
-        umma_commit(bar_acc);
+        if constexpr (PAIR) {
+          umma_commit_pair(bar_acc);
+          umma_commit_pair(peer_base + (bar_acc - base));
+        } else {
+          umma_commit(bar_acc);
+        }
       }
       __syncwarp();
     } else {
       // ------------------------------------------------------------ dequant warps, then epilogue
       const int dt = tid - 64;          // 0..511
-      const int r = dt >> 1;            // weight row of the tile
-      const int hf = dt & 1;            // which 32-wide half of the 64-wide K block (one scale each)
-      const int n = n0 + r;
-      const uint32_t bd_row = base + geo::kBdOffset + r * 128;
+      // a thread owns kWords packed words of one row: a 32-wide half of the K block (one CTA per tile), or a
+      // 16-wide quarter of it (CTA pair: this CTA unpacks 128 of the 256 rows)
+      constexpr int kWords = PAIR ? 2 : 4;
+      const int r = PAIR ? dt >> 2 : dt >> 1;   // row among the rows this CTA unpacks
+      const int part = PAIR ? dt & 3 : dt & 1;  // which run of kWords words of the row
+      const int hf = PAIR ? part >> 1 : part;   // which 32-wide half of the 64-wide K block (one scale each)
+      const int n = n0 + wr0 + r;               // the weight row
+      const uint32_t bd_off = geo::kBdOffset + r * 128;  // its place in this CTA's dequantised buffer
       const uint32_t sw = (uint32_t)(r & 7);
       // unpack constants pinned in registers: each (x & mask) | magic is then a single LOP3
       uint32_t k_mask = kNibblePairMask, k_magic = kMagic128x2;
@@ -214,17 +342,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (i + 1 < nkb) s2_next = load_scale(kb0 + i + 1);
 
         // one lane per warp polls: many threads spinning on a shared-memory barrier slow the copies down
-        if (lane == 0) mbar_wait(bar_full + 8 * s, ph, abort_flag);
+        if (lane == 0) mbar_wait((PAIR ? bar_full_w : bar_full) + 8 * s, ph, abort_flag);
         __syncwarp();
-        const uint4 w4 = lds128(base + s * geo::kStageBytes + MI * kATileBytes + r * 32 + hf * 16);
+        uint32_t words[kWords];
+        {
+          const uint32_t src = base + s * geo::kStageBytes + MI * kATileBytes + r * 32 + part * (4 * kWords);
+          if constexpr (PAIR) {
+            const uint2 w2 = lds64(src);
+            words[0] = w2.x; words[1] = w2.y;
+          } else {
+            const uint4 w4 = lds128(src);
+            words[0] = w4.x; words[1] = w4.y; words[2] = w4.z; words[3] = w4.w;
+          }
+        }
         mbar_arrive(bar_empty + 8 * s);  // packed words are in registers
-        const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
 
         if (lane == 0) mbar_wait(bar_bd_empty + 8 * b, bph ^ 1, abort_flag);
         __syncwarp();
-        const uint32_t dst = bd_row + b * kBdTileBytes;
+        const uint32_t dst = bd_off + b * geo::kBdBytes;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kWords; ++c) {
           uint32_t v[4];
           v[0] = lop3_and_or(words[c], k_mask, k_magic);
           v[1] = lop3_and_or(words[c] >> 4, k_mask, k_magic);
@@ -238,12 +375,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           o.y = __byte_perm(v[2], v[3], 0x5410);
           o.z = __byte_perm(v[0], v[1], 0x7632);
           o.w = __byte_perm(v[2], v[3], 0x7632);
-          sts128(dst + ((uint32_t(hf * 4 + c) ^ sw) << 4), o);
+          const uint32_t at = dst + ((uint32_t(part * kWords + c) ^ sw) << 4);
+          sts128(base + at, o);
         }
-        fence_proxy_async_smem();
-        mbar_arrive(bar_bd_full + 8 * b);
+        if constexpr (PAIR) {
+          // the MMA issuer sits in the rank-0 CTA: its own threads arrive one by one, the peer's once per warp (an
+          // arrival on another CTA's barrier is a transaction of its own)
+          fence_proxy_async_smem();
+          if (leader) {
+            mbar_arrive(bar_bd_full + 8 * b);
+          } else {
+            __syncwarp();  // the lanes' stores and fences are ordered before lane 0's release
+            if (lane == 0) mbar_arrive_remote(lead_base + (bar_bd_full - base) + 8 * b);
+          }
+        } else {
+          fence_proxy_async_smem();
+          mbar_arrive(bar_bd_full + 8 * b);
+        }
         if (++s == geo::kStages) { s = 0; ph ^= 1; }
-        if (++b == kBdBuffers) { b = 0; bph ^= 1; }
+        if (++b == geo::kBdCount) { b = 0; bph ^= 1; }
       }
 
       // ---- epilogue: TMEM -> registers -> bf16 -> global
@@ -359,29 +509,48 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int i = 0; i < 64; ++i) __nanosleep(2000);  // let copies in flight land before the smem is released
     __syncthreads();
   }
+  // a CTA of a pair stays until its peer is done with it: the peer writes into this CTA's shared memory and arrives
+  // on its barriers
+  if constexpr (PAIR) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, geo::kTmemCols);
+    if constexpr (PAIR)
+      tmem_dealloc_pair(tmem_base, geo::kTmemCols);
+    else
+      tmem_dealloc(tmem_base, geo::kTmemCols);
   }
 }
 
 // ------------------------------------------------------------------ host side
-template <int MI>
+template <int MI, bool PAIR>
 int launch_gemm(const CUtensorMap& tx, const CUtensorMap& tw, const GemmParams& p, cudaStream_t stream) {
-  auto kernel = w4_gemm_kernel<MI>;
+  auto kernel = w4_gemm_kernel<MI, PAIR>;
   cudaError_t e =
-      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmGeo<MI>::kSmemBytes);
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmGeo<MI, PAIR>::kSmemBytes);
   if (e != cudaSuccess) return (int)e;
-  const dim3 grid(p.n_whole + p.n_tail * p.tail_ks);
-  kernel<<<grid, kGemmThreads, GemmGeo<MI>::kSmemBytes, stream>>>(tx, tw, p);
-  return (int)cudaGetLastError();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.n_whole + p.n_tail * p.tail_ks);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = GemmGeo<MI, PAIR>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = PAIR ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kernel, tx, tw, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 }  // namespace
 
 int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G,
                 const Workspace& ws, int flags, int sm_count, cudaStream_t stream) {
-  static_assert(GemmGeo<2>::kSmemBytes <= kGemmSmemLimit && GemmGeo<1>::kSmemBytes <= kGemmSmemLimit, "smem");
+  static_assert(GemmGeo<2>::kSmemBytes <= kGemmSmemLimit && GemmGeo<1>::kSmemBytes <= kGemmSmemLimit &&
+                    GemmGeo<2, true>::kSmemBytes <= kGemmSmemLimit,
+                "smem");
   if (M < 1) return kErrUnsupportedM;
   if (N < 1 || K < 32 || G < 32 || K % 32 || G % 32 || K % G) return kErrBadShape;
   if (!X || !Wq || !S || !Y) return kErrBadPointer;
@@ -394,8 +563,13 @@ int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, in
   if (!make_tensor_map_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, (uint64_t)M, (uint64_t)K, 128, kBK,
                  CU_TENSOR_MAP_SWIZZLE_128B))
     return kErrDevice;
-  if (!make_tensor_map_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, Wq, (uint64_t)N, (uint64_t)K / 8, kBN, kBK / 8,
-                 CU_TENSOR_MAP_SWIZZLE_NONE))
+  // CTA pairs (each unpacks half of the weight tile for both): where the token tiles pair up without much padding.
+  // A lone token tile (M <= 256) would be paired with an empty one and do the whole unpack for half the product.
+  const int mi_ = M <= 128 ? 1 : 2;
+  const int tiles_m = (M + 128 * mi_ - 1) / (128 * mi_);
+  const bool pair = !(flags & kFlagGemmNoPairs) && mi_ == 2 && (tiles_m % 2 == 0 || tiles_m >= 7);
+  if (!make_tensor_map_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, Wq, (uint64_t)N, (uint64_t)K / 8, pair ? kBN / 2 : kBN,
+                 kBK / 8, CU_TENSOR_MAP_SWIZZLE_NONE))
     return kErrDevice;
 
   GemmParams p{};
@@ -410,12 +584,13 @@ int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, in
   // (e.g. the 3584 x 18944 projection: 28 tiles at M = 512 run as 5 splits each; at M = 8192 the 4 tiles that
   // 3 waves of 148 leave over run as 8 splits each instead of a fourth wave).
   {
-    const int mi = M <= 128 ? 1 : 2;
-    p.tiles_x = (M + 128 * mi - 1) / (128 * mi);
+    const int mi = mi_;
+    p.tiles_x = pair ? (tiles_m + 1) / 2 * 2 : tiles_m;  // pairs never straddle a row of tiles
     const long tiles = (long)p.tiles_x * ((N + kBN - 1) / kBN);
     if (tiles > 0x3fffffff) return kErrBadShape;
     const int sms = std::max(1, sm_count);
-    const long n_tail = tiles % sms ? tiles % sms : std::min<long>(tiles, sms);
+    const int sms_even = pair ? sms / 2 * 2 : sms;  // whole waves of pairs
+    const long n_tail = tiles % sms_even ? tiles % sms_even : std::min<long>(tiles, sms_even);
     long best_cost = -1;
     int best = 1;
     for (int ks = 1; ks <= 8; ++ks) {
@@ -438,7 +613,8 @@ int gemm_launch(const void* X, const void* Wq, const void* S, void* Y, int M, in
     p.partial = ws.partial;
     p.counters = ws.counters;
   }
-  return M <= 128 ? launch_gemm<1>(tx, tw, p, stream) : launch_gemm<2>(tx, tw, p, stream);
+  if (pair) return launch_gemm<2, true>(tx, tw, p, stream);
+  return M <= 128 ? launch_gemm<1, false>(tx, tw, p, stream) : launch_gemm<2, false>(tx, tw, p, stream);
 }
 
 }  // namespace b2

@@ -785,7 +785,7 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   const int tpc = kWarps / ks;
   pl.grid_x = (n_tiles + tpc - 1) / tpc;
   // K slices across CTAs: only when the staged X of one CTA does not fit otherwise
-  const int forced_ns = (flags >> 24) & 0x3F;
+  const int forced_ns = (flags >> 24) & 0x1F;
   const int forced_depth = (flags >> 4) & 0xF;  // bits 4-7: ring slots per warp (diagnostics)
   bool found = false;
   for (int pass = 0; pass < 2 && !found; ++pass) {

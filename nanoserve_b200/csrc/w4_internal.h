@@ -57,6 +57,7 @@ enum : int {
   kFlagRingKernel = 131072,  // GEMV: run the shared-memory ring kernel (w4_gemv.cu) even where the register-streaming
                              // kernel (w4_gemv_stream.cu) applies; bits 20-23: force that kernel's warps per row block
   kFlagStreamKernel = 262144 * 2,  // GEMV: run the streaming kernel for every M <= 16 it can serve (by default M <= 2)
+  kFlagGemmNoPairs = 1 << 29,     // GEMM: one CTA per tile unpacks the whole weight tile (no clusters of two)
   kFlagGemmWholeTiles = 1 << 30,  // GEMM: every CTA takes whole output tiles (no part-tiles, no scratch)
   kFlagNoPdl = 8,          // GEMV: do NOT launch with programmatic stream serialization (by default the kernel may
                            // begin -- weight prefetch only -- while the previous kernel of the stream still runs)

@@ -29,6 +29,7 @@ FLAG_SPLIT_SUM_KERNEL = 32768
 FLAG_NO_SPLIT_SUM_KERNEL = 65536
 FLAG_RING_KERNEL = 131072    # decode GEMV: the shared-memory ring kernel even where the streaming kernel applies
 EPI_SWIGLU_PAIRS = 1  # epilogue of b2_w4_linear_fused: silu(gate) * up over row blocks of 16 gate + 16 up rows
+FLAG_GEMM_NO_PAIRS = 1 << 29  # prefill GEMM: one CTA per tile unpacks the whole weight tile (no clusters of two)
 FLAG_GEMM_WHOLE_TILES = 1 << 30  # prefill GEMM: every CTA takes whole output tiles (no fp32 part-tiles)
 FLAG_STREAM_KERNEL = 524288  # decode GEMV: the streaming kernel for every M <= 16 it can serve (default: M <= 2)
 

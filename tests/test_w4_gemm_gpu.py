@@ -133,6 +133,27 @@ def test_split_tail_wave(kernels, M, N, K):
     assert kernels.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 768, 1024), (2048, 3584, 3584), (1800, 1000, 2048), (260, 512, 512)])
+def test_cta_pairs_equal_single_ctas(kernels, M, N, K):
+    """Clusters of two CTAs that unpack half of the weight tile each (the default where the token tiles pair up)
+    against one CTA per tile: the same dequantised tile, the same MMAs, so the same bits wherever both use the same
+    K split (whole tiles here), and both within the bound of the rounded-weight reference."""
+    from nanoserve_b200.ops import FLAG_GEMM_NO_PAIRS, FLAG_GEMM_WHOLE_TILES
+    G = 128
+    X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=31)
+    args = (bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S), G)
+    a = torch_to_bits(kernels.w4_linear(*args, flags=FLAG_GEMM_WHOLE_TILES))
+    b = torch_to_bits(kernels.w4_linear(*args, flags=FLAG_GEMM_WHOLE_TILES | FLAG_GEMM_NO_PAIRS))
+    c = torch_to_bits(kernels.w4_linear(*args))
+    torch.cuda.synchronize()
+    assert np.array_equal(a, b)
+    rows = np.unique(np.concatenate([[0, 127, 128, 255, M - 1], np.random.default_rng(5).integers(0, M, 8)]))
+    ref = rounded_weight_reference(X[rows], Wq, S, G)
+    check_bf16_output(a[rows], ref, 3e-5)
+    check_bf16_output(c[rows], ref, 3e-5)
+    assert kernels.device_status() == 0
+
+
 def test_x_doubling_is_exact(kernels):
     M, N, K, G = 256, 512, 1024, 128
     X, Wq, S = oracle.synth_inputs(M, N, K, G, seed=4)
