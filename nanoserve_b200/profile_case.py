@@ -2,6 +2,7 @@
 
     python -m nanoserve_b200.profile_case gemv --m 1 --n 18944 --k 3584 --copies 16 --launches 6
     python -m nanoserve_b200.profile_case gemm --m 2048 --n 18944 --k 3584 --copies 2 --launches 3
+    python -m nanoserve_b200.profile_case lm_head --m 1 --n 152064 --k 3584 --copies 1 --launches 4
 
 Weights are random nibbles with the benchmark's scale distribution, generated on the device; `copies`
 distinct matrices are used in rotation so that a launch reads DRAM rather than L2.  Each launch goes through
@@ -16,7 +17,7 @@ from .ops import Kernels
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["gemv", "gemm"])
+    ap.add_argument("kind", choices=["gemv", "gemm", "lm_head"])
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--n", type=int, default=18944)
     ap.add_argument("--k", type=int, default=3584)
@@ -33,6 +34,20 @@ def main():
     k.init()
     dev = torch.device("cuda")
     gen = torch.Generator(device=dev).manual_seed(1)
+    if a.kind == "lm_head":  # bf16 vocabulary projection with the block argmax (n = vocabulary rows)
+        ws = [(torch.randn(a.n, a.k, device=dev, generator=gen) * 0.02).to(torch.bfloat16) for _ in range(a.copies)]
+        x = torch.randn(a.m, a.k, device=dev, generator=gen).to(torch.bfloat16)
+        nblk = k.lm_head_blocks(a.n)
+        pv = torch.empty(nblk, dtype=torch.float32, device=dev)
+        pi = torch.empty(nblk, dtype=torch.int32, device=dev)
+        logits = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=dev)
+        for i in range(a.launches):
+            k.lm_head(x, ws[i % a.copies], logits=logits, part_max=pv, part_idx=pi)
+        torch.cuda.synchronize()
+        if k.device_status() != 0:
+            raise SystemExit("device status non-zero")
+        print(f"lm_head m={a.m} v={a.n} k={a.k}: {a.launches} launches done")
+        return
     ws = []
     for _ in range(a.copies):
         Wq = torch.randint(-2**31, 2**31 - 1, (a.n, a.k // 8), dtype=torch.int32, device=dev, generator=gen)
