@@ -110,10 +110,6 @@ int to_gemv_tp(const b2_tp_desc* tp, b2::GemvTp* out) {
     if (!tp->announce_peer[r] || (reinterpret_cast<uintptr_t>(tp->announce_peer[r]) & 3)) return b2::kErrBadPointer;
     t.announce_peer[r] = static_cast<unsigned*>(tp->announce_peer[r]);
   }
-  if (t.defer && t.world > 0) {  // the signal pointers are not used
-    for (int r = 0; r < t.world; ++r)
-      if (!t.sig_peer[r]) t.sig_peer[r] = reinterpret_cast<unsigned*>(t.y_peer[r]);
-  }
   *out = t;
   return 0;
 }

@@ -1426,9 +1426,14 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
                         const GemvTp* tp) {
   if (M < 1 || M > 16) return kErrUnsupportedM;
   if (tp != nullptr && tp->world > 0) {
-    if (tp->world > kMaxTpRanks || tp->ld < N || tp->seg_end[0] < 0 || tp->seg_end[1] < tp->seg_end[0]) return kErrBadShape;
+    // (with the SwiGLU epilogue a launch delivers N / 2 columns)
+    if (tp->world > kMaxTpRanks || tp->ld < (pro.epilogue == kEpiSwigluPairs ? N / 2 : N) || tp->seg_end[0] < 0 ||
+        tp->seg_end[1] < tp->seg_end[0])
+      return kErrBadShape;
     for (int r = 0; r < tp->world; ++r)
-      if (!tp->y_peer[r] || !tp->sig_peer[r] || (reinterpret_cast<uintptr_t>(tp->sig_peer[r]) & 3)) return kErrBadPointer;
+      if (!tp->y_peer[r] ||
+          (!tp->defer && (!tp->sig_peer[r] || (reinterpret_cast<uintptr_t>(tp->sig_peer[r]) & 3))))
+        return kErrBadPointer;
     Y = tp->y_peer[0];  // the plain output pointer is not used
   }
   if (tp != nullptr && tp->wait_sig != nullptr && !tp->epoch) return kErrBadPointer;

@@ -618,7 +618,8 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
     }
   }
 
-  if (NT == 1 && q.ks == 1 && p.nslices == 1 && p.tp.world == 0) {
+  if (NT == 1 && q.ks == 1 && p.nslices == 1 &&
+      (p.tp.world == 0 || (RB == 2 && q.epi == kEpiSwigluPairs && p.tp.defer))) {
     // ---- one tile, no K slices: the lanes of a quad hold the chunks and planes of the same rows; a shuffle or two,
     // and the outputs go straight from registers to Y
     float v_lo[RB], v_hi[RB];
@@ -656,9 +657,39 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
         return __float2bfloat16(a / (1.f + __expf(-a)) * b);
       };
       const int n = (wrow0 >> 1) + grow, n_act = p.N >> 1;
-      if (writer && active) {
-        if (n < n_act) p.Y[(size_t)m * n_act + n] = act(v_lo[0], v_lo[RB - 1]);
-        if (n + 8 < n_act) p.Y[(size_t)m * n_act + n + 8] = act(v_hi[0], v_hi[RB - 1]);
+      const __nv_bfloat16 a_lo = act(v_lo[0], v_lo[RB - 1]), a_hi = act(v_hi[0], v_hi[RB - 1]);
+      if (p.tp.world) {
+        // Tensor parallel (one token, deferred signal: nothing but the stores): the lanes t = 0 of four neighbouring
+        // quads hold four consecutive rows; one of them collects the four and stores 8 bytes into the gathered
+        // activation row of every rank (two-byte stores over NVLink are dear).
+        const uint32_t lo = __bfloat16_as_ushort(a_lo), hi = __bfloat16_as_ushort(a_hi);
+        uint32_t l[4] = {lo, 0, 0, 0}, h[4] = {hi, 0, 0, 0};
+#pragma unroll
+        for (int i = 1; i < 4; ++i) {
+          l[i] = __shfl_down_sync(0xffffffffu, lo, 4 * i);
+          h[i] = __shfl_down_sync(0xffffffffu, hi, 4 * i);
+        }
+        if ((lane & 15) == 0 && active) {  // rows n .. n + 3 and n + 8 .. n + 11 (n a multiple of 4)
+          const uint2 pl = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+          const uint2 ph = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+          const size_t at = (size_t)p.tp.seg_dst[0] + n;
+          for (int r = 0; r < p.tp.world; ++r) {
+            __nv_bfloat16* y = static_cast<__nv_bfloat16*>(p.tp.y_peer[r]) + at;
+            if ((reinterpret_cast<uintptr_t>(y) & 7) == 0) {
+              *reinterpret_cast<uint2*>(y) = pl;
+              *reinterpret_cast<uint2*>(y + 8) = ph;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                y[i] = __ushort_as_bfloat16((unsigned short)l[i]);
+                y[8 + i] = __ushort_as_bfloat16((unsigned short)h[i]);
+              }
+            }
+          }
+        }
+      } else if (writer && active) {
+        if (n < n_act) p.Y[(size_t)m * n_act + n] = a_lo;
+        if (n + 8 < n_act) p.Y[(size_t)m * n_act + n + 8] = a_hi;
       }
     } else {
 #pragma unroll
@@ -936,7 +967,8 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
   if (pro.epilogue == kEpiSwigluPairs) {
     // served by the register epilogue of the one-token kernel only: a caller that gets this code runs the plain
     // launch followed by the SwiGLU prologue of the next one
-    if (M != 1 || (N & 31) || (tp != nullptr && tp->world > 0)) return kErrNotImplemented;
+    // (tensor parallel: a producer with a deferred signal only -- the register epilogue has no CTA-wide tail)
+    if (M != 1 || (N & 31) || (tp != nullptr && tp->world > 0 && !tp->defer)) return kErrNotImplemented;
     no_split = true;
   } else if (pro.epilogue != kEpiNone) {
     return kErrBadShape;

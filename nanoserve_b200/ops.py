@@ -225,7 +225,7 @@ class Kernels:
         return y
 
     def w4_linear_tp(self, x, Wq, S, desc: "TpDesc", group=128, prologue=0, r=None, wn=None, eps=0.0, x_out=None,
-                     flags=0):
+                     flags=0, epilogue=0):
         """Decode GEMV of a tensor-parallel shard with the all-gather fused in (see b2_w4_linear_tp); the outputs
         go where `desc` says."""
         self._cuda(x, Wq, S, r, wn, x_out)
@@ -233,8 +233,9 @@ class Kernels:
         N, K = Wq.shape[0], Wq.shape[1] * 8
         assert x.is_contiguous() and x.shape[1] == (2 * K if prologue == 2 else K)
         p = lambda t: None if t is None else t.data_ptr()
-        rc = self.lib.b2_w4_linear_tp(x.data_ptr(), Wq.data_ptr(), S.data_ptr(), M, N, K, group, prologue, p(r), p(wn),
-                                      eps, p(x_out), ctypes.byref(desc), flags, self._stream())
+        rc = self.lib.b2_w4_linear_tp(x.data_ptr(), Wq.data_ptr(), S.data_ptr(), M, N, K, group,
+                                      prologue | (epilogue << 8), p(r), p(wn), eps, p(x_out), ctypes.byref(desc), flags,
+                                      self._stream())
         self._check(rc, "b2_w4_linear_tp")
 
     def lm_head(self, x, W, logits=None, part_max=None, part_idx=None, idx_offset=0, r=None, wn=None, eps=0.0):

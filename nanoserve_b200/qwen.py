@@ -84,15 +84,13 @@ class Qwen2Runner:
             g, u = w4(self.I, H), w4(self.I, H)
             d = w4(H, self.I)
             bias = (torch.randn(self.nq + 2 * self.nkv, device=device, generator=gen) * 0.02).to(torch.bfloat16)
-            if world == 1:
-                # 16 gate rows, their 16 up rows, the next 16 gate rows ...: the decode GEMV then holds a gate value
-                # and its up value in the same lane and applies SwiGLU in its epilogue (same rows, same arithmetic)
-                def pairs(a, b):
-                    return torch.stack([a.view(self.I // 16, 16, -1), b.view(self.I // 16, 16, -1)], 1).reshape(
-                        2 * self.I, -1).contiguous()
-                gu = (pairs(g[0], u[0]), pairs(g[1], u[1]))
-            else:
-                gu = (torch.cat([g[0], u[0]]), torch.cat([g[1], u[1]]))
+            # 16 gate rows, their 16 up rows, the next 16 gate rows ... (of this rank's shard): the decode GEMV then
+            # holds a gate value and its up value in the same lane and applies SwiGLU in its epilogue (same rows, same
+            # arithmetic)
+            def pairs(a, b):
+                return torch.stack([a.view(a.shape[0] // 16, 16, -1), b.view(b.shape[0] // 16, 16, -1)], 1).reshape(
+                    2 * a.shape[0], -1).contiguous()
+            gu = (pairs(g[0], u[0]), pairs(g[1], u[1]))
             self.layers.append({
                 "qkv": (torch.cat([q[0], k[0], v[0]]), torch.cat([q[1], k[1], v[1]])),
                 "o": o, "gu": gu, "d": d,
@@ -147,7 +145,7 @@ class Qwen2Runner:
         from .tp import PeerBuffers
         cfg, k, P, r = self.cfg, self.k, self.world, self.rank
         H, I, nq, nkv, G = cfg.hidden, self.I, self.nq, self.nkv, cfg.group
-        self.peer = peer = PeerBuffers({"qkv": nq + 2 * nkv, "o": H, "gu": 2 * I, "d": H}, 4 * cfg.n_layers,
+        self.peer = peer = PeerBuffers({"qkv": nq + 2 * nkv, "o": H, "act": I, "d": H}, 4 * cfg.n_layers,
                                        self.dev, self.group)
         ep = peer.epoch.data_ptr()
         self.tp_desc = []
@@ -165,8 +163,8 @@ class Qwen2Runner:
                                             (nkv // P, nq + nkv + r * nkv // P)], **(after(c - 1) if li > 0 else {})),
                 "attn": make_tp_desc(**after(c)),
                 "o": make_tp_desc(peer.peers("o"), ld=H, pieces=[(H // P, r * H // P)], defer=True),
-                "gu": make_tp_desc(peer.peers("gu"), ld=2 * I, defer=True,
-                                   pieces=[(I // P, r * I // P), (I // P, I + r * I // P)], **after(c + 1)),
+                # gate|up with SwiGLU in its epilogue: this rank's slice of the activation row
+                "gu": make_tp_desc(peer.peers("act"), ld=I, defer=True, pieces=[(I // P, r * I // P)], **after(c + 1)),
                 "d": make_tp_desc(peer.peers("d"), ld=H, pieces=[(H // P, r * H // P)], defer=True, **after(c + 2)),
             })
         self.tp_tail = make_tp_desc(**after(4 * cfg.n_layers - 1))
@@ -236,11 +234,8 @@ class Qwen2Runner:
             h = k.rmsnorm(x, self._gather(self.linear(a, L["o"])), L["ln_post"], cfg.rms_eps)
             gu = self.linear(h, L["gu"])
             il = self.I // self.world
-            if self.world == 1:  # blocks of 16 gate rows and 16 up rows alternate (see __init__)
-                gu = gu.view(T, il // 16, 2, 16)
-                act = k.swiglu(gu[:, :, 0].reshape(T, il), gu[:, :, 1].reshape(T, il))
-            else:
-                act = self._gather(k.swiglu(gu[:, :il].contiguous(), gu[:, il:].contiguous()))
+            gu = gu.view(T, il // 16, 2, 16)  # blocks of 16 gate rows and 16 up rows alternate (see __init__)
+            act = self._gather(k.swiglu(gu[:, :, 0].reshape(T, il), gu[:, :, 1].reshape(T, il)))
             nxt = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
             h = k.rmsnorm(x, self._gather(self.linear(act, L["d"])), nxt, cfg.rms_eps)
         self.pos.fill_(T - 1)  # the pick advances it to T, the position of the first generated token
@@ -304,16 +299,12 @@ class Qwen2Runner:
                                                self._st())
             k._check(rc, "b2_decode_attention_fused")
             o = self._gather(self.linear(a, L["o"]))
-            if self.world == 1:  # SwiGLU in the epilogue of gate|up: the down projection reads the activation as is
-                act = self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o, wn=L["ln_post"],
-                                             eps=cfg.rms_eps, x_out=x_alt, epilogue=EPI_SWIGLU_PAIRS)
-                x, x_alt = x_alt, x
-                d = self.linear(act, L["d"])
-            else:  # the activation is gathered between SwiGLU and the down projection
-                gu = self._fused(x, L["gu"], 1, r=o, wn=L["ln_post"], x_out=x_alt)
-                x, x_alt = x_alt, x
-                il = self.I // self.world
-                d = self._gather(self.linear(self._gather(k.swiglu(gu[:, :il], gu[:, il:])), L["d"]))
+            # SwiGLU in the epilogue of gate|up: the down projection reads the (gathered) activation as is
+            act = self._gather(self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o,
+                                                      wn=L["ln_post"], eps=cfg.rms_eps, x_out=x_alt,
+                                                      epilogue=EPI_SWIGLU_PAIRS))
+            x, x_alt = x_alt, x
+            d = self._gather(self.linear(act, L["d"]))
             r = d
             wn = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
         # final add + RMSNorm folded into the vocabulary projection, argmax partials in its epilogue.  The residual
@@ -329,7 +320,7 @@ class Qwen2Runner:
         D, G, eps = cfg.head_dim, cfg.group, cfg.rms_eps
         ep = peer.epoch.data_ptr()
         qkv_buf, o_buf = peer.local("qkv", 1), peer.local("o", 1)
-        gu_buf, d_buf = peer.local("gu", 1), peer.local("d", 1)
+        act_buf, d_buf = peer.local("act", 1), peer.local("d", 1)
         x, x_alt = self.x, self.x_alt
         for li, L in enumerate(self.layers):
             dsc = self.tp_desc[li]
@@ -348,9 +339,9 @@ class Qwen2Runner:
             k._check(rc, "b2_decode_attention_fused")
             k.w4_linear_tp(a, L["o"][0], L["o"][1], dsc["o"], G)
             k.w4_linear_tp(x, L["gu"][0], L["gu"][1], dsc["gu"], G, prologue=1, r=o_buf, wn=L["ln_post"], eps=eps,
-                           x_out=x_alt)
+                           x_out=x_alt, epilogue=EPI_SWIGLU_PAIRS)
             x, x_alt = x_alt, x
-            k.w4_linear_tp(gu_buf, L["d"][0], L["d"][1], dsc["d"], G, prologue=2)
+            k.w4_linear_tp(act_buf, L["d"][0], L["d"][1], dsc["d"], G)
         k.tp_wait_desc(self.tp_tail, advance_epoch=True)  # the last down projection; closes the step's epoch
         return self._lm_head_and_pick(x, d_buf, self.final_norm)
 

@@ -125,6 +125,31 @@ def test_deferred_signal_chain(kernels):
     assert kernels.device_status() == 0
 
 
+def test_swiglu_epilogue_into_gathered_row(kernels):
+    """gate|up with SwiGLU in its epilogue as a tensor-parallel producer (deferred signal): the slice of the activation
+    row lands at its column of the gathered row, 8 bytes at a time, bit-identical to the single-GPU epilogue; with an
+    odd element offset of the row the two-byte fallback is taken."""
+    G, K, I = 128, 1024, 1536
+    _, Wq, S = oracle.synth_inputs(1, 2 * I, K, G, seed=91)
+    wq, s = u32_to_torch(Wq), bits_to_torch(S)
+    x = torch.randn(1, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(2)).to(torch.bfloat16)
+    want = kernels.w4_linear_fused(x, wq, s, G, epilogue=ops.EPI_SWIGLU_PAIRS)
+    for off in (0, 1):
+        buf = torch.full((4 * I + 8,), 7.0, dtype=torch.bfloat16, device="cuda")
+        row = buf[off:off + 4 * I]  # a gathered row of four ranks' slices; this "rank" is the third
+        desc = ops.make_tp_desc(y_peers=[row.data_ptr()], ld=4 * I, pieces=[(I, 2 * I)], defer=True)
+        kernels.w4_linear_tp(x, wq, s, desc, G, epilogue=ops.EPI_SWIGLU_PAIRS)
+        torch.cuda.synchronize()
+        assert torch.equal(row[2 * I:3 * I], want[0])
+        assert torch.all(row[:2 * I] == 7.0) and torch.all(row[3 * I:] == 7.0)
+    # without the deferred signal the register epilogue cannot serve a producer: refused, nothing launched
+    sig = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="code -3"):
+        kernels.w4_linear_tp(x, wq, s, ops.make_tp_desc(y_peers=[buf.data_ptr()], sig_peers=[sig.data_ptr()], ld=4 * I,
+                                                        pieces=[(I, 0)]), G, epilogue=ops.EPI_SWIGLU_PAIRS)
+    assert kernels.device_status() == 0
+
+
 def test_bounded_wait_reports_a_time_out(kernels):
     """A counter nobody bumps: the consumer gives up after its bounded wait and the device status says so; the
     context stays usable."""
