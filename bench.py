@@ -216,7 +216,8 @@ def run_sweep(k, dev, stream, flags):
             y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
             t = time_graph([(lambda w=w: k.w4_linear(x, w[0], w[1], G, flags=flags, out=y)) for w in ws], 10)
             nb = synth.gemv_bytes(M, N, K, G)
-            out["gemv"].append({"shape": name, "N": N, "K": K, "M": M, "us": round(t * 1e6, 2),
+            out["gemv"].append({"shape": name, "N": N, "K": K, "M": M, "plan": k.gemv_describe(M, N, K, G, flags),
+                                "us": round(t * 1e6, 2),
                                 "gbs": round(nb / t / 1e9, 1), "frac": round(nb / t / 1e9 / peaks["hbm_gbs"], 3)})
         del ws
         torch.cuda.empty_cache()
@@ -793,6 +794,11 @@ def main():
     if rank == 0:
         metric = METRIC if args.layer == "7b" else METRIC_70B
         layer_name = "Qwen2.5-7B-shaped" if args.layer == "7b" else "70B-class (hidden 8192, intermediate 28672)"
+        # which kernel and launch shape the library picks for each launch of the pass (this rank's shard)
+        from nanoserve_b200.tp import ShardedLayer as _SL
+        groups = [(n, (n,)) for n in ORDER] if seven else list(_SL.FUSED)
+        plans = {f: k.gemv_describe(M, sum(shapes[n][0] for n in names) // world, shapes[names[0]][1], G, args.flags)
+                 for f, names in groups}
         line = {
             "metric": metric if M == 1 else metric.replace("M=1", f"M={M}"), "value": nbytes * args.steps / t_dev / 1e9,
             "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
@@ -810,6 +816,7 @@ def main():
                 "bytes_per_step": nbytes, "launch": "one CUDA graph per layer copy, replayed in rotation",
                 "timed": f"{blocks[0]} blocks of {args.steps} steps ({t_dev * blocks[0] * 1e3:.1f} ms in all), mean per step",
                 "seeds": "X 1/2, layer copy c: 1000+c", "flags": args.flags,
+                "plans": plans,
             },
             "e2e": {"value": nbytes * args.steps / t_e2e_wall / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e_wall / args.steps * 1e3, "path": e2e_path,

@@ -259,6 +259,8 @@ int b2_w4_linear_tp(const void* X, const void* Wq, const void* S, int M, int N, 
 int b2_tp_wait_desc(const b2_tp_desc* tp, int advance_epoch, void* stream);
 /* CTAs the decode GEMV launches for this shape on the current device (0: not served by the GEMV). */
 size_t b2_w4_gemv_grid(int M, int N, int K, int G, int flags);
+/* One line of text into buf: which kernel and launch shape a decode GEMV of this shape gets (benchmark records). */
+int b2_w4_gemv_describe(int M, int N, int K, int G, int flags, char* buf, int buflen);
 int b2_rope_kv_store_tp(void* qkv, const void* bias, const void* inv_freq, const void* pos, void* cache_k,
                         void* cache_v, int Hq, int Hk, int D, int max_len, const void* wait_sig, const void* epoch,
                         unsigned wait_per_epoch, void* stream);

@@ -175,6 +175,13 @@ size_t b2_w4_gemv_grid(int M, int N, int K, int G, int flags) {
   return b2::gemv_grid(M, N, K, G, flags, st->sm_count, st->ws.partial_bytes, st->ws.n_counters - 1);
 }
 
+int b2_w4_gemv_describe(int M, int N, int K, int G, int flags, char* buf, int buflen) {
+  int rc = 0;
+  DeviceState* st = device_state(&rc);
+  if (!st) return rc;
+  return b2::gemv_describe(M, N, K, G, flags, st->sm_count, st->ws.partial_bytes, st->ws.n_counters - 1, buf, buflen);
+}
+
 int b2_tp_wait(const void* wait_sig, const void* epoch, unsigned wait_per_epoch, void* stream) {
   int rc = 0;
   DeviceState* st = device_state(&rc);

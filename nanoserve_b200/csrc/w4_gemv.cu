@@ -1265,6 +1265,33 @@ size_t gemv_grid(int M, int N, int K, int G, int flags, int sm_count, size_t par
   return (size_t)pl.grid;
 }
 
+// One line of text saying which kernel and launch shape a decode GEMV of this shape gets (for benchmark records).
+int gemv_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap, char* buf,
+                  int buflen) {
+  if (!buf || buflen < 1) return kErrBadPointer;
+  if (gemv_stream_applies(nullptr, M, N, K, G, flags)) {
+    const int n = gemv_stream_describe(M, N, K, G, flags, sm_count, partial_cap, buf, buflen);
+    if (n > 0) return 0;
+  }
+  GemvPlan pl;
+  if (!make_plan(M, N, K, G, flags, sm_count, partial_cap, counters_cap, &pl)) {
+    snprintf(buf, buflen, "not served by the GEMV");
+    return 0;
+  }
+  snprintf(buf, buflen,
+           "ring kernel: %d persistent CTAs (%d per SM), %d consumer warps x %d chunk(s) per stage, %d stages, %d token "
+           "tile(s) of 8, X %s, K slices %d%s%s, %zu KB smem",
+           pl.grid, pl.ctas_per_sm, pl.ncw, pl.cpw, pl.nstages, pl.mt,
+           pl.mode == kModeI8x2   ? "16-bit fixed point"
+           : pl.mode == kModeI8x3 ? "24-bit fixed point"
+           : pl.mode == kModeGeneric ? "bf16 (groups below 128)"
+                                     : "fp16",
+           pl.nslices,
+           pl.nslices > 1 ? (pl.sum_kernel ? " (sum kernel)" : " (last CTA sums)") : "", pl.prestage ? ", X pre-staged" : "",
+           pl.smem >> 10);
+  return 0;
+}
+
 namespace {
 
 // ---- choice of the CTA shape by measurement ---------------------------------------------------------------

@@ -950,6 +950,16 @@ size_t gemv_stream_grid(int M, int N, int K, int G, int flags, int sm_count, siz
   return (size_t)pl.grid_x * pl.nslices;
 }
 
+int gemv_stream_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, char* buf, int buflen) {
+  StreamPlan pl;
+  if (!make_stream_plan(M, N, K, G, nullptr, flags, sm_count, partial_cap, &pl)) return 0;
+  return snprintf(buf, buflen,
+                  "streaming kernel: %d CTAs of 8 warps, %d rows per warp, %d warp(s) per row tile along K, %s layout, "
+                  "%d planes (%d-bit X), ring depth %d, K slices across CTAs %d, cluster %d, %zu KB smem",
+                  pl.grid_x * pl.nslices, pl.RB * 16, pl.ks, pl.one ? "one-group" : "two-chunk", pl.P, pl.P * 8, pl.q.depth,
+                  pl.nslices, pl.q.cluster, pl.smem >> 10);
+}
+
 size_t gemv_stream_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap) {
   StreamPlan pl;
   if (!make_stream_plan(M, N, K, G, nullptr, flags, sm_count, partial_cap, &pl)) return 0;

@@ -136,6 +136,9 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
                        const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream,
                        const GemvTp* tp);
 size_t gemv_stream_grid(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);
+int gemv_stream_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, char* buf, int buflen);
+int gemv_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap, char* buf,
+                  int buflen);
 size_t gemv_stream_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);
 
 // Status word of b2_w4_gemv_noalloc's fixed scratch array (w4_gemv_noalloc.cu); false when that entry point has not

@@ -62,6 +62,7 @@ SIGNATURES = {
     "b2_w4_gemv_grid": ([_i32, _i32, _i32, _i32, _i32], ctypes.c_size_t),
     "b2_decode_attention_fused": ([_vp] * 8 + [_i32, _i32, _i32, _i32, _vp, _i32, _vp], _i32),
     "b2_tp_wait_desc": ([_vp, _i32, _vp], _i32),
+    "b2_w4_gemv_describe": ([_i32, _i32, _i32, _i32, _i32, ctypes.c_char_p, _i32], _i32),
     "b2_decode_attention_fused_workspace_bytes": ([_i32, _i32, _i32], ctypes.c_size_t),
     "b2_rope_kv_store_tp": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_uint, _vp], _i32),
     "b2_tp_wait": ([_vp, _vp, ctypes.c_uint, _vp], _i32),
@@ -261,6 +262,12 @@ class Kernels:
         """The consumer side of a descriptor as a kernel of its own: announce, wait, optionally *epoch += 1."""
         self._check(self.lib.b2_tp_wait_desc(ctypes.byref(desc), 1 if advance_epoch else 0, self._stream()),
                     "b2_tp_wait_desc")
+
+    def gemv_describe(self, M, N, K, group=128, flags=0) -> str:
+        """Which kernel and launch shape a decode GEMV of this shape gets on the current device."""
+        buf = ctypes.create_string_buffer(512)
+        self._check(self.lib.b2_w4_gemv_describe(M, N, K, group, flags, buf, 512), "b2_w4_gemv_describe")
+        return buf.value.decode()
 
     def gemv_grid(self, M, N, K, group=128, flags=0) -> int:
         return int(self.lib.b2_w4_gemv_grid(M, N, K, group, flags))
