@@ -174,7 +174,10 @@ int b2_w4_gemv_noalloc(const void* X, const void* Wq, const void* S, void* Y, in
  *     flags 0: the merge of the key slices is a second launch (two launches in all; the faster form: 9.0 -> about
  *     7 us per layer at 600 positions).  flags 1: ONE launch; the last CTA of a KV head to finish merges the slices
  *     (an arrival counter per KV head; nobody waits), which puts a fence, an atomic and the merge's two L2 round
- *     trips behind the slowest CTA.  Results are bit-identical to the two calls above either way.
+ *     trips behind the slowest CTA.  flags 2 (may be added to either): the caller promises that the kernel launched
+ *     in front of this one on the stream writes neither *pos nor cached rows below *pos (true for a decode step, where
+ *     that kernel is the q|k|v projection); the first tile of cached rows is then requested before that kernel has
+ *     completed.  Results are bit-identical to the two calls above in every form.
  *     workspace: b2_decode_attention_fused_workspace_bytes(Hq, Hk, D) bytes, ZEROED once by the caller (the counters
  *     at its end return to zero after every launch).  tp: NULL, or the consumer side (wait_sig, epoch,
  *     wait_per_epoch, announce_peer) of the tensor-parallel GEMV that produced qkv (see b2_tp_desc).

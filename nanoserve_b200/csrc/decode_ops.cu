@@ -242,7 +242,8 @@ template <int D>
 __global__ void __launch_bounds__(256) decode_attention_fused_kernel(
     const bf16* qkv, const bf16* __restrict__ bias, const float* __restrict__ inv_freq, const int* pos_ptr,
     bf16* cache_k, bf16* cache_v, float* part, int* counters, bf16* out, int Hq, int Hk, int max_len, float scale,
-    const unsigned* wait_sig, const int* epoch, unsigned wait_per_epoch, int* status, const b2::GemvTp ann) {
+    const unsigned* wait_sig, const int* epoch, unsigned wait_per_epoch, int* status, const b2::GemvTp ann,
+    int early) {
   constexpr int E = D / 32;        // elements per lane
   constexpr int kRowU4 = D / 8;    // 16-byte units per row
   constexpr int half = D / 2;
@@ -255,8 +256,38 @@ __global__ void __launch_bounds__(256) decode_attention_fused_kernel(
   __shared__ int s_last;
   const int kh = blockIdx.x, sp = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rep = Hq / Hk;
-  pdl_begin();
-  // deferred signal of the tensor-parallel GEMV in front of this kernel (it has completed: see pdl_begin)
+  const uint4* kbase = reinterpret_cast<const uint4*>(cache_k + (size_t)kh * max_len * D);
+  const uint4* vbase = reinterpret_cast<const uint4*>(cache_v + (size_t)kh * max_len * D);
+  constexpr int kPerThread = (kTileRows * kRowU4 + 255) / 256;
+  uint4 kv[kPerThread], vv[kPerThread];
+  int pos = 0, n = 0, per = 0, j0 = 0, j1 = 0;
+  auto slice = [&]() {
+    pos = __ldcg(pos_ptr);
+    n = min(pos + 1, max_len);
+    per = (n + kSplits - 1) / kSplits;
+    j0 = sp * per;
+    j1 = min(n, j0 + per);
+  };
+  auto request = [&](int t0) {
+    const int units = min(kTileRows, j1 - t0) * kRowU4;
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int u = tid + i * 256;
+      if (u < units && t0 + u / kRowU4 != pos) {  // the row this launch appends is not in the cache yet
+        kv[i] = __ldcg(kbase + (size_t)t0 * kRowU4 + u);
+        vv[i] = __ldcg(vbase + (size_t)t0 * kRowU4 + u);
+      }
+    }
+  };
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // `early`: the position and the cached rows below it were written by earlier steps, not by the kernel in front of
+  // this one (which produces qkv): the first tile's rows are requested while that kernel still runs
+  if (early) {
+    slice();
+    if (j0 < j1) request(j0);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // deferred signal of the tensor-parallel GEMV in front of this kernel (it has completed)
   if (ann.announce_world && blockIdx.x == 0 && blockIdx.y == 0 && tid < ann.announce_world)
     asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ann.announce_peer[tid]) : "memory");
   if (wait_sig != nullptr) {
@@ -276,29 +307,11 @@ __global__ void __launch_bounds__(256) decode_attention_fused_kernel(
     }
     __syncthreads();
   }
-  const int pos = __ldcg(pos_ptr);
-  const int n = min(pos + 1, max_len);
-  const int per = (n + kSplits - 1) / kSplits;
-  const int j0 = sp * per, j1 = min(n, j0 + per);
+  if (!early) {
+    slice();
+    if (j0 < j1) request(j0);
+  }
   const bool owner = pos < max_len && pos >= j0 && pos < j1;  // this CTA's slice holds the new position
-
-  // the first tile's cache rows are requested before anything else: the q and new-row work below runs under them
-  const uint4* kbase = reinterpret_cast<const uint4*>(cache_k + (size_t)kh * max_len * D);
-  const uint4* vbase = reinterpret_cast<const uint4*>(cache_v + (size_t)kh * max_len * D);
-  constexpr int kPerThread = (kTileRows * kRowU4 + 255) / 256;
-  uint4 kv[kPerThread], vv[kPerThread];
-  auto request = [&](int t0) {
-    const int units = min(kTileRows, j1 - t0) * kRowU4;
-#pragma unroll
-    for (int i = 0; i < kPerThread; ++i) {
-      const int u = tid + i * 256;
-      if (u < units && t0 + u / kRowU4 != pos) {  // the row this launch appends is not in the cache yet
-        kv[i] = __ldcg(kbase + (size_t)t0 * kRowU4 + u);
-        vv[i] = __ldcg(vbase + (size_t)t0 * kRowU4 + u);
-      }
-    }
-  };
-  if (j0 < j1) request(j0);
 
   // ---- the new k and v rows (owner only): thread i < D/2 rotates the pair (i, i + D/2) of k, the next D/2 threads
   // add the bias to a pair of v
@@ -600,7 +613,7 @@ int decode_attention_fused_launch(const void* qkv, const void* bias, const void*
                       static_cast<const int*>(pos), static_cast<bf16*>(cache_k), static_cast<bf16*>(cache_v), part,
                       counters, static_cast<bf16*>(out), Hq, Hk, max_len, scale,
                       static_cast<const unsigned*>(wait_sig), static_cast<const int*>(epoch), wait_per_epoch, status,
-                      ann);
+                      ann, (flags & 2) ? 1 : 0);
   };
   cudaError_t e = D == 128 ? go(decode_attention_fused_kernel<128>) : go(decode_attention_fused_kernel<64>);
   if (e == cudaSuccess && !one_launch) {

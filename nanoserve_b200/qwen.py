@@ -121,7 +121,7 @@ class Qwen2Runner:
         self.stream = torch.cuda.Stream(device=device)
         self.scratch = torch.empty(int(kernels.lib.b2_decode_workspace_bytes(cfg.n_heads, D)), dtype=torch.uint8,
                                    device=device)
-        self.attn_flags = int(os.environ.get("B2_QWEN_ATTN_FLAGS", "0"))  # 1: merge inside the attention launch
+        self.attn_flags = int(os.environ.get("B2_QWEN_ATTN_FLAGS", "2"))  # 1: merge inside the launch; 2: early cache reads
         # partials and arrival counters (zero between launches) of the fused attention kernel
         self.attn_ws = torch.zeros(int(kernels.lib.b2_decode_attention_fused_workspace_bytes(
             cfg.n_heads, cfg.n_kv_heads, D)), dtype=torch.uint8, device=device)

@@ -178,7 +178,7 @@ def test_fused_attention_equals_the_two_calls(kernels, Hq, Hk, D, L, pos):
     # the fused form, twice
     ws = torch.zeros(int(lib.b2_decode_attention_fused_workspace_bytes(Hq, Hk, D)), dtype=torch.uint8, device="cuda")
     keep = qkv.clone()
-    for flags in (1, 1, 0):
+    for flags in (1, 1, 0, 2, 3):
         ck1, cv1 = ck.clone(), cv.clone()
         out = torch.full((Hq * D,), 7.0, dtype=torch.bfloat16, device="cuda")
         assert lib.b2_decode_attention_fused(qkv.data_ptr(), bias.data_ptr(), inv.data_ptr(), p.data_ptr(),
