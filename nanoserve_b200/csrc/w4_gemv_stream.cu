@@ -115,10 +115,14 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1,
 // info[chunk][column pair] = { zc, zc', up, up' }: zc = -128 * (digit sum of the chunk) -- the zero-point 8 times
 // the 16 the nibble products carry -- and up = 2^(e - 127 - (8P - 3)) * 256^p / 16 as a float.  A chunk that holds
 // an inf or a nan gets nan factors, so the outputs become nan.
-template <int P, bool CL>
+// NM: one token with the add + RMSNorm prologue whose whole row is one item per thread (K <= 4096, no K slices, no
+// cluster): X, R and the norm weights are loaded ONCE, the sum of squares is reduced over the CTA in the middle of the
+// item, and the conversion goes on from registers -- one L2 round trip and one barrier instead of two and two.  `ss`:
+// eight floats of shared memory.
+template <int P, bool CL, bool NM>
 __device__ __forceinline__ void stage_x_planes(const GemvParams& p, uint32_t xs_base, int pstride, uint32_t info_base,
                                                const float* inv, int cb, int nch, int tid, uint32_t crank,
-                                               uint32_t csize) {
+                                               uint32_t csize, float* ss) {
   constexpr int B = 8 * P;
   constexpr uint32_t kBias = P == 4 ? 0x00808080u : 0x00000080u;
   // items in flight per thread: a load from L2 takes a microsecond under the weight stream.  (Five -- all of a
@@ -129,20 +133,74 @@ __device__ __forceinline__ void stage_x_planes(const GemvParams& p, uint32_t xs_
   const int items_pad = (items + 31) & ~31;
   const int half_mp = (p.M * P) >> 1;
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-  // the CTAs of a cluster take rounds of kThreads * UN items in turn
-  for (int it0 = tid + (int)crank * kThreads * UN; it0 < items_pad; it0 += kThreads * UN * (int)csize) {
+  // the CTAs of a cluster take rounds of kThreads * UN items in turn; NM: exactly one trip for every thread
+  for (int it0 = tid + (int)crank * kThreads * UN; it0 < (NM ? kThreads : items_pad);
+       it0 += NM ? kThreads : kThreads * UN * (int)csize) {
     uint4 va[UN], vb[UN];
 #pragma unroll
     for (int q = 0; q < UN; ++q) {
       va[q] = zero4;
       vb[q] = zero4;
-      const int it = it0 + q * kThreads;
-      if (it < items) {
-        const int m = it / items_tok;
-        const int r = it - m * items_tok;
-        const int k0 = cb * 128 + r * 16;
-        va[q] = load_x_unit(p, m, k0, inv);
-        vb[q] = load_x_unit(p, m, k0 + 8, inv);
+    }
+    if constexpr (NM) {
+      const bool valid = it0 < items;
+      const int k0 = it0 * 16;
+      uint4 sv[2] = {zero4, zero4}, wv[2] = {zero4, zero4};
+      float acc = 0.f;
+      if (valid) {
+        uint4 xv[2], rv[2] = {zero4, zero4};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          xv[u] = ld_l2(reinterpret_cast<const uint4*>(p.X + k0 + 8 * u));
+          if (p.R != nullptr) rv[u] = ld_l2(reinterpret_cast<const uint4*>(p.R + k0 + 8 * u));
+          wv[u] = ld_l2(reinterpret_cast<const uint4*>(p.Wn + k0 + 8 * u));
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          float a[8], b[8];
+          unpack8_bf16(xv[u], a);
+          if (p.R != nullptr) {
+            unpack8_bf16(rv[u], b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = __bfloat162float(__float2bfloat16(a[e] + b[e]));
+          }
+          sv[u] = pack8_bf16(a);  // the (rounded) sum is a bf16 value: exact
+          if (p.R != nullptr && blockIdx.x == 0 && p.Xout != nullptr)
+            *reinterpret_cast<uint4*>(p.Xout + k0 + 8 * u) = sv[u];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc += a[e] * a[e];
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if ((tid & 31) == 0) ss[tid >> 5] = acc;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) tot += ss[w];
+      const float sc = rsqrtf(tot / p.K + p.eps);
+      if (valid) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          float a[8], b[8];
+          unpack8_bf16(sv[u], a);
+          unpack8_bf16(wv[u], b);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) a[e] = a[e] * sc * b[e];
+          (u == 0 ? va[0] : vb[0]) = pack8_bf16(a);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < UN; ++q) {
+        const int it = it0 + q * kThreads;
+        if (it < items) {
+          const int m = it / items_tok;
+          const int r = it - m * items_tok;
+          const int k0 = cb * 128 + r * 16;
+          va[q] = load_x_unit(p, m, k0, inv);
+          vb[q] = load_x_unit(p, m, k0 + 8, inv);
+        }
       }
     }
 #pragma unroll
@@ -446,7 +504,9 @@ __device__ __forceinline__ void gemv_step_one(LoopState<NT>& st, float (&fin)[1]
 // partial sum.
 // CL: launched in clusters of q.cluster CTAs that share the conversion of X.  The plain variant holds no cluster
 // instruction at all: with them in the code, a launch WITHOUT the cluster attribute was 0.7 us slower than before.
-template <int NT, int P, int RB, bool GD1, bool ONE, bool CL>
+// NM: the add + RMSNorm prologue merged into the conversion of X (see stage_x_planes); an instantiation of its own, so
+// that the plain kernel's code does not grow (with both forms inlined in one kernel the layer pass lost 2 us).
+template <int NT, int P, int RB, bool GD1, bool ONE, bool CL, bool NM>
 __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvParams p, const StreamParams q) {
   extern __shared__ __align__(1024) unsigned char smem[];
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
@@ -532,10 +592,16 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
   const uint32_t xs_base = smem_u32(smem + q.off_x);
   {
     float* inv = reinterpret_cast<float*>(smem + kNormInv);
-    if (p.pro == kProAddRmsNorm) rmsnorm_factors<kThreads>(p, reinterpret_cast<float*>(smem + kNormSs), inv, tid);
+    float* ss = reinterpret_cast<float*>(smem + kNormSs);
     uint32_t crank = 0;
     if constexpr (CL) crank = cluster_ctarank();
-    stage_x_planes<P, CL>(p, xs_base, q.pstride, info_base, inv, cb, ncc, tid, crank, CL ? (uint32_t)q.cluster : 1u);
+    if constexpr (NM) {
+      stage_x_planes<P, false, true>(p, xs_base, q.pstride, info_base, inv, cb, ncc, tid, 0u, 1u, ss);
+    } else {
+      if (p.pro == kProAddRmsNorm) rmsnorm_factors<kThreads>(p, ss, inv, tid);
+      stage_x_planes<P, CL, false>(p, xs_base, q.pstride, info_base, inv, cb, ncc, tid, crank,
+                                   CL ? (uint32_t)q.cluster : 1u, ss);
+    }
   }
   // The scales were copied with cp.async.wait_all semantics per thread; the weight copies of the ring are tracked by
   // their mbarriers, but wait_all waits for them as well, so only the scale copies' own group is waited for here.
@@ -876,9 +942,9 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   return true;
 }
 
-template <int NT, int P, int RB, bool GD1, bool ONE, bool CL>
+template <int NT, int P, int RB, bool GD1, bool ONE, bool CL, bool NM = false>
 int launch_stream_g(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStream_t stream) {
-  auto kernel = w4_gemv_stream_kernel<NT, P, RB, GD1, ONE, CL>;
+  auto kernel = w4_gemv_stream_kernel<NT, P, RB, GD1, ONE, CL, NM>;
   // Raising the dynamic shared-memory limit and the carve-out is remembered per device: done once.
   static bool attr_done[64] = {};
   int dev = 0;
@@ -920,6 +986,12 @@ int launch_stream(const GemvParams& p, const StreamPlan& pl, bool pdl, cudaStrea
   if (pl.q.cluster > 1)
     return p.gdiv == 1 ? launch_stream_g<NT, P, RB, true, ONE, true>(p, pl, pdl, stream)
                        : launch_stream_g<NT, P, RB, false, ONE, true>(p, pl, pdl, stream);
+  if constexpr (!ONE && NT == 1) {
+    // one token, add + RMSNorm over a row of at most 4096 values: the merged prologue
+    if (p.pro == kProAddRmsNorm && p.M == 1 && p.nslices == 1 && p.K <= 16 * kThreads)
+      return p.gdiv == 1 ? launch_stream_g<NT, P, RB, true, ONE, false, true>(p, pl, pdl, stream)
+                         : launch_stream_g<NT, P, RB, false, ONE, false, true>(p, pl, pdl, stream);
+  }
   return p.gdiv == 1 ? launch_stream_g<NT, P, RB, true, ONE, false>(p, pl, pdl, stream)
                      : launch_stream_g<NT, P, RB, false, ONE, false>(p, pl, pdl, stream);
 }
