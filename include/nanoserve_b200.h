@@ -126,10 +126,21 @@ int b2_w4_linear(const void* X, const void* Wq, const void* S, void* Y, int M, i
  *               X, R [M, K], Wn [K]; R may be NULL (plain norm).  If Xout is not NULL, bf16(X + R) is stored there
  *               (Xout must not alias X: other CTAs are still reading X).
  *   prologue 2: SwiGLU (semantics of ns_swiglu): X is [M, 2K] = gate | up; the input is bf16(silu(gate) * up).
+ *   prologue 3: X is one token's activations already in the kernel's converted form, as epilogue 2 of the producing
+ *               launch left them (4 K + K / 4 bytes, 16-byte aligned; M = 1; streaming kernel only, else -3).
+ * An epilogue may be added to the prologue as (epilogue << 8); one token, streaming kernel only (else -3):
+ *   epilogue 1: the rows of Wq / S are 16 gate rows, their 16 up rows, the next 16 gate rows ...; Y [M, N / 2] =
+ *               bf16(silu(gate) * up), each half rounded to bf16 first: bit-identical to the plain launch on the
+ *               row-concatenated matrix followed by ns_swiglu.  N % 32 == 0.
+ *   epilogue 2: the same values, written in the converted form that a following launch takes with prologue 3 (so that
+ *               launch need not convert 18944 activations in every CTA): Y is 4 (N/2) + (N/2) / 4 bytes.  N % 256 == 0.
  */
 #define B2_PROLOGUE_NONE 0
 #define B2_PROLOGUE_ADD_RMSNORM 1
 #define B2_PROLOGUE_SWIGLU 2
+#define B2_PROLOGUE_STAGED 3
+#define B2_EPILOGUE_SWIGLU_PAIRS (1 << 8)
+#define B2_EPILOGUE_SWIGLU_STAGED (2 << 8)
 int b2_w4_linear_fused(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G, int prologue,
                        const void* R, const void* Wn, float eps, void* Xout, int flags, void* stream);
 

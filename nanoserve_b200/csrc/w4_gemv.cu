@@ -1465,7 +1465,7 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
   }
   if (tp != nullptr && tp->wait_sig != nullptr && !tp->epoch) return kErrBadPointer;
   if (pro.kind != kProNone) {
-    if (pro.kind != kProAddRmsNorm && pro.kind != kProSwiglu) return kErrBadShape;
+    if (pro.kind != kProAddRmsNorm && pro.kind != kProSwiglu && pro.kind != kProStaged) return kErrBadShape;
     if (G % 128) return kErrNotImplemented;  // prologues live in the fp16 staging of the fast path
     if (pro.kind == kProAddRmsNorm) {
       if (!pro.Wn) return kErrBadPointer;
@@ -1484,7 +1484,8 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
     const int rc = gemv_stream_launch(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
     if (rc != kStreamNotApplicable) return rc;
   }
-  if (pro.epilogue != kEpiNone) return kErrNotImplemented;  // epilogues exist in the streaming kernel only
+  // epilogues and the pre-converted X exist in the streaming kernel only
+  if (pro.epilogue != kEpiNone || pro.kind == kProStaged) return kErrNotImplemented;
   const bool have_scratch = ws.partial && ws.counters;
   GemvPlan pl;
   if (reinterpret_cast<uintptr_t>(S) & 3) flags |= 0x800;  // scale copies need a 4-byte aligned base: one chunk per warp

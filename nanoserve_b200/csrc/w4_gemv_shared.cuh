@@ -11,9 +11,11 @@
 namespace b2 {
 
 // What the kernel does to its input before the product (the operators that precede a linear in a decoder layer)
-enum : int { kProNone = 0, kProAddRmsNorm = 1, kProSwiglu = 2 };
+// kProStaged: X is not activations but their converted form, as the kEpiSwigluStaged epilogue of the producing GEMV left
+// it: four digit planes of K bytes, then one 32-byte info block per 128-chunk (streaming kernel, one token).
+enum : int { kProNone = 0, kProAddRmsNorm = 1, kProSwiglu = 2, kProStaged = 3 };
 // Epilogues (bits above the prologue kind in the `prologue` argument of the fused entry points).
-enum : int { kEpiNone = 0, kEpiSwigluPairs = 1, kEpiShift = 8 };
+enum : int { kEpiNone = 0, kEpiSwigluPairs = 1, kEpiSwigluStaged = 2, kEpiShift = 8 };
 
 struct GemvParams {
   const __nv_bfloat16* X;

@@ -47,6 +47,7 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kHeader = 3072;       // abort flag; mbarriers [warp][slot] at 64; RMSNorm partial sums [16][16] at 1024,
 constexpr int kBarOffset = 64;      // factors [16] at 2048; the weight ring follows (1024-byte aligned)
 constexpr int kMaxDepth = 8;
+constexpr int kStagedBarOffset = 576;  // mbarrier of the bulk copies of a pre-staged X
 constexpr int kZeroOffset = 640;    // 64 bytes of zeros: what lanes without a real B column or info record read
 constexpr int kNormSs = 1024;
 constexpr int kNormInv = 2048;
@@ -532,6 +533,7 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < kWarps * kMaxDepth; ++i) mbar_init(smem_u32(smem + kBarOffset) + 8 * i, 32);
+    mbar_init(smem_u32(smem + kStagedBarOffset), 1);
     fence_mbar_init();
   }
   __syncthreads();
@@ -595,7 +597,21 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
     float* ss = reinterpret_cast<float*>(smem + kNormSs);
     uint32_t crank = 0;
     if constexpr (CL) crank = cluster_ctarank();
-    if constexpr (NM) {
+    if (P == 4 && !ONE && p.pro == kProStaged) {
+      // X arrives converted (the producing GEMV's epilogue did it, one 128-chunk per CTA): four digit planes of K
+      // bytes and 32 bytes of info per chunk, in the layout of this kernel's shared memory -- five bulk copies
+      const uint32_t xbar = smem_u32(smem + kStagedBarOffset);
+      const unsigned char* xb = reinterpret_cast<const unsigned char*>(p.X);
+      const uint32_t plane_bytes = (uint32_t)ncc * 128u, info_bytes = (uint32_t)ncc * 32u;
+      if (tid == 0) {
+        mbar_arrive_expect_tx(xbar, 4u * plane_bytes + info_bytes);
+#pragma unroll
+        for (int l = 0; l < 4; ++l)
+          bulk_g2s(xs_base + l * q.pstride, xb + (size_t)l * p.K + (size_t)cb * 128, plane_bytes, xbar);
+        bulk_g2s(info_base, xb + (size_t)4 * p.K + (size_t)cb * 32, info_bytes, xbar);
+      }
+      mbar_wait(xbar, 0, abort_flag);
+    } else if constexpr (NM) {
       stage_x_planes<P, false, true>(p, xs_base, q.pstride, info_base, inv, cb, ncc, tid, 0u, 1u, ss);
     } else {
       if (p.pro == kProAddRmsNorm) rmsnorm_factors<kThreads>(p, ss, inv, tid);
@@ -714,7 +730,81 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
         writer = P == 4 ? t == 0 : (t < 2 && t < p.M);
       }
     }
-    if (RB == 2 && q.epi == kEpiSwigluPairs) {
+    if (RB == 2 && P == 4 && !ONE && q.epi == kEpiSwigluStaged) {
+      // silu(gate) * up as above, then straight into the converted form the next GEMV (kProStaged) copies into its
+      // shared memory: this CTA's 128 activations are one 128-chunk of that GEMV's K, a warp's 16 are one item.
+      // Same arithmetic as stage_x_planes on the bf16 activations, so that GEMV's outputs are bit-identical.
+      auto act = [](float gv, float uv) {
+        const float a = __bfloat162float(__float2bfloat16(gv)), b = __bfloat162float(__float2bfloat16(uv));
+        return __float2bfloat16(a / (1.f + __expf(-a)) * b);
+      };
+      const uint32_t blo = t == 0 ? (uint32_t)__bfloat16_as_ushort(act(v_lo[0], v_lo[RB - 1])) : 0u;
+      const uint32_t bhi = t == 0 ? (uint32_t)__bfloat16_as_ushort(act(v_hi[0], v_hi[RB - 1])) : 0u;
+      uint32_t mx = max(blo & 0x7FFFu, bhi & 0x7FFFu);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      uint32_t* s_mx = reinterpret_cast<uint32_t*>(smem + kNormSs);   // [8] warp maxima
+      int* s_zc = reinterpret_cast<int*>(smem + kNormSs + 64);        // [8][4] digit sums of the warps' items
+      if (lane == 0) s_mx[warp] = mx;
+      __syncthreads();
+      uint32_t cm = 0;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) cm = max(cm, s_mx[w]);
+      uint32_t eb = cm >> 7;
+      const bool bad = eb == 255u;
+      eb = min(254u, max(40u, eb));
+      constexpr int B = 32;
+      constexpr uint32_t kBias = 0x00808080u;
+      const float down = __uint_as_float((uint32_t)(B + 251 - (int)eb) << 23);
+      const uint32_t u_lo = ((uint32_t)__float2int_rn(__uint_as_float(blo << 16) * down) + kBias) ^ kBias;
+      const uint32_t u_hi = ((uint32_t)__float2int_rn(__uint_as_float(bhi << 16) * down) + kBias) ^ kBias;
+      uint32_t u[16];  // digit sets of the item's 16 values: lane 4 g holds k = g and k = g + 8
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        u[i] = __shfl_sync(0xffffffffu, u_lo, 4 * i);
+        u[i + 8] = __shfl_sync(0xffffffffu, u_hi, 4 * i);
+      }
+      const int k_act = p.N >> 1;
+      unsigned char* yb = reinterpret_cast<unsigned char*>(p.Y);
+      if (lane == 0) {
+        uint32_t pl[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int b = (j & 1) * 8 + (j >> 1);
+          const uint32_t t0 = __byte_perm(u[b], u[b + 2], 0x5140), t2 = __byte_perm(u[b + 4], u[b + 6], 0x5140);
+          const uint32_t t1 = __byte_perm(u[b], u[b + 2], 0x7362), t3 = __byte_perm(u[b + 4], u[b + 6], 0x7362);
+          pl[0][j] = __byte_perm(t0, t2, 0x5410);
+          pl[1][j] = __byte_perm(t0, t2, 0x7632);
+          pl[2][j] = __byte_perm(t1, t3, 0x5410);
+          pl[3][j] = __byte_perm(t1, t3, 0x7632);
+        }
+        const size_t item = (size_t)(wrow0 >> 5);  // 16 activations per warp
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+          int c = __dp4a((int)pl[l][0], 0x01010101, 0);
+          c = __dp4a((int)pl[l][1], 0x01010101, c);
+          c = __dp4a((int)pl[l][2], 0x01010101, c);
+          c = __dp4a((int)pl[l][3], 0x01010101, c);
+          s_zc[warp * 4 + l] = c;
+          if (active)
+            *reinterpret_cast<uint4*>(yb + (size_t)l * k_act + item * 16) =
+                make_uint4(pl[l][0], pl[l][1], pl[l][2], pl[l][3]);
+        }
+      }
+      __syncthreads();
+      if (tid < 2 && row0 < p.N) {  // the chunk's two info records (column pairs of planes 0,1 and 2,3)
+        int z0 = 0, z1 = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          z0 += s_zc[w * 4 + 2 * tid];
+          z1 += s_zc[w * 4 + 2 * tid + 1];
+        }
+        const uint32_t up0 = bad ? 0x7FC00000u : (uint32_t)((int)eb - B - 1 + 16 * tid) << 23;
+        const uint32_t up1 = bad ? 0x7FC00000u : (uint32_t)((int)eb - B + 7 + 16 * tid) << 23;
+        *reinterpret_cast<uint4*>(yb + (size_t)4 * k_act + ((size_t)blockIdx.x * 2 + tid) * 16) =
+            make_uint4((uint32_t)(-128 * z0), (uint32_t)(-128 * z1), up0, up1);
+      }
+    } else if (RB == 2 && q.epi == kEpiSwigluPairs) {
       // rows come as 16 gate rows followed by their 16 up rows: the warp's first block is gate, its second up, and a
       // lane holds both halves of its rows.  Each half is rounded to bf16 first (what a plain launch would have
       // stored), then silu(gate) * up in fp32 as ns_swiglu computes it, one rounding at the store.
@@ -867,7 +957,7 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   if (((flags >> 10) & 3) == 1) pl.RB = 1;
   if (((flags >> 10) & 3) == 2) pl.RB = 2;
   if (pl.one) pl.RB = 1;
-  if (epilogue == kEpiSwigluPairs) pl.RB = 2;  // a warp then owns a gate block and its up block
+  if (epilogue != kEpiNone) pl.RB = 2;  // a warp then owns a gate block and its up block
   const int rows = pl.RB * 16;
   const int nsc = K / 256, gdiv = G / 128, KG = K / G;
   const int n_tiles = (N + rows - 1) / rows;
@@ -877,7 +967,7 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   while (ks < 8 && (long)n_tiles * ks < (long)sm_count * kWarps * 3 / 4 && nsc / (ks * 2) >= 2) ks *= 2;
   const int forced_ks = (flags >> 20) & 0xF;
   if (forced_ks == 1 || forced_ks == 2 || forced_ks == 4 || forced_ks == 8) ks = forced_ks;
-  if (epilogue == kEpiSwigluPairs) ks = 1;  // the register epilogue: a warp holds whole dot products
+  if (epilogue != kEpiNone) ks = 1;  // the register epilogue: a warp holds whole dot products
   pl.ks = ks;
   const int tpc = kWarps / ks;
   pl.grid_x = (n_tiles + tpc - 1) / tpc;
@@ -1046,7 +1136,13 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
   const bool have_scratch = ws.partial != nullptr;
   // a tensor-parallel producer signals its peers after its stores: no sum kernel behind it, so no split across CTAs
   bool no_split = !have_scratch || (tp != nullptr && tp->world > 0);
-  if (pro.epilogue == kEpiSwigluPairs) {
+  if (pro.kind == kProStaged && (M != 1 || (reinterpret_cast<uintptr_t>(X) & 15) || (K & 127))) return kErrNotImplemented;
+  if (pro.epilogue == kEpiSwigluStaged) {
+    // a CTA must own exactly one 128-chunk of the consumer's K: 256 rows; no tensor-parallel form
+    if (M != 1 || (N & 255) || (tp != nullptr && tp->world > 0) || (reinterpret_cast<uintptr_t>(Y) & 15))
+      return kErrNotImplemented;
+    no_split = true;
+  } else if (pro.epilogue == kEpiSwigluPairs) {
     // served by the register epilogue of the one-token kernel only: a caller that gets this code runs the plain
     // launch followed by the SwiGLU prologue of the next one
     // (tensor parallel: a producer with a deferred signal only -- the register epilogue has no CTA-wide tail)

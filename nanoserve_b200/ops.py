@@ -28,6 +28,8 @@ FLAG_NO_PRE_STAGE_X = 16384
 FLAG_SPLIT_SUM_KERNEL = 32768
 FLAG_NO_SPLIT_SUM_KERNEL = 65536
 FLAG_RING_KERNEL = 131072    # decode GEMV: the shared-memory ring kernel even where the streaming kernel applies
+PRO_STAGED = 3        # prologue of b2_w4_linear_fused: x is the converted form EPI_SWIGLU_STAGED left (uint8 buffer)
+EPI_SWIGLU_STAGED = 2  # like EPI_SWIGLU_PAIRS, but the output is the converted form the next GEMV takes with PRO_STAGED
 EPI_SWIGLU_PAIRS = 1  # epilogue of b2_w4_linear_fused: silu(gate) * up over row blocks of 16 gate + 16 up rows
 FLAG_GEMM_NO_PAIRS = 1 << 29  # prefill GEMM: one CTA per tile unpacks the whole weight tile (no clusters of two)
 FLAG_GEMM_WHOLE_TILES = 1 << 30  # prefill GEMM: every CTA takes whole output tiles (no fp32 part-tiles)
@@ -76,6 +78,11 @@ class TpDesc(ctypes.Structure):
                 ("seg_dst", _i32 * 3), ("y_local", _vp), ("wait_sig", _vp), ("epoch", _vp),
                 ("wait_per_epoch", ctypes.c_uint), ("defer_signal", _i32), ("announce_world", _i32),
                 ("announce_peer", _vp * 8)]
+
+
+def staged_x_bytes(K: int) -> int:
+    """Bytes of one token's activations in the converted form EPI_SWIGLU_STAGED writes and PRO_STAGED reads."""
+    return 4 * K + (K // 128) * 32
 
 
 def make_tp_desc(y_peers=(), sig_peers=(), ld=0, pieces=None, y_local=None, wait_sig=None, epoch=None,
@@ -215,10 +222,17 @@ class Kernels:
         the rows of Wq are 16 gate rows, their 16 up rows, the next 16 gate rows ... and the output is
         silu(gate) * up, [M, N / 2] (one token; raises with code -3 where the kernel cannot serve it)."""
         self._cuda(x, Wq, S, r, wn, x_out)
-        M = x.shape[0]
         N, K = Wq.shape[0], Wq.shape[1] * 8
-        assert x.is_contiguous() and x.shape[1] == (2 * K if prologue == 2 else K)
-        y = torch.empty((M, N // 2 if epilogue == EPI_SWIGLU_PAIRS else N), dtype=torch.bfloat16, device=x.device)
+        if prologue == PRO_STAGED:  # one token; x: four digit planes of K bytes + 32 bytes per 128-chunk
+            M = 1
+            assert x.is_contiguous() and x.dtype == torch.uint8 and x.numel() == staged_x_bytes(K)
+        else:
+            M = x.shape[0]
+            assert x.is_contiguous() and x.shape[1] == (2 * K if prologue == 2 else K)
+        if epilogue == EPI_SWIGLU_STAGED:
+            y = torch.empty(staged_x_bytes(N // 2), dtype=torch.uint8, device=x.device)
+        else:
+            y = torch.empty((M, N // 2 if epilogue == EPI_SWIGLU_PAIRS else N), dtype=torch.bfloat16, device=x.device)
         p = lambda t: None if t is None else t.data_ptr()
         rc = self.lib.b2_w4_linear_fused(x.data_ptr(), Wq.data_ptr(), S.data_ptr(), y.data_ptr(), M, N, K, group,
                                          prologue | (epilogue << 8), p(r), p(wn), eps, p(x_out), flags, self._stream())

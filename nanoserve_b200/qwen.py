@@ -27,7 +27,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from .ops import EPI_SWIGLU_PAIRS, Kernels, make_tp_desc
+from .ops import EPI_SWIGLU_PAIRS, EPI_SWIGLU_STAGED, PRO_STAGED, Kernels, make_tp_desc
 
 
 @dataclass
@@ -299,12 +299,19 @@ class Qwen2Runner:
                                                self._st())
             k._check(rc, "b2_decode_attention_fused")
             o = self._gather(self.linear(a, L["o"]))
-            # SwiGLU in the epilogue of gate|up: the down projection reads the (gathered) activation as is
-            act = self._gather(self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o,
-                                                      wn=L["ln_post"], eps=cfg.rms_eps, x_out=x_alt,
-                                                      epilogue=EPI_SWIGLU_PAIRS))
-            x, x_alt = x_alt, x
-            d = self._gather(self.linear(act, L["d"]))
+            if self.world == 1:
+                # SwiGLU in the epilogue of gate|up, written in the converted form the down projection copies into
+                # its shared memory (no conversion of 18944 activations in every CTA of the down projection)
+                staged = self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o, wn=L["ln_post"],
+                                                eps=cfg.rms_eps, x_out=x_alt, epilogue=EPI_SWIGLU_STAGED)
+                x, x_alt = x_alt, x
+                d = self.k.w4_linear_fused(staged, L["d"][0], L["d"][1], cfg.group, prologue=PRO_STAGED)
+            else:  # SwiGLU in the epilogue; the activation is gathered by NCCL
+                act = self._gather(self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o,
+                                                          wn=L["ln_post"], eps=cfg.rms_eps, x_out=x_alt,
+                                                          epilogue=EPI_SWIGLU_PAIRS))
+                x, x_alt = x_alt, x
+                d = self._gather(self.linear(act, L["d"]))
             r = d
             wn = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
         # final add + RMSNorm folded into the vocabulary projection, argmax partials in its epilogue.  The residual

@@ -120,3 +120,35 @@ def test_swiglu_pairs_epilogue_is_refused_where_it_cannot_run(kernels):
         with pytest.raises(RuntimeError, match="code -3"):
             kernels.w4_linear_fused(x, u32_to_torch(Wq), bits_to_torch(S), grp, epilogue=ops.EPI_SWIGLU_PAIRS)
     assert kernels.device_status() == 0
+
+
+@pytest.mark.parametrize("I,K,H", [(18944, 3584, 3584), (1024, 512, 320)])
+def test_staged_handover_between_two_gemvs(kernels, I, K, H):
+    """gate|up writes silu(gate) * up in the converted form (epilogue 2), the down projection copies it into its
+    shared memory instead of converting (prologue 3): the down output must equal, bit for bit, the one computed from
+    the bf16 activations of epilogue 1."""
+    G = 128
+    _, Wa, Sa = oracle.synth_inputs(1, 2 * I, K, G, seed=51)
+    _, Wb, Sb = oracle.synth_inputs(1, H, I, G, seed=52)
+    wa, sa, wb, sb = u32_to_torch(Wa), bits_to_torch(Sa), u32_to_torch(Wb), bits_to_torch(Sb)
+    wa, sa = _pairs(wa[:I], wa[I:]), _pairs(sa[:I], sa[I:])
+    g = torch.Generator(device="cuda").manual_seed(I)
+    x = torch.randn(1, K, device="cuda", generator=g).to(torch.bfloat16)
+    act = kernels.w4_linear_fused(x, wa, sa, G, epilogue=ops.EPI_SWIGLU_PAIRS)
+    want = kernels.w4_linear(act, wb, sb, G)
+    staged = kernels.w4_linear_fused(x, wa, sa, G, epilogue=ops.EPI_SWIGLU_STAGED)
+    assert staged.dtype == torch.uint8 and staged.numel() == ops.staged_x_bytes(I)
+    got = kernels.w4_linear_fused(staged, wb, sb, G, prologue=ops.PRO_STAGED)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    # an inf among the activations poisons its chunk in both forms alike
+    x2 = x.clone()
+    x2[0, 3] = float("inf")
+    a2 = kernels.w4_linear_fused(x2, wa, sa, G, epilogue=ops.EPI_SWIGLU_PAIRS)
+    w2 = kernels.w4_linear(a2, wb, sb, G)
+    s2 = kernels.w4_linear_fused(x2, wa, sa, G, epilogue=ops.EPI_SWIGLU_STAGED)
+    g2 = kernels.w4_linear_fused(s2, wb, sb, G, prologue=ops.PRO_STAGED)
+    torch.cuda.synchronize()
+    assert torch.equal(torch.isnan(g2), torch.isnan(w2))
+    assert torch.equal(torch.nan_to_num(g2.float()), torch.nan_to_num(w2.float()))
+    assert kernels.device_status() == 0
