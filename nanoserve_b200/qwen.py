@@ -57,7 +57,7 @@ def _rand_w4(N, K, G, gen, device):
 
 class Qwen2Runner:
     def __init__(self, cfg: Qwen2Config, kernels: Kernels, device, rank: int = 0, world: int = 1, seed: int = 0,
-                 max_len: int = 1024, group=None, fused_gather: bool = True):
+                 max_len: int = 1024, group=None, fused_gather: bool = True, norm_gain: float = 0.001):
         self.cfg, self.k, self.dev = cfg, kernels, device
         self.rank, self.world, self.group = rank, world, group
         self.max_len = max_len
@@ -77,7 +77,6 @@ class Qwen2Runner:
             return shard(Wq), shard(S)
 
         self.layers = []
-        norm_gain = 0.001
         for _ in range(cfg.n_layers):
             q, k, v = w4(self.nq, H), w4(self.nkv, H), w4(self.nkv, H)
             o = w4(H, self.nq)
@@ -299,7 +298,7 @@ class Qwen2Runner:
                                                self._st())
             k._check(rc, "b2_decode_attention_fused")
             o = self._gather(self.linear(a, L["o"]))
-            if self.world == 1:
+            if self.world == 1 and self.I % 128 == 0:
                 # SwiGLU in the epilogue of gate|up, written in the converted form the down projection copies into
                 # its shared memory (no conversion of 18944 activations in every CTA of the down projection)
                 staged = self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o, wn=L["ln_post"],

@@ -22,8 +22,9 @@ def dequant(wt, G):
     return q * S.float().repeat_interleave(G, dim=1)
 
 
-def torch_forward(r, ids):
-    """fp32 forward over the whole sequence `ids` (prompt + generated so far); returns logits of the last token."""
+def torch_forward(r, ids, skip_mlp=False, skip_attn=False):
+    """fp32 forward over the whole sequence `ids` (prompt + generated so far); returns logits of the last token.
+    skip_mlp / skip_attn drop a sub-layer: used to show that the comparison would notice its absence."""
     cfg = r.cfg
     T, D, G = ids.shape[0], cfg.head_dim, cfg.group
     x = F.embedding(ids, r.embed).float()
@@ -47,11 +48,14 @@ def torch_forward(r, ids):
         k = rope(qkv[:, r.nq:r.nq + r.nkv], cfg.n_kv_heads).transpose(0, 1)[None]
         v = qkv[:, r.nq + r.nkv:].view(T, cfg.n_kv_heads, D).transpose(0, 1)[None]
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)[0].transpose(0, 1).reshape(T, r.nq)
-        x = x + a @ dequant(L["o"], G).T
+        if not skip_attn:
+            x = x + a @ dequant(L["o"], G).T
         h = norm(x, L["ln_post"])
-        gu = h @ dequant(L["gu"], G).T
-        act = F.silu(gu[:, :r.I]) * gu[:, r.I:]
-        x = x + act @ dequant(L["d"], G).T
+        # the runner stores gate|up as 16 gate rows, their 16 up rows, the next 16 gate rows ...
+        gu = (h @ dequant(L["gu"], G).T).view(T, r.I // 16, 2, 16)
+        act = F.silu(gu[:, :, 0].reshape(T, r.I)) * gu[:, :, 1].reshape(T, r.I)
+        if not skip_mlp:
+            x = x + act @ dequant(L["d"], G).T
         nxt = r.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else r.final_norm
         h = norm(x, nxt)
     return h[-1:] @ r.lm_head.float().T
@@ -59,7 +63,9 @@ def torch_forward(r, ids):
 
 def test_decode_logits_and_graph(kernels):
     dev = torch.device("cuda")
-    r = Qwen2Runner(CFG, kernels, dev, seed=3, max_len=96)
+    # norm gains large enough that attention and the MLP move the logits (the benchmark's model uses 0.001 so that
+    # greedy decoding of a random model stays input-dependent; with that the layers would hardly show here)
+    r = Qwen2Runner(CFG, kernels, dev, seed=3, max_len=96, norm_gain=1.0)
     prompt = torch.randint(0, CFG.vocab, (40,), device=dev, generator=torch.Generator(device=dev).manual_seed(5))
     with torch.cuda.stream(r.stream):
         first = int(r.prefill(prompt))
@@ -70,6 +76,9 @@ def test_decode_logits_and_graph(kernels):
             scale = ref.abs().max()
             assert torch.all(torch.isfinite(logits))
             assert (logits - ref).abs().max() <= 3e-2 * scale, float((logits - ref).abs().max() / scale)
+            # the bound means something only if a missing sub-layer would break it
+            assert (torch_forward(r, seq, skip_mlp=True) - ref).abs().max() > 0.1 * scale
+            assert (torch_forward(r, seq, skip_attn=True) - ref).abs().max() > 0.1 * scale
             seq = torch.cat([seq, r.tokens[int(r.step.item()) - 1:int(r.step.item())]])
     torch.cuda.synchronize()
     eager = r.generate(prompt, 12, use_graph=False)
