@@ -442,6 +442,31 @@ def decode_rate(kernels: Kernels, device, rank: int = 0, world: int = 1, cfg: Op
             del r1
             torch.cuda.empty_cache()
         dist.barrier()
+        # The benchmark's model has small norm gains (so that greedy decoding of random weights stays input-dependent),
+        # which also means its logits say little about attention and the MLP.  A second, short comparison with unit
+        # gains, where every sub-layer moves the logits: four layers, 64-token prompt, six decode steps.
+        import copy
+        c4 = copy.copy(cfg)
+        c4.n_layers = min(4, cfg.n_layers)
+        short = prompt[:64]
+        rs = Qwen2Runner(c4, kernels, device, rank=rank, world=world, seed=seed + 1, max_len=96,
+                         fused_gather=fused_gather, norm_gain=1.0)
+        toks_s = rs.generate(short, 6)
+        torch.cuda.synchronize()
+        rs.check_status()
+        mine_s = rs.logits.float().clone()
+        if rank == 0:
+            r1s = Qwen2Runner(c4, kernels, device, rank=0, world=1, seed=seed + 1, max_len=96, norm_gain=1.0)
+            toks_1 = r1s.generate(short, 6)
+            torch.cuda.synchronize()
+            want_s = r1s.logits.float()[:, :mine_s.shape[1]]
+            rel = float(((mine_s - want_s).abs() / want_s.abs().max()).max())
+            tp_check["unit_gain"] = {"layers": c4.n_layers, "logits_max_rel": rel, "tokens_equal": toks_1 == toks_s}
+            tp_check["ok"] = bool(tp_check["ok"] and rel <= 2e-2 and toks_1 == toks_s)
+            del r1s
+        del rs
+        torch.cuda.empty_cache()
+        dist.barrier()
     return {"tp_check": tp_check, "tokens_sha1": sha, "distinct_tokens": len(set(tokens)), "tok_s": (n_new - 1) / t_decode, "ms_per_token": t_decode / (n_new - 1) * 1e3,
             "prefill_tok_s": prompt_len / t_prefill, "prompt_len": prompt_len, "n_new": n_new,
             "weight_bytes_per_token_per_rank": r.weight_bytes_per_token(), "first_tokens": tokens[:8],
