@@ -81,7 +81,8 @@ def test_reference_bench_case(kernels):
     assert oracle.max_rel_err(y, ref) < 1e-2
 
 
-@pytest.mark.parametrize("M,N,K", [(512, 18944, 3584), (2048, 3584, 18944)])
+@pytest.mark.parametrize("M,N,K", [(512, 18944, 3584), (2048, 3584, 18944), (8192, 18944, 3584), (8192, 3584, 18944),
+                                   (4096, 28672, 8192)])
 def test_prefill_shapes_sampled(kernels, M, N, K):
     """Full benchmark shapes; the oracle checks a sample of output rows (the full product is ~1e11 MACs)."""
     G = 128
