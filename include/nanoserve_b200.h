@@ -132,6 +132,7 @@ int b2_w4_linear(const void* X, const void* Wq, const void* S, void* Y, int M, i
  *   epilogue 1: the rows of Wq / S are 16 gate rows, their 16 up rows, the next 16 gate rows ...; Y [M, N / 2] =
  *               bf16(silu(gate) * up), each half rounded to bf16 first: bit-identical to the plain launch on the
  *               row-concatenated matrix followed by ns_swiglu.  N % 32 == 0.
+ *   epilogue 3: epilogue 1 with row blocks of 8 gate + 8 up rows (the kernel then gives a warp 16 rows).  N % 16 == 0.
  *   epilogue 2: the same values, written in the converted form that a following launch takes with prologue 3 (so that
  *               launch need not convert 18944 activations in every CTA): Y is 4 (N/2) + (N/2) / 4 bytes.  N % 256 == 0.
  */
@@ -141,6 +142,7 @@ int b2_w4_linear(const void* X, const void* Wq, const void* S, void* Y, int M, i
 #define B2_PROLOGUE_STAGED 3
 #define B2_EPILOGUE_SWIGLU_PAIRS (1 << 8)
 #define B2_EPILOGUE_SWIGLU_STAGED (2 << 8)
+#define B2_EPILOGUE_SWIGLU_PAIRS8 (3 << 8)
 int b2_w4_linear_fused(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int G, int prologue,
                        const void* R, const void* Wn, float eps, void* Xout, int flags, void* stream);
 

@@ -1454,7 +1454,7 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
   if (M < 1 || M > 16) return kErrUnsupportedM;
   if (tp != nullptr && tp->world > 0) {
     // (with the SwiGLU epilogue a launch delivers N / 2 columns)
-    if (tp->world > kMaxTpRanks || tp->ld < (pro.epilogue == kEpiSwigluPairs ? N / 2 : N) || tp->seg_end[0] < 0 ||
+    if (tp->world > kMaxTpRanks || tp->ld < (pro.epilogue != kEpiNone ? N / 2 : N) || tp->seg_end[0] < 0 ||
         tp->seg_end[1] < tp->seg_end[0])
       return kErrBadShape;
     for (int r = 0; r < tp->world; ++r)

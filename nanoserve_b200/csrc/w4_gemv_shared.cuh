@@ -15,7 +15,8 @@ namespace b2 {
 // it: four digit planes of K bytes, then one 32-byte info block per 128-chunk (streaming kernel, one token).
 enum : int { kProNone = 0, kProAddRmsNorm = 1, kProSwiglu = 2, kProStaged = 3 };
 // Epilogues (bits above the prologue kind in the `prologue` argument of the fused entry points).
-enum : int { kEpiNone = 0, kEpiSwigluPairs = 1, kEpiSwigluStaged = 2, kEpiShift = 8 };
+// kEpiSwigluPairs8: as kEpiSwigluPairs with row blocks of 8 gate + 8 up rows (16 rows per warp instead of 32).
+enum : int { kEpiNone = 0, kEpiSwigluPairs = 1, kEpiSwigluStaged = 2, kEpiSwigluPairs8 = 3, kEpiShift = 8 };
 
 struct GemvParams {
   const __nv_bfloat16* X;

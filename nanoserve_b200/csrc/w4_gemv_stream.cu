@@ -804,6 +804,11 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
         *reinterpret_cast<uint4*>(yb + (size_t)4 * k_act + ((size_t)blockIdx.x * 2 + tid) * 16) =
             make_uint4((uint32_t)(-128 * z0), (uint32_t)(-128 * z1), up0, up1);
       }
+    } else if (RB == 1 && q.epi == kEpiSwigluPairs8 && p.tp.world == 0) {
+      // blocks of 8 gate rows and their 8 up rows: the lane's row g is a gate row, its row g + 8 the matching up row
+      const float a = __bfloat162float(__float2bfloat16(v_lo[0])), b = __bfloat162float(__float2bfloat16(v_hi[0]));
+      const int n = (wrow0 >> 1) + grow, n_act = p.N >> 1;
+      if (writer && active && n < n_act) p.Y[(size_t)m * n_act + n] = __float2bfloat16(a / (1.f + __expf(-a)) * b);
     } else if (RB == 2 && q.epi == kEpiSwigluPairs) {
       // rows come as 16 gate rows followed by their 16 up rows: the warp's first block is gate, its second up, and a
       // lane holds both halves of its rows.  Each half is rounded to bf16 first (what a plain launch would have
@@ -953,11 +958,17 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   pl.NT = pl.one ? (M * pl.P + 7) / 8 : 1;
   // 32 rows per warp where 16 would make more than 1.25 CTAs per SM (fewer, longer CTAs stream better than an
   // uneven second wave); bits 10-11 of the flags force 16 (1) or 32 (2) rows (diagnostics)
-  pl.RB = (long)((N + 15) / 16 + kWarps - 1) / kWarps * 4 > (long)sm_count * 5 ? 2 : 1;
+  {
+    const long c1 = ((N + 15) / 16 + kWarps - 1) / kWarps;  // CTAs with 16 rows per warp
+    pl.RB = c1 * 4 > (long)sm_count * 5 ? 2 : 1;
+    // ... except where they fill both CTA slots of every SM almost exactly (37888 rows on 148 SMs: 296 CTAs): sixteen
+    // warps per SM with five ring slots each then stream better than eight with two (13.1 against 14.1 us)
+    if (c1 * 100 > (long)sm_count * 185 && c1 <= 2l * sm_count) pl.RB = 1;
+  }
   if (((flags >> 10) & 3) == 1) pl.RB = 1;
   if (((flags >> 10) & 3) == 2) pl.RB = 2;
   if (pl.one) pl.RB = 1;
-  if (epilogue != kEpiNone) pl.RB = 2;  // a warp then owns a gate block and its up block
+  if (epilogue != kEpiNone) pl.RB = epilogue == kEpiSwigluPairs8 ? 1 : 2;  // a warp owns a gate block and its up block
   const int rows = pl.RB * 16;
   const int nsc = K / 256, gdiv = G / 128, KG = K / G;
   const int n_tiles = (N + rows - 1) / rows;
@@ -1142,6 +1153,9 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
     if (M != 1 || (N & 255) || (tp != nullptr && tp->world > 0) || (reinterpret_cast<uintptr_t>(Y) & 15))
       return kErrNotImplemented;
     no_split = true;
+  } else if (pro.epilogue == kEpiSwigluPairs8) {
+    if (M != 1 || (N & 15) || (tp != nullptr && tp->world > 0)) return kErrNotImplemented;
+    no_split = true;
   } else if (pro.epilogue == kEpiSwigluPairs) {
     // served by the register epilogue of the one-token kernel only: a caller that gets this code runs the plain
     // launch followed by the SwiGLU prologue of the next one
@@ -1154,7 +1168,9 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
   if (!make_stream_plan(M, N, K, G, S, no_split ? (flags | kFlagForceNoSplitK) : flags, sm_count, ws.partial_bytes, &pl,
                         pro.epilogue))
     return pro.epilogue != kEpiNone ? kErrNotImplemented : kStreamNotApplicable;
-  if (pro.epilogue != kEpiNone && (pl.nslices != 1 || pl.one || pl.RB != 2 || pl.ks != 1)) return kErrNotImplemented;
+  if (pro.epilogue != kEpiNone &&
+      (pl.nslices != 1 || pl.one || pl.RB != (pro.epilogue == kEpiSwigluPairs8 ? 1 : 2) || pl.ks != 1))
+    return kErrNotImplemented;
   GemvParams p{};
   p.X = static_cast<const __nv_bfloat16*>(X);
   p.S = static_cast<const __nv_bfloat16*>(S);

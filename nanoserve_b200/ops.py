@@ -30,6 +30,7 @@ FLAG_NO_SPLIT_SUM_KERNEL = 65536
 FLAG_RING_KERNEL = 131072    # decode GEMV: the shared-memory ring kernel even where the streaming kernel applies
 PRO_STAGED = 3        # prologue of b2_w4_linear_fused: x is the converted form EPI_SWIGLU_STAGED left (uint8 buffer)
 EPI_SWIGLU_STAGED = 2  # like EPI_SWIGLU_PAIRS, but the output is the converted form the next GEMV takes with PRO_STAGED
+EPI_SWIGLU_PAIRS8 = 3  # EPI_SWIGLU_PAIRS with row blocks of 8 gate + 8 up rows (the kernel then gives a warp 16 rows)
 EPI_SWIGLU_PAIRS = 1  # epilogue of b2_w4_linear_fused: silu(gate) * up over row blocks of 16 gate + 16 up rows
 FLAG_GEMM_NO_PAIRS = 1 << 29  # prefill GEMM: one CTA per tile unpacks the whole weight tile (no clusters of two)
 FLAG_GEMM_WHOLE_TILES = 1 << 30  # prefill GEMM: every CTA takes whole output tiles (no fp32 part-tiles)
@@ -232,7 +233,8 @@ class Kernels:
         if epilogue == EPI_SWIGLU_STAGED:
             y = torch.empty(staged_x_bytes(N // 2), dtype=torch.uint8, device=x.device)
         else:
-            y = torch.empty((M, N // 2 if epilogue == EPI_SWIGLU_PAIRS else N), dtype=torch.bfloat16, device=x.device)
+            y = torch.empty((M, N // 2 if epilogue in (EPI_SWIGLU_PAIRS, EPI_SWIGLU_PAIRS8) else N), dtype=torch.bfloat16,
+                            device=x.device)
         p = lambda t: None if t is None else t.data_ptr()
         rc = self.lib.b2_w4_linear_fused(x.data_ptr(), Wq.data_ptr(), S.data_ptr(), y.data_ptr(), M, N, K, group,
                                          prologue | (epilogue << 8), p(r), p(wn), eps, p(x_out), flags, self._stream())

@@ -27,7 +27,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from .ops import EPI_SWIGLU_PAIRS, EPI_SWIGLU_STAGED, PRO_STAGED, Kernels, make_tp_desc
+from .ops import EPI_SWIGLU_PAIRS, EPI_SWIGLU_PAIRS8, EPI_SWIGLU_STAGED, PRO_STAGED, Kernels, make_tp_desc
 
 
 @dataclass
@@ -76,6 +76,8 @@ class Qwen2Runner:
             Wq, S = _rand_w4(N, K, cfg.group, gen, device)  # same seed on every rank, then each keeps its rows
             return shard(Wq), shard(S)
 
+        # gate|up row blocks: 16 gate rows + their 16 up rows (8 + 8 with B2_QWEN_GU_BLOCK=8: the 16-rows-per-warp epilogue)
+        self.gu_block = int(os.environ.get("B2_QWEN_GU_BLOCK", "16")) if world == 1 else 16
         self.layers = []
         for _ in range(cfg.n_layers):
             q, k, v = w4(self.nq, H), w4(self.nkv, H), w4(self.nkv, H)
@@ -86,9 +88,9 @@ class Qwen2Runner:
             # 16 gate rows, their 16 up rows, the next 16 gate rows ... (of this rank's shard): the decode GEMV then
             # holds a gate value and its up value in the same lane and applies SwiGLU in its epilogue (same rows, same
             # arithmetic)
-            def pairs(a, b):
-                return torch.stack([a.view(a.shape[0] // 16, 16, -1), b.view(b.shape[0] // 16, 16, -1)], 1).reshape(
-                    2 * a.shape[0], -1).contiguous()
+            def pairs(a, b, blk=self.gu_block):
+                return torch.stack([a.view(a.shape[0] // blk, blk, -1), b.view(b.shape[0] // blk, blk, -1)],
+                                   1).reshape(2 * a.shape[0], -1).contiguous()
             gu = (pairs(g[0], u[0]), pairs(g[1], u[1]))
             self.layers.append({
                 "qkv": (torch.cat([q[0], k[0], v[0]]), torch.cat([q[1], k[1], v[1]])),
@@ -233,7 +235,7 @@ class Qwen2Runner:
             h = k.rmsnorm(x, self._gather(self.linear(a, L["o"])), L["ln_post"], cfg.rms_eps)
             gu = self.linear(h, L["gu"])
             il = self.I // self.world
-            gu = gu.view(T, il // 16, 2, 16)  # blocks of 16 gate rows and 16 up rows alternate (see __init__)
+            gu = gu.view(T, il // self.gu_block, 2, self.gu_block)  # gate and up row blocks alternate (see __init__)
             act = self._gather(k.swiglu(gu[:, :, 0].reshape(T, il), gu[:, :, 1].reshape(T, il)))
             nxt = self.layers[li + 1]["ln_in"] if li + 1 < cfg.n_layers else self.final_norm
             h = k.rmsnorm(x, self._gather(self.linear(act, L["d"])), nxt, cfg.rms_eps)
@@ -298,7 +300,12 @@ class Qwen2Runner:
                                                self._st())
             k._check(rc, "b2_decode_attention_fused")
             o = self._gather(self.linear(a, L["o"]))
-            if self.world == 1 and self.I % 128 == 0:
+            if self.world == 1 and self.gu_block == 8:
+                act = self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o, wn=L["ln_post"],
+                                             eps=cfg.rms_eps, x_out=x_alt, epilogue=EPI_SWIGLU_PAIRS8)
+                x, x_alt = x_alt, x
+                d = self.linear(act, L["d"])
+            elif self.world == 1 and self.I % 128 == 0:
                 # SwiGLU in the epilogue of gate|up, written in the converted form the down projection copies into
                 # its shared memory (no conversion of 18944 activations in every CTA of the down projection)
                 staged = self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o, wn=L["ln_post"],

@@ -81,10 +81,10 @@ def test_prologue_error_codes(kernels):
         kernels.w4_linear_fused(x, wq, s, 128, prologue=7)
 
 
-def _pairs(a, b):
-    """16 rows of a, the same 16 rows of b, the next 16 of a ..."""
+def _pairs(a, b, blk=16):
+    """`blk` rows of a, the same rows of b, the next `blk` of a ..."""
     n = a.shape[0]
-    return torch.stack([a.view(n // 16, 16, -1), b.view(n // 16, 16, -1)], 1).reshape(2 * n, -1).contiguous()
+    return torch.stack([a.view(n // blk, blk, -1), b.view(n // blk, blk, -1)], 1).reshape(2 * n, -1).contiguous()
 
 
 @pytest.mark.parametrize("I,K,norm", [(18944, 3584, True), (18944, 3584, False), (2048, 1024, False), (160, 512, True)])
@@ -104,9 +104,13 @@ def test_swiglu_pairs_epilogue(kernels, I, K, norm):
     ref = kernels.swiglu(gu[:, :I].contiguous(), gu[:, I:].contiguous())
     wq2, s2 = _pairs(wq[:I], wq[I:]), _pairs(s[:I], s[I:])
     act = kernels.w4_linear_fused(x, wq2, s2, G, prologue=pro, r=r, wn=wn, eps=1e-6, epilogue=ops.EPI_SWIGLU_PAIRS)
+    # the same with row blocks of 8 (16 rows per warp)
+    wq3, s3 = _pairs(wq[:I], wq[I:], 8), _pairs(s[:I], s[I:], 8)
+    act8 = kernels.w4_linear_fused(x, wq3, s3, G, prologue=pro, r=r, wn=wn, eps=1e-6, epilogue=ops.EPI_SWIGLU_PAIRS8)
     torch.cuda.synchronize()
     assert act.shape == (1, I)
     assert torch.equal(act, ref)
+    assert torch.equal(act8, ref)
     assert kernels.device_status() == 0
 
 
