@@ -649,7 +649,7 @@ def main():
     # copies inside (one graph launch + one stream synchronisation per step)
     t_e2e_wall, e2e_path = t_e2e_eager, "Kernels.w4_linear per launch (ctypes -> C ABI), pinned host X in, all outputs out"
     if not seven:
-        host_steps = [l.host_step(M, stream) for l in lb.layers]
+        host_steps = [l.host_step(M, stream, zero_copy_out=(world == 1)) for l in lb.layers]
         for hs in host_steps:
             hs.x_host.copy_(lb.x_h)
             hs.act_host.copy_(lb.a_h)
@@ -663,7 +663,9 @@ def main():
             lb.barrier()
             t_e2e_wall = time.perf_counter() - t0
         e2e_path = ("ShardedLayer.host_step: one CUDA graph per step (pinned host X in, 4 GEMV launches through the C "
-                    "ABI, all outputs out to pinned host memory), graph launch + stream synchronise per step")
+                    "ABI, all outputs out to pinned host memory" +
+                    (": the kernels store them there themselves" if world == 1 else "") +
+                    "), graph launch + stream synchronise per step")
         if world == 1:
             last = (args.steps - 1) % n_copies  # the layer copy both paths ran last
             assert torch.equal(host_steps[last].out_host, out_h), "host_step and the per-launch path disagree"

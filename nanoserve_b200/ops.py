@@ -201,7 +201,9 @@ class Kernels:
 
     # x [M, K] -> [M, N] for any M >= 1 (decode GEMV for M <= 16, tensor-core GEMM above).
     def w4_linear(self, x, Wq, S, group=128, flags=0, out=None):
-        self._cuda(x, Wq, S, out)
+        """`out` may also be a pinned host tensor: the kernel then stores its outputs straight into host memory
+        (unified addressing), which saves a copy node when the outputs are wanted on the host anyway."""
+        self._cuda(x, Wq, S, None if out is not None and not out.is_cuda and out.is_pinned() else out)
         M, K = x.shape
         N = Wq.shape[0]
         x = x.contiguous()

@@ -203,9 +203,9 @@ class ShardedLayer:
         k.tp_wait_desc(self.tail_desc, advance_epoch=True)
         return outs
 
-    def host_step(self, M: int, stream: "torch.cuda.Stream") -> "HostStep":
+    def host_step(self, M: int, stream: "torch.cuda.Stream", zero_copy_out: bool = False) -> "HostStep":
         """The pass as a serving loop calls it -- inputs and outputs in pinned host memory: see HostStep."""
-        return HostStep(self, M, stream)
+        return HostStep(self, M, stream, zero_copy_out)
 
     def resident_bytes(self) -> int:
         return sum(w.numel() * 4 + s.numel() * 2 for w, s in self.shards.values())
@@ -252,7 +252,7 @@ class HostStep:
     one graph launch and one stream synchronisation per step, whatever the number of kernels inside.  Fill the input
     views before the call; read `outs` (views of `out_host`) after it."""
 
-    def __init__(self, layer: ShardedLayer, M: int, stream):
+    def __init__(self, layer: ShardedLayer, M: int, stream, zero_copy_out: bool = False):
         dev = layer.fused["qkv"][0].device
         hidden, inter = layer.shapes["q"][1], layer.shapes["down"][1]
         widths = [sum(layer.shapes[n][0] for n in names) for _, names in layer.FUSED]
@@ -273,6 +273,10 @@ class HostStep:
 
         def body():
             self.in_dev.copy_(self.in_host, non_blocking=True)
+            if layer.peer is None and zero_copy_out:
+                # the kernels store straight into the pinned output buffer: no copy node behind them
+                layer.decode_pass_fused4(x_d, a_d, outs=self.outs)
+                return
             if layer.peer is None:
                 layer.decode_pass_fused4(x_d, a_d, outs=views)
             else:  # the gathered rows live in the symmetric buffers: bring them together for the one copy back

@@ -195,16 +195,16 @@ def test_host_step_equals_the_device_pass(kernels):
     layer = ShardedLayer.synthetic(kernels, shapes, order, 128, seed=3, rank=0, world=1, device=torch.device("cuda"))
     layer.fuse()
     st = torch.cuda.Stream()
-    hs = layer.host_step(1, st)
     g = torch.Generator().manual_seed(1)
-    for _ in range(2):
-        x = torch.randn(1, 256, generator=g).to(torch.bfloat16)
-        a = torch.randn(1, 512, generator=g).to(torch.bfloat16)
-        hs.x_host.copy_(x)
-        hs.act_host.copy_(a)
-        outs = hs()
-        want = layer.decode_pass_fused4(x.cuda(), a.cuda())
-        torch.cuda.synchronize()
-        for o, w in zip(outs, want):
-            assert torch.equal(o, w.cpu())
+    for hs in (layer.host_step(1, st), layer.host_step(1, st, zero_copy_out=True)):
+        for _ in range(2):
+            x = torch.randn(1, 256, generator=g).to(torch.bfloat16)
+            a = torch.randn(1, 512, generator=g).to(torch.bfloat16)
+            hs.x_host.copy_(x)
+            hs.act_host.copy_(a)
+            outs = hs()
+            want = layer.decode_pass_fused4(x.cuda(), a.cuda())
+            torch.cuda.synchronize()
+            for o, w in zip(outs, want):
+                assert torch.equal(o, w.cpu())
     assert kernels.device_status() == 0
