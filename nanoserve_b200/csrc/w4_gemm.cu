@@ -15,13 +15,16 @@
 //   tile     MI x 128 tokens by 256 output features, K walked in blocks of 64
 //   warp 0   TMA producer: per K block, the X tile(s) (128 rows x 128 B, 128-byte swizzle) and the packed
 //            weight tile (256 rows x 32 B) land in a ring stage; completion counted on an mbarrier
-//   warp 1   MMA issuer: one elected lane issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=256, K=16)
-//            from shared-memory descriptors into fp32 accumulators in TMEM (MI x 256 columns); the weight
-//            operand is shared by the MI token tiles, so every weight is dequantised once per 128*MI tokens
-//   warps 2-17 dequant: two threads per weight row of the tile, each owning a 32-wide half of the K block:
-//            one 16-byte shared load of packed nibbles, LOP3 unpack to bf16 pairs, exact -8 (bf16x2
+//   warp 1   MMA issuer: one elected lane issues tcgen05.mma (kind::f16, N=256, K=16) from shared-memory
+//            descriptors into fp32 accumulators in TMEM (MI x 256 columns); the weight operand is shared by the MI
+//            token tiles.  One CTA per tile: cta_group::1, M=128.  CTA pairs (the default where token tiles pair
+//            up; see the block comment further down): cta_group::2, M=256 across the two CTAs, issued by the
+//            rank-0 CTA, each CTA holding and unpacking half of the weight tile
+//   warps 2-17 dequant: two threads per weight row of the tile, each owning a 32-wide half of the K block (pairs:
+//            four threads per row of the CTA's 128 rows, a 16-wide quarter each):
+//            one 16-byte (8-byte) shared load of packed nibbles, LOP3 unpack to bf16 pairs, exact -8 (bf16x2
 //            subtract), one bf16x2 multiply by the group scale, and four 16-byte stores into a K-major,
-//            128-byte-swizzled bf16 tile (three buffers in rotation) that the MMA reads through the async
+//            128-byte-swizzled bf16 tile (three buffers in rotation, four for pairs) that the MMA reads through the async
 //            proxy (fence.proxy.async before the arrive)
 //   epilogue the same sixteen warps read the accumulators with tcgen05.ld (32 lanes x 32 columns), convert to
 //            bf16 and store rows of Y
