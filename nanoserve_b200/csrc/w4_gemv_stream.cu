@@ -35,6 +35,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 #include "w4_gemv_shared.cuh"
 
@@ -66,6 +67,7 @@ struct StreamParams {
   int pstride;       // bytes between planes of the staged X
   int depth;         // ring slots per warp
   int epi;           // kEpi*
+  int n_tiles;       // row tiles of the matrix; > 0: the CTAs share them evenly (tile range from blockIdx.x), ks == 1
   int cluster;       // CTAs per cluster (1: no cluster launch); they share the conversion of X
 };
 
@@ -520,13 +522,20 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
   // ---- geometry: the CTA owns kWarps / ks row tiles of kRows rows; a warp one K slice of one of them
   const int tpc = kWarps / q.ks;
   const int tl = warp / q.ks, sl_in = warp - tl * q.ks;
-  const int row0 = blockIdx.x * tpc * kRows;               // first row of the CTA
-  const int rows_cta = max(0, min(tpc * kRows, p.N - row0));  // 0: a CTA that only pads the grid to whole clusters
+  // balanced form: the grid is two CTAs per SM and every CTA takes its even share of the row tiles (6 or 7 of its 8
+  // warps busy) -- for row counts that are neither one nor two full CTAs per SM
+  int tile0 = blockIdx.x * tpc, ntile = tpc;
+  if (q.n_tiles > 0) {
+    tile0 = (int)(((long)blockIdx.x * q.n_tiles) / gridDim.x);
+    ntile = (int)(((long)(blockIdx.x + 1) * q.n_tiles) / gridDim.x) - tile0;
+  }
+  const int row0 = tile0 * kRows;                          // first row of the CTA
+  const int rows_cta = max(0, min(ntile * kRows, p.N - row0));  // 0: a CTA that only pads the grid to whole clusters
   const int wrow0 = row0 + tl * kRows;                     // first row of the warp
   const int scb = blockIdx.y * q.scps, sce = min(q.nsc, scb + q.scps);  // the CTA's super-chunks of K
   const int nscc = sce - scb;
   const int s0 = scb + (nscc * sl_in) / q.ks, s1 = scb + (nscc * (sl_in + 1)) / q.ks;  // the warp's
-  const bool active = wrow0 < p.N && s0 < s1;
+  const bool active = tl < ntile && wrow0 < p.N && s0 < s1;
   const uint32_t bar0 = smem_u32(smem + kBarOffset) + warp * (8 * kMaxDepth);
   const uint32_t ring0 = smem_u32(smem + kHeader) + warp * q.depth * kSlotBytes;
   if (tid < 4) sts128(smem_u32(smem + kZeroOffset) + tid * 16, make_uint4(0u, 0u, 0u, 0u));
@@ -982,6 +991,18 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   pl.ks = ks;
   const int tpc = kWarps / ks;
   pl.grid_x = (n_tiles + tpc - 1) / tpc;
+  // Uneven waves.  (a) 16 rows per warp and a few CTAs more than SMs (1.05 to 1.25 per SM): the SMs that hold two are
+  // the critical path (20000 x 4096: 12.4 us); instead two CTAs on EVERY SM, each with its even share of the row tiles
+  // and some of its warps idle (10.4 us).  (b) below, after the shared-memory search: CTAs that fit one per SM only.
+  // Row counts that leave some CTA slots empty otherwise (28672 or 65536 rows) gain nothing from the even shares
+  // (24.6 against 24.2 us, 23.0 against 22.5): bandwidth is a shared resource, a lighter SM just finishes early.
+  // Not with forced rows per warp / K warps (diagnostics), an epilogue, or several tokens.
+  int balanced_tiles = 0;
+  const bool may_balance = !pl.one && epilogue == kEpiNone && ks == 1 && ((flags >> 10) & 3) == 0 && !forced_ks;
+  if (may_balance && pl.RB == 1 && pl.grid_x * 100l > sm_count * 105l && pl.grid_x * 4l <= sm_count * 5l) {
+    balanced_tiles = n_tiles;
+    pl.grid_x = 2 * sm_count;
+  }
   // K slices across CTAs: only when the staged X of one CTA does not fit otherwise
   const int forced_ns = (flags >> 24) & 0x1F;
   const int forced_depth = (flags >> 4) & 0xF;  // bits 4-7: ring slots per warp (diagnostics)
@@ -1013,12 +1034,23 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
     }
   }
   if (!found) return false;
+  // (b) CTAs that fit one per SM only (32 rows per warp at K = 8192) and do not fill their last wave: whole waves of
+  // CTAs with even shares of the tiles, at least four warps busy (57344 x 8192: 224 CTAs 50.7 us, 296 CTAs 47.5 us)
+  if (may_balance && !balanced_tiles && pl.smem > kSmemTwoPerSm && pl.nslices == 1 && pl.grid_x > sm_count &&
+      pl.grid_x % sm_count != 0) {
+    const int waves = (pl.grid_x + sm_count - 1) / sm_count;
+    if ((long)n_tiles >= (long)waves * sm_count * 4) {
+      balanced_tiles = n_tiles;
+      pl.grid_x = waves * sm_count;
+    }
+  }
   pl.q.ks = ks;
   pl.q.nsc = nsc;
   pl.q.scps = pl.scps;
   pl.q.wrow = K / 8;
   pl.q.sc_contig = pl.nslices == 1 && (reinterpret_cast<uintptr_t>(S) & 15) == 0;
   pl.q.epi = epilogue;
+  pl.q.n_tiles = balanced_tiles;
   // CTAs per cluster.  The conversion of X (M * K / 16 items; every CTA needs all of them) can go round by round of
   // 512 items over the CTAs of a cluster, which write every piece into the shared memory of all of them.  Measured,
   // it does not pay: a cluster launch costs more than the rounds it saves (3584 x 18944 at one token, three rounds:
@@ -1130,7 +1162,8 @@ int gemv_stream_describe(int M, int N, int K, int G, int flags, int sm_count, si
                   "streaming kernel: %d CTAs of 8 warps, %d rows per warp, %d warp(s) per row tile along K, %s layout, "
                   "%d planes (%d-bit X), ring depth %d, K slices across CTAs %d, cluster %d, %zu KB smem",
                   pl.grid_x * pl.nslices, pl.RB * 16, pl.ks, pl.one ? "one-group" : "two-chunk", pl.P, pl.P * 8, pl.q.depth,
-                  pl.nslices, pl.q.cluster, pl.smem >> 10);
+                  pl.nslices, pl.q.cluster, pl.smem >> 10) +
+         (pl.q.n_tiles ? snprintf(buf + strlen(buf), buflen - strlen(buf), ", %d row tiles shared evenly", pl.q.n_tiles) : 0);
 }
 
 size_t gemv_stream_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap) {

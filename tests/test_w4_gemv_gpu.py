@@ -362,3 +362,15 @@ torch.save(out, sys.argv[1])
     for c in ("4", "2"):
         for a, b in zip(res["1"], res[c]):
             assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("N,K", [(20000, 512), (22000, 1024), (19700, 256), (45000, 8192)])
+def test_row_counts_between_one_and_two_ctas_per_sm(kernels, N, K):
+    """Row counts for which the streaming kernel launches whole waves of CTAs and gives each its even share of the row
+    tiles (some warps of a CTA idle): every row must still be computed exactly once -- against the oracle, all rows."""
+    G = 128
+    X, Wq, S = oracle.synth_inputs(1, N, K, G, seed=N % 97)
+    y = kernels.w4_linear(bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S), G)
+    torch.cuda.synchronize()
+    check_bf16_output(torch_to_bits(y), oracle.w4_linear_f32(X, Wq, S, G, threads=oracle.max_threads()), 3e-6)
+    assert kernels.device_status() == 0
