@@ -1239,7 +1239,18 @@ int launch_mode(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan& pl
 
 }  // namespace
 
+// Plain launches of five to sixteen tokens whose converted X fits in shared memory run the many-token kernel.
+// (Pointers: null = "assume aligned", for the queries that have no operands.)
+static bool mid_serves(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, const GemvPrologue& pro,
+                       const Workspace& ws, int flags, int sm_count, const GemvTp* tp) {
+  if (pro.kind != kProNone || pro.epilogue != kEpiNone) return false;
+  if (!ws.xstage || gemv_mid_image_bytes(M, K) > ws.xstage_bytes) return false;
+  if (tp != nullptr && (tp->world > 0 || tp->wait_sig != nullptr || tp->announce_world > 0)) return false;
+  return gemv_mid_applies(X, Wq, S, M, N, K, G, flags, sm_count);
+}
+
 size_t gemv_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap) {
+  if (gemv_mid_applies(nullptr, nullptr, nullptr, M, N, K, G, flags, sm_count)) return 0;
   if (gemv_stream_applies(nullptr, M, N, K, G, flags)) {
     // (0 also when no streaming plan fits and the ring kernel runs: its own answer follows)
     const size_t b = gemv_stream_scratch_bytes(M, N, K, G, flags, sm_count, partial_cap);
@@ -1269,6 +1280,9 @@ size_t gemv_grid(int M, int N, int K, int G, int flags, int sm_count, size_t par
 int gemv_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap, char* buf,
                   int buflen) {
   if (!buf || buflen < 1) return kErrBadPointer;
+  if (gemv_mid_applies(nullptr, nullptr, nullptr, M, N, K, G, flags, sm_count) &&
+      gemv_mid_describe(M, N, K, flags, sm_count, buf, buflen) > 0)
+    return 0;
   if (gemv_stream_applies(nullptr, M, N, K, G, flags)) {
     const int n = gemv_stream_describe(M, N, K, G, flags, sm_count, partial_cap, buf, buflen);
     if (n > 0) return 0;
@@ -1335,7 +1349,8 @@ int gemv_launch_ex(const void* X, const void* Wq, const void* S, void* Y, int M,
   // a tensor-parallel producer sums its slices in the kernel (its CTAs signal the peers after their stores): plans and
   // trial launches must assume that too
   if (tp != nullptr && tp->world > 0) flags |= kFlagNoSplitSumKernel;
-  const bool tunable = !gemv_stream_applies(Wq, M, N, K, G, flags) &&
+  const bool tunable = !mid_serves(X, Wq, S, M, N, K, G, pro, ws, flags, sm_count, tp) &&
+                       !gemv_stream_applies(Wq, M, N, K, G, flags) &&
                        !(flags & (kShapeFlagMask | kFlagNarrowCta | kFlagNoAutotune)) && autotune_enabled() &&
                        ws.partial && ws_in.partial_bytes > 2 * kTrialBytes && (size_t)M * N * 2 <= kTrialBytes;
   if (!tunable) return gemv_launch_planned(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
@@ -1480,6 +1495,8 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
       (reinterpret_cast<uintptr_t>(S) & 1) || (reinterpret_cast<uintptr_t>(Y) & 1))
     return kErrBadPointer;
   if (!ws.status) return kErrWorkspace;
+  if (mid_serves(X, Wq, S, M, N, K, G, pro, ws, flags, sm_count, tp))
+    return gemv_mid_launch(X, Wq, S, Y, M, N, K, ws.status, ws.xstage, ws.xstage_bytes, flags, sm_count, stream);
   if (gemv_stream_applies(Wq, M, N, K, G, flags)) {
     const int rc = gemv_stream_launch(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
     if (rc != kStreamNotApplicable) return rc;

@@ -56,6 +56,9 @@ enum : int {
   kFlagNoSplitSumKernel = 65536,  // GEMV: never do that
   kFlagRingKernel = 131072,  // GEMV: run the shared-memory ring kernel (w4_gemv.cu) even where the register-streaming
                              // kernel (w4_gemv_stream.cu) applies; bits 20-23: force that kernel's warps per row block
+  kFlagNoMidKernel = 262144,  // GEMV: never run the many-token kernel (w4_gemv_mid.cu, 5 <= M <= 16)
+  kFlagMidKernel = 131072 | 524288,  // (ring | streaming, both) GEMV: the many-token kernel for every shape it can
+                                     // serve (by default not where another kernel measured faster)
   kFlagStreamKernel = 262144 * 2,  // GEMV: run the streaming kernel for every M <= 16 it can serve (by default M <= 2)
   kFlagGemmNoPairs = 1 << 29,     // GEMM: one CTA per tile unpacks the whole weight tile (no clusters of two)
   kFlagGemmWholeTiles = 1 << 30,  // GEMM: every CTA takes whole output tiles (no part-tiles, no scratch)
@@ -140,6 +143,17 @@ int gemv_stream_describe(int M, int N, int K, int G, int flags, int sm_count, si
 int gemv_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap, char* buf,
                   int buflen);
 size_t gemv_stream_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);
+
+// The many-token GEMV (w4_gemv_mid.cu): 5 <= M <= 16, G == 128, K % 256 == 0, at least 16 rows per SM, a converted X
+// that fits in shared memory; plain launches only (no prologue, epilogue or tensor-parallel form), and only with the
+// scratch for the converted X (Workspace::xstage).
+bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, int flags,
+                      int sm_count);
+// `image`: scratch for the converted X (gemv_mid_image_bytes, 16-byte aligned), written by a small kernel in front.
+int gemv_mid_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int* status,
+                    unsigned char* image, size_t image_cap, int flags, int sm_count, cudaStream_t stream);
+size_t gemv_mid_image_bytes(int M, int K);
+int gemv_mid_describe(int M, int N, int K, int flags, int sm_count, char* buf, int buflen);
 
 // Status word of b2_w4_gemv_noalloc's fixed scratch array (w4_gemv_noalloc.cu); false when that entry point has not
 // run on the device.
