@@ -1244,7 +1244,6 @@ int launch_mode(const CUtensorMap& tmap, const GemvParams& p, const GemvPlan& pl
 static bool mid_serves(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, const GemvPrologue& pro,
                        const Workspace& ws, int flags, int sm_count, const GemvTp* tp) {
   if (pro.kind != kProNone || pro.epilogue != kEpiNone) return false;
-  if (!ws.xstage || gemv_mid_image_bytes(M, K) > ws.xstage_bytes) return false;
   if (tp != nullptr && (tp->world > 0 || tp->wait_sig != nullptr || tp->announce_world > 0)) return false;
   return gemv_mid_applies(X, Wq, S, M, N, K, G, flags, sm_count);
 }
@@ -1496,7 +1495,7 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
     return kErrBadPointer;
   if (!ws.status) return kErrWorkspace;
   if (mid_serves(X, Wq, S, M, N, K, G, pro, ws, flags, sm_count, tp))
-    return gemv_mid_launch(X, Wq, S, Y, M, N, K, ws.status, ws.xstage, ws.xstage_bytes, flags, sm_count, stream);
+    return gemv_mid_launch(X, Wq, S, Y, M, N, K, ws.status, flags, sm_count, stream);
   if (gemv_stream_applies(Wq, M, N, K, G, flags)) {
     const int rc = gemv_stream_launch(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
     if (rc != kStreamNotApplicable) return rc;

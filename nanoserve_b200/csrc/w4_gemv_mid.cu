@@ -10,9 +10,9 @@
 // the columns of B.  What differs is everything around it, because with many tokens the launch is bound by shared
 // memory bandwidth and instruction issue, not by start-up:
 //   * One CTA of sixteen warps per SM (four per scheduler) instead of two CTAs of eight: the converted X of all
-//     tokens (2 M (K + 16) bytes) is held once per SM.  It is converted ONCE per launch by a small kernel in front
-//     (w4_mid_stage_kernel, into the library's scratch) and fetched by every CTA with bulk copies while its weight
-//     ring fills: converting in every CTA cost 3.7 us at eight tokens and 6.5 us at sixteen, with HBM idle.
+//     tokens (2 M (K + 16) bytes) is held once per SM, and every thread converts a 512th of it while the weight ring
+//     fills.  (Converting once, in a small kernel in front, and fetching the result with bulk copies was measured:
+//     the second launch and its completion cost more than the conversion, 7.5 us fixed per GEMV against 4.)
 //   * The nibbles reach the mma as SIGNED bytes 16 (q - 8): (w & 0xF0F0F0F0) ^ 0x80808080 is one LOP3, and the
 //     zero-point needs no term of its own (no per-chunk digit sums, no accumulator start values).  Shared-memory
 //     bandwidth bounds the loop (the B fragments of 32 mma per 2 KB of weights), so what a lane reads besides them is
@@ -37,14 +37,10 @@ namespace b2 {
 
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kWarps = kThreads / 32;
 constexpr int kMaxDepth = 6;
 constexpr int kBarOffset = 64;    // mbarriers [warp][slot], 8 bytes each
-constexpr int kXBarOffset = 896;  // mbarrier of the bulk copies of X
-constexpr int kCopyBytes = 32768;
 constexpr int kHeader = 1024;
-constexpr int kSlotBytes = 2048 + 128;  // 16 rows x 128 bytes of packed weights (swizzled), 16 x 4 bytes of scales
+constexpr int kBlockBytes = 2048 + 128;  // 16 rows x 128 bytes of packed weights (swizzled), 16 x 4 bytes of scales
 constexpr int kSmemMax = 227 * 1024;
 
 struct MidParams {
@@ -55,14 +51,12 @@ struct MidParams {
   int* status;
   int M, N, K;
   int nsc;      // 256-wide super-chunks of K
-  int n_tiles;  // 16-row tiles of the matrix
+  int n_tiles;  // row tiles of the matrix (16 or 32 rows)
   int depth;    // ring slots per warp
   int pstride;  // bytes between digit planes of the staged X: K + 16 (the eight lanes of a shared-memory phase, two
                 // planes x four 32-byte pieces, then cover all banks)
-  int off_x;          // the image of the converted X in shared memory: digit planes, then the factors
-  int info_off;       // offset of the factors inside the image
-  int image_bytes;    // a multiple of 16
-  unsigned char* image;  // the same image in global memory (written by the kernel in front)
+  int off_x;          // the converted X in shared memory: digit planes, then the factors
+  int info_off;       // offset of the factors inside it
 };
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
@@ -78,18 +72,31 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
   asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
   return v;
 }
-// d = A (s8) * B + c; B unsigned (the low plane) or signed (the high plane)
+// d = A (s8) * B (+ d); B unsigned (the low plane) or signed (the high plane).  The accumulators are tied operands:
+// written as separate inputs and outputs they cost a register move each.
 template <bool BSIGNED>
-__device__ __forceinline__ void imma(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                     uint32_t b1, int c0, int c1, int c2, int c3) {
+__device__ __forceinline__ void imma_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
   if constexpr (BSIGNED)
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
   else
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+template <bool BSIGNED>
+__device__ __forceinline__ void imma_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  if constexpr (BSIGNED)
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ float2 lds64f(uint32_t addr) {
   float2 v;
@@ -97,109 +104,145 @@ __device__ __forceinline__ float2 lds64f(uint32_t addr) {
   return v;
 }
 
-// Converts X into the B operand, once per launch: a thread per item of 16 consecutive k of one token; the eight items
-// of a 128-chunk sit in eight consecutive lanes.  Per (token, chunk): e = biased exponent of the largest |x|
-// (clamped), every x is multiplied by 2^(14 - (e - 127)) -- exact: a bf16 value has eight significant bits, the
-// largest becomes at most 255 * 2^7 -- and taken as a 16-bit two's complement integer v = d0 + 256 d1, d0 its unsigned
-// low byte, d1 its signed high byte.  Plane p of the item: 16 bytes { d_p of k = 0,2,4,6 | 8,10,12,14 | 1,3,5,7 |
-// 9,11,13,15 } -- the B fragments of one even-nibble and one odd-nibble mma (the contraction index is a dummy: this
-// order is what the nibble masks produce).  factor[chunk][token] = 2^(e - 127 - 14) / 16 (the 16 every nibble product
-// carries).  Tokens beyond M (the token count is padded to eight or sixteen) convert zeros.  A chunk with an inf or a
-// nan gets a nan factor.  The image -- planes [2][Mp][K + 16], then the factors [K / 128][Mp] -- is what every CTA of the
-// GEMV copies into its shared memory.
-constexpr int kStageThreads = 256;
-__global__ void __launch_bounds__(kStageThreads) w4_mid_stage_kernel(const MidParams q, int Mp) {
-  pdl_launch_dependents();  // the GEMV behind may start its weight stream
-  pdl_wait_prior_grid();    // X may come from the kernel in front; the previous GEMV must be done with the image
+// Converts X into the B operand, all threads of the CTA, while the first weights are in flight.  An item is 16
+// consecutive k of one token; the eight items of a 128-chunk sit in eight consecutive lanes.  Per (token, chunk): e =
+// biased exponent of the largest |x| (clamped), every x is multiplied by 2^(14 - (e - 127)) -- the largest becomes at
+// most 255 * 2^7: a bf16 value has eight significant bits -- and rounded to a 16-bit two's complement integer
+// v = d0 + 256 d1, d0 its unsigned low byte, d1 its signed high byte.  The rounding is one fused multiply-add with
+// 1.5 * 2^23, which leaves v in the low mantissa bits (round to nearest even, like cvt.rni, at the full rate of the
+// fma pipe instead of the quarter rate of the conversion unit).  Plane p of the item: 16 bytes { d_p of k = 0,2,4,6 |
+// 8,10,12,14 | 1,3,5,7 | 9,11,13,15 } -- the B fragments of one even-nibble and one odd-nibble mma (the contraction
+// index is a dummy: this order is what the nibble masks produce).  factor[chunk][token] = 2^(e - 127 - 14) / 16 (the 16
+// every nibble product carries).  Tokens beyond M (the token count is padded to eight or sixteen) convert zeros.  A
+// chunk with an inf or a nan gets a nan factor.  Layout: planes [2][Mp][K + 16], then the factors [K / 128][Mp].
+template <typename F>
+__device__ __forceinline__ void convert_x(const MidParams& q, uint32_t xs, uint32_t info, int Mp, int tid,
+                                          int nthreads, F&& after_first_loads) {
+  // All of a thread's loads (up to UN items) are in flight before the first conversion, and AHEAD of the weight
+  // stream, which `after_first_loads` starts: behind the ring's first fill (a third of the matrix) they took 2 us.
+  constexpr int UN = 8;
   const int items_tok = q.K >> 4;
-  const int it = blockIdx.x * kStageThreads + threadIdx.x;  // (the grid covers a multiple of 32 items: Mp * K / 16)
-  if (it >= Mp * items_tok) return;
-  const int m = it / items_tok, r = it - m * items_tok;
-  uint4 va = make_uint4(0u, 0u, 0u, 0u), vb = va;
-  if (m < q.M) {
-    const uint4* src = reinterpret_cast<const uint4*>(q.X + (size_t)m * q.K + r * 16);
-    va = ld_l2(src);
-    vb = ld_l2(src + 1);
-  }
-  const uint32_t w[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-  uint32_t mx = 0;  // bf16 magnitudes order like their bit patterns
+  const int items = Mp * items_tok;  // a multiple of 32: whole warps stay together for the shuffles
+  // (token, item in token) of the thread's items advance by a fixed step: two divisions per thread, not two per item
+  const int step_m = nthreads / items_tok, step_r = nthreads - step_m * items_tok;
+  int m0 = tid / items_tok, r0 = tid - m0 * items_tok;
+  for (int it0 = tid; it0 == tid || it0 < items; it0 += nthreads * UN) {  // (at least once: the callback)
+    uint4 va[UN], vb[UN];
+    int ms[UN], rs[UN];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) mx = max(mx, max(w[i] & 0x7FFFu, (w[i] >> 16) & 0x7FFFu));
-  mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-  mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-  mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-  uint32_t eb = mx >> 7;
-  const bool bad = eb == 255u;
-  eb = min(254u, max(40u, eb));
-  const float down = __uint_as_float((uint32_t)(16 + 252 - (int)eb) << 23);
-  uint32_t v[16];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    v[2 * i] = (uint32_t)__float2int_rn(__uint_as_float(w[i] << 16) * down);
-    v[2 * i + 1] = (uint32_t)__float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * down);
-  }
-#pragma unroll
-  for (int p = 0; p < 2; ++p) {
-    uint32_t pl[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int b = (j & 1) * 8 + (j >> 1);  // first k of the word: 0, 8, 1, 9; then every second one
-      const uint32_t t0 = __byte_perm(v[b], v[b + 2], 0x5140), t1 = __byte_perm(v[b + 4], v[b + 6], 0x5140);
-      pl[j] = __byte_perm(t0, t1, p ? 0x7632 : 0x5410);
+    for (int u = 0; u < UN; ++u) {
+      const int it = it0 + u * nthreads;
+      ms[u] = m0;
+      rs[u] = r0;
+      va[u] = make_uint4(0u, 0u, 0u, 0u);
+      vb[u] = va[u];
+      if (it < items && m0 < q.M) {
+        const uint4* src = reinterpret_cast<const uint4*>(q.X + (size_t)m0 * q.K + r0 * 16);
+        va[u] = ld_l2(src);
+        vb[u] = ld_l2(src + 1);
+      }
+      m0 += step_m;
+      r0 += step_r;
+      if (r0 >= items_tok) {
+        r0 -= items_tok;
+        ++m0;
+      }
     }
-    *reinterpret_cast<uint4*>(q.image + (size_t)(p * Mp + m) * q.pstride + r * 16) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+    if (it0 == tid) after_first_loads();
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int it = it0 + u * nthreads;
+      if (it < items) {  // (warp-uniform)
+        const int m = ms[u], r = rs[u];
+        const uint32_t w[8] = {va[u].x, va[u].y, va[u].z, va[u].w, vb[u].x, vb[u].y, vb[u].z, vb[u].w};
+        uint32_t mx2 = 0;  // bf16 magnitudes order like their bit patterns; both halves of a word at once
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx2 = __vmaxu2(mx2, w[i] & 0x7FFF7FFFu);
+        uint32_t mx = max(mx2 & 0xFFFFu, mx2 >> 16);
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        uint32_t eb = mx >> 7;
+        const bool bad = eb == 255u;
+        eb = min(254u, max(40u, eb));
+        const float down = __uint_as_float((uint32_t)(16 + 252 - (int)eb) << 23);
+        uint32_t v[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[2 * i] = __float_as_uint(fmaf(__uint_as_float(w[i] << 16), down, 12582912.f));
+          v[2 * i + 1] = __float_as_uint(fmaf(__uint_as_float(w[i] & 0xFFFF0000u), down, 12582912.f));
+        }
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          uint32_t pl[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int b = (j & 1) * 8 + (j >> 1);  // first k of the word: 0, 8, 1, 9; then every second one
+            const uint32_t t0 = __byte_perm(v[b], v[b + 2], 0x5140), t1 = __byte_perm(v[b + 4], v[b + 6], 0x5140);
+            pl[j] = __byte_perm(t0, t1, p ? 0x7632 : 0x5410);
+          }
+          sts128(xs + (uint32_t)(p * Mp + m) * q.pstride + r * 16, make_uint4(pl[0], pl[1], pl[2], pl[3]));
+        }
+        if ((r & 7) == 0)
+          sts32f(info + (uint32_t)((r >> 3) * Mp + m) * 4,
+                 __uint_as_float(bad ? 0x7FC00000u : (uint32_t)((int)eb - 18) << 23));
+      }
+    }
   }
-  if ((r & 7) == 0)
-    *reinterpret_cast<uint32_t*>(q.image + q.info_off + (size_t)((r >> 3) * Mp + m) * 4) =
-        bad ? 0x7FC00000u : (uint32_t)((int)eb - 18) << 23;
 }
 
 // NP: groups of eight tokens (M <= 8 NP), two column tiles each: the low planes and the high planes.
-template <int NP>
-__global__ void __launch_bounds__(kThreads, 1) w4_gemv_mid_kernel(const MidParams q) {
+// RB: 16-row blocks per tile.  With two, the B fragments of a chunk serve both blocks: shared memory moves 69 (eight
+// tokens) or 87 (sixteen) 128-byte wavefronts per 2 KB of weights instead of 120 or 156 -- fills included, which take
+// two per 128 bytes -- and the loop stops being bound by it.
+// W: warps.  Sixteen, or twelve where the converted X leaves no room for sixteen rings of two 32-row slots.
+template <int NP, int RB, int W>
+__global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams q) {
   extern __shared__ __align__(1024) unsigned char smem[];
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  constexpr int Mp = NP * 8;
+  constexpr int Mp = NP * 8, kRows = RB * 16, kSlotBytes = RB * kBlockBytes, kThreads = W * 32;
+  constexpr int kSegBytes = Mp * kRows * 4;  // a partial tile parked in shared memory: [token][row] floats
 
   // ---- the CTA's tiles and the warp's run of (tile, super-chunk) units
   const int T0 = (int)(((long)blockIdx.x * q.n_tiles) / gridDim.x);
   const int T1 = (int)(((long)(blockIdx.x + 1) * q.n_tiles) / gridDim.x);
   const int U = (T1 - T0) * q.nsc;
-  const int u0 = (int)(((long)warp * U) >> 4), u1 = (int)(((long)(warp + 1) * U) >> 4);
+  const int u0 = (int)(((long)warp * U) / W), u1 = (int)(((long)(warp + 1) * U) / W);
   const int n = u1 - u0;
   const uint32_t bar0 = smem_u32(smem + kBarOffset) + warp * (8 * kMaxDepth);
   const uint32_t ring0 = smem_u32(smem + kHeader) + warp * q.depth * kSlotBytes;
   if (tid == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < kWarps * kMaxDepth; ++i) mbar_init(smem_u32(smem + kBarOffset) + 8 * i, 32);
-    mbar_init(smem_u32(smem + kXBarOffset), 1);
+    for (int i = 0; i < W * kMaxDepth; ++i) mbar_init(smem_u32(smem + kBarOffset) + 8 * i, 32);
     fence_mbar_init();
   }
   __syncthreads();
   pdl_launch_dependents();
 
-  // ---- weight stream (constant data: needs nothing from the previous kernel).  Lane l copies 16 bytes of rows
-  // (l >> 3) + 4 j: a warp instruction covers four rows x 128 bytes, whole lines.  Rows beyond N are zero-filled.
+  // ---- weight stream.  Lane l copies 16 bytes of rows (l >> 3) + 4 j of every 16-row block: a warp instruction
+  // covers four rows x 128 bytes, whole lines.  Rows beyond N are zero-filled.
   int ftile = T0 + u0 / q.nsc, fsc = u0 % q.nsc;  // the next unit to feed
   const int r4 = lane >> 3, c16 = lane & 7;
   const size_t row_bytes = (size_t)q.K >> 1;
   const int KG = q.K >> 7;
   auto feed = [&](uint32_t slot, uint32_t bar) {
-    const int rowbase = ftile * 16;
+    const int rowbase = ftile * kRows;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int row = r4 + 4 * j;
-      const bool ok = rowbase + row < q.N;
-      const unsigned char* src = q.Wq + (ok ? (size_t)(rowbase + row) * row_bytes + (size_t)fsc * 128 + c16 * 16 : 0);
-      asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(slot + row * 128 +
+    for (int j = 0; j < 4 * RB; ++j) {
+      const int row = r4 + 4 * (j & 3), blk = j >> 2;
+      const bool ok = rowbase + blk * 16 + row < q.N;
+      const unsigned char* src =
+          q.Wq + (ok ? (size_t)(rowbase + blk * 16 + row) * row_bytes + (size_t)fsc * 128 + c16 * 16 : 0);
+      asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(slot + blk * kBlockBytes + row * 128 +
                                                                                   ((uint32_t)(c16 ^ (row & 7)) << 4)),
                    "l"(src), "r"(ok ? 16u : 0u)
                    : "memory");
     }
-    if (lane < 16) {
+    if (lane < kRows) {  // the two scales of the super-chunk, a row per lane
       const bool ok = rowbase + lane < q.N;
-      cp_async<4>(slot + 2048 + lane * 4, q.S + (ok ? (size_t)(rowbase + lane) * KG + 2 * fsc : 0), ok ? 4u : 0u);
+      cp_async<4>(slot + (lane >> 4) * kBlockBytes + 2048 + (lane & 15) * 4,
+                  q.S + (ok ? (size_t)(rowbase + lane) * KG + 2 * fsc : 0), ok ? 4u : 0u);
     }
     cp_async_mbar_arrive_noinc(bar);
     if (++fsc == q.nsc) {
@@ -207,21 +250,16 @@ __global__ void __launch_bounds__(kThreads, 1) w4_gemv_mid_kernel(const MidParam
       ++ftile;
     }
   };
-  {
-    const int pre = min(q.depth, n);
-    for (int i = 0; i < pre; ++i) feed(ring0 + i * kSlotBytes, bar0 + 8 * i);
-  }
 
-  // ---- X: the image the kernel in front has written, by bulk copies onto one mbarrier
+  // ---- X: every thread converts its share once the previous kernel's output is visible; the ring's first fill is
+  // issued between the loads of X and their use
   pdl_wait_prior_grid();
   const uint32_t xs = smem_u32(smem + q.off_x), info = xs + q.info_off;
-  const uint32_t xbar = smem_u32(smem + kXBarOffset);
-  if (tid == 0) {
-    mbar_arrive_expect_tx(xbar, (uint32_t)q.image_bytes);
-    for (int o = 0; o < q.image_bytes; o += kCopyBytes)
-      bulk_g2s(xs + o, q.image + o, (uint32_t)min(kCopyBytes, q.image_bytes - o), xbar);
-  }
-  mbar_wait(xbar, 0, abort_flag);
+  convert_x(q, xs, info, Mp, tid, kThreads, [&]() {
+    const int pre = min(q.depth, n);
+    for (int i = 0; i < pre; ++i) feed(ring0 + i * kSlotBytes, bar0 + 8 * i);
+  });
+  __syncthreads();
 
   // ---- main loop.  mma row g is slot row rho(g) (and rho + 8): the eight lanes of a shared-memory phase then land in
   // opposite halves of the swizzled 128-byte rows.
@@ -232,74 +270,102 @@ __global__ void __launch_bounds__(kThreads, 1) w4_gemv_mid_kernel(const MidParam
   const uint32_t xlane = xs + (uint32_t)g * q.pstride + t * 32, xhigh = (uint32_t)Mp * q.pstride;
   const uint32_t ilane = info + (uint32_t)(2 * t) * 4;
   const int first_tile = T0 + u0 / q.nsc, last_tile = n > 0 ? T0 + (u1 - 1) / q.nsc : first_tile;
-  float fin[NP][4], first[NP][4];  // [token 2t | 2t + 1][row rho | rho + 8]: index 2 * row half + token
+  float fin[RB][NP][4], first[RB][NP][4];  // [token 2t | 2t + 1][row rho | rho + 8]: index 2 * row half + token
 #pragma unroll
-  for (int j = 0; j < NP; ++j)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) fin[j][e] = first[j][e] = 0.f;
-  auto store_tile = [&](int tile, const float (&v)[NP][4]) {
+  for (int b = 0; b < RB; ++b)
 #pragma unroll
     for (int j = 0; j < NP; ++j)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int tok = j * 8 + 2 * t + (e & 1), r = tile * 16 + rho + (e >> 1) * 8;
-        if (tok < q.M && r < q.N) q.Y[(size_t)tok * q.N + r] = __float2bfloat16(v[j][e]);
-      }
+      for (int e = 0; e < 4; ++e) fin[b][j][e] = first[b][j][e] = 0.f;
+  auto store_tile = [&](int tile, const float (&v)[RB][NP][4]) {
+#pragma unroll
+    for (int b = 0; b < RB; ++b)
+#pragma unroll
+      for (int j = 0; j < NP; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = j * 8 + 2 * t + (e & 1), r = tile * kRows + b * 16 + rho + (e >> 1) * 8;
+          if (tok < q.M && r < q.N) q.Y[(size_t)tok * q.N + r] = __float2bfloat16(v[b][j][e]);
+        }
   };
-  auto park = [&](uint32_t base, const float (&v)[NP][4]) {  // [token][row] floats
+  auto park = [&](uint32_t base, const float (&v)[RB][NP][4]) {
 #pragma unroll
-    for (int j = 0; j < NP; ++j)
+    for (int b = 0; b < RB; ++b)
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        sts32f(base + (uint32_t)((j * 8 + 2 * t + (e & 1)) * 16 + rho + (e >> 1) * 8) * 4, v[j][e]);
+      for (int j = 0; j < NP; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          sts32f(base + (uint32_t)((j * 8 + 2 * t + (e & 1)) * kRows + b * 16 + rho + (e >> 1) * 8) * 4, v[b][j][e]);
   };
   int tile = first_tile, sc = u0 % q.nsc, sc_start = sc;
   uint32_t slot = ring0, bar = bar0, ph = 0;
   int d = 0;
   for (int i = 0; i < n; ++i) {
     mbar_wait(bar, ph, abort_flag);
-    const uint4 wl0 = lds128(slot + a_u0), wh0 = lds128(slot + 1024 + a_u0);
-    const uint4 wl1 = lds128(slot + a_u1), wh1 = lds128(slot + 1024 + a_u1);
-    const uint32_t s2_lo = lds32(slot + 2048 + rho * 4), s2_hi = lds32(slot + 2048 + 32 + rho * 4);
+    uint4 wl[RB][2], wh[RB][2];  // rows rho / rho + 8 of every block; even chunk, odd chunk
+    uint32_t s2_lo[RB], s2_hi[RB];
+    uint32_t all = 0;
+#pragma unroll
+    for (int b = 0; b < RB; ++b) {
+      const uint32_t blk = slot + b * kBlockBytes;
+      wl[b][0] = lds128(blk + a_u0);
+      wh[b][0] = lds128(blk + 1024 + a_u0);
+      wl[b][1] = lds128(blk + a_u1);
+      wh[b][1] = lds128(blk + 1024 + a_u1);
+      s2_lo[b] = lds32(blk + 2048 + rho * 4);
+      s2_hi[b] = lds32(blk + 2048 + 32 + rho * 4);
+    }
+#pragma unroll
+    for (int b = 0; b < RB; ++b)
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+        all ^= (wl[b][c].x ^ wl[b][c].y ^ wl[b][c].z) ^ (wl[b][c].w ^ wh[b][c].x ^ wh[b][c].y) ^
+               (wh[b][c].z ^ wh[b][c].w ^ (c ? s2_hi[b] : s2_lo[b]));
+    // The slot is free as soon as every lane's loads from it have returned: an instruction that reads all of their
+    // results is issued (in order) before the barrier, so the slot takes the unit `depth` ahead BEFORE the products,
+    // and a slot's period is the longer of the memory latency and the work on `depth` units, not their sum.
+    asm volatile("" ::"r"(all) : "memory");
+    __syncwarp();
+    if (i + q.depth < n) feed(slot, bar);
     const uint32_t xo = (uint32_t)sc * 256, io = (uint32_t)sc * (2 * Mp * 4);
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
-      const uint32_t lo[4] = {c ? wl1.x : wl0.x, c ? wl1.y : wl0.y, c ? wl1.z : wl0.z, c ? wl1.w : wl0.w};
-      const uint32_t hi[4] = {c ? wh1.x : wh0.x, c ? wh1.y : wh0.y, c ? wh1.z : wh0.z, c ? wh1.w : wh0.w};
-      uint32_t le[4], lq[4], he[4], hq[4];  // signed bytes 16 (q - 8) of the even and of the odd nibbles
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        le[k] = ((lo[k] << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
-        lq[k] = (lo[k] & 0xF0F0F0F0u) ^ 0x80808080u;
-        he[k] = ((hi[k] << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
-        hq[k] = (hi[k] & 0xF0F0F0F0u) ^ 0x80808080u;
-      }
-      const float s_lo = c ? __uint_as_float(s2_lo & 0xFFFF0000u) : __uint_as_float(s2_lo << 16);
-      const float s_hi = c ? __uint_as_float(s2_hi & 0xFFFF0000u) : __uint_as_float(s2_hi << 16);
 #pragma unroll
       for (int j = 0; j < NP; ++j) {
         const uint32_t xa = xlane + (uint32_t)(j * 8) * q.pstride + xo + c * 128;
         const uint4 p0 = lds128(xa), p1 = lds128(xa + 16);                  // low plane, items 2t and 2t + 1
         const uint4 h0 = lds128(xa + xhigh), h1 = lds128(xa + xhigh + 16);  // high plane
         const float2 up = lds64f(ilane + io + (uint32_t)(c * Mp + j * 8) * 4);
-        int al[4], ah[4];
-        imma<false>(al, le[0], he[0], le[1], he[1], p0.x, p0.y, 0, 0, 0, 0);
-        imma<true>(ah, le[0], he[0], le[1], he[1], h0.x, h0.y, 0, 0, 0, 0);
-        imma<false>(al, lq[0], hq[0], lq[1], hq[1], p0.z, p0.w, al[0], al[1], al[2], al[3]);
-        imma<true>(ah, lq[0], hq[0], lq[1], hq[1], h0.z, h0.w, ah[0], ah[1], ah[2], ah[3]);
-        imma<false>(al, le[2], he[2], le[3], he[3], p1.x, p1.y, al[0], al[1], al[2], al[3]);
-        imma<true>(ah, le[2], he[2], le[3], he[3], h1.x, h1.y, ah[0], ah[1], ah[2], ah[3]);
-        imma<false>(al, lq[2], hq[2], lq[3], hq[3], p1.z, p1.w, al[0], al[1], al[2], al[3]);
-        imma<true>(ah, lq[2], hq[2], lq[3], hq[3], h1.z, h1.w, ah[0], ah[1], ah[2], ah[3]);
-        fin[j][0] = fmaf(s_lo * up.x, (float)(al[0] + (ah[0] << 8)), fin[j][0]);
-        fin[j][1] = fmaf(s_lo * up.y, (float)(al[1] + (ah[1] << 8)), fin[j][1]);
-        fin[j][2] = fmaf(s_hi * up.x, (float)(al[2] + (ah[2] << 8)), fin[j][2]);
-        fin[j][3] = fmaf(s_hi * up.y, (float)(al[3] + (ah[3] << 8)), fin[j][3]);
+#pragma unroll
+        for (int b = 0; b < RB; ++b) {
+          const uint32_t lo[4] = {wl[b][c].x, wl[b][c].y, wl[b][c].z, wl[b][c].w};
+          const uint32_t hi[4] = {wh[b][c].x, wh[b][c].y, wh[b][c].z, wh[b][c].w};
+          uint32_t le[4], lq[4], he[4], hq[4];  // signed bytes 16 (q - 8) of the even and of the odd nibbles
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            le[k] = ((lo[k] << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+            lq[k] = (lo[k] & 0xF0F0F0F0u) ^ 0x80808080u;
+            he[k] = ((hi[k] << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+            hq[k] = (hi[k] & 0xF0F0F0F0u) ^ 0x80808080u;
+          }
+          const float s_lo = c ? __uint_as_float(s2_lo[b] & 0xFFFF0000u) : __uint_as_float(s2_lo[b] << 16);
+          const float s_hi = c ? __uint_as_float(s2_hi[b] & 0xFFFF0000u) : __uint_as_float(s2_hi[b] << 16);
+          int al[4], ah[4];
+          imma_first<false>(al, le[0], he[0], le[1], he[1], p0.x, p0.y);
+          imma_first<true>(ah, le[0], he[0], le[1], he[1], h0.x, h0.y);
+          imma_acc<false>(al, lq[0], hq[0], lq[1], hq[1], p0.z, p0.w);
+          imma_acc<true>(ah, lq[0], hq[0], lq[1], hq[1], h0.z, h0.w);
+          imma_acc<false>(al, le[2], he[2], le[3], he[3], p1.x, p1.y);
+          imma_acc<true>(ah, le[2], he[2], le[3], he[3], h1.x, h1.y);
+          imma_acc<false>(al, lq[2], hq[2], lq[3], hq[3], p1.z, p1.w);
+          imma_acc<true>(ah, lq[2], hq[2], lq[3], hq[3], h1.z, h1.w);
+          fin[b][j][0] = fmaf(s_lo * up.x, (float)(al[0] + (ah[0] << 8)), fin[b][j][0]);
+          fin[b][j][1] = fmaf(s_lo * up.y, (float)(al[1] + (ah[1] << 8)), fin[b][j][1]);
+          fin[b][j][2] = fmaf(s_hi * up.x, (float)(al[2] + (ah[2] << 8)), fin[b][j][2]);
+          fin[b][j][3] = fmaf(s_hi * up.y, (float)(al[3] + (ah[3] << 8)), fin[b][j][3]);
+        }
       }
     }
-    // every product has consumed the fragments: the slot takes the unit `depth` ahead
-    __syncwarp();
-    if (i + q.depth < n) feed(slot, bar);
     slot += kSlotBytes;
     bar += 8;
     if (++d == q.depth) {
@@ -315,14 +381,18 @@ __global__ void __launch_bounds__(kThreads, 1) w4_gemv_mid_kernel(const MidParam
         store_tile(tile, fin);
       } else {
 #pragma unroll
-        for (int j = 0; j < NP; ++j)
+        for (int b = 0; b < RB; ++b)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) first[j][e] = fin[j][e];
+          for (int j = 0; j < NP; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) first[b][j][e] = fin[b][j][e];
       }
 #pragma unroll
-      for (int j = 0; j < NP; ++j)
+      for (int b = 0; b < RB; ++b)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) fin[j][e] = 0.f;
+        for (int j = 0; j < NP; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) fin[b][j][e] = 0.f;
       sc = 0;
       sc_start = 0;
       ++tile;
@@ -335,27 +405,30 @@ __global__ void __launch_bounds__(kThreads, 1) w4_gemv_mid_kernel(const MidParam
     if (sc_start == 0 && sc == q.nsc)
       store_tile(tile, fin);
     else
-      park(ring0 + Mp * 64, fin);
+      park(ring0 + kSegBytes, fin);
     if (first_tile != last_tile) park(ring0, first);
   }
   __syncthreads();
   // ---- tiles shared by several warps: their parts are added in warp order
   const int ring_bytes = q.depth * kSlotBytes;
   const uint32_t rings = smem_u32(smem + kHeader);
-  for (int idx = tid; idx < (T1 - T0) * 16 * Mp; idx += kThreads) {
-    const int tl = idx / (16 * Mp), rem = idx - tl * (16 * Mp), tok = rem >> 4, row = rem & 15;
-    const int r = (T0 + tl) * 16 + row;
-    if (tok >= q.M || r >= q.N) continue;
-    const long ua = (long)tl * q.nsc, ub = ua + q.nsc - 1;
-    const int wa = min(kWarps - 1, (int)((16 * (ua + 1) - 1) / U)), wb = min(kWarps - 1, (int)((16 * (ub + 1) - 1) / U));
+  constexpr int kGroups = kRows * Mp / 32;  // a warp takes 32 outputs of one tile at a time
+  for (int it = warp; it < (T1 - T0) * kGroups; it += W) {
+    const int tl = it / kGroups, rem = (it - tl * kGroups) * 32 + lane;
+    const unsigned ua = (unsigned)tl * q.nsc, ub = ua + q.nsc - 1;  // (W * units of a CTA stays far below 2^32)
+    // the warp that holds unit u: the last one whose run begins at or before u
+    const int wa = min(W - 1, (int)((W * (ua + 1) - 1) / (unsigned)U)), wb = min(W - 1, (int)((W * (ub + 1) - 1) / (unsigned)U));
     if (wa == wb) continue;  // one warp had the whole tile
+    const int tok = rem / kRows, row = rem - tok * kRows;
+    const int r = (T0 + tl) * kRows + row;
+    if (tok >= q.M || r >= q.N) continue;
     float sum = 0.f;
     for (int w = wa; w <= wb; ++w) {
-      const int w0 = (int)(((long)w * U) >> 4), w1 = (int)(((long)(w + 1) * U) >> 4);
+      const unsigned w0 = (unsigned)(w * U) / W, w1 = (unsigned)((w + 1) * U) / W;
       if (w0 == w1) continue;  // (fewer units than warps: a warp without work)
-      const int ft = w0 / q.nsc, lt = (w1 - 1) / q.nsc;
-      const int which = (tl == ft && lt != tl) ? 0 : 1;
-      sum += lds32f(rings + w * ring_bytes + which * (Mp * 64) + (tok * 16 + row) * 4);
+      // the first tile of its run, when more tiles follow, is the part parked first; any other part second
+      const int which = (w0 >= ua && w1 - 1 > ub) ? 0 : 1;
+      sum += lds32f(rings + w * ring_bytes + which * kSegBytes + (tok * kRows + row) * 4);
     }
     q.Y[(size_t)tok * q.N + r] = __float2bfloat16(sum);
   }
@@ -363,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4_gemv_mid_kernel(const MidParam
 }
 
 struct MidPlan {
-  int NP, depth, grid;
+  int NP, RB, W, depth, grid;
   size_t smem;
   MidParams q;
 };
@@ -375,34 +448,46 @@ bool make_mid_plan(int M, int N, int K, int flags, int sm_count, MidPlan* out) {
   pl.q.pstride = K + 16;
   const size_t x_bytes = (size_t)2 * Mp * pl.q.pstride, info_bytes = (size_t)nch * Mp * 4;
   const int forced_depth = (flags >> 4) & 0xF;  // bits 4-7: ring slots per warp (diagnostics)
-  int depth = kMaxDepth;
-  if (forced_depth >= 2 && forced_depth <= kMaxDepth) depth = forced_depth;
-  for (; depth >= 2; --depth) {
-    const size_t ring = (size_t)kWarps * depth * kSlotBytes;
-    if (kHeader + ring + x_bytes + info_bytes <= (size_t)kSmemMax) break;
+  const int forced_rb = (flags >> 10) & 3;      // bits 10-11: 16-row blocks per tile (diagnostics)
+  // 32-row tiles where every SM still gets one and the rings fit beside X (twelve warps for sixteen tokens), else 16
+  struct Shape { int RB, W; };
+  const Shape shapes[2] = {{2, pl.NP == 2 ? 12 : 16}, {1, 16}};
+  bool found = false;
+  for (const Shape& sh : shapes) {
+    if (forced_rb && forced_rb != sh.RB) continue;
+    if (sh.RB == 2 && !forced_rb) continue;  // measured slower (8 tokens: 14.9 against 13.5 us; 16: 22.6 against 19.4)
+    const int slot = sh.RB * kBlockBytes;
+    int depth = kMaxDepth;
+    if (forced_depth >= 2 && forced_depth <= kMaxDepth) depth = forced_depth;
+    for (; depth >= 2; --depth)
+      if (kHeader + (size_t)sh.W * depth * slot + x_bytes + info_bytes <= (size_t)kSmemMax) break;
+    if (depth < 2) continue;
+    // the parts of the at most two partial tiles of a warp go into its drained ring
+    if ((size_t)2 * Mp * sh.RB * 16 * 4 > (size_t)depth * slot) continue;
+    pl.RB = sh.RB;
+    pl.W = sh.W;
+    pl.depth = depth;
+    found = true;
+    break;
   }
-  if (depth < 2) return false;
-  // the parts of the at most two partial tiles of a warp go into its drained ring
-  if ((size_t)2 * Mp * 64 > (size_t)depth * kSlotBytes) return false;
-  pl.depth = depth;
-  pl.q.depth = depth;
-  pl.q.off_x = kHeader + kWarps * depth * kSlotBytes;
+  if (!found) return false;
+  pl.q.depth = pl.depth;
+  pl.q.off_x = kHeader + pl.W * pl.depth * pl.RB * kBlockBytes;
   pl.q.info_off = (int)x_bytes;
-  pl.q.image_bytes = (int)(x_bytes + info_bytes);
-  pl.smem = pl.q.off_x + pl.q.image_bytes;
+  pl.smem = pl.q.off_x + x_bytes + info_bytes;
   pl.q.M = M;
   pl.q.N = N;
   pl.q.K = K;
   pl.q.nsc = K / 256;
-  pl.q.n_tiles = (N + 15) / 16;
+  pl.q.n_tiles = (N + pl.RB * 16 - 1) / (pl.RB * 16);
   pl.grid = std::min(sm_count, pl.q.n_tiles);
   *out = pl;
   return true;
 }
 
-template <int NP>
+template <int NP, int RB, int W>
 int launch_mid(const MidPlan& pl, bool pdl, cudaStream_t stream) {
-  auto kernel = w4_gemv_mid_kernel<NP>;
+  auto kernel = w4_gemv_mid_kernel<NP, RB, W>;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -413,7 +498,7 @@ int launch_mid(const MidPlan& pl, bool pdl, cudaStream_t stream) {
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(W * 32);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -425,23 +510,11 @@ int launch_mid(const MidPlan& pl, bool pdl, cudaStream_t stream) {
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  // the conversion of X in front: a thread per item
-  cudaLaunchConfig_t pre = cfg;
-  pre.gridDim = dim3((NP * 8 * (pl.q.K / 16) + kStageThreads - 1) / kStageThreads);
-  pre.blockDim = dim3(kStageThreads);
-  pre.dynamicSmemBytes = 0;
-  cudaError_t e = cudaLaunchKernelEx(&pre, w4_mid_stage_kernel, pl.q, NP * 8);
-  if (e != cudaSuccess) return (int)e;
-  e = cudaLaunchKernelEx(&cfg, kernel, pl.q);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, pl.q);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 }  // namespace
-
-size_t gemv_mid_image_bytes(int M, int K) {
-  const size_t Mp = (size_t)(M + 7) / 8 * 8;
-  return 2 * Mp * (K + 16) + (size_t)(K / 128) * Mp * 4;
-}
 
 bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, int flags,
                       int sm_count) {
@@ -449,14 +522,9 @@ bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N
   if (flags & (kFlagFloatX | kFlagWideX | kFlagNoMidKernel)) return false;
   if (!forced && (flags & kFlagMidKernel)) return false;  // one of the other two kernels is asked for
   if (M < 5 || M > 16 || G != 128 || K % 256 || N < 16 * sm_count) return false;
-  // Measured against the other two kernels (chained launches, weights from DRAM): nine tokens and more always win
-  // here (18944 x 3584 at 16: 19.7 against 25.4 us; 37888 x 3584: 29.7 against 40.8); five to eight win on the 70B
-  // class (28672 x 8192 at 8: 35.2 against 42.6 us; 8192 x 8192: 13.6 against 24.0) and tie on the 7B-shaped ones,
-  // except the row-concatenated gate|up, where the streaming kernel is up to 2 us shorter, and the small q / o.
-  if (M <= 8 && K <= 4096 && !forced) {
-    if (N >= 32768 && N < 49152) return false;
-    if ((long)N * K < (16l << 20)) return false;
-  }
+  // Measured against the other two kernels (chained launches, weights from DRAM), five to sixteen tokens: shorter on
+  // every shape tried, 7B-shaped and 70B class, from 3584 x 3584 (6.8 against 7.9 us at five tokens) to 152064 x 3584
+  // (65 against 77 us); 18944 x 3584: 12.6 against 15.8 us at eight tokens, 17.4 against 25.4 at sixteen.
   if ((reinterpret_cast<uintptr_t>(Wq) & 15) || (reinterpret_cast<uintptr_t>(S) & 3) ||
       (reinterpret_cast<uintptr_t>(X) & 15))
     return false;
@@ -468,25 +536,23 @@ int gemv_mid_describe(int M, int N, int K, int flags, int sm_count, char* buf, i
   MidPlan pl;
   if (!make_mid_plan(M, N, K, flags, sm_count, &pl)) return 0;
   return snprintf(buf, buflen,
-                  "many-token kernel: %d CTAs of 16 warps (1 per SM), %d row tiles x %d super-chunks cut into equal "
-                  "runs per warp, %d token group(s) of 8, 2 planes (16-bit X) converted by a kernel in front, ring depth "
-                  "%d, %zu KB smem",
-                  pl.grid, pl.q.n_tiles, pl.q.nsc, pl.NP, pl.depth, pl.smem >> 10);
+                  "many-token kernel: %d CTAs of %d warps (1 per SM), %d tiles of %d rows x %d super-chunks cut into "
+                  "equal runs per warp, %d token group(s) of 8, 2 planes (16-bit X), ring depth %d, %zu KB smem",
+                  pl.grid, pl.W, pl.q.n_tiles, pl.RB * 16, pl.q.nsc, pl.NP, pl.depth, pl.smem >> 10);
 }
 
-int gemv_mid_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int* status,
-                    unsigned char* image, size_t image_cap, int flags, int sm_count, cudaStream_t stream) {
+int gemv_mid_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int* status, int flags,
+                    int sm_count, cudaStream_t stream) {
   MidPlan pl;
   if (!make_mid_plan(M, N, K, flags, sm_count, &pl)) return kErrTooLarge;
-  if (!image || (reinterpret_cast<uintptr_t>(image) & 15) || (size_t)pl.q.image_bytes > image_cap) return kErrWorkspace;
-  pl.q.image = image;
   pl.q.X = static_cast<const __nv_bfloat16*>(X);
   pl.q.Wq = static_cast<const unsigned char*>(Wq);
   pl.q.S = static_cast<const __nv_bfloat16*>(S);
   pl.q.Y = static_cast<__nv_bfloat16*>(Y);
   pl.q.status = status;
   const bool pdl = (flags & kFlagNoPdl) == 0;
-  return pl.NP == 1 ? launch_mid<1>(pl, pdl, stream) : launch_mid<2>(pl, pdl, stream);
+  if (pl.RB == 1) return pl.NP == 1 ? launch_mid<1, 1, 16>(pl, pdl, stream) : launch_mid<2, 1, 16>(pl, pdl, stream);
+  return pl.NP == 1 ? launch_mid<1, 2, 16>(pl, pdl, stream) : launch_mid<2, 2, 12>(pl, pdl, stream);
 }
 
 }  // namespace b2

@@ -21,7 +21,6 @@ SLACK_DEFAULT, SLACK_HEAVY = 2e-5, 5e-4
 
 
 def run(k, X, Wq, S, G=128, flags=0):
-    # (forced: by default a few shapes of five to eight tokens go to the other kernels, which measured faster there)
     if not flags & ops.FLAG_NO_MID_KERNEL:
         flags |= ops.FLAG_MID_KERNEL
     y = k.w4_linear(bits_to_torch(X), u32_to_torch(Wq), bits_to_torch(S), G, flags=flags)
@@ -36,7 +35,7 @@ def served(k, M, N, K, flags=ops.FLAG_MID_KERNEL):
 def test_dispatch(kernels):
     assert served(kernels, 8, 18944, 3584) and served(kernels, 16, 18944, 3584) and served(kernels, 5, 2368, 256)
     assert served(kernels, 8, 28672, 8192, 0) and served(kernels, 16, 18944, 3584, 0) and served(kernels, 9, 37888, 3584, 0)
-    assert not served(kernels, 8, 37888, 3584, 0) and not served(kernels, 8, 3584, 3584, 0)  # measured slower there
+    assert served(kernels, 8, 37888, 3584, 0) and served(kernels, 5, 3584, 3584, 0)
     assert not served(kernels, 4, 18944, 3584) and not served(kernels, 16, 2000, 3584)
     assert not served(kernels, 16, 3584, 18944)  # the converted X does not fit in shared memory
     assert not kernels.gemv_describe(8, 18944, 3584, 128, ops.FLAG_NO_MID_KERNEL).startswith("many-token")
@@ -75,6 +74,25 @@ def test_every_token_count(kernels, N, K):
         check_bf16_output(a, ref, SLACK_DEFAULT)
         assert np.array_equal(a, run(kernels, X, Wq, S)), "two identical launches differ"
         assert np.array_equal(a, run(kernels, X, Wq, S, flags=ops.FLAG_NO_PDL))
+    assert kernels.device_status() == 0
+
+
+@pytest.mark.parametrize("rows", [16, 32])
+@pytest.mark.parametrize("N,K", [(2368, 512), (4736, 256), (4750, 1024), (9001, 768), (20000, 256), (6000, 3584)])
+def test_both_tile_heights(kernels, rows, N, K):
+    """Tiles of 16 and of 32 rows (two row blocks share the B fragments; twelve warps instead of sixteen above eight
+    tokens), forced: the default takes 32 where every SM gets a tile and the rings fit."""
+    force = (rows // 16) << 10
+    for M in (5, 8, 9, 13, 16):
+        plan = kernels.gemv_describe(M, N, K, 128, ops.FLAG_MID_KERNEL | force)
+        if not plan.startswith("many-token kernel"):
+            continue  # (32-row slots of twelve warps do not fit beside sixteen tokens of a long K)
+        assert f"tiles of {rows} rows" in plan
+        X, Wq, S = oracle.synth_inputs(M, N, K, 128, seed=M + rows)
+        ref = oracle.w4_linear_f32(X, Wq, S, 128, threads=oracle.max_threads())
+        a = run(kernels, X, Wq, S, flags=force)
+        check_bf16_output(a, ref, SLACK_DEFAULT)
+        assert np.array_equal(a, run(kernels, X, Wq, S, flags=force))
     assert kernels.device_status() == 0
 
 
