@@ -356,6 +356,19 @@ __device__ __forceinline__ void gemv_step(LoopState<NT>& st, float (&fin)[RB][NT
   uint32_t cur[2 * RB][8];
   mbar_wait(st.bar, st.ph, st.abort_flag);
   load_fragments<RB>(st, cur);
+  {
+    // The slot is free as soon as every lane's loads from it have returned: an instruction that reads all of their
+    // results is issued (in order) before the barrier, so the slot takes the super-chunk `depth` ahead BEFORE the
+    // products -- a slot's period is the longer of the memory latency and the work on `depth` super-chunks, not
+    // their sum.
+    uint32_t all = 0;
+#pragma unroll
+    for (int i = 0; i < 2 * RB; ++i)
+      all ^= (cur[i][0] ^ cur[i][1] ^ cur[i][2]) ^ (cur[i][3] ^ cur[i][4] ^ cur[i][5]) ^ (cur[i][6] ^ cur[i][7]);
+    asm volatile("" ::"r"(all) : "memory");
+    __syncwarp();
+    if (refill) feed_slot<RB>(st, st.slot, st.bar);
+  }
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     uint4 x[4];
@@ -393,10 +406,6 @@ __device__ __forceinline__ void gemv_step(LoopState<NT>& st, float (&fin)[RB][NT
       fin[rb][nt][3] = fmaf(sh * up1, (float)(acc_e[3] * 16 + acc_o[3]), fin[rb][nt][3]);
     }
   }
-  // every product above has consumed `cur`, so every lane's loads from the slot have completed: the slot takes the
-  // super-chunk `depth` ahead
-  __syncwarp();
-  if (refill) feed_slot<RB>(st, st.slot, st.bar);
   st.slot += kSlotBytes;
   st.bar += 8;
   if (++st.d == st.depth) {
@@ -438,6 +447,16 @@ __device__ __forceinline__ void gemv_step_one(LoopState<NT>& st, float (&fin)[1]
   wh[0] = lds128(st.slot + 1024 + st.a_u0);
   wl[1] = lds128(st.slot + st.a_u1);
   wh[1] = lds128(st.slot + 1024 + st.a_u1);
+  {
+    // (the slot is refilled before the products, as in gemv_step)
+    uint32_t all = 0;
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+      all ^= (wl[c].x ^ wl[c].y ^ wl[c].z) ^ (wl[c].w ^ wh[c].x ^ wh[c].y) ^ (wh[c].z ^ wh[c].w);
+    asm volatile("" ::"r"(all) : "memory");
+    __syncwarp();
+    if (refill) feed_slot<1>(st, st.slot, st.bar);
+  }
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     const uint32_t lo[4] = {wl[c].x, wl[c].y, wl[c].z, wl[c].w};
@@ -469,8 +488,6 @@ __device__ __forceinline__ void gemv_step_one(LoopState<NT>& st, float (&fin)[1]
     st.xaddr[nt] += st.xstep[nt];
     st.iaddr[nt] += st.istep[nt];
   }
-  __syncwarp();
-  if (refill) feed_slot<1>(st, st.slot, st.bar);
   st.slot += kSlotBytes;
   st.bar += 8;
   if (++st.d == st.depth) {
