@@ -222,32 +222,61 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
 
   // ---- weight stream.  Lane l copies 16 bytes of rows (l >> 3) + 4 j of every 16-row block: a warp instruction
   // covers four rows x 128 bytes, whole lines.  Rows beyond N are zero-filled.
-  int ftile = T0 + u0 / q.nsc, fsc = u0 % q.nsc;  // the next unit to feed
+  // Running source pointers (the next unit to feed): row l >> 3 of the tile for the weights, row l of the tile for the
+  // scales; they advance by one super-chunk per unit and by fifteen rows more at the end of a tile.
+  int ftile = T0 + u0 / q.nsc, fsc = u0 % q.nsc;
   const int r4 = lane >> 3, c16 = lane & 7;
   const size_t row_bytes = (size_t)q.K >> 1;
   const int KG = q.K >> 7;
-  auto feed = [&](uint32_t slot, uint32_t bar) {
-    const int rowbase = ftile * kRows;
+  const unsigned char* wsrc = q.Wq + ((size_t)ftile * kRows + r4) * row_bytes + (size_t)fsc * 128 + c16 * 16;
+  const __nv_bfloat16* ssrc = q.S + ((size_t)ftile * kRows + lane) * KG + 2 * fsc;
+  const uint32_t dst_lane = r4 * 128;  // + the swizzled 16-byte column, per row
+  auto rows_mask = [&](int tile) {  // bit j: row r4 + 4 j of the tile exists; bit 31: row `lane` exists (scales)
+    const int left = q.N - tile * kRows;
+    uint32_t m = lane < left ? 0x80000000u : 0u;
 #pragma unroll
-    for (int j = 0; j < 4 * RB; ++j) {
-      const int row = r4 + 4 * (j & 3), blk = j >> 2;
-      const bool ok = rowbase + blk * 16 + row < q.N;
-      const unsigned char* src =
-          q.Wq + (ok ? (size_t)(rowbase + blk * 16 + row) * row_bytes + (size_t)fsc * 128 + c16 * 16 : 0);
-      asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(slot + blk * kBlockBytes + row * 128 +
+    for (int j = 0; j < 4 * RB; ++j)
+      if (r4 + 4 * j < left) m |= 1u << j;
+    return m;
+  };
+  uint32_t fvalid = rows_mask(ftile);
+  constexpr uint32_t kAllRows = (1u << (4 * RB)) - 1u;
+  auto feed = [&](uint32_t slot, uint32_t bar) {
+    if ((fvalid & kAllRows) == kAllRows) {
+#pragma unroll
+      for (int j = 0; j < 4 * RB; ++j) {
+        const int row = r4 + 4 * (j & 3);
+        asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(slot + (j >> 2) * kBlockBytes + dst_lane +
+                                                                              (j & 3) * 512 +
+                                                                              ((uint32_t)(c16 ^ (row & 7)) << 4)),
+                     "l"(wsrc + (size_t)(4 * j) * row_bytes)
+                     : "memory");
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4 * RB; ++j) {
+        const int row = r4 + 4 * (j & 3);
+        const bool ok = (fvalid >> j) & 1u;
+        asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(slot + (j >> 2) * kBlockBytes +
+                                                                                  dst_lane + (j & 3) * 512 +
                                                                                   ((uint32_t)(c16 ^ (row & 7)) << 4)),
-                   "l"(src), "r"(ok ? 16u : 0u)
-                   : "memory");
+                     "l"(ok ? wsrc + (size_t)(4 * j) * row_bytes : q.Wq), "r"(ok ? 16u : 0u)
+                     : "memory");
+      }
     }
     if (lane < kRows) {  // the two scales of the super-chunk, a row per lane
-      const bool ok = rowbase + lane < q.N;
-      cp_async<4>(slot + (lane >> 4) * kBlockBytes + 2048 + (lane & 15) * 4,
-                  q.S + (ok ? (size_t)(rowbase + lane) * KG + 2 * fsc : 0), ok ? 4u : 0u);
+      const bool ok = fvalid >> 31;
+      cp_async<4>(slot + (lane >> 4) * kBlockBytes + 2048 + (lane & 15) * 4, ok ? ssrc : q.S, ok ? 4u : 0u);
     }
     cp_async_mbar_arrive_noinc(bar);
+    wsrc += 128;
+    ssrc += 2;
     if (++fsc == q.nsc) {
       fsc = 0;
       ++ftile;
+      wsrc += (size_t)(kRows - 1) * row_bytes;
+      ssrc += (size_t)(kRows - 1) * KG;
+      fvalid = rows_mask(ftile);
     }
   };
 
