@@ -1245,11 +1245,12 @@ static bool mid_serves(const void* X, const void* Wq, const void* S, int M, int 
                        const Workspace& ws, int flags, int sm_count, const GemvTp* tp) {
   if (pro.kind != kProNone || pro.epilogue != kEpiNone) return false;
   if (tp != nullptr && (tp->world > 0 || tp->wait_sig != nullptr || tp->announce_world > 0)) return false;
-  return gemv_mid_applies(X, Wq, S, M, N, K, G, flags, sm_count);
+  return gemv_mid_applies(X, Wq, S, M, N, K, G, flags, sm_count, ws.partial ? ws.partial_bytes : 0);
 }
 
 size_t gemv_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap) {
-  if (gemv_mid_applies(nullptr, nullptr, nullptr, M, N, K, G, flags, sm_count)) return 0;
+  if (gemv_mid_applies(nullptr, nullptr, nullptr, M, N, K, G, flags, sm_count, partial_cap))
+    return gemv_mid_scratch_bytes(M, N, K, flags, sm_count, partial_cap);
   if (gemv_stream_applies(nullptr, M, N, K, G, flags)) {
     // (0 also when no streaming plan fits and the ring kernel runs: its own answer follows)
     const size_t b = gemv_stream_scratch_bytes(M, N, K, G, flags, sm_count, partial_cap);
@@ -1279,8 +1280,8 @@ size_t gemv_grid(int M, int N, int K, int G, int flags, int sm_count, size_t par
 int gemv_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap, char* buf,
                   int buflen) {
   if (!buf || buflen < 1) return kErrBadPointer;
-  if (gemv_mid_applies(nullptr, nullptr, nullptr, M, N, K, G, flags, sm_count) &&
-      gemv_mid_describe(M, N, K, flags, sm_count, buf, buflen) > 0)
+  if (gemv_mid_applies(nullptr, nullptr, nullptr, M, N, K, G, flags, sm_count, partial_cap) &&
+      gemv_mid_describe(M, N, K, flags, sm_count, partial_cap, buf, buflen) > 0)
     return 0;
   if (gemv_stream_applies(nullptr, M, N, K, G, flags)) {
     const int n = gemv_stream_describe(M, N, K, G, flags, sm_count, partial_cap, buf, buflen);
@@ -1495,7 +1496,7 @@ int gemv_launch_planned(const void* X, const void* Wq, const void* S, void* Y, i
     return kErrBadPointer;
   if (!ws.status) return kErrWorkspace;
   if (mid_serves(X, Wq, S, M, N, K, G, pro, ws, flags, sm_count, tp))
-    return gemv_mid_launch(X, Wq, S, Y, M, N, K, ws.status, flags, sm_count, stream);
+    return gemv_mid_launch(X, Wq, S, Y, M, N, K, ws, flags, sm_count, stream);
   if (gemv_stream_applies(Wq, M, N, K, G, flags)) {
     const int rc = gemv_stream_launch(X, Wq, S, Y, M, N, K, G, pro, ws, flags, sm_count, stream, tp);
     if (rc != kStreamNotApplicable) return rc;

@@ -57,6 +57,8 @@ struct MidParams {
                 // planes x four 32-byte pieces, then cover all banks)
   int off_x;          // the converted X in shared memory: digit planes, then the factors
   int info_off;       // offset of the factors inside it
+  int scps;           // super-chunks of K per slice (blockIdx.y); nsc when K is not cut
+  float* partial;     // K cut into slices: fp32 partial sums [slice][M][N], added up by the kernel behind; else null
 };
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
@@ -117,11 +119,11 @@ __device__ __forceinline__ float2 lds64f(uint32_t addr) {
 // chunk with an inf or a nan gets a nan factor.  Layout: planes [2][Mp][K + 16], then the factors [K / 128][Mp].
 template <typename F>
 __device__ __forceinline__ void convert_x(const MidParams& q, uint32_t xs, uint32_t info, int Mp, int tid,
-                                          int nthreads, F&& after_first_loads) {
+                                          int nthreads, int k0, int klen, F&& after_first_loads) {
   // All of a thread's loads (up to UN items) are in flight before the first conversion, and AHEAD of the weight
   // stream, which `after_first_loads` starts: behind the ring's first fill (a third of the matrix) they took 2 us.
   constexpr int UN = 8;
-  const int items_tok = q.K >> 4;
+  const int items_tok = klen >> 4;   // the CTA's slice of K: [k0, k0 + klen)
   const int items = Mp * items_tok;  // a multiple of 32: whole warps stay together for the shuffles
   // (token, item in token) of the thread's items advance by a fixed step: two divisions per thread, not two per item
   const int step_m = nthreads / items_tok, step_r = nthreads - step_m * items_tok;
@@ -137,7 +139,7 @@ __device__ __forceinline__ void convert_x(const MidParams& q, uint32_t xs, uint3
       va[u] = make_uint4(0u, 0u, 0u, 0u);
       vb[u] = va[u];
       if (it < items && m0 < q.M) {
-        const uint4* src = reinterpret_cast<const uint4*>(q.X + (size_t)m0 * q.K + r0 * 16);
+        const uint4* src = reinterpret_cast<const uint4*>(q.X + (size_t)m0 * q.K + k0 + r0 * 16);
         va[u] = ld_l2(src);
         vb[u] = ld_l2(src + 1);
       }
@@ -207,7 +209,8 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
   // ---- the CTA's tiles and the warp's run of (tile, super-chunk) units
   const int T0 = (int)(((long)blockIdx.x * q.n_tiles) / gridDim.x);
   const int T1 = (int)(((long)(blockIdx.x + 1) * q.n_tiles) / gridDim.x);
-  const int U = (T1 - T0) * q.nsc;
+  const int scb = blockIdx.y * q.scps, nscl = min(q.nsc, scb + q.scps) - scb;  // the CTA's slice of K
+  const int U = (T1 - T0) * nscl;
   const int u0 = (int)(((long)warp * U) / W), u1 = (int)(((long)(warp + 1) * U) / W);
   const int n = u1 - u0;
   const uint32_t bar0 = smem_u32(smem + kBarOffset) + warp * (8 * kMaxDepth);
@@ -224,12 +227,12 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
   // covers four rows x 128 bytes, whole lines.  Rows beyond N are zero-filled.
   // Running source pointers (the next unit to feed): row l >> 3 of the tile for the weights, row l of the tile for the
   // scales; they advance by one super-chunk per unit and by fifteen rows more at the end of a tile.
-  int ftile = T0 + u0 / q.nsc, fsc = u0 % q.nsc;
+  int ftile = T0 + u0 / nscl, fsc = u0 % nscl;
   const int r4 = lane >> 3, c16 = lane & 7;
   const size_t row_bytes = (size_t)q.K >> 1;
   const int KG = q.K >> 7;
-  const unsigned char* wsrc = q.Wq + ((size_t)ftile * kRows + r4) * row_bytes + (size_t)fsc * 128 + c16 * 16;
-  const __nv_bfloat16* ssrc = q.S + ((size_t)ftile * kRows + lane) * KG + 2 * fsc;
+  const unsigned char* wsrc = q.Wq + ((size_t)ftile * kRows + r4) * row_bytes + (size_t)(scb + fsc) * 128 + c16 * 16;
+  const __nv_bfloat16* ssrc = q.S + ((size_t)ftile * kRows + lane) * KG + 2 * (scb + fsc);
   const uint32_t dst_lane = r4 * 128;  // + the swizzled 16-byte column, per row
   auto rows_mask = [&](int tile) {  // bit j: row r4 + 4 j of the tile exists; bit 31: row `lane` exists (scales)
     const int left = q.N - tile * kRows;
@@ -271,11 +274,11 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
     cp_async_mbar_arrive_noinc(bar);
     wsrc += 128;
     ssrc += 2;
-    if (++fsc == q.nsc) {
+    if (++fsc == nscl) {
       fsc = 0;
       ++ftile;
-      wsrc += (size_t)(kRows - 1) * row_bytes;
-      ssrc += (size_t)(kRows - 1) * KG;
+      wsrc += (size_t)kRows * row_bytes - (size_t)nscl * 128;
+      ssrc += (size_t)kRows * KG - 2 * nscl;
       fvalid = rows_mask(ftile);
     }
   };
@@ -284,7 +287,7 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
   // issued between the loads of X and their use
   pdl_wait_prior_grid();
   const uint32_t xs = smem_u32(smem + q.off_x), info = xs + q.info_off;
-  convert_x(q, xs, info, Mp, tid, kThreads, [&]() {
+  convert_x(q, xs, info, Mp, tid, kThreads, scb * 256, nscl * 256, [&]() {
     const int pre = min(q.depth, n);
     for (int i = 0; i < pre; ++i) feed(ring0 + i * kSlotBytes, bar0 + 8 * i);
   });
@@ -298,7 +301,7 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
   // accumulator columns 2t, 2t + 1 are tokens 8 j + 2t, + 1
   const uint32_t xlane = xs + (uint32_t)g * q.pstride + t * 32, xhigh = (uint32_t)Mp * q.pstride;
   const uint32_t ilane = info + (uint32_t)(2 * t) * 4;
-  const int first_tile = T0 + u0 / q.nsc, last_tile = n > 0 ? T0 + (u1 - 1) / q.nsc : first_tile;
+  const int first_tile = T0 + u0 / nscl, last_tile = n > 0 ? T0 + (u1 - 1) / nscl : first_tile;
   float fin[RB][NP][4], first[RB][NP][4];  // [token 2t | 2t + 1][row rho | rho + 8]: index 2 * row half + token
 #pragma unroll
   for (int b = 0; b < RB; ++b)
@@ -306,6 +309,14 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
     for (int j = 0; j < NP; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) fin[b][j][e] = first[b][j][e] = 0.f;
+  // an output: bf16 into Y, or -- K cut into slices -- the slice's fp32 partial sum
+  float* const part = q.partial ? q.partial + (size_t)blockIdx.y * q.M * q.N : nullptr;
+  auto out = [&](int tok, int r, float v) {
+    if (part)
+      part[(size_t)tok * q.N + r] = v;
+    else
+      q.Y[(size_t)tok * q.N + r] = __float2bfloat16(v);
+  };
   auto store_tile = [&](int tile, const float (&v)[RB][NP][4]) {
 #pragma unroll
     for (int b = 0; b < RB; ++b)
@@ -314,7 +325,7 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int tok = j * 8 + 2 * t + (e & 1), r = tile * kRows + b * 16 + rho + (e >> 1) * 8;
-          if (tok < q.M && r < q.N) q.Y[(size_t)tok * q.N + r] = __float2bfloat16(v[b][j][e]);
+          if (tok < q.M && r < q.N) out(tok, r, v[b][j][e]);
         }
   };
   auto park = [&](uint32_t base, const float (&v)[RB][NP][4]) {
@@ -326,7 +337,7 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
         for (int e = 0; e < 4; ++e)
           sts32f(base + (uint32_t)((j * 8 + 2 * t + (e & 1)) * kRows + b * 16 + rho + (e >> 1) * 8) * 4, v[b][j][e]);
   };
-  int tile = first_tile, sc = u0 % q.nsc, sc_start = sc;
+  int tile = first_tile, sc = u0 % nscl, sc_start = sc;
   uint32_t slot = ring0, bar = bar0, ph = 0;
   int d = 0;
   for (int i = 0; i < n; ++i) {
@@ -403,7 +414,7 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
       bar = bar0;
       ph ^= 1;
     }
-    if (++sc == q.nsc && i + 1 < n) {
+    if (++sc == nscl && i + 1 < n) {
       // the tile is finished and more follow.  Whole (begun at its first super-chunk): out from registers; begun by
       // the previous warp (only the first tile of a run can be): kept for the sums at the end.
       if (sc_start == 0) {
@@ -431,7 +442,7 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
   // The part of a first tile begun by the previous warp goes there too.
   cp_async_wait_all();
   if (n > 0) {
-    if (sc_start == 0 && sc == q.nsc)
+    if (sc_start == 0 && sc == nscl)
       store_tile(tile, fin);
     else
       park(ring0 + kSegBytes, fin);
@@ -444,7 +455,7 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
   constexpr int kGroups = kRows * Mp / 32;  // a warp takes 32 outputs of one tile at a time
   for (int it = warp; it < (T1 - T0) * kGroups; it += W) {
     const int tl = it / kGroups, rem = (it - tl * kGroups) * 32 + lane;
-    const unsigned ua = (unsigned)tl * q.nsc, ub = ua + q.nsc - 1;  // (W * units of a CTA stays far below 2^32)
+    const unsigned ua = (unsigned)tl * nscl, ub = ua + nscl - 1;  // (W * units of a CTA stays far below 2^32)
     // the warp that holds unit u: the last one whose run begins at or before u
     const int wa = min(W - 1, (int)((W * (ua + 1) - 1) / (unsigned)U)), wb = min(W - 1, (int)((W * (ub + 1) - 1) / (unsigned)U));
     if (wa == wb) continue;  // one warp had the whole tile
@@ -459,57 +470,76 @@ __global__ void __launch_bounds__(W * 32, 1) w4_gemv_mid_kernel(const MidParams 
       const int which = (w0 >= ua && w1 - 1 > ub) ? 0 : 1;
       sum += lds32f(rings + w * ring_bytes + which * kSegBytes + (tok * kRows + row) * 4);
     }
-    q.Y[(size_t)tok * q.N + r] = __float2bfloat16(sum);
+    out(tok, r, sum);
   }
   if (*abort_flag && tid == 0) atomicCAS(q.status, kStatusOk, kStatusGemvTimeout);
 }
 
 struct MidPlan {
-  int NP, RB, W, depth, grid;
+  int NP, RB, W, depth, grid, ns;
   size_t smem;
   MidParams q;
 };
 
-bool make_mid_plan(int M, int N, int K, int flags, int sm_count, MidPlan* out) {
+// partial_cap: bytes of fp32 scratch for cutting K into slices across CTAs (0: K must fit whole)
+bool make_mid_plan(int M, int N, int K, int flags, int sm_count, size_t partial_cap, MidPlan* out) {
   MidPlan pl{};
   pl.NP = (M + 7) / 8;
-  const int Mp = pl.NP * 8, nch = K / 128;
-  pl.q.pstride = K + 16;
-  const size_t x_bytes = (size_t)2 * Mp * pl.q.pstride, info_bytes = (size_t)nch * Mp * 4;
+  const int Mp = pl.NP * 8, nsc = K / 256;
   const int forced_depth = (flags >> 4) & 0xF;  // bits 4-7: ring slots per warp (diagnostics)
   const int forced_rb = (flags >> 10) & 3;      // bits 10-11: 16-row blocks per tile (diagnostics)
-  // 32-row tiles where every SM still gets one and the rings fit beside X (twelve warps for sixteen tokens), else 16
+  const int forced_ns = (flags >> 24) & 0xF;    // bits 24-27: K slices across CTAs (diagnostics)
+  // 32-row tiles (twelve warps for sixteen tokens) measured slower (8 tokens: 14.9 against 13.5 us; 16: 22.6 against
+  // 19.4) and run only when asked for
   struct Shape { int RB, W; };
   const Shape shapes[2] = {{2, pl.NP == 2 ? 12 : 16}, {1, 16}};
+  // K whole where its X fits beside rings of two slots (28672 x 8192 at eight tokens: 31.5 us whole, 37.2 in two
+  // slices); else K slices across CTAs (blockIdx.y), as few as let the slice's X fit beside rings of three slots (two
+  // at worst): 3584 x 18944 takes 3 at eight tokens, 5 at sixteen.  The slices' fp32 partial sums are added by a
+  // kernel behind.
   bool found = false;
-  for (const Shape& sh : shapes) {
-    if (forced_rb && forced_rb != sh.RB) continue;
-    if (sh.RB == 2 && !forced_rb) continue;  // measured slower (8 tokens: 14.9 against 13.5 us; 16: 22.6 against 19.4)
-    const int slot = sh.RB * kBlockBytes;
-    int depth = kMaxDepth;
-    if (forced_depth >= 2 && forced_depth <= kMaxDepth) depth = forced_depth;
-    for (; depth >= 2; --depth)
-      if (kHeader + (size_t)sh.W * depth * slot + x_bytes + info_bytes <= (size_t)kSmemMax) break;
-    if (depth < 2) continue;
-    // the parts of the at most two partial tiles of a warp go into its drained ring
-    if ((size_t)2 * Mp * sh.RB * 16 * 4 > (size_t)depth * slot) continue;
-    pl.RB = sh.RB;
-    pl.W = sh.W;
-    pl.depth = depth;
-    found = true;
-    break;
+  for (int want_depth = 4; want_depth >= 2 && !found; --want_depth) {
+    for (int ns = 1; ns <= std::min(nsc, 8) && !found; ++ns) {
+      if (want_depth == 4 && ns > 1) break;  // first pass: K whole, any depth
+      if (forced_ns && ns != forced_ns) continue;
+      if (ns > 1 && ((flags & kFlagForceNoSplitK) || (size_t)ns * M * N * sizeof(float) > partial_cap)) continue;
+      const int scps = (nsc + ns - 1) / ns;
+      if ((nsc + scps - 1) / scps != ns) continue;
+      const int pstride = scps * 256 + 16;
+      const size_t x_bytes = (size_t)2 * Mp * pstride, info_bytes = (size_t)2 * scps * Mp * 4;
+      for (const Shape& sh : shapes) {
+        if (forced_rb ? forced_rb != sh.RB : sh.RB == 2) continue;
+        const int slot = sh.RB * kBlockBytes;
+        int depth = kMaxDepth;
+        if (forced_depth >= 2 && forced_depth <= kMaxDepth) depth = forced_depth;
+        for (; depth >= 2; --depth)
+          if (kHeader + (size_t)sh.W * depth * slot + x_bytes + info_bytes <= (size_t)kSmemMax) break;
+        if (depth < std::min(want_depth, 3) && ns > 1 && !(forced_depth && depth >= 2)) continue;
+        if (depth < 2) continue;
+        // the parts of the at most two partial tiles of a warp go into its drained ring
+        if ((size_t)2 * Mp * sh.RB * 16 * 4 > (size_t)depth * slot) continue;
+        pl.RB = sh.RB;
+        pl.W = sh.W;
+        pl.depth = depth;
+        pl.ns = ns;
+        pl.q.scps = scps;
+        pl.q.pstride = pstride;
+        pl.q.info_off = (int)x_bytes;
+        pl.q.off_x = kHeader + sh.W * depth * slot;
+        pl.smem = pl.q.off_x + x_bytes + info_bytes;
+        found = true;
+        break;
+      }
+    }
   }
   if (!found) return false;
   pl.q.depth = pl.depth;
-  pl.q.off_x = kHeader + pl.W * pl.depth * pl.RB * kBlockBytes;
-  pl.q.info_off = (int)x_bytes;
-  pl.smem = pl.q.off_x + x_bytes + info_bytes;
   pl.q.M = M;
   pl.q.N = N;
   pl.q.K = K;
-  pl.q.nsc = K / 256;
+  pl.q.nsc = nsc;
   pl.q.n_tiles = (N + pl.RB * 16 - 1) / (pl.RB * 16);
-  pl.grid = std::min(sm_count, pl.q.n_tiles);
+  pl.grid = std::max(1, std::min(sm_count / pl.ns, pl.q.n_tiles));
   *out = pl;
   return true;
 }
@@ -526,7 +556,7 @@ int launch_mid(const MidPlan& pl, bool pdl, cudaStream_t stream) {
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(pl.grid);
+  cfg.gridDim = dim3(pl.grid, pl.ns);
   cfg.blockDim = dim3(W * 32);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
@@ -546,7 +576,7 @@ int launch_mid(const MidPlan& pl, bool pdl, cudaStream_t stream) {
 }  // namespace
 
 bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, int flags,
-                      int sm_count) {
+                      int sm_count, size_t partial_cap) {
   const bool forced = (flags & kFlagMidKernel) == kFlagMidKernel;
   if (flags & (kFlagFloatX | kFlagWideX | kFlagNoMidKernel)) return false;
   if (!forced && (flags & kFlagMidKernel)) return false;  // one of the other two kernels is asked for
@@ -558,30 +588,52 @@ bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N
       (reinterpret_cast<uintptr_t>(X) & 15))
     return false;
   MidPlan pl;
-  return make_mid_plan(M, N, K, flags, sm_count, &pl);
+  return make_mid_plan(M, N, K, flags, sm_count, partial_cap, &pl);
 }
 
-int gemv_mid_describe(int M, int N, int K, int flags, int sm_count, char* buf, int buflen) {
+size_t gemv_mid_scratch_bytes(int M, int N, int K, int flags, int sm_count, size_t partial_cap) {
   MidPlan pl;
-  if (!make_mid_plan(M, N, K, flags, sm_count, &pl)) return 0;
+  if (!make_mid_plan(M, N, K, flags, sm_count, partial_cap, &pl)) return 0;
+  return pl.ns > 1 ? (size_t)pl.ns * M * N * sizeof(float) : 0;
+}
+
+int gemv_mid_describe(int M, int N, int K, int flags, int sm_count, size_t partial_cap, char* buf, int buflen) {
+  MidPlan pl;
+  if (!make_mid_plan(M, N, K, flags, sm_count, partial_cap, &pl)) return 0;
   return snprintf(buf, buflen,
                   "many-token kernel: %d CTAs of %d warps (1 per SM), %d tiles of %d rows x %d super-chunks cut into "
-                  "equal runs per warp, %d token group(s) of 8, 2 planes (16-bit X), ring depth %d, %zu KB smem",
-                  pl.grid, pl.W, pl.q.n_tiles, pl.RB * 16, pl.q.nsc, pl.NP, pl.depth, pl.smem >> 10);
+                  "equal runs per warp, %d token group(s) of 8, 2 planes (16-bit X), ring depth %d, K slices across "
+                  "CTAs %d%s, %zu KB smem",
+                  pl.grid * pl.ns, pl.W, pl.q.n_tiles, pl.RB * 16, pl.q.scps, pl.NP, pl.depth, pl.ns,
+                  pl.ns > 1 ? " (sum kernel)" : "", pl.smem >> 10);
 }
 
-int gemv_mid_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int* status, int flags,
-                    int sm_count, cudaStream_t stream) {
+int gemv_mid_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, const Workspace& ws,
+                    int flags, int sm_count, cudaStream_t stream) {
   MidPlan pl;
-  if (!make_mid_plan(M, N, K, flags, sm_count, &pl)) return kErrTooLarge;
+  if (!make_mid_plan(M, N, K, flags, sm_count, ws.partial ? ws.partial_bytes : 0, &pl)) return kErrTooLarge;
   pl.q.X = static_cast<const __nv_bfloat16*>(X);
   pl.q.Wq = static_cast<const unsigned char*>(Wq);
   pl.q.S = static_cast<const __nv_bfloat16*>(S);
   pl.q.Y = static_cast<__nv_bfloat16*>(Y);
-  pl.q.status = status;
+  pl.q.status = ws.status;
+  pl.q.partial = pl.ns > 1 ? ws.partial : nullptr;
   const bool pdl = (flags & kFlagNoPdl) == 0;
-  if (pl.RB == 1) return pl.NP == 1 ? launch_mid<1, 1, 16>(pl, pdl, stream) : launch_mid<2, 1, 16>(pl, pdl, stream);
-  return pl.NP == 1 ? launch_mid<1, 2, 16>(pl, pdl, stream) : launch_mid<2, 2, 12>(pl, pdl, stream);
+  int rc;
+  if (pl.RB == 1)
+    rc = pl.NP == 1 ? launch_mid<1, 1, 16>(pl, pdl, stream) : launch_mid<2, 1, 16>(pl, pdl, stream);
+  else
+    rc = pl.NP == 1 ? launch_mid<1, 2, 16>(pl, pdl, stream) : launch_mid<2, 2, 12>(pl, pdl, stream);
+  if (rc != 0 || pl.ns == 1) return rc;
+  GemvParams p{};  // what the kernel that adds the slices reads
+  p.Y = pl.q.Y;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.nslices = pl.ns;
+  p.partial = ws.partial;
+  p.status = ws.status;
+  return launch_sum_slices(p, sm_count, pdl, stream);
 }
 
 }  // namespace b2

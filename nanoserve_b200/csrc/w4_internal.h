@@ -145,12 +145,14 @@ int gemv_describe(int M, int N, int K, int G, int flags, int sm_count, size_t pa
 size_t gemv_stream_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);
 
 // The many-token GEMV (w4_gemv_mid.cu): 5 <= M <= 16, G == 128, K % 256 == 0, at least 16 rows per SM, a converted X
-// that fits in shared memory; plain launches only (no prologue, epilogue or tensor-parallel form).
+// that fits in shared memory -- whole, or, with split-K scratch, in up to eight slices of K across CTAs; plain launches only
+// (no prologue, epilogue or tensor-parallel form).
 bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, int flags,
-                      int sm_count);
-int gemv_mid_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int* status, int flags,
-                    int sm_count, cudaStream_t stream);
-int gemv_mid_describe(int M, int N, int K, int flags, int sm_count, char* buf, int buflen);
+                      int sm_count, size_t partial_cap);
+int gemv_mid_launch(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, const Workspace& ws,
+                    int flags, int sm_count, cudaStream_t stream);
+int gemv_mid_describe(int M, int N, int K, int flags, int sm_count, size_t partial_cap, char* buf, int buflen);
+size_t gemv_mid_scratch_bytes(int M, int N, int K, int flags, int sm_count, size_t partial_cap);
 
 // Status word of b2_w4_gemv_noalloc's fixed scratch array (w4_gemv_noalloc.cu); false when that entry point has not
 // run on the device.

@@ -37,7 +37,10 @@ def test_dispatch(kernels):
     assert served(kernels, 8, 28672, 8192, 0) and served(kernels, 16, 18944, 3584, 0) and served(kernels, 9, 37888, 3584, 0)
     assert served(kernels, 8, 37888, 3584, 0) and served(kernels, 5, 3584, 3584, 0)
     assert not served(kernels, 4, 18944, 3584) and not served(kernels, 16, 2000, 3584)
-    assert not served(kernels, 16, 3584, 18944)  # the converted X does not fit in shared memory
+    plan = kernels.gemv_describe(16, 3584, 18944, 128, 0)  # the converted X fits in slices of K only
+    assert plan.startswith("many-token kernel") and "K slices across CTAs 5 (sum kernel)" in plan
+    assert "K slices across CTAs 1," in kernels.gemv_describe(16, 18944, 3584, 128, 0)
+    assert not served(kernels, 16, 3584, 18944, ops.FLAG_MID_KERNEL | ops.FLAG_NO_SPLIT_K)
     assert not kernels.gemv_describe(8, 18944, 3584, 128, ops.FLAG_NO_MID_KERNEL).startswith("many-token")
 
 
@@ -93,6 +96,27 @@ def test_both_tile_heights(kernels, rows, N, K):
         a = run(kernels, X, Wq, S, flags=force)
         check_bf16_output(a, ref, SLACK_DEFAULT)
         assert np.array_equal(a, run(kernels, X, Wq, S, flags=force))
+    assert kernels.device_status() == 0
+
+
+@pytest.mark.parametrize("N,K,slices", [(2400, 2048, 2), (2400, 2048, 4), (3000, 1792, 3), (5000, 768, 3),
+                                        (3584, 18944, 0), (2399, 18944, 0)])
+def test_k_slices_across_ctas(kernels, N, K, slices):
+    """K cut into slices across CTAs (fp32 partial sums, added in slice order by the kernel behind): forced on short
+    K, chosen by the plan where the converted X of the whole K does not fit in shared memory."""
+    force = slices << 24
+    for M in (5, 8, 11, 16):
+        plan = kernels.gemv_describe(M, N, K, 128, ops.FLAG_MID_KERNEL | force)
+        assert plan.startswith("many-token kernel"), plan
+        if slices:
+            assert f"K slices across CTAs {slices} " in plan
+        else:
+            assert "(sum kernel)" in plan
+        X, Wq, S = oracle.synth_inputs(M, N, K, 128, seed=M + slices)
+        ref = oracle.w4_linear_f32(X, Wq, S, 128, threads=oracle.max_threads())
+        a = run(kernels, X, Wq, S, flags=force)
+        check_bf16_output(a, ref, SLACK_DEFAULT)
+        assert np.array_equal(a, run(kernels, X, Wq, S, flags=force)), "two identical launches differ"
     assert kernels.device_status() == 0
 
 
