@@ -92,7 +92,7 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
 #define B2_FLAG_NO_SPLIT_SUM_KERNEL 65536 /* ring kernel: the last CTA of a row group to arrive adds them up (a hand-shake of
                                            three L2 round trips per tile, but no second kernel) */
 #define B2_FLAG_RING_KERNEL 131072 /* GEMV: the ring kernel even where the streaming kernel would run */
-#define B2_FLAG_NO_MID_KERNEL 262144 /* GEMV: never the many-token kernel (5 <= M <= 16, G == 128, K % 256 == 0, plain launches) */
+#define B2_FLAG_NO_MID_KERNEL 262144 /* GEMV: never the many-token kernel (2 <= M <= 16, G == 128, K % 256 == 0, plain launches) */
 #define B2_FLAG_MID_KERNEL (131072 | 524288) /* GEMV (both kernel flags): the many-token kernel for every shape it can serve */
 #define B2_FLAG_STREAM_KERNEL 524288 /* GEMV: the streaming kernel for every M <= 16 it can serve */
 #define B2_FLAG_GEMM_NO_PAIRS 536870912 /* prefill GEMM: no clusters of two CTAs (by default two CTAs on neighbouring token

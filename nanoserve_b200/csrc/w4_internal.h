@@ -56,7 +56,7 @@ enum : int {
   kFlagNoSplitSumKernel = 65536,  // GEMV: never do that
   kFlagRingKernel = 131072,  // GEMV: run the shared-memory ring kernel (w4_gemv.cu) even where the register-streaming
                              // kernel (w4_gemv_stream.cu) applies; bits 20-23: force that kernel's warps per row block
-  kFlagNoMidKernel = 262144,  // GEMV: never run the many-token kernel (w4_gemv_mid.cu, 5 <= M <= 16)
+  kFlagNoMidKernel = 262144,  // GEMV: never run the many-token kernel (w4_gemv_mid.cu, 2 <= M <= 16)
   kFlagMidKernel = 131072 | 524288,  // (ring | streaming, both) GEMV: the many-token kernel for every shape it can
                                      // serve (by default not where another kernel measured faster)
   kFlagStreamKernel = 262144 * 2,  // GEMV: run the streaming kernel for every M <= 16 it can serve (by default M <= 2)
@@ -144,7 +144,7 @@ int gemv_describe(int M, int N, int K, int G, int flags, int sm_count, size_t pa
                   int buflen);
 size_t gemv_stream_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);
 
-// The many-token GEMV (w4_gemv_mid.cu): 5 <= M <= 16, G == 128, K % 256 == 0, at least 16 rows per SM, a converted X
+// The many-token GEMV (w4_gemv_mid.cu): 2 <= M <= 16, G == 128, K % 256 == 0, at least 16 rows per SM, a converted X
 // that fits in shared memory -- whole, or, with split-K scratch, in up to eight slices of K across CTAs; plain launches only
 // (no prologue, epilogue or tensor-parallel form).
 bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, int flags,

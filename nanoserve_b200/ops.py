@@ -34,7 +34,7 @@ EPI_SWIGLU_PAIRS8 = 3  # EPI_SWIGLU_PAIRS with row blocks of 8 gate + 8 up rows 
 EPI_SWIGLU_PAIRS = 1  # epilogue of b2_w4_linear_fused: silu(gate) * up over row blocks of 16 gate + 16 up rows
 FLAG_GEMM_NO_PAIRS = 1 << 29  # prefill GEMM: one CTA per tile unpacks the whole weight tile (no clusters of two)
 FLAG_GEMM_WHOLE_TILES = 1 << 30  # prefill GEMM: every CTA takes whole output tiles (no fp32 part-tiles)
-FLAG_NO_MID_KERNEL = 262144  # decode GEMV: never the many-token kernel (5 <= M <= 16 on plain launches)
+FLAG_NO_MID_KERNEL = 262144  # decode GEMV: never the many-token kernel (2 <= M <= 16 on plain launches)
 FLAG_MID_KERNEL = 131072 | 524288  # decode GEMV (both kernel flags): the many-token kernel for every shape it can serve
 FLAG_STREAM_KERNEL = 524288  # decode GEMV: the streaming kernel for every M <= 16 it can serve (default: M <= 2)
 
