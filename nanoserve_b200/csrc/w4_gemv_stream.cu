@@ -1005,52 +1005,70 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   const int forced_ks = (flags >> 20) & 0xF;
   if (forced_ks == 1 || forced_ks == 2 || forced_ks == 4 || forced_ks == 8) ks = forced_ks;
   if (epilogue != kEpiNone) ks = 1;  // the register epilogue: a warp holds whole dot products
+  // K slices across CTAs: only when the staged X of one CTA does not fit otherwise
+  const int forced_ns = (flags >> 24) & 0x1F;
+  const int forced_depth = (flags >> 4) & 0xF;  // bits 4-7: ring slots per warp (diagnostics)
+  // the shared-memory plan for `k` warps per row tile; passes: 1 = only plans that fit two CTAs per SM
+  auto search = [&](int k, int passes) {
+    const int tpc_k = kWarps / k;
+    for (int pass = 0; pass < passes; ++pass) {
+      const size_t cap = pass == 0 ? kSmemTwoPerSm : kSmemMax;
+      for (int ns = 1; ns <= std::min(nsc, 16); ++ns) {
+        if (forced_ns && ns != forced_ns) continue;
+        if (pass == 0 && ns > 1 && !forced_ns) break;  // first choice: no split, two CTAs per SM
+        const int scps = (nsc + ns - 1) / ns;
+        if ((nsc + scps - 1) / scps != ns) continue;
+        if (ns > 1 && ((flags & kFlagForceNoSplitK) || (size_t)ns * M * N * sizeof(float) > partial_cap)) continue;
+        const int gs_pitch = ns == 1 ? KG : (2 * scps + gdiv - 1) / gdiv + 1;
+        // as many ring slots as fit (a warp never needs more than its own super-chunks), at least two
+        const int longest = (scps + k - 1) / k;
+        for (int depth = std::min(kMaxDepth, std::max(2, longest)); depth >= 2; --depth) {
+          if (forced_depth >= 2 && forced_depth <= kMaxDepth && depth != forced_depth && depth > 2) continue;
+          StreamParams q{};
+          const size_t smem = stream_smem(M, pl.P, pl.NT, pl.RB, tpc_k, scps, gs_pitch, depth, &q);
+          if (smem > cap) continue;
+          pl.nslices = ns;
+          pl.scps = scps;
+          pl.smem = smem;
+          pl.q = q;
+          pl.q.gs_pitch = gs_pitch;
+          return true;
+        }
+      }
+    }
+    return false;
+  };
+  // Fewer CTAs than SMs (SMs idle, the second CTA slot of the others empty): twice the warps per tile double the CTAs,
+  // if those still fit two per SM and all at once.  One token: 16384 x 4096 11.3 -> 9.4 us, 14336 x 4096 11.1 -> 8.6,
+  // 28672 x 4096 (32 rows per warp) 16.4 -> 12.3, 16384 x 8192 23.0 -> 16.0.  Not at 148 or 296 CTAs (18944 x 3584:
+  // 8.2 against 9.4 us), nor where a CTA needs an SM of its own (28672 x 8192 with 32 rows per warp: 23.0 against 30.3).
+  bool found = false;
+  {
+    const long ctas = (n_tiles + kWarps / ks - 1) / (kWarps / ks);
+    if (!pl.one && epilogue == kEpiNone && !forced_ks && ks < 8 && nsc / (ks * 2) >= 2 && ctas * 100 < sm_count * 97l &&
+        (n_tiles + kWarps / (2 * ks) - 1) / (kWarps / (2 * ks)) <= 2l * sm_count && search(2 * ks, 1)) {
+      ks *= 2;
+      found = true;
+    }
+  }
+  if (!found) found = search(ks, 2);
+  if (!found) return false;
   pl.ks = ks;
   const int tpc = kWarps / ks;
   pl.grid_x = (n_tiles + tpc - 1) / tpc;
   // Uneven waves.  (a) 16 rows per warp and a few CTAs more than SMs (1.05 to 1.25 per SM): the SMs that hold two are
   // the critical path (20000 x 4096: 12.4 us); instead two CTAs on EVERY SM, each with its even share of the row tiles
-  // and some of its warps idle (10.4 us).  (b) below, after the shared-memory search: CTAs that fit one per SM only.
+  // and some of its warps idle (10.4 us).  (b) CTAs that fit one per SM only, below.
   // Row counts that leave some CTA slots empty otherwise (28672 or 65536 rows) gain nothing from the even shares
   // (24.6 against 24.2 us, 23.0 against 22.5): bandwidth is a shared resource, a lighter SM just finishes early.
   // Not with forced rows per warp / K warps (diagnostics), an epilogue, or several tokens.
   int balanced_tiles = 0;
   const bool may_balance = !pl.one && epilogue == kEpiNone && ks == 1 && ((flags >> 10) & 3) == 0 && !forced_ks;
-  if (may_balance && pl.RB == 1 && pl.grid_x * 100l > sm_count * 105l && pl.grid_x * 4l <= sm_count * 5l) {
+  if (may_balance && pl.RB == 1 && pl.smem <= kSmemTwoPerSm && pl.grid_x * 100l > sm_count * 105l &&
+      pl.grid_x * 4l <= sm_count * 5l) {
     balanced_tiles = n_tiles;
     pl.grid_x = 2 * sm_count;
   }
-  // K slices across CTAs: only when the staged X of one CTA does not fit otherwise
-  const int forced_ns = (flags >> 24) & 0x1F;
-  const int forced_depth = (flags >> 4) & 0xF;  // bits 4-7: ring slots per warp (diagnostics)
-  bool found = false;
-  for (int pass = 0; pass < 2 && !found; ++pass) {
-    const size_t cap = pass == 0 ? kSmemTwoPerSm : kSmemMax;
-    for (int ns = 1; ns <= std::min(nsc, 16) && !found; ++ns) {
-      if (forced_ns && ns != forced_ns) continue;
-      if (pass == 0 && ns > 1 && !forced_ns) break;  // first choice: no split, two CTAs per SM
-      const int scps = (nsc + ns - 1) / ns;
-      if ((nsc + scps - 1) / scps != ns) continue;
-      if (ns > 1 && ((flags & kFlagForceNoSplitK) || (size_t)ns * M * N * sizeof(float) > partial_cap)) continue;
-      const int gs_pitch = ns == 1 ? KG : (2 * scps + gdiv - 1) / gdiv + 1;
-      // as many ring slots as fit (a warp never needs more than its own super-chunks), at least two
-      const int longest = (scps + ks - 1) / ks;
-      for (int depth = std::min(kMaxDepth, std::max(2, longest)); depth >= 2; --depth) {
-        if (forced_depth >= 2 && forced_depth <= kMaxDepth && depth != forced_depth && depth > 2) continue;
-        StreamParams q{};
-        const size_t smem = stream_smem(M, pl.P, pl.NT, pl.RB, tpc, scps, gs_pitch, depth, &q);
-        if (smem > cap) continue;
-        pl.nslices = ns;
-        pl.scps = scps;
-        pl.smem = smem;
-        pl.q = q;
-        pl.q.gs_pitch = gs_pitch;
-        found = true;
-        break;
-      }
-    }
-  }
-  if (!found) return false;
   // (b) CTAs that fit one per SM only (32 rows per warp at K = 8192) and do not fill their last wave: whole waves of
   // CTAs with even shares of the tiles, at least four warps busy (57344 x 8192: 224 CTAs 50.7 us, 296 CTAs 47.5 us)
   if (may_balance && !balanced_tiles && pl.smem > kSmemTwoPerSm && pl.nslices == 1 && pl.grid_x > sm_count &&
