@@ -30,6 +30,7 @@ import argparse
 import ctypes
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -397,7 +398,7 @@ class LayerBench:
         import torch
         from nanoserve_b200.tp import PeerBuffers, ShardedLayer
         self.k, self.shapes, self.M, self.world, self.rank, self.dev = k, shapes, M, world, rank, dev
-        self.seven, self.n_copies, self.seed0 = seven, n_copies, seed0
+        self.seven, self.n_copies, self.seed0, self.flags = seven, n_copies, seed0, flags
         self.layers = [ShardedLayer.synthetic(k, shapes, ORDER, G, seed=seed0 + c, rank=rank, world=world, device=dev,
                                               flags=flags) for c in range(n_copies)]
         self.peer = None
@@ -475,7 +476,16 @@ class LayerBench:
         from nanoserve_b200.tp import ShardedLayer
         if self.seven:
             return len(ORDER) + (len(ShardedLayer.BOUNDARIES) if self.peer is not None else 0)
-        return len(ShardedLayer.FUSED) + (1 if self.peer is not None else 0)
+        # (a launch whose K is cut into slices across CTAs is followed by the kernel that adds the slices)
+        sums = 0
+        if self.peer is None:
+            for _, names in ShardedLayer.FUSED:
+                N = sum(self.shapes[n][0] for n in names)
+                plan = self.k.gemv_describe(self.M, N, self.shapes[names[0]][1], G, self.flags)
+                m = re.search(r"K slices(?: across CTAs)? (\d+)", plan)
+                if m and int(m.group(1)) > 1:
+                    sums += 1
+        return len(ShardedLayer.FUSED) + sums + (1 if self.peer is not None else 0)
 
 
 def tp_check(lb, k, dev):

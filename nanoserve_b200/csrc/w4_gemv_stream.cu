@@ -974,8 +974,9 @@ size_t stream_smem(int M, int P, int NT, int RB, int tpc, int scps, int gs_pitch
   return off;
 }
 
+// plain: no prologue (a launch inside a fused decode step keeps its launch count: no sum kernel where K need not be cut)
 bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int sm_count, size_t partial_cap,
-                      StreamPlan* out, int epilogue = kEpiNone) {
+                      StreamPlan* out, int epilogue = kEpiNone, bool plain = true) {
   StreamPlan pl{};
   // One token: the two-chunk layout, four planes (32-bit block fixed point): its 2 x 4 columns fill exactly one mma
   // tile.  More tokens: the one-group layout, M P columns; four planes while they fit one tile (M <= 2), two above.
@@ -1009,13 +1010,14 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   const int forced_ns = (flags >> 24) & 0x1F;
   const int forced_depth = (flags >> 4) & 0xF;  // bits 4-7: ring slots per warp (diagnostics)
   // the shared-memory plan for `k` warps per row tile; passes: 1 = only plans that fit two CTAs per SM
-  auto search = [&](int k, int passes) {
+  auto search = [&](int k, int passes, int only_ns = 0) {
     const int tpc_k = kWarps / k;
     for (int pass = 0; pass < passes; ++pass) {
       const size_t cap = pass == 0 ? kSmemTwoPerSm : kSmemMax;
       for (int ns = 1; ns <= std::min(nsc, 16); ++ns) {
         if (forced_ns && ns != forced_ns) continue;
-        if (pass == 0 && ns > 1 && !forced_ns) break;  // first choice: no split, two CTAs per SM
+        if (only_ns && ns != only_ns) continue;
+        if (pass == 0 && ns > 1 && !forced_ns && !only_ns) break;  // first choice: no split, two CTAs per SM
         const int scps = (nsc + ns - 1) / ns;
         if ((nsc + scps - 1) / scps != ns) continue;
         if (ns > 1 && ((flags & kFlagForceNoSplitK) || (size_t)ns * M * N * sizeof(float) > partial_cap)) continue;
@@ -1053,6 +1055,22 @@ bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int 
   }
   if (!found) found = search(ks, 2);
   if (!found) return false;
+  // A long K with few rows, one token: the converted X of the whole K takes an SM per CTA (3584 x 18944: 112 CTAs of
+  // 214 KB, every one converting 18944 values).  K slices across CTAs instead -- as many as still give at most two
+  // CTAs per SM, one warp per row tile, every CTA converting its slice only -- and the sum kernel behind:
+  // 3584 x 18944 13.4 -> 11.0 us (10 slices), 8192 x 28672 29.5 -> 27.7 (4 slices).
+  if (plain && !pl.one && epilogue == kEpiNone && pl.RB == 1 && pl.smem > kSmemTwoPerSm && pl.nslices == 1 && !forced_ns &&
+      !forced_ks && !(flags & kFlagForceNoSplitK)) {
+    const long ctas_x = (n_tiles + kWarps - 1) / kWarps;
+    for (int ns = (int)std::min<long>(16, 2l * sm_count / ctas_x); ns >= 2; --ns) {
+      const StreamPlan keep = pl;
+      if (search(1, 1, ns)) {
+        ks = 1;
+        break;
+      }
+      pl = keep;
+    }
+  }
   pl.ks = ks;
   const int tpc = kWarps / ks;
   pl.grid_x = (n_tiles + tpc - 1) / tpc;
@@ -1234,7 +1252,7 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
     return kErrBadShape;
   }
   if (!make_stream_plan(M, N, K, G, S, no_split ? (flags | kFlagForceNoSplitK) : flags, sm_count, ws.partial_bytes, &pl,
-                        pro.epilogue))
+                        pro.epilogue, pro.kind == kProNone))
     return pro.epilogue != kEpiNone ? kErrNotImplemented : kStreamNotApplicable;
   if (pro.epilogue != kEpiNone &&
       (pl.nslices != 1 || pl.one || pl.RB != (pro.epilogue == kEpiSwigluPairs8 ? 1 : 2) || pl.ks != 1))
