@@ -252,6 +252,26 @@ def test_70b_class_shapes_sampled_rows(kernels, N, K, M):
     assert kernels.device_status() == 0
 
 
+# one-token launches whose plan departs from one warp per row tile and a whole K: twice the warps per tile where the CTAs
+# leave SMs idle (16384 x 4096, 28672 x 4096 with 32 rows per warp, 8192 x 8192), K slices across CTAs for a long K with
+# few rows (3584 x 18944, 5120 x 13824), even shares of the tiles (20000 x 4096)
+@pytest.mark.parametrize("N,K,what", [(16384, 4096, "2 warp(s) per row tile"), (28672, 4096, "2 warp(s) per row tile"),
+                                      (8192, 8192, "4 warp(s) per row tile"), (3584, 18944, "K slices across CTAs 10"),
+                                      (5120, 13824, "K slices across CTAs"), (20000, 4096, "shared evenly"),
+                                      (14200, 1024, "2 warp(s) per row tile")])
+def test_one_token_plans_sampled_rows(kernels, N, K, what):
+    G = 128
+    assert what in kernels.gemv_describe(1, N, K, G, 0), kernels.gemv_describe(1, N, K, G, 0)
+    X, Wq, S = oracle.synth_inputs(1, N, K, G, seed=N % 89)
+    y = run(kernels, X, Wq, S, G)
+    rows = np.unique(np.concatenate([np.arange(0, 64), np.arange(N - 64, N),
+                                     np.random.default_rng(2).integers(0, N, 512)]))
+    ref = oracle.w4_linear_f32(X, Wq[rows], S[rows], G, threads=oracle.max_threads())
+    check_bf16_output(y[:, rows], ref, SLACK_EXACT)
+    assert np.array_equal(y, run(kernels, X, Wq, S, G)), "two identical launches differ"
+    assert kernels.device_status() == 0
+
+
 def test_random_shapes_property(kernels):
     """Property test over random M, ragged N >= 16 (the slack is relative to the largest output), K = G j, G in {32, 64, 128, 256}, every kernel choice: the bf16 output is
     within one rounding plus the path's slack of the oracle."""
