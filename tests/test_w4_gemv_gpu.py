@@ -1,9 +1,11 @@
 """GPU parity tests of the decode GEMV (M <= 16) through the C ABI, against the CPU oracle.
 
-Two kernels serve the GEMV.  The streaming kernel (default for M <= 2 when G % 128 == 0 and K % 256 == 0; every
-M <= 16 with FLAG_STREAM_KERNEL) carries X as block fixed point per (token, 128-chunk): 32 bits for one token, 15 bits
-plus sign above.  The ring kernel (everything else, or FLAG_RING_KERNEL) carries it as 16-bit block fixed point
-(24 bits with FLAG_WIDE_X) or, with FLAG_FLOAT_X, in fp16 on the floating-point mma.
+Three kernels serve the GEMV.  The streaming kernel (default for one token, and up to four on tall matrices, when
+G % 128 == 0 and K % 256 == 0; every M <= 16 with FLAG_STREAM_KERNEL) carries X as block fixed point per (token,
+128-chunk): 32 bits for one and two tokens, 15 bits plus sign above.  The many-token kernel (five to sixteen tokens, two
+to four on a long K; its own tests are in test_w4_gemv_mid_gpu.py) and the ring kernel (everything else, or
+FLAG_RING_KERNEL) carry it as 16-bit block fixed point (ring kernel: 24 bits with FLAG_WIDE_X, or, with FLAG_FLOAT_X,
+in fp16 on the floating-point mma).
 
 Integer work (the int4 unpack) must be bit-exact.  Floating-point outputs are bf16: the bound is one correct
 rounding (2^-8 relative) plus slack relative to the largest output:
