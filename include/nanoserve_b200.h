@@ -92,7 +92,7 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
 #define B2_FLAG_NO_PRE_STAGE_X 16384 /* ring kernel: every CTA converts the slice of X it needs itself, at every M */
 #define B2_FLAG_SPLIT_SUM_KERNEL 32768   /* GEMV with K split across CTAs: a small kernel behind the GEMV adds up the slices'
                                            partial sums (the default; never for tensor-parallel producers) */
-#define B2_FLAG_NO_SPLIT_SUM_KERNEL 65536 /* ring kernel: the last CTA of a row group to arrive adds them up (a hand-shake of
+#define B2_FLAG_NO_SPLIT_SUM_KERNEL 65536 /* GEMV: the last CTA of a row group to arrive adds them up (a hand-shake of
                                            three L2 round trips per tile, but no second kernel) */
 #define B2_FLAG_RING_KERNEL 131072 /* GEMV: the ring kernel even where the streaming kernel would run */
 #define B2_FLAG_NO_MID_KERNEL 262144 /* GEMV: never the many-token kernel (2 <= M <= 16, G == 128, K % 256 == 0, plain launches) */

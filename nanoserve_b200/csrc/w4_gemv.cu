@@ -1284,7 +1284,7 @@ int gemv_describe(int M, int N, int K, int G, int flags, int sm_count, size_t pa
       gemv_mid_describe(M, N, K, flags, sm_count, partial_cap, buf, buflen) > 0)
     return 0;
   if (gemv_stream_applies(nullptr, M, N, K, G, flags)) {
-    const int n = gemv_stream_describe(M, N, K, G, flags, sm_count, partial_cap, buf, buflen);
+    const int n = gemv_stream_describe(M, N, K, G, flags, sm_count, partial_cap, counters_cap, buf, buflen);
     if (n > 0) return 0;
   }
   GemvPlan pl;

@@ -49,6 +49,7 @@ constexpr int kHeader = 3072;       // abort flag; mbarriers [warp][slot] at 64;
 constexpr int kBarOffset = 64;      // factors [16] at 2048; the weight ring follows (1024-byte aligned)
 constexpr int kMaxDepth = 8;
 constexpr int kStagedBarOffset = 576;  // mbarrier of the bulk copies of a pre-staged X
+constexpr int kLastOffset = 32;    // split K summed in the kernel: "this CTA is the last of its row group"
 constexpr int kZeroOffset = 640;    // 64 bytes of zeros: what lanes without a real B column or info record read
 constexpr int kNormSs = 1024;
 constexpr int kNormInv = 2048;
@@ -936,6 +937,28 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
         store_out4(p, m, n0, make_float4(f[0], f[1], f[2], f[3]));
       }
     }
+    if (p.nslices > 1 && !p.sum_kernel) {
+      // K slices added up in the kernel: the CTAs of a row group count themselves in; the last one to arrive -- which
+      // has thereby seen the partial sums of the others -- adds the slices in slice order (the same sums, the same
+      // bits, as the kernel behind would produce) and resets the counter for the next launch.
+      volatile int* s_last = reinterpret_cast<volatile int*>(smem + kLastOffset);
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        const int old = atomicAdd(p.counters + blockIdx.x, 1);
+        const int last = old == p.nslices - 1;
+        if (last) p.counters[blockIdx.x] = 0;
+        *s_last = last;
+      }
+      __syncthreads();
+      if (*s_last) {
+        __threadfence();
+        for (int idx = tid; idx < p.M * quads; idx += kThreads) {
+          const int m = idx / quads, n0 = row0 + (idx - m * quads) * 4;
+          store_out4(p, m, n0, sum_slices4(p, m, n0));
+        }
+      }
+    }
     if (p.tp.world && !p.tp.defer) {
       __syncthreads();
       if (warp == 0) tp_signal(p.tp, lane);
@@ -974,7 +997,9 @@ size_t stream_smem(int M, int P, int NT, int RB, int tpc, int scps, int gs_pitch
   return off;
 }
 
-// plain: no prologue (a launch inside a fused decode step keeps its launch count: no sum kernel where K need not be cut)
+// plain: no prologue.  Launches with one sit in fused decode steps and keep K whole where it fits: with the slices
+// the step was slower, whoever adds them (3584 x 18944 with a pre-converted X: 633 -> 617 tok/s with the sum kernel
+// behind, 601 with the last CTA adding)
 bool make_stream_plan(int M, int N, int K, int G, const void* S, int flags, int sm_count, size_t partial_cap,
                       StreamPlan* out, int epilogue = kEpiNone, bool plain = true) {
   StreamPlan pl{};
@@ -1208,14 +1233,19 @@ size_t gemv_stream_grid(int M, int N, int K, int G, int flags, int sm_count, siz
   return (size_t)pl.grid_x * pl.nslices;
 }
 
-int gemv_stream_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, char* buf, int buflen) {
+int gemv_stream_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap,
+                         char* buf, int buflen) {
   StreamPlan pl;
   if (!make_stream_plan(M, N, K, G, nullptr, flags, sm_count, partial_cap, &pl)) return 0;
+  const char* sums = pl.nslices == 1 ? ""
+                     : ((flags & kFlagNoSplitSumKernel) && !(flags & kFlagSplitSumKernel) && pl.grid_x <= counters_cap)
+                         ? " (last CTA sums)"
+                         : " (sum kernel)";
   return snprintf(buf, buflen,
                   "streaming kernel: %d CTAs of 8 warps, %d rows per warp, %d warp(s) per row tile along K, %s layout, "
-                  "%d planes (%d-bit X), ring depth %d, K slices across CTAs %d, cluster %d, %zu KB smem",
+                  "%d planes (%d-bit X), ring depth %d, K slices across CTAs %d%s, cluster %d, %zu KB smem",
                   pl.grid_x * pl.nslices, pl.RB * 16, pl.ks, pl.one ? "one-group" : "two-chunk", pl.P, pl.P * 8, pl.q.depth,
-                  pl.nslices, pl.q.cluster, pl.smem >> 10) +
+                  pl.nslices, sums, pl.q.cluster, pl.smem >> 10) +
          (pl.q.n_tiles ? snprintf(buf + strlen(buf), buflen - strlen(buf), ", %d row tiles shared evenly", pl.q.n_tiles) : 0);
 }
 
@@ -1282,7 +1312,14 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
       p.tp.local_count = ws.counters + ws.n_counters - 1;
     }
   }
+  // K slices: added up by the last CTA of a row group to arrive (the default where the counters suffice; no launch
+  // behind), or by the sum kernel (kFlagSplitSumKernel)
+  // K slices: added up by the sum kernel behind (the default: 3584 x 18944 11.0 us against 11.7), or by the last CTA
+  // of a row group to arrive (kFlagNoSplitSumKernel)
   p.sum_kernel = pl.nslices > 1 ? 1 : 0;
+  if (pl.nslices > 1 && (flags & kFlagNoSplitSumKernel) && !(flags & kFlagSplitSumKernel) &&
+      ws.counters && pl.grid_x <= ws.n_counters - 1 && !(tp != nullptr && tp->world > 0))
+    p.sum_kernel = 0;
   pl.q.Wq = static_cast<const uint32_t*>(Wq);
   const bool pdl = (flags & kFlagNoPdl) == 0;
   int rc;

@@ -139,7 +139,8 @@ int gemv_stream_launch(const void* X, const void* Wq, const void* S, void* Y, in
                        const GemvPrologue& pro, const Workspace& ws, int flags, int sm_count, cudaStream_t stream,
                        const GemvTp* tp);
 size_t gemv_stream_grid(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);
-int gemv_stream_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, char* buf, int buflen);
+int gemv_stream_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap,
+                         char* buf, int buflen);
 int gemv_describe(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap, int counters_cap, char* buf,
                   int buflen);
 size_t gemv_stream_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);

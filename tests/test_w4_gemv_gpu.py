@@ -258,7 +258,7 @@ def test_70b_class_shapes_sampled_rows(kernels, N, K, M):
 # leave SMs idle (16384 x 4096, 28672 x 4096 with 32 rows per warp, 8192 x 8192), K slices across CTAs for a long K with
 # few rows (3584 x 18944, 5120 x 13824), even shares of the tiles (20000 x 4096)
 @pytest.mark.parametrize("N,K,what", [(16384, 4096, "2 warp(s) per row tile"), (28672, 4096, "2 warp(s) per row tile"),
-                                      (8192, 8192, "4 warp(s) per row tile"), (3584, 18944, "K slices across CTAs 10"),
+                                      (8192, 8192, "4 warp(s) per row tile"), (3584, 18944, "K slices across CTAs 10 (sum kernel)"),
                                       (5120, 13824, "K slices across CTAs"), (20000, 4096, "shared evenly"),
                                       (14200, 1024, "2 warp(s) per row tile")])
 def test_one_token_plans_sampled_rows(kernels, N, K, what):
@@ -271,6 +271,9 @@ def test_one_token_plans_sampled_rows(kernels, N, K, what):
     ref = oracle.w4_linear_f32(X, Wq[rows], S[rows], G, threads=oracle.max_threads())
     check_bf16_output(y[:, rows], ref, SLACK_EXACT)
     assert np.array_equal(y, run(kernels, X, Wq, S, G)), "two identical launches differ"
+    # K slices added up by the last CTA of a row group instead of the kernel behind: the same sums in the same order
+    assert np.array_equal(y, run(kernels, X, Wq, S, G, ops.FLAG_NO_SPLIT_SUM_KERNEL))
+    assert np.array_equal(y, run(kernels, X, Wq, S, G, ops.FLAG_NO_SPLIT_SUM_KERNEL))
     assert kernels.device_status() == 0
 
 
