@@ -908,14 +908,20 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
     // a thread sums four consecutive rows of one token: 16-byte partial-sum stores, 8-byte output stores (also into
     // the peers' gathered rows, where two-byte stores over NVLink are dear)
     const int quads = (rows_cta + 3) >> 2;
-    for (int idx = tid; idx < p.M * quads; idx += kThreads) {
-      const int m = idx / quads, r0 = (idx - m * quads) * 4;
+    // a work item is (token, four rows, warp of the row tile along K): the ks items of an output sit in adjacent
+    // lanes and meet in a butterfly of shuffles (a fixed tree: deterministic).  One thread per output used to walk
+    // all ks warps' sums alone -- with four warps per tile eight threads of the CTA did all the adding.
+    const int items = p.M * quads * q.ks;
+    for (int it = tid; it < ((items + 31) & ~31); it += kThreads) {
+      const int s = it % q.ks, idx = it / q.ks;
+      const bool valid = it < items;
+      const int m = valid ? idx / quads : 0, r0 = valid ? (idx - m * quads) * 4 : 0;
       float f[4] = {0.f, 0.f, 0.f, 0.f};
+      if (valid) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = min(r0 + i, rows_cta - 1);
-        const int tile = r / kRows, rr = r - tile * kRows;
-        for (int s = 0; s < q.ks; ++s) {
+        for (int i = 0; i < 4; ++i) {
+          const int r = min(r0 + i, rows_cta - 1);
+          const int tile = r / kRows, rr = r - tile * kRows;
           const float* src = red + ((tile * q.ks + s) * kSlots) * kRows + rr;
 #pragma unroll
           for (int h = 0; h < (ONE ? 1 : 2); ++h)
@@ -923,6 +929,10 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemv_stream_kernel(const GemvP
             for (int j = 0; j < P / 2; ++j) f[i] += src[(h * half_mp + ((m * P) >> 1) + j) * kRows];
         }
       }
+      for (int o = 1; o < q.ks; o <<= 1)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] += __shfl_xor_sync(0xffffffffu, f[i], o);
+      if (!valid || s != 0) continue;
       const int n0 = row0 + r0;
       if (p.nslices > 1) {
         float* d = p.partial + ((size_t)slice * p.M + m) * p.N + n0;
