@@ -584,8 +584,9 @@ bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N
   if (M < 2 || M > 16 || G != 128 || K % 256 || N < 16 * sm_count) return false;
   // Two to four tokens (padded to eight): only where K is long -- 3584 x 18944: 14.2-14.7 us against 17.4-21.5 with
   // the other kernels, 28672 x 8192: 31 against 32-34.5, 5120 x 13824: 15 against 20-26 -- not on the 7B-shaped tall
-  // matrices, where the streaming kernel is 2.5-3.7 us shorter, nor at two tokens on 8192 x 28672 (39.0 against 37.2).
-  if (M < 5 && !forced && (K < 8192 || (M == 2 && (long)N * K > (192l << 20)))) return false;
+  // matrices, where the streaming kernel is 2.5-3.7 us shorter, nor at two tokens on 8192 x 28672 (39.0 against 37.2;
+  // 28672 x 8192 at two tokens: 30.8 against 32.0).
+  if (M < 5 && !forced && (K < 8192 || (M == 2 && K >= 16384 && (long)N * K > (192l << 20)))) return false;
   // Measured against the other two kernels (chained launches, weights from DRAM), five to sixteen tokens: shorter on
   // every shape tried, 7B-shaped and 70B class, from 3584 x 3584 (6.8 against 7.9 us at five tokens) to 152064 x 3584
   // (65 against 77 us); 18944 x 3584: 12.6 against 15.8 us at eight tokens, 17.4 against 25.4 at sixteen.
