@@ -69,8 +69,8 @@ int ns_flash_fwd(const void* q, const void* k, const void* v, void* o, int N, in
  * Flags for b2_w4_linear.  Three kernels serve the decode GEMV (M <= 16).  The streaming kernel (G % 128 == 0,
  * K % 256 == 0, Wq 16-byte aligned) runs one token always and two to four tokens on tall matrices with K < 8192; it
  * carries X as block fixed point per (token, 128-wide chunk of K) -- 32 bits for M <= 2 (exact to fp32 summation
- * order), 15 bits + sign above -- on an 8-bit integer mma.  The many-token kernel (G == 128, K % 256 == 0, at least 16
- * rows per SM, plain launches) runs five to sixteen tokens, and two to four where K >= 8192, with X as 16-bit block
+ * order), 15 bits + sign above -- on an 8-bit integer mma.  The many-token kernel (G == 128, K % 256 == 0, plain
+ * launches) runs five to sixteen tokens, and two to four where K >= 8192, with X as 16-bit block
  * fixed point.  The ring kernel runs everything else, with X as 16-bit block fixed point (every element off by at most
  * 2^-16 of its chunk's largest magnitude) or as the flags below say.  No kernel measures anything or synchronises:
  * every call is asynchronous.  A K that is cut into slices across CTAs (long K, few rows) is followed by a small

@@ -498,10 +498,22 @@ bool make_mid_plan(int M, int N, int K, int flags, int sm_count, size_t partial_
   // slices); else K slices across CTAs (blockIdx.y), as few as let the slice's X fit beside rings of three slots (two
   // at worst): 3584 x 18944 takes 3 at eight tokens, 5 at sixteen.  The slices' fp32 partial sums are added by a
   // kernel behind.
+  // Fewer row tiles than half the SMs: K slices also where X would fit whole, as many as fill the SMs (512 x 3584: 32
+  // tiles, 4 slices)
+  int ns_min = 1;
+  {
+    const int n16 = (N + 15) / 16;
+    if (n16 * 2 <= sm_count && !forced_ns && !(flags & kFlagForceNoSplitK))
+      for (int ns = std::min(std::min(nsc, 8), sm_count / n16); ns >= 2; --ns)
+        if ((nsc + (nsc + ns - 1) / ns - 1) / ((nsc + ns - 1) / ns) == ns && (size_t)ns * M * N * sizeof(float) <= partial_cap) {
+          ns_min = ns;
+          break;
+        }
+  }
   bool found = false;
   for (int want_depth = 4; want_depth >= 2 && !found; --want_depth) {
-    for (int ns = 1; ns <= std::min(nsc, 8) && !found; ++ns) {
-      if (want_depth == 4 && ns > 1) break;  // first pass: K whole, any depth
+    for (int ns = ns_min; ns <= std::min(nsc, 8) && !found; ++ns) {
+      if (want_depth == 4 && ns > ns_min) break;  // first pass: K whole (or in its fewest slices), any depth
       if (forced_ns && ns != forced_ns) continue;
       if (ns > 1 && ((flags & kFlagForceNoSplitK) || (size_t)ns * M * N * sizeof(float) > partial_cap)) continue;
       const int scps = (nsc + ns - 1) / ns;
@@ -515,7 +527,7 @@ bool make_mid_plan(int M, int N, int K, int flags, int sm_count, size_t partial_
         if (forced_depth >= 2 && forced_depth <= kMaxDepth) depth = forced_depth;
         for (; depth >= 2; --depth)
           if (kHeader + (size_t)sh.W * depth * slot + x_bytes + info_bytes <= (size_t)kSmemMax) break;
-        if (depth < std::min(want_depth, 3) && ns > 1 && !(forced_depth && depth >= 2)) continue;
+        if (depth < std::min(want_depth, 3) && ns > ns_min && !(forced_depth && depth >= 2)) continue;
         if (depth < 2) continue;
         // the parts of the at most two partial tiles of a warp go into its drained ring
         if ((size_t)2 * Mp * sh.RB * 16 * 4 > (size_t)depth * slot) continue;
@@ -581,7 +593,7 @@ bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N
   const bool forced = (flags & kFlagMidKernel) == kFlagMidKernel;
   if (flags & (kFlagFloatX | kFlagWideX | kFlagNoMidKernel)) return false;
   if (!forced && (flags & kFlagMidKernel)) return false;  // one of the other two kernels is asked for
-  if (M < 2 || M > 16 || G != 128 || K % 256 || N < 16 * sm_count) return false;
+  if (M < 2 || M > 16 || G != 128 || K % 256 || N < 1) return false;
   // Two to four tokens (padded to eight): only where K is long -- 3584 x 18944: 14.2-14.7 us against 17.4-21.5 with
   // the other kernels, 28672 x 8192: 31 against 32-34.5, 5120 x 13824: 15 against 20-26 -- not on the 7B-shaped tall
   // matrices, where the streaming kernel is 2.5-3.7 us shorter, nor at two tokens on 8192 x 28672 (39.0 against 37.2;
@@ -589,7 +601,9 @@ bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N
   if (M < 5 && !forced && (K < 8192 || (M == 2 && K >= 16384 && (long)N * K > (192l << 20)))) return false;
   // Measured against the other two kernels (chained launches, weights from DRAM), five to sixteen tokens: shorter on
   // every shape tried, 7B-shaped and 70B class, from 3584 x 3584 (6.8 against 7.9 us at five tokens) to 152064 x 3584
-  // (65 against 77 us); 18944 x 3584: 12.6 against 15.8 us at eight tokens, 17.4 against 25.4 at sixteen.
+  // (65 against 77 us); 18944 x 3584: 12.6 against 15.8 us at eight tokens, 17.4 against 25.4 at sixteen.  Matrices with
+  // few rows too, their K in slices across CTAs (512 x 3584: 6.2 against 7.6 us at eight tokens, 7.0 against 9.1 at
+  // sixteen; 64 x 3584: 5.5 against 9.1).
   if ((reinterpret_cast<uintptr_t>(Wq) & 15) || (reinterpret_cast<uintptr_t>(S) & 3) ||
       (reinterpret_cast<uintptr_t>(X) & 15))
     return false;

@@ -145,7 +145,7 @@ int gemv_describe(int M, int N, int K, int G, int flags, int sm_count, size_t pa
                   int buflen);
 size_t gemv_stream_scratch_bytes(int M, int N, int K, int G, int flags, int sm_count, size_t partial_cap);
 
-// The many-token GEMV (w4_gemv_mid.cu): 2 <= M <= 16, G == 128, K % 256 == 0, at least 16 rows per SM, a converted X
+// The many-token GEMV (w4_gemv_mid.cu): 2 <= M <= 16, G == 128, K % 256 == 0, a converted X
 // that fits in shared memory -- whole, or, with split-K scratch, in up to eight slices of K across CTAs; plain launches only
 // (no prologue, epilogue or tensor-parallel form).
 bool gemv_mid_applies(const void* X, const void* Wq, const void* S, int M, int N, int K, int G, int flags,

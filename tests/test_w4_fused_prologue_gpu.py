@@ -59,7 +59,9 @@ def test_swiglu_prologue(kernels, M, N, K):
     # every CTA, or once by the kernel in front of the GEMV
     for flags in (ops.FLAG_NO_AUTOTUNE, ops.FLAG_NO_AUTOTUNE | ops.FLAG_PRE_STAGE_X,
                   ops.FLAG_NO_AUTOTUNE | ops.FLAG_NO_PRE_STAGE_X):
-        y_seq = kernels.w4_linear(act, wq, s, G, flags=flags)
+        # (a plain launch of several tokens would go to the many-token kernel, which has no prologues: keep both
+        # calls on the same kernel)
+        y_seq = kernels.w4_linear(act, wq, s, G, flags=flags | ops.FLAG_NO_MID_KERNEL)
         y = kernels.w4_linear_fused(gu, wq, s, G, prologue=2, flags=flags)
         torch.cuda.synchronize()
         assert torch.equal(y, y_seq), flags  # same element-wise arithmetic, same product: identical
