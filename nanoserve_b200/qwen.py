@@ -78,6 +78,8 @@ class Qwen2Runner:
 
         # gate|up row blocks: 16 gate rows + their 16 up rows (8 + 8 with B2_QWEN_GU_BLOCK=8: the 16-rows-per-warp epilogue)
         self.gu_block = int(os.environ.get("B2_QWEN_GU_BLOCK", "16")) if world == 1 else 16
+        # library flags of the down projection that takes the converted activations (diagnostics: plan choices)
+        self.down_flags = int(os.environ.get("B2_QWEN_DOWN_FLAGS", "0"), 0)
         self.layers = []
         for _ in range(cfg.n_layers):
             q, k, v = w4(self.nq, H), w4(self.nkv, H), w4(self.nkv, H)
@@ -311,7 +313,8 @@ class Qwen2Runner:
                 staged = self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o, wn=L["ln_post"],
                                                 eps=cfg.rms_eps, x_out=x_alt, epilogue=EPI_SWIGLU_STAGED)
                 x, x_alt = x_alt, x
-                d = self.k.w4_linear_fused(staged, L["d"][0], L["d"][1], cfg.group, prologue=PRO_STAGED)
+                d = self.k.w4_linear_fused(staged, L["d"][0], L["d"][1], cfg.group, prologue=PRO_STAGED,
+                                           flags=self.down_flags)
             else:  # SwiGLU in the epilogue; the activation is gathered by NCCL
                 act = self._gather(self.k.w4_linear_fused(x, L["gu"][0], L["gu"][1], cfg.group, prologue=1, r=o,
                                                           wn=L["ln_post"], eps=cfg.rms_eps, x_out=x_alt,
