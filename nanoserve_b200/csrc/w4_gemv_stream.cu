@@ -232,8 +232,17 @@ __device__ __forceinline__ void stage_x_planes(const GemvParams& p, uint32_t xs_
       uint32_t u[16];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        u[2 * i] = ((uint32_t)__float2int_rn(__uint_as_float(w[i] << 16) * down) + kBias) ^ kBias;
-        u[2 * i + 1] = ((uint32_t)__float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * down) + kBias) ^ kBias;
+        if constexpr (P == 2) {
+          // |v| < 2^14: the rounding is one fused multiply-add with 1.5 * 2^23, which leaves v in the low mantissa
+          // bits (round to nearest even, like cvt.rni, at the rate of the fma pipe instead of the conversion unit's)
+          constexpr uint32_t kMagicBits = 0x4B400000u;
+          u[2 * i] = (__float_as_uint(fmaf(__uint_as_float(w[i] << 16), down, 12582912.f)) - kMagicBits + kBias) ^ kBias;
+          u[2 * i + 1] =
+              (__float_as_uint(fmaf(__uint_as_float(w[i] & 0xFFFF0000u), down, 12582912.f)) - kMagicBits + kBias) ^ kBias;
+        } else {
+          u[2 * i] = ((uint32_t)__float2int_rn(__uint_as_float(w[i] << 16) * down) + kBias) ^ kBias;
+          u[2 * i + 1] = ((uint32_t)__float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) * down) + kBias) ^ kBias;
+        }
       }
       // byte transposes: four values x P digits -> P words of four digits
       uint32_t pl[P][4];  // [plane][even lo, even hi, odd lo, odd hi]
