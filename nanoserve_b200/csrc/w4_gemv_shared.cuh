@@ -219,14 +219,16 @@ __device__ __forceinline__ float4 sum_slices4(const GemvParams& p, int tok, int 
   const size_t qstride = (size_t)p.M * p.N;
   float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
   if ((p.N & 3) == 0 && n0 + 3 < p.N) {
-    // four slices' loads in flight together (an L2 round trip takes a microsecond under the weight stream)
-    for (int q0 = 0; q0 < p.nslices; q0 += 4) {
-      float4 v[4];
+    // sixteen slices' loads in flight together (an L2 round trip takes a microsecond under the weight stream, and
+    // this kernel is nothing but round trips: with four at a time ten slices took three of them)
+    constexpr int kInFlight = 16;
+    for (int q0 = 0; q0 < p.nslices; q0 += kInFlight) {
+      float4 v[kInFlight];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < kInFlight; ++i)
         if (q0 + i < p.nslices) v[i] = __ldcg(reinterpret_cast<const float4*>(s0 + (q0 + i) * qstride));
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < kInFlight; ++i)
         if (q0 + i < p.nslices) {
           sum.x += v[i].x;
           sum.y += v[i].y;
