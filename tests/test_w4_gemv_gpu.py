@@ -277,6 +277,31 @@ def test_one_token_plans_sampled_rows(kernels, N, K, what):
     assert kernels.device_status() == 0
 
 
+def test_random_large_shapes_one_token_property(kernels):
+    """Random row counts from a few to tens of thousands and K = 256 j at one token: whatever plan the library picks
+    (warps per row tile, K slices across CTAs, even tile shares, rows per warp), sampled rows agree with the oracle to
+    the one-token bound and two launches agree bit for bit."""
+    from hypothesis import given, settings, strategies as st_
+
+    @settings(max_examples=30, deadline=None, derandomize=True)
+    @given(N=st_.integers(300, 60000), j=st_.sampled_from([1, 2, 3, 4, 7, 8, 14, 16, 20, 32, 54, 74]),
+           seed=st_.integers(0, 1000))
+    def prop(N, j, seed):
+        K, G = 256 * j, 128
+        if N * K > 300 << 20:
+            N = (300 << 20) // K
+        X, Wq, S = oracle.synth_inputs(1, N, K, G, seed=seed)
+        y = run(kernels, X, Wq, S, G)
+        rows = np.unique(np.concatenate([np.arange(0, min(N, 40)), np.arange(max(0, N - 40), N),
+                                         np.random.default_rng(seed).integers(0, N, 256)]))
+        ref = oracle.w4_linear_f32(X, Wq[rows], S[rows], G, threads=oracle.max_threads())
+        check_bf16_output(y[:, rows], ref, SLACK_EXACT)
+        assert np.array_equal(y, run(kernels, X, Wq, S, G))
+
+    prop()
+    assert kernels.device_status() == 0
+
+
 def test_random_shapes_property(kernels):
     """Property test over random M, ragged N >= 16 (the slack is relative to the largest output), K = G j, G in {32, 64, 128, 256}, every kernel choice: the bf16 output is
     within one rounding plus the path's slack of the oracle."""
