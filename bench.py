@@ -817,7 +817,9 @@ def main():
             "config": {
                 "workload": f"decode GEMV pass over the 7 linears of a {layer_name} layer, M={M}, int4 g128",
                 "launches": ("7 GEMV launches per pass" if seven else
-                             "4 GEMV launches per pass: q|k|v and gate|up as row-concatenated matrices (same arithmetic)"),
+                             "4 GEMV launches per pass: q|k|v and gate|up as row-concatenated matrices (same arithmetic)"
+                             "; a GEMV whose K is cut into slices across CTAs is followed by the kernel that adds them "
+                             "(counted in gpu_launches, see plans)"),
                 "parallelism": (f"tp{world}, all-gather " + ("fused into the GEMVs (peer stores + arrival counters; each "
                                                              "launch waits for the previous gathered row in-kernel)"
                                                              if fused_gather else "by NCCL at the 4 layer boundaries"))
